@@ -1,0 +1,268 @@
+/*
+ * nsa_b200.h -- C ABI of the B200 (sm_100a) Native Sparse Attention hot path.
+ *
+ * Every entry point replaces one piece of upstream's Python/Triton hot path;
+ * the piece is cited beside each declaration as
+ *   NSA:<line>  native_sparse_attention_pytorch/native_sparse_attention.py
+ *   TRI:<line>  native_sparse_attention_pytorch/triton_native_sparse_attention.py
+ *
+ * Conventions
+ *   - All pointers are DEVICE pointers owned by the caller.  Nothing here
+ *     allocates or frees; work buffers are passed in and sized with
+ *     nsa_sel_workspace_bytes().
+ *   - Every call is asynchronous on the given CUDA stream (a cudaStream_t
+ *     passed as void*, NULL = default stream).
+ *   - Return value: 0 on success; a negative NSA_ERR_* for an argument the
+ *     library rejects (nothing was launched); a positive value is a CUDA
+ *     runtime error code from a launch.  nsa_last_error() returns a static
+ *     message for the last non-zero return on the calling thread.
+ *   - 4-D activations are described by nsa_tensor: logical shape
+ *     [batch, heads, seq, dim_head], last axis contiguous, the other three
+ *     strides given in ELEMENTS, so the "b n (h d)" views produced by a fused
+ *     qkv projection are consumed without a copy.
+ *   - dtype is NSA_F32 or NSA_BF16 and applies to q/k/v/out/do; statistics
+ *     (lse), scores, gradients accumulated across queries (dq, dk, dv) and
+ *     work buffers are always fp32; block indices are int64 as in upstream.
+ *   - Head grouping everywhere: query head = group * G + g (NSA:164, NSA:805).
+ */
+#ifndef NSA_B200_H
+#define NSA_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { NSA_F32 = 0, NSA_BF16 = 1 };
+
+enum {
+  NSA_OK = 0,
+  NSA_ERR_NULL = -1,        /* a required pointer is NULL                     */
+  NSA_ERR_SHAPE = -2,       /* sizes inconsistent or outside supported range  */
+  NSA_ERR_DTYPE = -3,       /* dtype is neither NSA_F32 nor NSA_BF16          */
+  NSA_ERR_ALIGN = -4,       /* pointer or stride breaks the 16-byte rule      */
+  NSA_ERR_WORKSPACE = -5,   /* work buffer missing or too small               */
+  NSA_ERR_UNSUPPORTED = -6, /* valid request that this build cannot serve     */
+  NSA_ERR_DEVICE = -7       /* a kernel reported a bounded wait that ran out  */
+};
+
+/* own-block ("diagonal") handling of the selected-block branch */
+enum {
+  NSA_DIAG_NONE = 0,   /* non-causal: only the selected blocks (NSA:769-770)            */
+  NSA_DIAG_CAUSAL = 1, /* causal: keys floor(i/sel)*sel..i of the own block (NSA:754-767) */
+  NSA_DIAG_FULL = 2    /* the whole zero-padded own block (non-causal NSA:821-837)       */
+};
+
+/* kernel family */
+enum {
+  NSA_IMPL_AUTO = 0,  /* tensor-core (tcgen05/TMA) kernels where the shape allows, else SIMT */
+  NSA_IMPL_SIMT = 1,  /* generic fp32-accumulate CUDA-core kernels                            */
+  NSA_IMPL_SM100 = 2  /* tensor-core kernels only; NSA_ERR_UNSUPPORTED if the shape does not fit */
+};
+
+typedef struct {
+  void* ptr;
+  int64_t stride_b, stride_h, stride_n; /* in elements; the dim_head axis has stride 1 */
+} nsa_tensor;
+
+/* ------------------------------------------------------------------------
+ * Selected-block attention, forward.
+ * Replaces native_sparse_attend -> NSA.forward -> native_sparse_attn_forward
+ * -> forward_kernel (TRI:1938-1987, 1826-1872, 599-694, 494-597) and the
+ * gather formulation NSA:741-819; with nsel == 0 and a diagonal mode it is
+ * the no-selection fallback NSA:821-837.
+ *
+ * Query i of selection head hs (there are sel_heads of them, sel_heads ==
+ * kv_heads when the query heads of a KV head share one selection, == q_heads
+ * otherwise) attends, for every slot s with mask[b,hs,i,s] != 0, the `block`
+ * keys of block idx[b,hs,i,s], plus its own block as `diag` says.  Keys at
+ * positions >= seq inside a selected block count as zero keys with zero
+ * values (upstream zero-pads K and V).  Slots whose mask is 0 carry the logit
+ * -FLT_MAX, so a query with no visible key gets the plain average of the
+ * values its slots point at, as upstream's masked_fill + softmax does.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  nsa_tensor q;          /* [B, q_heads, N, d]  (rotary already applied)      */
+  nsa_tensor k, v;       /* [B, kv_heads, N, d]                               */
+  nsa_tensor out;        /* [B, q_heads, N, d]  written                       */
+  const int64_t* idx;    /* [B, sel_heads, N, nsel] contiguous                */
+  const uint8_t* mask;   /* [B, sel_heads, N, nsel] contiguous, 0 / non-zero  */
+  float* lse;            /* [B, q_heads, N] natural-log sum-exp, written      */
+  int32_t batch, q_heads, kv_heads, sel_heads, seq, dim_head;
+  int32_t block;         /* selection_block_size                              */
+  int32_t nsel;          /* slots per query, may be 0                         */
+  int32_t diag;          /* NSA_DIAG_*                                        */
+  int32_t dtype;         /* NSA_F32 / NSA_BF16                                */
+  int32_t impl;          /* NSA_IMPL_*                                        */
+  float scale;           /* logit scale, upstream uses dim_head^-0.5          */
+  void* workspace;       /* nsa_sel_workspace_bytes(args, 0) bytes, may be NULL if that is 0 */
+  int64_t workspace_bytes;
+} nsa_sel_fwd_args;
+
+int nsa_sel_fwd(const nsa_sel_fwd_args* args, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Selected-block attention, backward.
+ * Replaces NSA.backward -> native_sparse_attn_backward -> backward_preprocess_do_o_dot,
+ * backward_kernel (TRI:1874-1925, 1646-1818, 696-756, 1427-1644).
+ * dq [B,q_heads,N,d], dk, dv [B,kv_heads,N,d] are contiguous fp32 and are
+ * zeroed by the call before accumulation (upstream returns fp32 too,
+ * TRI:1900-1902).  slot_grads, if not NULL, receives for every slot the
+ * gradient of a multiplier of 1 on that slot's logits (TRI:1061-1080), fp32
+ * [B, sel_heads, N, nsel].
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  nsa_sel_fwd_args fwd;  /* same tensors as the forward call; out and lse are read */
+  nsa_tensor dout;       /* [B, q_heads, N, d]                                */
+  float* dq;             /* [B, q_heads, N, d]  contiguous fp32, written      */
+  float* dk;             /* [B, kv_heads, N, d] contiguous fp32, written      */
+  float* dv;             /* [B, kv_heads, N, d] contiguous fp32, written      */
+  float* slot_grads;     /* optional                                          */
+} nsa_sel_bwd_args;
+
+int nsa_sel_bwd(const nsa_sel_bwd_args* args, void* stream);
+
+/* Bytes of work buffer the selected-block kernels need for this problem
+ * (backward != 0: for nsa_sel_bwd).  0 when the SIMT family serves it.
+ * Negative = NSA_ERR_*. */
+int64_t nsa_sel_workspace_bytes(const nsa_sel_fwd_args* args, int backward);
+
+/* ------------------------------------------------------------------------
+ * Compressed-KV attention with the importance reduction fused in.
+ * Replaces NSA:621-639 + attend NSA:153-184 and the first half of the
+ * selection chain NSA:652-680, without materialising the logits tensor.
+ *
+ * ck, cv hold num_mem memory slots followed by ncb compressed blocks
+ * ([B, kv_heads, num_mem + ncb, d]).  Causal: compressed block w is visible
+ * to query i iff (w+1)*stride-1 < i; memory slots always are.
+ * importance, if not NULL, receives [B, sel_heads, N, ncb] fp32: the logits
+ * of the ncb block columns, invisible ones replaced by `sentinel` (upstream's
+ * finite (-max)//10 in the tensor dtype, NSA:171), averaged over the
+ * q_heads / sel_heads query heads of a selection head (NSA:659-662).  With
+ * dtype NSA_BF16 every intermediate is rounded to bf16 where upstream's bf16
+ * tensors would be (product, scaled logit, mean).
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  nsa_tensor q;          /* [B, q_heads, N, d]  NOT rotated                   */
+  nsa_tensor ck, cv;     /* [B, kv_heads, num_mem + ncb, d]                   */
+  nsa_tensor out;        /* [B, q_heads, N, d]  written                       */
+  float* lse;            /* [B, q_heads, N]     written                       */
+  float* importance;     /* [B, sel_heads, N, ncb] or NULL                    */
+  int32_t batch, q_heads, kv_heads, sel_heads, seq, dim_head;
+  int32_t num_mem, ncb;
+  int32_t stride;        /* compress_block_sliding_stride                     */
+  int32_t causal;
+  int32_t dtype;
+  int32_t impl;
+  float scale;
+  float sentinel;        /* value an invisible logit is replaced by            */
+} nsa_cmp_fwd_args;
+
+int nsa_cmp_fwd(const nsa_cmp_fwd_args* args, void* stream);
+
+/* Backward of the compressed branch (autograd of NSA:621-639 in upstream).
+ * dq [B,q_heads,N,d], dck, dcv [B,kv_heads,num_mem+ncb,d] contiguous fp32,
+ * zeroed by the call.  The importance output carries no gradient. */
+typedef struct {
+  nsa_cmp_fwd_args fwd;
+  nsa_tensor dout;
+  float* dq;
+  float* dck;
+  float* dcv;
+} nsa_cmp_bwd_args;
+
+int nsa_cmp_bwd(const nsa_cmp_bwd_args* args, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Block selection: per-block mean, own-block exclusion, sink softmax, top-k.
+ * Replaces NSA:672-713.
+ * importance [rows, N, ncb] fp32 (as written by nsa_cmp_fwd).  For every
+ * query: the first cols*cpf columns are averaged in runs of cpf (NSA:672-680,
+ * cols = ncb / cpf; cpf == 1 leaves them as they are); if exclude_own, column
+ * i / block is overwritten with -max of `dtype` (NSA:686-691); a sink logit
+ * of -1000 joins the softmax and is then dropped (NSA:693-695); the k <= cols
+ * largest probabilities are written in descending order with their column
+ * indices; equal values are ordered by ascending index.  With input_is_prob
+ * != 0 (and cpf == 1) the input is ranked as it is, no mean and no softmax.
+ * With dtype NSA_BF16 the mean and the probabilities are rounded to bf16 as
+ * upstream's bf16 tensors would be.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  const float* importance;
+  int64_t* idx;          /* [rows, N, k] written                              */
+  float* vals;           /* [rows, N, k] written                              */
+  int32_t rows;          /* B * sel_heads                                     */
+  int32_t seq, ncb, cpf, k;
+  int32_t block;         /* selection_block_size (for the own-block column)   */
+  int32_t exclude_own;
+  int32_t input_is_prob;
+  int32_t dtype;         /* dtype whose rounding the probabilities follow     */
+} nsa_select_args;
+
+int nsa_select(const nsa_select_args* args, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Sliding-window attention.  Replaces the LocalAttention call NSA:841-850.
+ * Causal: keys j with 0 <= i-j <= window; otherwise |i-j| <= window.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  nsa_tensor q;          /* [B, q_heads, N, d]                                */
+  nsa_tensor k, v;       /* [B, kv_heads, N, d]  (not repeated over groups)   */
+  nsa_tensor out;        /* written                                           */
+  float* lse;            /* [B, q_heads, N] written                           */
+  int32_t batch, q_heads, kv_heads, seq, dim_head;
+  int32_t window, causal, dtype, impl;
+  float scale;
+} nsa_swa_fwd_args;
+
+int nsa_swa_fwd(const nsa_swa_fwd_args* args, void* stream);
+
+typedef struct {
+  nsa_swa_fwd_args fwd;
+  nsa_tensor dout;
+  float* dq;             /* contiguous fp32, zeroed by the call               */
+  float* dk;
+  float* dv;
+} nsa_swa_bwd_args;
+
+int nsa_swa_bwd(const nsa_swa_bwd_args* args, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Gated combine of the three branches and head merge.
+ * Replaces NSA:854-860: out[b,n,h*d+c] = sum_s gates[b,h,n,s] * o_s[b,h,n,c],
+ * s = compressed, selected, sliding.  gates is a strided [B,q_heads,N,3] view.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  nsa_tensor o_cmp, o_sel, o_swa; /* [B, q_heads, N, d]                       */
+  nsa_tensor gates;               /* [B, q_heads, N, 3]                       */
+  void* out;                      /* [B, N, q_heads*d] contiguous, written    */
+  int32_t batch, q_heads, seq, dim_head, dtype;
+} nsa_combine_fwd_args;
+
+int nsa_combine_fwd(const nsa_combine_fwd_args* args, void* stream);
+
+/* Backward of the combine: d_o_s = gates_s * dout, d_gates_s = sum_c dout * o_s. */
+typedef struct {
+  nsa_combine_fwd_args fwd;       /* out is unused                            */
+  const void* dout;               /* [B, N, q_heads*d] contiguous             */
+  void* d_cmp;                    /* [B, q_heads, N, d] contiguous, dtype     */
+  void* d_sel;
+  void* d_swa;
+  float* d_gates;                 /* [B, q_heads, N, 3] contiguous fp32       */
+} nsa_combine_bwd_args;
+
+int nsa_combine_bwd(const nsa_combine_bwd_args* args, void* stream);
+
+/* Library information.  nsa_struct_size(i) is sizeof() of the i-th argument
+ * struct in declaration order (0 nsa_tensor, 1 sel_fwd, 2 sel_bwd, 3 cmp_fwd,
+ * 4 cmp_bwd, 5 select, 6 swa_fwd, 7 swa_bwd, 8 combine_fwd, 9 combine_bwd), so
+ * a foreign-function binding can verify its own layout; -1 for other i. */
+const char* nsa_last_error(void);
+int nsa_abi_version(void);
+int nsa_struct_size(int which);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NSA_B200_H */

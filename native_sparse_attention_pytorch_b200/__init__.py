@@ -1,0 +1,13 @@
+"""B200-native Native Sparse Attention hot path (sm_100a CUDA kernels behind a C ABI)."""
+from .native_sparse_attention import SparseAttention
+from .ops import (
+    native_sparse_attend,
+    block_diagonal_attend,
+    compressed_attend,
+    select_blocks,
+    sliding_window_attend,
+    gated_combine,
+)
+
+__all__ = ['SparseAttention', 'native_sparse_attend', 'block_diagonal_attend', 'compressed_attend',
+           'select_blocks', 'sliding_window_attend', 'gated_combine']

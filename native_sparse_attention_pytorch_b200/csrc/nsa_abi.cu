@@ -1,0 +1,312 @@
+// extern "C" entry points: argument checks, family dispatch, launches.
+
+#include <stdio.h>
+#include <string.h>
+
+#include "nsa_common.cuh"
+#include "nsa_kernels.h"
+
+namespace nsa {
+
+static thread_local char g_error[256] = "";
+
+int fail(int code, const char* msg) {
+  snprintf(g_error, sizeof(g_error), "%s", msg ? msg : "");
+  return code;
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// A [B,H,N,d] view is usable when rows start on 16-byte boundaries.
+static int check_tensor(const nsa_tensor& t, int dtype, const char* name) {
+  static thread_local char msg[128];
+  if (t.ptr == nullptr) {
+    snprintf(msg, sizeof(msg), "%s: NULL pointer", name);
+    return fail(NSA_ERR_NULL, msg);
+  }
+  const int64_t per16 = dtype == NSA_F32 ? 4 : 8;
+  if (!aligned16(t.ptr) || t.stride_b % per16 || t.stride_h % per16 || t.stride_n % per16) {
+    snprintf(msg, sizeof(msg), "%s: pointer and strides must keep every row 16-byte aligned", name);
+    return fail(NSA_ERR_ALIGN, msg);
+  }
+  return NSA_OK;
+}
+
+static int check_common(int dtype, int batch, int q_heads, int kv_heads, int seq, int d) {
+  if (dtype != NSA_F32 && dtype != NSA_BF16) return fail(NSA_ERR_DTYPE, "dtype must be NSA_F32 or NSA_BF16");
+  if (batch < 0 || seq < 0 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads)
+    return fail(NSA_ERR_SHAPE, "batch/seq must be >= 0 and q_heads a positive multiple of kv_heads");
+  if (d <= 0 || d > 128 || d % 8) return fail(NSA_ERR_SHAPE, "dim_head must be a multiple of 8, at most 128");
+  return NSA_OK;
+}
+
+#define NSA_TRY(expr)            \
+  do {                           \
+    const int rc_ = (expr);      \
+    if (rc_ != NSA_OK) return rc_; \
+  } while (0)
+
+static void set_qkvo(AttnParams& P, const nsa_tensor& q, const nsa_tensor& k, const nsa_tensor& v, const nsa_tensor& o) {
+  P.q = q.ptr; P.q_sb = q.stride_b; P.q_sh = q.stride_h; P.q_sn = q.stride_n;
+  P.k = k.ptr; P.k_sb = k.stride_b; P.k_sh = k.stride_h; P.k_sn = k.stride_n;
+  P.v = v.ptr; P.v_sb = v.stride_b; P.v_sh = v.stride_h; P.v_sn = v.stride_n;
+  P.out = o.ptr; P.o_sb = o.stride_b; P.o_sh = o.stride_h; P.o_sn = o.stride_n;
+}
+
+static void set_dout(AttnParams& P, const nsa_tensor& t) {
+  P.dout = t.ptr; P.do_sb = t.stride_b; P.do_sh = t.stride_h; P.do_sn = t.stride_n;
+}
+
+static int zero_async(float* p, int64_t count, cudaStream_t stream) {
+  if (count == 0) return NSA_OK;
+  const cudaError_t err = cudaMemsetAsync(p, 0, (size_t)count * sizeof(float), stream);
+  return err == cudaSuccess ? NSA_OK : fail((int)err, cudaGetErrorString(err));
+}
+
+// ---- selected-block branch ---------------------------------------------------
+
+static int fill_sel(AttnParams& P, const nsa_sel_fwd_args& a) {
+  NSA_TRY(check_common(a.dtype, a.batch, a.q_heads, a.kv_heads, a.seq, a.dim_head));
+  if (a.sel_heads != a.kv_heads && a.sel_heads != a.q_heads)
+    return fail(NSA_ERR_SHAPE, "sel_heads must equal kv_heads or q_heads");
+  if (a.block <= 0 || a.nsel < 0) return fail(NSA_ERR_SHAPE, "block must be > 0 and nsel >= 0");
+  if (a.diag < NSA_DIAG_NONE || a.diag > NSA_DIAG_FULL) return fail(NSA_ERR_SHAPE, "unknown diag mode");
+  if (a.impl < NSA_IMPL_AUTO || a.impl > NSA_IMPL_SM100) return fail(NSA_ERR_SHAPE, "unknown impl");
+  NSA_TRY(check_tensor(a.q, a.dtype, "q"));
+  NSA_TRY(check_tensor(a.k, a.dtype, "k"));
+  NSA_TRY(check_tensor(a.v, a.dtype, "v"));
+  NSA_TRY(check_tensor(a.out, a.dtype, "out"));
+  if (a.lse == nullptr) return fail(NSA_ERR_NULL, "lse: NULL pointer");
+  if (a.nsel > 0 && (a.idx == nullptr || a.mask == nullptr)) return fail(NSA_ERR_NULL, "idx/mask: NULL pointer");
+  memset(&P, 0, sizeof(P));
+  set_qkvo(P, a.q, a.k, a.v, a.out);
+  P.lse = a.lse;
+  P.batch = a.batch; P.q_heads = a.q_heads; P.kv_heads = a.kv_heads; P.groups = a.sel_heads;
+  P.seq = a.seq; P.d = a.dim_head; P.key_rows = a.seq; P.scale = a.scale;
+  P.idx = a.idx; P.mask = a.mask; P.block = a.block; P.nsel = a.nsel; P.diag = a.diag;
+  return NSA_OK;
+}
+
+}  // namespace nsa
+
+using namespace nsa;
+
+extern "C" {
+
+int nsa_abi_version(void) { return 1; }
+
+const char* nsa_last_error(void) { return g_error; }
+
+int nsa_struct_size(int which) {
+  switch (which) {
+    case 0: return (int)sizeof(nsa_tensor);
+    case 1: return (int)sizeof(nsa_sel_fwd_args);
+    case 2: return (int)sizeof(nsa_sel_bwd_args);
+    case 3: return (int)sizeof(nsa_cmp_fwd_args);
+    case 4: return (int)sizeof(nsa_cmp_bwd_args);
+    case 5: return (int)sizeof(nsa_select_args);
+    case 6: return (int)sizeof(nsa_swa_fwd_args);
+    case 7: return (int)sizeof(nsa_swa_bwd_args);
+    case 8: return (int)sizeof(nsa_combine_fwd_args);
+    case 9: return (int)sizeof(nsa_combine_bwd_args);
+    default: return -1;
+  }
+}
+
+int64_t nsa_sel_workspace_bytes(const nsa_sel_fwd_args* a, int backward) {
+  if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
+  AttnParams P;
+  const int rc = fill_sel(P, *a);
+  if (rc != NSA_OK && rc != NSA_ERR_NULL) return rc;
+  if (a->impl == NSA_IMPL_SIMT) return 0;
+  const int64_t need = sm100_sel_workspace_bytes(*a, backward != 0);
+  if (need < 0) return a->impl == NSA_IMPL_SM100 ? need : 0;
+  return need;
+}
+
+int nsa_sel_fwd(const nsa_sel_fwd_args* a, void* stream) {
+  if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
+  AttnParams P;
+  NSA_TRY(fill_sel(P, *a));
+  cudaStream_t st = (cudaStream_t)stream;
+  if (a->impl != NSA_IMPL_SIMT) {
+    const int rc = sm100_sel_fwd(*a, st);
+    if (rc != NSA_ERR_UNSUPPORTED || a->impl == NSA_IMPL_SM100) return rc;
+  }
+  return simt_attend(P, BR_SEL, a->dtype, false, st);
+}
+
+int nsa_sel_bwd(const nsa_sel_bwd_args* a, void* stream) {
+  if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
+  AttnParams P;
+  NSA_TRY(fill_sel(P, a->fwd));
+  NSA_TRY(check_tensor(a->dout, a->fwd.dtype, "dout"));
+  if (!a->dq || !a->dk || !a->dv) return fail(NSA_ERR_NULL, "dq/dk/dv: NULL pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t d = a->fwd.dim_head, n = a->fwd.seq, b = a->fwd.batch;
+  NSA_TRY(zero_async(a->dq, b * a->fwd.q_heads * n * d, st));
+  NSA_TRY(zero_async(a->dk, b * a->fwd.kv_heads * n * d, st));
+  NSA_TRY(zero_async(a->dv, b * a->fwd.kv_heads * n * d, st));
+  if (a->fwd.impl != NSA_IMPL_SIMT) {
+    const int rc = sm100_sel_bwd(*a, st);
+    if (rc != NSA_ERR_UNSUPPORTED || a->fwd.impl == NSA_IMPL_SM100) return rc;
+  }
+  set_dout(P, a->dout);
+  P.dq = a->dq; P.dk = a->dk; P.dv = a->dv; P.slot_grads = a->slot_grads;
+  return simt_attend(P, BR_SEL, a->fwd.dtype, true, st);
+}
+
+// ---- compressed branch -------------------------------------------------------
+
+static int fill_cmp(AttnParams& P, const nsa_cmp_fwd_args& a) {
+  NSA_TRY(check_common(a.dtype, a.batch, a.q_heads, a.kv_heads, a.seq, a.dim_head));
+  if (a.sel_heads != a.kv_heads && a.sel_heads != a.q_heads)
+    return fail(NSA_ERR_SHAPE, "sel_heads must equal kv_heads or q_heads");
+  if (a.num_mem < 1 || a.ncb < 0 || a.stride <= 0) return fail(NSA_ERR_SHAPE, "need num_mem >= 1, ncb >= 0, stride > 0");
+  NSA_TRY(check_tensor(a.q, a.dtype, "q"));
+  NSA_TRY(check_tensor(a.ck, a.dtype, "ck"));
+  NSA_TRY(check_tensor(a.cv, a.dtype, "cv"));
+  NSA_TRY(check_tensor(a.out, a.dtype, "out"));
+  if (a.lse == nullptr) return fail(NSA_ERR_NULL, "lse: NULL pointer");
+  memset(&P, 0, sizeof(P));
+  set_qkvo(P, a.q, a.ck, a.cv, a.out);
+  P.lse = a.lse;
+  P.batch = a.batch; P.q_heads = a.q_heads; P.kv_heads = a.kv_heads; P.groups = a.kv_heads;
+  P.seq = a.seq; P.d = a.dim_head; P.key_rows = a.num_mem + a.ncb; P.scale = a.scale;
+  P.num_mem = a.num_mem; P.ncb = a.ncb; P.stride = a.stride; P.causal = a.causal;
+  P.imp_heads = a.sel_heads; P.round_bf16 = a.dtype == NSA_BF16; P.sentinel = a.sentinel;
+  P.importance = a.importance;
+  return NSA_OK;
+}
+
+int nsa_cmp_fwd(const nsa_cmp_fwd_args* a, void* stream) {
+  if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
+  AttnParams P;
+  NSA_TRY(fill_cmp(P, *a));
+  if (a->impl == NSA_IMPL_SM100) return fail(NSA_ERR_UNSUPPORTED, "compressed branch: only the SIMT family is built");
+  return simt_attend(P, BR_CMP, a->dtype, false, (cudaStream_t)stream);
+}
+
+int nsa_cmp_bwd(const nsa_cmp_bwd_args* a, void* stream) {
+  if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
+  AttnParams P;
+  NSA_TRY(fill_cmp(P, a->fwd));
+  NSA_TRY(check_tensor(a->dout, a->fwd.dtype, "dout"));
+  if (!a->dq || !a->dck || !a->dcv) return fail(NSA_ERR_NULL, "dq/dck/dcv: NULL pointer");
+  if (a->fwd.impl == NSA_IMPL_SM100) return fail(NSA_ERR_UNSUPPORTED, "compressed branch: only the SIMT family is built");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t d = a->fwd.dim_head, rows = a->fwd.num_mem + a->fwd.ncb, b = a->fwd.batch;
+  NSA_TRY(zero_async(a->dq, b * a->fwd.q_heads * a->fwd.seq * d, st));
+  NSA_TRY(zero_async(a->dck, b * a->fwd.kv_heads * rows * d, st));
+  NSA_TRY(zero_async(a->dcv, b * a->fwd.kv_heads * rows * d, st));
+  set_dout(P, a->dout);
+  P.importance = nullptr;
+  P.dq = a->dq; P.dk = a->dck; P.dv = a->dcv;
+  return simt_attend(P, BR_CMP, a->fwd.dtype, true, st);
+}
+
+// ---- selection -----------------------------------------------------------------
+
+int nsa_select(const nsa_select_args* a, void* stream) {
+  if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
+  if (a->dtype != NSA_F32 && a->dtype != NSA_BF16) return fail(NSA_ERR_DTYPE, "dtype must be NSA_F32 or NSA_BF16");
+  if (a->rows < 0 || a->seq < 0 || a->ncb < 0 || a->cpf < 1 || a->block <= 0 || a->k < 0)
+    return fail(NSA_ERR_SHAPE, "negative size, cpf < 1 or block <= 0");
+  const int cols = a->ncb / a->cpf;
+  if (a->k > cols) return fail(NSA_ERR_SHAPE, "k exceeds the number of block columns");
+  if (a->input_is_prob && a->cpf != 1) return fail(NSA_ERR_SHAPE, "input_is_prob needs cpf == 1");
+  if (!a->importance || !a->idx || !a->vals) return fail(NSA_ERR_NULL, "importance/idx/vals: NULL pointer");
+  SelectParams P;
+  P.imp = a->importance; P.idx = a->idx; P.vals = a->vals;
+  P.rows = a->rows; P.seq = a->seq; P.ncb = a->ncb; P.cpf = a->cpf; P.cols = cols; P.k = a->k;
+  P.block = a->block; P.exclude_own = a->exclude_own; P.input_is_prob = a->input_is_prob;
+  P.round_bf16 = a->dtype == NSA_BF16;
+  P.neg_max = a->dtype == NSA_BF16 ? -3.3895313892515355e38f : -FLT_MAX;
+  return launch_select(P, (cudaStream_t)stream);
+}
+
+// ---- sliding window ------------------------------------------------------------
+
+static int fill_swa(AttnParams& P, const nsa_swa_fwd_args& a) {
+  NSA_TRY(check_common(a.dtype, a.batch, a.q_heads, a.kv_heads, a.seq, a.dim_head));
+  if (a.window < 0) return fail(NSA_ERR_SHAPE, "window must be >= 0");
+  NSA_TRY(check_tensor(a.q, a.dtype, "q"));
+  NSA_TRY(check_tensor(a.k, a.dtype, "k"));
+  NSA_TRY(check_tensor(a.v, a.dtype, "v"));
+  NSA_TRY(check_tensor(a.out, a.dtype, "out"));
+  if (a.lse == nullptr) return fail(NSA_ERR_NULL, "lse: NULL pointer");
+  memset(&P, 0, sizeof(P));
+  set_qkvo(P, a.q, a.k, a.v, a.out);
+  P.lse = a.lse;
+  P.batch = a.batch; P.q_heads = a.q_heads; P.kv_heads = a.kv_heads; P.groups = a.kv_heads;
+  P.seq = a.seq; P.d = a.dim_head; P.key_rows = a.seq; P.scale = a.scale;
+  P.window = a.window; P.causal = a.causal;
+  return NSA_OK;
+}
+
+int nsa_swa_fwd(const nsa_swa_fwd_args* a, void* stream) {
+  if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
+  AttnParams P;
+  NSA_TRY(fill_swa(P, *a));
+  if (a->impl == NSA_IMPL_SM100) return fail(NSA_ERR_UNSUPPORTED, "sliding branch: only the SIMT family is built");
+  return simt_attend(P, BR_SWA, a->dtype, false, (cudaStream_t)stream);
+}
+
+int nsa_swa_bwd(const nsa_swa_bwd_args* a, void* stream) {
+  if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
+  AttnParams P;
+  NSA_TRY(fill_swa(P, a->fwd));
+  NSA_TRY(check_tensor(a->dout, a->fwd.dtype, "dout"));
+  if (!a->dq || !a->dk || !a->dv) return fail(NSA_ERR_NULL, "dq/dk/dv: NULL pointer");
+  if (a->fwd.impl == NSA_IMPL_SM100) return fail(NSA_ERR_UNSUPPORTED, "sliding branch: only the SIMT family is built");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t d = a->fwd.dim_head, n = a->fwd.seq, b = a->fwd.batch;
+  NSA_TRY(zero_async(a->dq, b * a->fwd.q_heads * n * d, st));
+  NSA_TRY(zero_async(a->dk, b * a->fwd.kv_heads * n * d, st));
+  NSA_TRY(zero_async(a->dv, b * a->fwd.kv_heads * n * d, st));
+  set_dout(P, a->dout);
+  P.dq = a->dq; P.dk = a->dk; P.dv = a->dv;
+  return simt_attend(P, BR_SWA, a->fwd.dtype, true, st);
+}
+
+// ---- combine ---------------------------------------------------------------------
+
+static int fill_combine(CombineParams& P, const nsa_combine_fwd_args& a) {
+  if (a.dtype != NSA_F32 && a.dtype != NSA_BF16) return fail(NSA_ERR_DTYPE, "dtype must be NSA_F32 or NSA_BF16");
+  if (a.batch < 0 || a.seq < 0 || a.q_heads <= 0 || a.dim_head <= 0 || a.dim_head % 2)
+    return fail(NSA_ERR_SHAPE, "negative size or odd dim_head");
+  const nsa_tensor* o[3] = {&a.o_cmp, &a.o_sel, &a.o_swa};
+  memset(&P, 0, sizeof(P));
+  for (int s = 0; s < 3; ++s) {
+    if (o[s]->ptr == nullptr) return fail(NSA_ERR_NULL, "branch output: NULL pointer");
+    if ((reinterpret_cast<uintptr_t>(o[s]->ptr) & 7u) || o[s]->stride_b % 2 || o[s]->stride_h % 2 || o[s]->stride_n % 2)
+      return fail(NSA_ERR_ALIGN, "branch outputs must keep feature pairs aligned");
+    P.o[s] = o[s]->ptr; P.o_sb[s] = o[s]->stride_b; P.o_sh[s] = o[s]->stride_h; P.o_sn[s] = o[s]->stride_n;
+  }
+  if (a.gates.ptr == nullptr) return fail(NSA_ERR_NULL, "gates: NULL pointer");
+  P.gates = a.gates.ptr; P.g_sb = a.gates.stride_b; P.g_sh = a.gates.stride_h; P.g_sn = a.gates.stride_n;
+  P.batch = a.batch; P.q_heads = a.q_heads; P.seq = a.seq; P.d = a.dim_head;
+  return NSA_OK;
+}
+
+int nsa_combine_fwd(const nsa_combine_fwd_args* a, void* stream) {
+  if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
+  CombineParams P;
+  NSA_TRY(fill_combine(P, *a));
+  if (a->out == nullptr) return fail(NSA_ERR_NULL, "out: NULL pointer");
+  P.out = a->out;
+  return launch_combine(P, a->dtype, false, (cudaStream_t)stream);
+}
+
+int nsa_combine_bwd(const nsa_combine_bwd_args* a, void* stream) {
+  if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
+  CombineParams P;
+  NSA_TRY(fill_combine(P, a->fwd));
+  if (!a->dout || !a->d_cmp || !a->d_sel || !a->d_swa || !a->d_gates) return fail(NSA_ERR_NULL, "gradient buffer: NULL pointer");
+  P.dout = a->dout;
+  P.d_o[0] = a->d_cmp; P.d_o[1] = a->d_sel; P.d_o[2] = a->d_swa;
+  P.d_gates = a->d_gates;
+  return launch_combine(P, a->fwd.dtype, true, (cudaStream_t)stream);
+}
+
+}  // extern "C"

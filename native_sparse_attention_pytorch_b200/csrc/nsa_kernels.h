@@ -1,0 +1,71 @@
+// Internal interface between the C ABI layer and the kernel files.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "nsa_b200.h"
+
+namespace nsa {
+
+enum { BR_SEL = 0, BR_CMP = 1, BR_SWA = 2 };
+
+// Parameters of the generic attention kernels (all three branches).
+struct AttnParams {
+  const void *q, *k, *v, *dout;
+  void* out;
+  int64_t q_sb, q_sh, q_sn;
+  int64_t k_sb, k_sh, k_sn;
+  int64_t v_sb, v_sh, v_sn;
+  int64_t o_sb, o_sh, o_sn;
+  int64_t do_sb, do_sh, do_sn;
+  float* lse;
+  float *dq, *dk, *dv;  // contiguous fp32; dk/dv have `key_rows` rows per head
+  float* slot_grads;
+  int batch, q_heads, kv_heads, groups, seq, d;
+  int key_rows;  // rows of k/v per head (seq, or num_mem + ncb)
+  float scale;
+  // selected branch
+  const int64_t* idx;
+  const uint8_t* mask;
+  int block, nsel, diag;
+  // compressed branch
+  int num_mem, ncb, stride, causal, imp_heads, round_bf16;
+  float sentinel;
+  float* importance;
+  // sliding branch
+  int window;
+};
+
+struct SelectParams {
+  const float* imp;
+  int64_t* idx;
+  float* vals;
+  int rows, seq, ncb, cpf, cols, k, block, exclude_own, input_is_prob, round_bf16;
+  float neg_max;
+};
+
+struct CombineParams {
+  const void *o[3], *gates, *dout;
+  int64_t o_sb[3], o_sh[3], o_sn[3];
+  int64_t g_sb, g_sh, g_sn;
+  void* out;
+  void* d_o[3];
+  float* d_gates;
+  int batch, q_heads, seq, d;
+};
+
+int fail(int code, const char* msg);
+
+int simt_attend(const AttnParams& P, int branch, int dtype, bool backward, cudaStream_t stream);
+int launch_select(const SelectParams& P, cudaStream_t stream);
+int launch_combine(const CombineParams& P, int dtype, bool backward, cudaStream_t stream);
+
+// Tensor-core family for the selected-block branch.  Each returns
+// NSA_ERR_UNSUPPORTED (without touching the error message state of a later
+// successful call) when the shape is outside what it serves.
+int64_t sm100_sel_workspace_bytes(const nsa_sel_fwd_args& a, bool backward);
+int sm100_sel_fwd(const nsa_sel_fwd_args& a, cudaStream_t stream);
+int sm100_sel_bwd(const nsa_sel_bwd_args& a, cudaStream_t stream);
+
+}  // namespace nsa

@@ -1,0 +1,308 @@
+"""PyTorch operators over the C-ABI kernels: one autograd Function per NSA
+branch plus the block selection and the gated combine.  Tensors stay owned by
+PyTorch's allocator; the library only sees device pointers, sizes and the
+current CUDA stream."""
+import ctypes as C
+
+import torch
+from torch.autograd import Function
+
+from . import _lib as L
+
+
+def _empty_like_rows(t):
+    """Contiguous [B,H,N,d] buffer of t's dtype."""
+    return torch.empty(t.shape, dtype=t.dtype, device=t.device)
+
+
+# --------------------------------------------------------------------------
+# selected-block attention (replaces upstream's Triton NSA Function, TRI:1824-1927)
+# --------------------------------------------------------------------------
+
+def _sel_args(q, k, v, out, idx, mask, lse, block, diag, impl, scale):
+    b, hq, n, d = q.shape
+    hkv = k.shape[1]
+    nsel = 0 if idx is None else idx.shape[-1]
+    hs = hkv if idx is None else idx.shape[1]
+    return L.SelFwdArgs(q=L.t4(q), k=L.t4(k), v=L.t4(v), out=L.t4(out), idx=L.ptr(idx), mask=L.ptr(mask),
+                        lse=L.ptr(lse), batch=b, q_heads=hq, kv_heads=hkv, sel_heads=hs, seq=n, dim_head=d,
+                        block=block, nsel=nsel, diag=diag, dtype=L.dtype_code(q), impl=impl, scale=scale,
+                        workspace=None, workspace_bytes=0)
+
+
+def _with_workspace(args, backward, device):
+    lib = L.load()
+    need = lib.nsa_sel_workspace_bytes(C.byref(args), int(backward))
+    if need < 0:
+        L.check(int(need))
+    ws = None
+    if need > 0:
+        ws = torch.empty(need, dtype=torch.uint8, device=device)
+        args.workspace, args.workspace_bytes = ws.data_ptr(), need
+    return ws
+
+
+class SelectedAttention(Function):
+    """out, lse = f(q, k, v, idx, mask, slot_scale, block, diag, impl)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, idx, mask, slot_scale, block, diag, impl):
+        L.require_cuda(q, k, v, idx, mask)
+        lib = L.load()
+        q, k, v = L.rowwise(q), L.rowwise(k), L.rowwise(v)
+        if idx is not None:
+            idx = idx.to(torch.int64).contiguous()
+            mask = mask.to(torch.bool).contiguous().view(torch.uint8)
+        b, hq, n, d = q.shape
+        out = _empty_like_rows(q)
+        lse = torch.empty(b, hq, n, dtype=torch.float32, device=q.device)
+        scale = d ** -0.5
+        with torch.cuda.device(q.device):
+            args = _sel_args(q, k, v, out, idx, mask, lse, block, diag, impl, scale)
+            ws = _with_workspace(args, False, q.device)
+            L.check(lib.nsa_sel_fwd(C.byref(args), L.stream_of(q)))
+        del ws
+        ctx.save_for_backward(q, k, v, idx, mask, out, lse)
+        ctx.cfg = (block, diag, impl, scale, None if slot_scale is None else slot_scale.dtype)
+        ctx.mark_non_differentiable(lse)
+        return out, lse
+
+    @staticmethod
+    def backward(ctx, dout, _dlse):
+        q, k, v, idx, mask, out, lse = ctx.saved_tensors
+        block, diag, impl, scale, slot_dtype = ctx.cfg
+        want_slot_grads = slot_dtype is not None
+        lib = L.load()
+        dout = L.rowwise(dout)
+        dq = torch.empty(q.shape, dtype=torch.float32, device=q.device)
+        dk = torch.empty(k.shape, dtype=torch.float32, device=q.device)
+        dv = torch.empty(v.shape, dtype=torch.float32, device=q.device)
+        slot = torch.zeros(idx.shape, dtype=torch.float32, device=q.device) if want_slot_grads else None
+        with torch.cuda.device(q.device):
+            fwd = _sel_args(q, k, v, out, idx, mask, lse, block, diag, impl, scale)
+            ws = _with_workspace(fwd, True, q.device)
+            args = L.SelBwdArgs(fwd=fwd, dout=L.t4(dout), dq=L.ptr(dq), dk=L.ptr(dk), dv=L.ptr(dv),
+                                slot_grads=L.ptr(slot))
+            L.check(lib.nsa_sel_bwd(C.byref(args), L.stream_of(q)))
+        del ws
+        return (dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), None, None,
+                None if slot is None else slot.to(slot_dtype), None, None, None)
+
+
+def native_sparse_attend(fq, fk, fv, block_size, selected_block_indices, fmask, sel_scale=None,
+                         include_block_causal=True, return_lse=False, block_dk_dv_use_dot=False,
+                         return_sliding_window_out=False, impl='auto'):
+    """Drop-in for upstream's ``native_sparse_attend`` (TRI:1938-1987): selected-
+    block attention with GQA head grouping.  fq [b,qh,n,d]; fk, fv [b,kh,n,d];
+    indices / mask / sel_scale [b,kh,n,sel] or [b,qh,n,sel].  ``sel_scale`` must
+    be all ones (TRI:1860-1861) and only adds a gradient output for it.
+    ``block_dk_dv_use_dot`` is accepted and ignored (a Triton tuning switch).
+    The fused second sliding-window output of upstream's kernel is not offered;
+    use ``sliding_window_attend``.  Unlike upstream there is no block_size >= 16
+    or fp16 restriction, and float32 inputs are computed in float32."""
+    if return_sliding_window_out:
+        raise NotImplementedError('return_sliding_window_out: use sliding_window_attend for the sliding branch')
+    q_heads, kv_heads, sel_heads = fq.shape[1], fk.shape[1], selected_block_indices.shape[1]
+    assert q_heads % kv_heads == 0
+    assert sel_heads in (q_heads, kv_heads)
+    diag = L.DIAG_CAUSAL if include_block_causal else L.DIAG_NONE
+    out, lse = SelectedAttention.apply(fq, fk, fv, selected_block_indices, fmask, sel_scale, block_size, diag,
+                                       L.IMPL_BY_NAME[impl])
+    return (out, lse) if return_lse else out
+
+
+def block_diagonal_attend(fq, fk, fv, block_size, causal, impl='auto'):
+    """The no-selection fallback (NSA:821-837): every query attends its own block only."""
+    diag = L.DIAG_CAUSAL if causal else L.DIAG_FULL
+    out, _ = SelectedAttention.apply(fq, fk, fv, None, None, None, block_size, diag, L.IMPL_BY_NAME[impl])
+    return out
+
+
+# --------------------------------------------------------------------------
+# compressed attention + importance (replaces NSA:621-639, 652-662)
+# --------------------------------------------------------------------------
+
+def mask_sentinel(dtype):
+    """The finite value upstream writes over invisible logits: (-finfo.max)//10 stored in `dtype` (NSA:168-171)."""
+    return torch.tensor(-torch.finfo(dtype).max // 10, dtype=dtype).float().item()
+
+
+def _cmp_args(q, ck, cv, out, lse, imp, sel_heads, num_mem, stride, causal, impl, scale):
+    b, hq, n, d = q.shape
+    return L.CmpFwdArgs(q=L.t4(q), ck=L.t4(ck), cv=L.t4(cv), out=L.t4(out), lse=L.ptr(lse), importance=L.ptr(imp),
+                        batch=b, q_heads=hq, kv_heads=ck.shape[1], sel_heads=sel_heads, seq=n, dim_head=d,
+                        num_mem=num_mem, ncb=ck.shape[2] - num_mem, stride=stride, causal=int(causal),
+                        dtype=L.dtype_code(q), impl=impl, scale=scale, sentinel=mask_sentinel(q.dtype))
+
+
+class CompressedAttention(Function):
+    """out, importance = f(q, ck, cv, num_mem, stride, causal, sel_heads, want_importance, impl);
+    ck, cv carry the memory slots in front.  importance is [B, sel_heads, N, ncb] fp32, no gradient."""
+
+    @staticmethod
+    def forward(ctx, q, ck, cv, num_mem, stride, causal, sel_heads, want_importance, impl):
+        L.require_cuda(q, ck, cv)
+        lib = L.load()
+        q, ck, cv = L.rowwise(q), L.rowwise(ck), L.rowwise(cv)
+        b, hq, n, d = q.shape
+        ncb = ck.shape[2] - num_mem
+        out = _empty_like_rows(q)
+        lse = torch.empty(b, hq, n, dtype=torch.float32, device=q.device)
+        imp = torch.empty(b, sel_heads, n, ncb, dtype=torch.float32, device=q.device) if want_importance else None
+        scale = d ** -0.5
+        with torch.cuda.device(q.device):
+            args = _cmp_args(q, ck, cv, out, lse, imp, sel_heads, num_mem, stride, causal, impl, scale)
+            L.check(lib.nsa_cmp_fwd(C.byref(args), L.stream_of(q)))
+        ctx.save_for_backward(q, ck, cv, out, lse)
+        ctx.cfg = (num_mem, stride, causal, sel_heads, impl, scale)
+        if imp is None:
+            imp = torch.empty(0, device=q.device)
+        ctx.mark_non_differentiable(imp)
+        return out, imp
+
+    @staticmethod
+    def backward(ctx, dout, _dimp):
+        q, ck, cv, out, lse = ctx.saved_tensors
+        num_mem, stride, causal, sel_heads, impl, scale = ctx.cfg
+        lib = L.load()
+        dout = L.rowwise(dout)
+        dq = torch.empty(q.shape, dtype=torch.float32, device=q.device)
+        dck = torch.empty(ck.shape, dtype=torch.float32, device=q.device)
+        dcv = torch.empty(cv.shape, dtype=torch.float32, device=q.device)
+        with torch.cuda.device(q.device):
+            fwd = _cmp_args(q, ck, cv, out, lse, None, sel_heads, num_mem, stride, causal, impl, scale)
+            args = L.CmpBwdArgs(fwd=fwd, dout=L.t4(dout), dq=L.ptr(dq), dck=L.ptr(dck), dcv=L.ptr(dcv))
+            L.check(lib.nsa_cmp_bwd(C.byref(args), L.stream_of(q)))
+        return dq.to(q.dtype), dck.to(ck.dtype), dcv.to(cv.dtype), None, None, None, None, None, None
+
+
+def compressed_attend(q, ck, cv, num_mem, stride, causal, sel_heads=None, want_importance=True, impl='auto'):
+    sel_heads = ck.shape[1] if sel_heads is None else sel_heads
+    out, imp = CompressedAttention.apply(q, ck, cv, num_mem, stride, causal, sel_heads, want_importance,
+                                         L.IMPL_BY_NAME[impl])
+    return (out, imp) if want_importance else out
+
+
+# --------------------------------------------------------------------------
+# block selection (replaces NSA:672-713); integer output, no gradient
+# --------------------------------------------------------------------------
+
+@torch.no_grad()
+def select_blocks(importance, block, stride, nsel, dtype=torch.float32, input_is_prob=False):
+    """importance [B, Hs, N, ncb] fp32 -> (values [B,Hs,N,k] in `dtype`, int64 indices [B,Hs,N,k]),
+    k = min(nsel, ncb // (block // stride)).  See nsa_select in include/nsa_b200.h."""
+    L.require_cuda(importance)
+    lib = L.load()
+    importance = importance.contiguous().float()
+    b, hs, n, ncb = importance.shape
+    cpf = 1 if input_is_prob else block // stride
+    cols = ncb // cpf
+    k = min(nsel, cols)
+    idx = torch.empty(b, hs, n, k, dtype=torch.int64, device=importance.device)
+    vals = torch.empty(b, hs, n, k, dtype=torch.float32, device=importance.device)
+    if k > 0 and idx.numel() > 0:
+        code = L.NSA_BF16 if dtype == torch.bfloat16 else L.NSA_F32
+        args = L.SelectArgs(importance=L.ptr(importance), idx=L.ptr(idx), vals=L.ptr(vals), rows=b * hs, seq=n,
+                            ncb=ncb, cpf=cpf, k=k, block=block, exclude_own=int(block != stride and not input_is_prob),
+                            input_is_prob=int(input_is_prob), dtype=code)
+        with torch.cuda.device(importance.device):
+            L.check(lib.nsa_select(C.byref(args), L.stream_of(importance)))
+    return vals.to(dtype), idx
+
+
+# --------------------------------------------------------------------------
+# sliding window (replaces the LocalAttention call NSA:841-850)
+# --------------------------------------------------------------------------
+
+def _swa_args(q, k, v, out, lse, window, causal, impl, scale):
+    b, hq, n, d = q.shape
+    return L.SwaFwdArgs(q=L.t4(q), k=L.t4(k), v=L.t4(v), out=L.t4(out), lse=L.ptr(lse), batch=b, q_heads=hq,
+                        kv_heads=k.shape[1], seq=n, dim_head=d, window=window, causal=int(causal),
+                        dtype=L.dtype_code(q), impl=impl, scale=scale)
+
+
+class SlidingAttention(Function):
+    @staticmethod
+    def forward(ctx, q, k, v, window, causal, impl):
+        L.require_cuda(q, k, v)
+        lib = L.load()
+        q, k, v = L.rowwise(q), L.rowwise(k), L.rowwise(v)
+        b, hq, n, d = q.shape
+        out = _empty_like_rows(q)
+        lse = torch.empty(b, hq, n, dtype=torch.float32, device=q.device)
+        scale = d ** -0.5
+        with torch.cuda.device(q.device):
+            args = _swa_args(q, k, v, out, lse, window, causal, impl, scale)
+            L.check(lib.nsa_swa_fwd(C.byref(args), L.stream_of(q)))
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.cfg = (window, causal, impl, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse = ctx.saved_tensors
+        window, causal, impl, scale = ctx.cfg
+        lib = L.load()
+        dout = L.rowwise(dout)
+        dq = torch.empty(q.shape, dtype=torch.float32, device=q.device)
+        dk = torch.empty(k.shape, dtype=torch.float32, device=q.device)
+        dv = torch.empty(v.shape, dtype=torch.float32, device=q.device)
+        with torch.cuda.device(q.device):
+            fwd = _swa_args(q, k, v, out, lse, window, causal, impl, scale)
+            args = L.SwaBwdArgs(fwd=fwd, dout=L.t4(dout), dq=L.ptr(dq), dk=L.ptr(dk), dv=L.ptr(dv))
+            L.check(lib.nsa_swa_bwd(C.byref(args), L.stream_of(q)))
+        return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), None, None, None
+
+
+def sliding_window_attend(q, k, v, window, causal, impl='auto'):
+    """q [b,qh,n,d]; k, v [b,kh,n,d] (not repeated over the query-head groups)."""
+    return SlidingAttention.apply(q, k, v, window, causal, L.IMPL_BY_NAME[impl])
+
+
+# --------------------------------------------------------------------------
+# gated combine + head merge (replaces NSA:854-860)
+# --------------------------------------------------------------------------
+
+def _pairwise(t):
+    ok = t.stride(-1) == 1 and t.data_ptr() % 8 == 0 and all(s % 2 == 0 for s in t.stride()[:-1])
+    return t if ok else t.contiguous()
+
+
+class GatedCombine(Function):
+    """merged [B,N,H*d] = sum_s gates[...,s] * branch_s; gates [B,H,N,3] (any strides)."""
+
+    @staticmethod
+    def forward(ctx, o_cmp, o_sel, o_swa, gates):
+        L.require_cuda(o_cmp, o_sel, o_swa, gates)
+        lib = L.load()
+        o_cmp, o_sel, o_swa = _pairwise(o_cmp), _pairwise(o_sel), _pairwise(o_swa)
+        if gates.stride(-1) != 1:
+            gates = gates.contiguous()
+        b, h, n, d = o_cmp.shape
+        out = torch.empty(b, n, h * d, dtype=o_cmp.dtype, device=o_cmp.device)
+        args = L.CombineFwdArgs(o_cmp=L.t4(o_cmp), o_sel=L.t4(o_sel), o_swa=L.t4(o_swa), gates=L.t4(gates),
+                                out=L.ptr(out), batch=b, q_heads=h, seq=n, dim_head=d, dtype=L.dtype_code(o_cmp))
+        with torch.cuda.device(out.device):
+            L.check(lib.nsa_combine_fwd(C.byref(args), L.stream_of(out)))
+        ctx.save_for_backward(o_cmp, o_sel, o_swa, gates)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        o_cmp, o_sel, o_swa, gates = ctx.saved_tensors
+        lib = L.load()
+        dout = dout.contiguous()
+        b, h, n, d = o_cmp.shape
+        d_cmp, d_sel, d_swa = (torch.empty(b, h, n, d, dtype=o_cmp.dtype, device=o_cmp.device) for _ in range(3))
+        d_gates = torch.empty(b, h, n, 3, dtype=torch.float32, device=o_cmp.device)
+        fwd = L.CombineFwdArgs(o_cmp=L.t4(o_cmp), o_sel=L.t4(o_sel), o_swa=L.t4(o_swa), gates=L.t4(gates),
+                               out=None, batch=b, q_heads=h, seq=n, dim_head=d, dtype=L.dtype_code(o_cmp))
+        args = L.CombineBwdArgs(fwd=fwd, dout=L.ptr(dout), d_cmp=L.ptr(d_cmp), d_sel=L.ptr(d_sel),
+                                d_swa=L.ptr(d_swa), d_gates=L.ptr(d_gates))
+        with torch.cuda.device(dout.device):
+            L.check(lib.nsa_combine_bwd(C.byref(args), L.stream_of(dout)))
+        return d_cmp, d_sel, d_swa, d_gates.to(gates.dtype)
+
+
+def gated_combine(o_cmp, o_sel, o_swa, gates):
+    return GatedCombine.apply(o_cmp, o_sel, o_swa, gates)

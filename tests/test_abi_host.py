@@ -1,0 +1,80 @@
+"""Host-side checks that need no GPU: the library loads, exports every entry
+point the header declares, agrees with the binding on struct layouts, and
+rejects bad arguments before touching a device."""
+import ctypes as C
+import os
+import re
+
+import pytest
+import torch
+
+from native_sparse_attention_pytorch_b200 import _lib as L
+from native_sparse_attention_pytorch_b200 import SparseAttention, native_sparse_attend
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_entry_points():
+    text = open(os.path.join(ROOT, 'include', 'nsa_b200.h')).read()
+    return sorted(set(re.findall(r'\b(nsa_[a-z0-9_]+)\s*\(', text)))
+
+
+def test_header_symbols_are_exported():
+    lib = L.load()
+    names = declared_entry_points()
+    assert set(names) == set(L.ENTRY_POINTS), (names, L.ENTRY_POINTS)
+    for n in names:
+        assert getattr(lib, n) is not None
+
+
+def test_struct_layouts_agree():
+    lib = L.load()
+    for which, st in enumerate(L._STRUCTS):
+        assert lib.nsa_struct_size(which) == C.sizeof(st), st.__name__
+    assert lib.nsa_struct_size(99) == -1
+    assert lib.nsa_abi_version() >= 1
+
+
+def test_null_and_shape_errors_are_reported_without_a_device():
+    lib = L.load()
+    assert lib.nsa_sel_fwd(None, None) == -1
+    a = L.SelFwdArgs(batch=1, q_heads=3, kv_heads=2, sel_heads=2, seq=8, dim_head=64, block=4, nsel=0, diag=1,
+                     dtype=L.NSA_F32, impl=L.IMPL_SIMT, scale=0.125)
+    assert lib.nsa_sel_fwd(C.byref(a), None) == -2          # 3 query heads over 2 kv heads
+    assert b'q_heads' in lib.nsa_last_error()
+    a.q_heads = 4
+    a.dim_head = 60
+    assert lib.nsa_sel_fwd(C.byref(a), None) == -2          # dim_head not a multiple of 8
+    a.dim_head = 64
+    a.dtype = 7
+    assert lib.nsa_sel_fwd(C.byref(a), None) == -3
+    a.dtype = L.NSA_BF16
+    assert lib.nsa_sel_fwd(C.byref(a), None) == -1          # q pointer is NULL
+    s = L.SelectArgs(importance=None, idx=None, vals=None, rows=1, seq=1, ncb=4, cpf=2, k=3, block=4, dtype=0)
+    assert lib.nsa_select(C.byref(s), None) == -2           # k > ncb / cpf
+
+
+def test_no_cpu_fallback():
+    attn = SparseAttention(dim=64, dim_head=16, heads=4, sliding_window_size=2, compress_block_size=4,
+                           compress_block_sliding_stride=2, selection_block_size=4, num_selected_blocks=2,
+                           use_triton_kernel=True)
+    with pytest.raises(RuntimeError):
+        attn(torch.randn(1, 8, 64))
+    q = torch.randn(1, 2, 8, 16)
+    idx = torch.zeros(1, 2, 8, 1, dtype=torch.long)
+    with pytest.raises(RuntimeError):
+        native_sparse_attend(q, q, q, 4, idx, idx.bool())
+    eager = SparseAttention(dim=64, dim_head=16, heads=4, sliding_window_size=2, compress_block_size=4,
+                            compress_block_sliding_stride=2, selection_block_size=4, num_selected_blocks=2)
+    with pytest.raises(RuntimeError):
+        eager(torch.randn(1, 8, 64))
+
+
+def test_state_dict_names_match_upstream():
+    attn = SparseAttention(dim=64, dim_head=16, heads=4, kv_heads=2, sliding_window_size=2, compress_block_size=4,
+                           compress_block_sliding_stride=2, selection_block_size=4, num_selected_blocks=2)
+    assert sorted(attn.state_dict()) == [
+        'combine_heads.weight', 'compress_mem_kv', 'k_compress.1.bias', 'k_compress.1.weight', 'k_compress.3.bias',
+        'k_compress.3.weight', 'k_intrablock_positions', 'norm.weight', 'to_qkv.weight',
+        'to_strategy_combine.0.bias', 'to_strategy_combine.0.weight', 'v_compress.1.bias', 'v_compress.1.weight',
+        'v_compress.3.bias', 'v_compress.3.weight', 'v_intrablock_positions']

@@ -1,0 +1,74 @@
+"""The whole SparseAttention layer on the GPU against the vectors stored from
+the unmodified upstream layer (fp32) and against the fp32 oracle (bf16)."""
+import pytest
+import torch
+
+import recipe
+from oracle import nsa_oracle as O
+from util import assert_close_bf16, assert_close_f32, load_golden, same_selection
+
+from native_sparse_attention_pytorch_b200 import SparseAttention
+
+pytestmark = pytest.mark.gpu
+DEV = 'cuda'
+LAYER = [n for n in recipe.LAYER_CASES if n != 'causal_diff_topk']
+
+
+def build(name, dtype=torch.float32):
+    c = recipe.LAYER_CASES[name]
+    attn = SparseAttention(**c['kw'], use_triton_kernel=True)
+    recipe.fill_weights(attn, seed=7, rich=c['rich'])
+    return attn.to(DEV).to(dtype)
+
+
+@pytest.mark.parametrize('name', LAYER)
+def test_layer_matches_upstream_vectors(name):
+    gold = load_golden('layer_' + name)
+    attn = build(name)
+    x = recipe.layer_input(name).to(DEV).requires_grad_()
+    out, mid = attn(x, return_intermediates=True)
+    mid['o_sel'].retain_grad()
+    mid['gates'].retain_grad()
+    (out * recipe.randn(out.shape, 13).to(DEV)).sum().backward()
+
+    if 'idx' in gold:
+        assert same_selection(mid['idx'], mid['fmask'], gold['idx'], gold['vals'] > 1e-10)
+        assert_close_f32(mid['vals'], gold['vals'], 'selection values', tol=1e-5)
+    else:
+        assert mid['idx'] is None
+    assert_close_f32(mid['o_sel'], gold['o_sel'], 'selected branch')
+    for key in ('o_cmp', 'o_swa', 'qr', 'kr'):
+        if key in gold:
+            assert_close_f32(mid[key], gold[key], key)
+    assert_close_f32(out, gold['out'], 'out')
+    assert_close_f32(x.grad, gold['x_grad'], 'd input')
+    assert_close_f32(mid['gates'].grad, gold['gates_grad'], 'd gates')
+    if 'o_sel_grad' in gold:
+        assert_close_f32(mid['o_sel'].grad, gold['o_sel_grad'], 'd selected branch')
+    for pname, p in attn.named_parameters():
+        g = gold.get('pgrad.' + pname)
+        if g is None:
+            assert p.grad is None or p.grad.abs().sum().item() == 0, pname
+            continue
+        got = torch.tensor([p.grad.abs().sum().item(), p.grad.pow(2).sum().item()], dtype=torch.float64)
+        assert torch.allclose(got, g, rtol=1e-3, atol=1e-6), (pname, got, g)
+
+
+@pytest.mark.parametrize('name', ['causal_gqa', 'causal_gqa_win', 'noncausal_gqa', 'causal_nsel0'])
+def test_layer_bf16_boundary_tensors(name):
+    """bf16 run against the fp32 oracle fed the same bf16-rounded weights and
+    input.  The selection is compared first; the branch outputs are compared
+    on the queries whose selection agrees (bf16 scores tie often, and a tie
+    broken differently is a different but equally valid selection)."""
+    c = recipe.LAYER_CASES[name]
+    attn = build(name, torch.bfloat16)
+    ref = O.OracleSparseAttention(**c['kw'])
+    ref.load_state_dict({k: v.float().cpu() for k, v in attn.state_dict().items()})
+    x = recipe.layer_input(name).to(torch.bfloat16)
+    out, mid = attn(x.to(DEV), return_intermediates=True)
+    rout, rmid = ref(x.float(), return_intermediates=True)
+    assert_close_bf16(mid['o_cmp'], rmid['o_cmp'], 'compressed branch')
+    assert_close_bf16(mid['o_swa'], rmid['o_swa'], 'sliding branch')
+    if rmid['idx'] is None:
+        assert_close_bf16(mid['o_sel'], rmid['o_sel'], 'selected branch')
+        assert_close_bf16(out, rout, 'out', tol=4e-2)

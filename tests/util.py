@@ -1,0 +1,47 @@
+"""Helpers shared by the GPU parity tests."""
+import os
+
+import numpy as np
+import torch
+
+GOLDEN = os.path.join(os.path.dirname(__file__), 'golden')
+
+# tolerances of the parity contract
+F32_REL = 1e-4      # fp32: max |a-b| <= F32_REL * max(1, max |b|)
+BF16_ABS = 2e-2     # bf16: max |a-b| <= BF16_ABS
+
+
+def load_golden(name):
+    z = np.load(os.path.join(GOLDEN, name + '.npz'))
+    return {k: torch.from_numpy(z[k]) for k in z.files}
+
+
+def assert_close_f32(got, ref, what='', tol=F32_REL):
+    got, ref = got.detach().float().cpu(), ref.detach().float().cpu()
+    assert got.shape == ref.shape, (what, got.shape, ref.shape)
+    if ref.numel() == 0:
+        return
+    err = (got - ref).abs().max().item()
+    bound = tol * max(1.0, ref.abs().max().item())
+    assert err <= bound, f'{what}: max abs err {err:.3e} > {bound:.3e}'
+
+
+def assert_close_bf16(got, ref, what='', tol=BF16_ABS):
+    got, ref = got.detach().float().cpu(), ref.detach().float().cpu()
+    assert got.shape == ref.shape, (what, got.shape, ref.shape)
+    if ref.numel() == 0:
+        return
+    err = (got - ref).abs().max().item()
+    assert err <= tol, f'{what}: max abs err {err:.3e} > {tol:.1e}'
+
+
+def same_selection(idx_a, mask_a, idx_b, mask_b):
+    """Selections agree when the masks are identical and, per query, the sets
+    of visible block indices are identical (order inside equal values and the
+    indices of invisible slots carry no meaning)."""
+    if not torch.equal(mask_a.cpu(), mask_b.cpu()):
+        return False
+    big = idx_a.max().item() + idx_b.max().item() + 1 if idx_a.numel() else 0
+    a = torch.where(mask_a.cpu(), idx_a.cpu(), torch.full_like(idx_a.cpu(), big)).sort(dim=-1).values
+    b = torch.where(mask_b.cpu(), idx_b.cpu(), torch.full_like(idx_b.cpu(), big)).sort(dim=-1).values
+    return torch.equal(a, b)
