@@ -203,9 +203,12 @@ def test_selection_is_bit_exact_given_the_scores(st, sel, nsel, causal):
     vals0, idx0 = nsa.select_blocks(probs.to(DEV), sel, st, nsel, input_is_prob=True)
     assert torch.equal(vals0.cpu(), ref_vals)
     assert same_selection(idx0, vals0 > 1e-10, ref_idx, ref_vals > 1e-10)
-    distinct = (ref_vals[..., 1:] != ref_vals[..., :-1]).all(dim=-1) if ref_vals.shape[-1] > 1 else None
-    if distinct is not None:
-        assert torch.equal(idx0.cpu()[distinct], ref_idx[distinct])
+    k = ref_vals.shape[-1]
+    if probs.shape[-1] > k:   # rows whose k+1 largest values are all different have one valid answer
+        top = probs.topk(k + 1, dim=-1).values
+        unique = (top[..., :-1] > top[..., 1:]).all(dim=-1)
+        assert unique.any()
+        assert torch.equal(idx0.cpu()[unique], ref_idx[unique])
 
     # (L1) the whole chain from head-averaged logits: mean over cpf, own-block fill, sink softmax, top-k
     imp = csim[..., 1:].reshape(b, hkv, hq // hkv, n, ncb).mean(dim=2)
