@@ -312,7 +312,10 @@ def main():
 
 def launches_per_step(kernels, w):
     """Kernels of this library launched by one forward+backward of the operator."""
-    return 2   # SIMT family: one forward kernel, one backward kernel (gradient buffers are cleared by memset)
+    if kernels == 'simt':
+        return 2   # one forward kernel, one backward kernel (gradient buffers are cleared by memset)
+    # tensor-core family: index pre-pass (4 kernels) + main + merge forward; pre-pass + delta + main backward
+    return 6 + 6
 
 
 if __name__ == '__main__':

@@ -1,11 +1,876 @@
-// Tensor-core (tcgen05 / TMA) family for the selected-block branch.
+// Tensor-core (tcgen05 / TMEM / TMA) family for the selected-block branch.
+//
+// The computation is organised KV-block-stationary.  An integer pre-pass turns
+// the per-query selection (idx, mask) into, for every (batch, KV head, KV
+// block j), the list of queries that attend block j -- the selected slots and,
+// for the own block, its 64 queries.  A list is cut into chunks of 128/G
+// queries; with the G query heads of the group that makes a dense 128-row
+// tile.  A persistent CTA takes an item (one list, up to kChunksPerItem
+// chunks), brings the K and V tiles of block j into shared memory once with
+// TMA, and for every chunk gathers the 128 query rows and runs dense tcgen05
+// MMAs against the resident tiles:
+//
+//   forward : S = Q K^T -> per-row softmax of that block -> O_part = P V.
+//             Every (row, slot) writes a normalised partial output and its
+//             (max, sum); a second kernel merges the <= nsel+1 partials of a
+//             row into the output and the log-sum-exp.
+//   backward: S = Q K^T and dP = dO V^T -> P = exp(S - lse), dS = P (dP - delta)
+//             -> dV += P^T dO and dK += dS^T Q stay in tensor memory across the
+//             chunks of the item (flushed once with fp32 reductions), and
+//             dQ_chunk = dS K is reduced into dq row by row.
+//
+// All operand tiles are [rows x 64 columns] bf16 with 128-byte rows and the
+// 128-byte swizzle, which serves both as a K-major and as an MN-major operand.
+// Every wait on an mbarrier is bounded; a wait that runs out raises a status
+// word in the work buffer instead of hanging, and the CTA still frees its
+// tensor memory.
+
+#include <cuda_bf16.h>
+#include <string.h>
+
 #include "nsa_common.cuh"
 #include "nsa_kernels.h"
+#include "nsa_sm100_ptx.cuh"
 
 namespace nsa {
 
-int64_t sm100_sel_workspace_bytes(const nsa_sel_fwd_args&, bool) { return NSA_ERR_UNSUPPORTED; }
-int sm100_sel_fwd(const nsa_sel_fwd_args&, cudaStream_t) { return NSA_ERR_UNSUPPORTED; }
-int sm100_sel_bwd(const nsa_sel_bwd_args&, cudaStream_t) { return NSA_ERR_UNSUPPORTED; }
+using namespace ptx;
+
+constexpr int kBlock = 64;           // keys per selection block served by this family
+constexpr int kRows = 128;           // rows of a chunk tile (queries x heads of the group)
+constexpr int kChunksPerItem = 16;   // chunks a CTA processes per resident K/V tile
+constexpr uint32_t kInvalidEntry = 0xffffffffu;
+
+struct SelPlan {
+  int nfb, G, QT, nlists;
+  int64_t entries_cap, items_cap;
+  // byte offsets into the work buffer
+  int64_t off_status, off_num_items, off_counts, off_totals, off_list_base, off_items, off_entries;
+  int64_t off_partial, off_stats, off_delta;
+  int64_t total_bytes;
+};
+
+struct SelParams {
+  const __nv_bfloat16 *q, *dout;
+  __nv_bfloat16* out;
+  int64_t q_sb, q_sh, q_sn, do_sb, do_sh, do_sn, o_sb, o_sh, o_sn;
+  const int64_t* idx;
+  const uint8_t* mask;
+  const uint32_t* entries;
+  const int4* items;
+  const int* num_items;
+  __nv_bfloat16* partial;
+  float2* stats;
+  float* lse;
+  const float* delta;
+  float *dq, *dk, *dv, *slot_grads;
+  int* status;
+  int B, Hq, Hkv, N, G, nsel, nfb, diag;
+  float scale, scale_log2;
+};
+
+// ---- index pre-pass --------------------------------------------------------------
+
+// counts[(bh*nfb + qb)*nfb + j] = entries that the queries of block qb contribute to list (bh, j)
+__global__ void __launch_bounds__(kBlock) sel_hist_kernel(const int64_t* idx, const uint8_t* mask, int* counts, int N,
+                                                          int nsel, int nfb, int diag) {
+  extern __shared__ int hist[];
+  const int qb = blockIdx.x, bh = blockIdx.y * gridDim.z + blockIdx.z;  // gridDim = (nfb, B, Hkv) -> bh = b*Hkv + h
+  for (int j = threadIdx.x; j < nfb; j += kBlock) hist[j] = 0;
+  __syncthreads();
+  const int i = qb * kBlock + threadIdx.x;
+  if (i < N) {
+    const int64_t base = ((int64_t)bh * N + i) * nsel;
+    for (int s = 0; s < nsel; ++s) {
+      const int64_t blk = idx[base + s];
+      if (mask[base + s] != 0 && blk >= 0 && blk < nfb) atomicAdd(&hist[(int)blk], 1);
+    }
+    if (diag != NSA_DIAG_NONE) atomicAdd(&hist[qb], 1);
+  }
+  __syncthreads();
+  int* row = counts + ((int64_t)bh * nfb + qb) * nfb;
+  for (int j = threadIdx.x; j < nfb; j += kBlock) row[j] = hist[j];
+}
+
+// per list: exclusive prefix over the contributing query blocks, and the list total
+__global__ void sel_scan_kernel(int* counts, int* totals, int nlists, int nfb) {
+  const int l = blockIdx.x * blockDim.x + threadIdx.x;
+  if (l >= nlists) return;
+  const int bh = l / nfb, j = l - bh * nfb;
+  int running = 0;
+  for (int qb = 0; qb < nfb; ++qb) {
+    int* c = counts + ((int64_t)bh * nfb + qb) * nfb + j;
+    const int v = *c;
+    *c = running;
+    running += v;
+  }
+  totals[l] = running;
+}
+
+// list bases (padded to whole chunks) and the item table; one CTA of 1024 threads
+__global__ void __launch_bounds__(1024) sel_items_kernel(const int* totals, int* list_base, int4* items, int* num_items,
+                                                         int nlists, int QT) {
+  __shared__ int s_pad[1024], s_it[1024];
+  __shared__ int carry_pad, carry_it;
+  if (threadIdx.x == 0) carry_pad = carry_it = 0;
+  __syncthreads();
+  for (int t0 = 0; t0 < nlists; t0 += 1024) {
+    const int l = t0 + threadIdx.x;
+    const int cnt = l < nlists ? totals[l] : 0;
+    const int nch = (cnt + QT - 1) / QT;
+    const int nit = (nch + kChunksPerItem - 1) / kChunksPerItem;
+    s_pad[threadIdx.x] = nch * QT;
+    s_it[threadIdx.x] = nit;
+    __syncthreads();
+    for (int o = 1; o < 1024; o <<= 1) {
+      int a = 0, b = 0;
+      if ((int)threadIdx.x >= o) { a = s_pad[threadIdx.x - o]; b = s_it[threadIdx.x - o]; }
+      __syncthreads();
+      s_pad[threadIdx.x] += a;
+      s_it[threadIdx.x] += b;
+      __syncthreads();
+    }
+    const int base = carry_pad + s_pad[threadIdx.x] - nch * QT;  // exclusive
+    const int ibase = carry_it + s_it[threadIdx.x] - nit;
+    if (l < nlists) {
+      list_base[l] = base;
+      for (int k = 0; k < nit; ++k) {
+        const int c0 = k * kChunksPerItem;
+        items[ibase + k] = make_int4(l, c0, min(kChunksPerItem, nch - c0), base + c0 * QT);
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 1023) { carry_pad += s_pad[1023]; carry_it += s_it[1023]; }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) *num_items = carry_it;
+}
+
+// writes the entries (query | slot << 24) in a fixed order: by query block, then slot, then query
+__global__ void __launch_bounds__(kBlock) sel_fill_kernel(const int64_t* idx, const uint8_t* mask, const int* counts,
+                                                          const int* list_base, uint32_t* entries, int N, int nsel,
+                                                          int nfb, int diag) {
+  extern __shared__ int cursor[];
+  const int qb = blockIdx.x, bh = blockIdx.y * gridDim.z + blockIdx.z;
+  const int* row = counts + ((int64_t)bh * nfb + qb) * nfb;
+  for (int j = threadIdx.x; j < nfb; j += kBlock) cursor[j] = list_base[bh * nfb + j] + row[j];
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int i = qb * kBlock + threadIdx.x;
+  const int64_t base = ((int64_t)bh * N + min(i, N - 1)) * nsel;
+  for (int s = 0; s < nsel; ++s) {
+    const int64_t blk = idx[base + s];
+    const bool valid = i < N && mask[base + s] != 0 && blk >= 0 && blk < nfb;
+    for (int w = 0; w < 2; ++w) {
+      if (warp == w) {
+        const unsigned vm = __ballot_sync(kFullMask, valid);
+        if (valid) {
+          const unsigned peers = __match_any_sync(vm, (int)blk);
+          const int rank = __popc(peers & ((1u << lane) - 1u));
+          const int leader = __ffs(peers) - 1;
+          int pos = 0;
+          if (lane == leader) {
+            pos = cursor[(int)blk];
+            cursor[(int)blk] = pos + __popc(peers);
+          }
+          pos = __shfl_sync(peers, pos, leader);
+          entries[pos + rank] = (uint32_t)i | ((uint32_t)s << 24);
+        }
+      }
+      __syncthreads();
+    }
+  }
+  if (diag != NSA_DIAG_NONE && i < N) entries[cursor[qb] + threadIdx.x] = (uint32_t)i | ((uint32_t)nsel << 24);
+}
+
+// ---- shared pieces of the two main kernels -----------------------------------------
+
+struct RowInfo {
+  int i, slot, lim;   // query position, slot, last visible key column of the block (-1: row is padding)
+  bool valid;
+};
+
+__device__ __forceinline__ RowInfo decode_row(uint32_t e, int j, int nsel, int diag) {
+  RowInfo r;
+  r.valid = e != kInvalidEntry;
+  r.i = (int)(e & 0xffffffu);
+  r.slot = (int)(e >> 24);
+  r.lim = !r.valid ? -1 : ((r.slot == nsel && diag == NSA_DIAG_CAUSAL) ? r.i - j * kBlock : kBlock - 1);
+  return r;
+}
+
+// copies one row of D bf16 from global memory into swizzled [128 x 128 B] tiles (one tile per 64 columns)
+template <int D>
+__device__ __forceinline__ void gather_row(uint32_t tile, int row, const __nv_bfloat16* src, bool valid) {
+#pragma unroll
+  for (int c = 0; c < D / 8; ++c) {
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (valid) v = ldg_nc_v4(src + c * 8);
+    sts_v4(tile + (c / 8) * (kRows * 128) + sw128_offset(row, c % 8), v);
+  }
+}
+
+__device__ __forceinline__ void store_row_bf16(uint32_t tile, int row, const float (&x)[64]) {
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    uint4 v;
+    v.x = pack_bf16(x[c * 8 + 0], x[c * 8 + 1]);
+    v.y = pack_bf16(x[c * 8 + 2], x[c * 8 + 3]);
+    v.z = pack_bf16(x[c * 8 + 4], x[c * 8 + 5]);
+    v.w = pack_bf16(x[c * 8 + 6], x[c * 8 + 7]);
+    sts_v4(tile + sw128_offset(row, c), v);
+  }
+}
+
+// ---- forward -------------------------------------------------------------------------
+
+template <int D>
+__global__ void __launch_bounds__(kRows, D == 64 ? 4 : 2)
+sel_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const SelParams P) {
+  constexpr int NC = D / 64;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ int abort_flag;
+  __shared__ uint32_t tmem_slot;
+  __shared__ __align__(8) uint64_t bars[3];
+  const int nitems = *P.num_items;
+  if ((int)blockIdx.x >= nitems) return;
+
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sQ = base, sK = sQ + NC * 16384, sV = sK + NC * 8192, sP = sV + NC * 8192;
+  const uint32_t bar_kv = smem_u32(&bars[0]), bar_s = smem_u32(&bars[1]), bar_o = smem_u32(&bars[2]);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  constexpr uint32_t kCols = D == 64 ? 128 : 256;
+
+  if (tid == 0) {
+    abort_flag = 0;
+    mbar_init(bar_kv, 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_o, 1);
+    fence_mbar_init();
+    prefetch_tensormap(&tmK);
+    prefetch_tensormap(&tmV);
+  }
+  __syncthreads();
+  if (warp == 0) {
+    tmem_alloc(smem_u32(&tmem_slot), kCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tm = tmem_slot;
+  const uint32_t tm_lane = tm + ((uint32_t)(warp * 32) << 16);
+  const uint32_t tS = 0, tO = 64;
+
+  const int G = P.G, QT = kRows / G;
+  const int q_local = tid / G, g = tid - q_local * G;
+  uint32_t ph_kv = 0, ph_s = 0, ph_o = 0;
+  constexpr uint32_t idS = instr_desc_bf16(128, 64, false, false);
+  constexpr uint32_t idO = instr_desc_bf16(128, D, false, true);
+
+  for (int it = blockIdx.x; it < nitems; it += gridDim.x) {
+    const int4 item = P.items[it];
+    const int list = item.x, j = list % P.nfb, bh = list / P.nfb, h = bh % P.Hkv, b = bh / P.Hkv;
+    if (tid == 0) {
+      mbar_arrive_expect_tx(bar_kv, 2 * NC * 8192);
+#pragma unroll
+      for (int c = 0; c < NC; ++c) {
+        tma_load_4d(sK + c * 8192, &tmK, bar_kv, c * 64, j * kBlock, h, b);
+        tma_load_4d(sV + c * 8192, &tmV, bar_kv, c * 64, j * kBlock, h, b);
+      }
+    }
+    for (int c = 0; c < item.z; ++c) {
+      const uint32_t e = P.entries[item.w + c * QT + q_local];
+      const RowInfo r = decode_row(e, j, P.nsel, P.diag);
+      const int64_t hq = (int64_t)h * G + g;
+      gather_row<D>(sQ, tid, P.q + b * P.q_sb + hq * P.q_sh + (int64_t)r.i * P.q_sn, r.valid);
+      fence_proxy_async_smem();
+      __syncthreads();
+      if (tid == 0) {
+        if (c == 0) {
+          mbar_wait_bounded(bar_kv, ph_kv, &abort_flag);
+        }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t ch = k / 4, in = (k % 4) * 32;
+          mma_bf16(tm + tS, smem_desc_sw128(sQ + ch * 16384 + in, 16), smem_desc_sw128(sK + ch * 8192 + in, 16), idS,
+                   k > 0);
+        }
+        mma_commit(bar_s);
+      }
+      __syncwarp();
+      mbar_wait_bounded(bar_s, ph_s, &abort_flag);
+      ph_s ^= 1;
+      tc_fence_after_sync();
+      __syncwarp();
+      float s[64];
+      {
+        float t[32];
+        tmem_ld32(tm_lane + tS, t);
+        tmem_ld_wait();
+#pragma unroll
+        for (int x = 0; x < 32; ++x) s[x] = t[x];
+        tmem_ld32(tm_lane + tS + 32, t);
+        tmem_ld_wait();
+#pragma unroll
+        for (int x = 0; x < 32; ++x) s[32 + x] = t[x];
+      }
+      float m = -INFINITY;
+#pragma unroll
+      for (int x = 0; x < 64; ++x) m = x <= r.lim ? fmaxf(m, s[x]) : m;
+      const float m2 = r.valid ? m * P.scale_log2 : 0.f;
+      float l = 0.f;
+#pragma unroll
+      for (int x = 0; x < 64; ++x) {
+        const float p = x <= r.lim ? ex2(s[x] * P.scale_log2 - m2) : 0.f;
+        s[x] = p;
+        l += p;   // the fp32 sum: the log-sum-exp stays exact although P is rounded to bf16 for the MMA
+      }
+      store_row_bf16(sP, tid, s);
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      __syncthreads();
+      if (tid == 0) {
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          mma_bf16(tm + tO, smem_desc_sw128(sP + k * 32, 16), smem_desc_sw128(sV + k * 2048, 8192), idO, k > 0);
+        mma_commit(bar_o);
+      }
+      __syncwarp();
+      mbar_wait_bounded(bar_o, ph_o, &abort_flag);
+      ph_o ^= 1;
+      tc_fence_after_sync();
+      __syncwarp();
+      const int64_t row_global = ((int64_t)b * P.Hq + hq) * P.N + r.i;
+      const int64_t pslot = r.valid ? row_global * (P.nsel + 1) + r.slot : 0;
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+      for (int c2 = 0; c2 < D / 32; ++c2) {
+        float t[32];
+        tmem_ld32(tm_lane + tO + c2 * 32, t);
+        tmem_ld_wait();
+        if (r.valid) {
+          uint4* dst = reinterpret_cast<uint4*>(P.partial + pslot * D + c2 * 32);
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            uint4 v;
+            v.x = pack_bf16(t[x * 8 + 0] * inv, t[x * 8 + 1] * inv);
+            v.y = pack_bf16(t[x * 8 + 2] * inv, t[x * 8 + 3] * inv);
+            v.z = pack_bf16(t[x * 8 + 4] * inv, t[x * 8 + 5] * inv);
+            v.w = pack_bf16(t[x * 8 + 6] * inv, t[x * 8 + 7] * inv);
+            dst[x] = v;
+          }
+        }
+      }
+      if (r.valid) P.stats[pslot] = make_float2(m2, l);
+      tc_fence_before_sync();
+    }
+    ph_kv ^= 1;
+    __syncthreads();   // every thread is done with this item's tiles before the next TMA overwrites them
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tm, kCols);
+  if (tid == 0 && abort_flag) atomicExch(P.status, 1);
+}
+
+// merges the partial results of every (batch, query head, query): one group of D/8 threads per row
+template <int D>
+__global__ void __launch_bounds__(256) sel_merge_kernel(const SelParams P) {
+  constexpr int TPR = D / 8;
+  const int64_t row = ((int64_t)blockIdx.x * 256 + threadIdx.x) / TPR;
+  const int part = threadIdx.x % TPR;
+  const int64_t nrows = (int64_t)P.B * P.Hq * P.N;
+  if (row >= nrows) return;
+  const int i = (int)(row % P.N);
+  const int hq = (int)((row / P.N) % P.Hq);
+  const int b = (int)(row / ((int64_t)P.N * P.Hq));
+  const int h = hq / P.G;
+  const int64_t sbase = (((int64_t)b * P.Hkv + h) * P.N + i) * P.nsel;
+  const int ns = P.nsel + 1;
+  const float2* st = P.stats + row * ns;
+  float M = -INFINITY;
+  for (int s = 0; s < ns; ++s) {
+    bool ok = s == P.nsel ? P.diag != NSA_DIAG_NONE : false;
+    if (s < P.nsel) {
+      const int64_t blk = P.idx[sbase + s];
+      ok = P.mask[sbase + s] != 0 && blk >= 0 && blk < P.nfb;
+    }
+    if (ok) M = fmaxf(M, st[s].x);
+  }
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  float L = 0.f;
+  for (int s = 0; s < ns; ++s) {
+    bool ok = s == P.nsel ? P.diag != NSA_DIAG_NONE : false;
+    if (s < P.nsel) {
+      const int64_t blk = P.idx[sbase + s];
+      ok = P.mask[sbase + s] != 0 && blk >= 0 && blk < P.nfb;
+    }
+    if (!ok) continue;
+    const float2 ml = st[s];
+    const float w = ex2(ml.x - M) * ml.y;
+    L += w;
+    const uint4 v = *reinterpret_cast<const uint4*>(P.partial + (row * ns + s) * D + part * 8);
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      acc[2 * x] = fmaf(w, __uint_as_float(u[x] << 16), acc[2 * x]);
+      acc[2 * x + 1] = fmaf(w, __uint_as_float(u[x] & 0xffff0000u), acc[2 * x + 1]);
+    }
+  }
+  const float inv = L > 0.f ? 1.f / L : 0.f;
+  uint4 o;
+  o.x = pack_bf16(acc[0] * inv, acc[1] * inv);
+  o.y = pack_bf16(acc[2] * inv, acc[3] * inv);
+  o.z = pack_bf16(acc[4] * inv, acc[5] * inv);
+  o.w = pack_bf16(acc[6] * inv, acc[7] * inv);
+  *reinterpret_cast<uint4*>(P.out + b * P.o_sb + (int64_t)hq * P.o_sh + (int64_t)i * P.o_sn + part * 8) = o;
+  if (part == 0) P.lse[row] = L > 0.f ? (M + log2f(L)) * kLn2 : -INFINITY;
+}
+
+// ---- backward --------------------------------------------------------------------------
+
+// delta[row] = sum_c out[row][c] * dout[row][c]; D/8 threads per row
+template <int D>
+__global__ void __launch_bounds__(256) sel_delta_kernel(const SelParams P, float* delta) {
+  constexpr int TPR = D / 8;
+  const int64_t row = ((int64_t)blockIdx.x * 256 + threadIdx.x) / TPR;
+  const int part = threadIdx.x % TPR;
+  const int64_t nrows = (int64_t)P.B * P.Hq * P.N;
+  float acc = 0.f;
+  if (row < nrows) {
+    const int i = (int)(row % P.N);
+    const int hq = (int)((row / P.N) % P.Hq);
+    const int b = (int)(row / ((int64_t)P.N * P.Hq));
+    const uint4 o = *reinterpret_cast<const uint4*>(P.out + b * P.o_sb + (int64_t)hq * P.o_sh + (int64_t)i * P.o_sn + part * 8);
+    const uint4 g = *reinterpret_cast<const uint4*>(P.dout + b * P.do_sb + (int64_t)hq * P.do_sh + (int64_t)i * P.do_sn + part * 8);
+    const uint32_t ou[4] = {o.x, o.y, o.z, o.w}, gu[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      acc = fmaf(__uint_as_float(ou[x] << 16), __uint_as_float(gu[x] << 16), acc);
+      acc = fmaf(__uint_as_float(ou[x] & 0xffff0000u), __uint_as_float(gu[x] & 0xffff0000u), acc);
+    }
+  }
+#pragma unroll
+  for (int o = TPR / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(kFullMask, acc, o);
+  if (row < nrows && part == 0) delta[row] = acc;
+}
+
+template <int D>
+__global__ void __launch_bounds__(kRows, D == 64 ? 2 : 1)
+sel_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const SelParams P) {
+  constexpr int NC = D / 64;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ int abort_flag;
+  __shared__ uint32_t tmem_slot;
+  __shared__ __align__(8) uint64_t bars[3];
+  const int nitems = *P.num_items;
+  if ((int)blockIdx.x >= nitems) return;
+
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sQ = base, sDO = sQ + NC * 16384, sK = sDO + NC * 16384, sV = sK + NC * 8192;
+  const uint32_t sP = sV + NC * 8192, sDS = sP + 16384;
+  const uint32_t bar_kv = smem_u32(&bars[0]), bar_1 = smem_u32(&bars[1]), bar_2 = smem_u32(&bars[2]);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  constexpr uint32_t kCols = D == 64 ? 256 : 512;
+  // tensor-memory columns: S and dP first; dQ overwrites them once they have been read
+  constexpr uint32_t tS = 0, tDP = 64, tDQ = 0, tDK = 128, tDV = 128 + D;
+
+  if (tid == 0) {
+    abort_flag = 0;
+    mbar_init(bar_kv, 1);
+    mbar_init(bar_1, 1);
+    mbar_init(bar_2, 1);
+    fence_mbar_init();
+    prefetch_tensormap(&tmK);
+    prefetch_tensormap(&tmV);
+  }
+  __syncthreads();
+  if (warp == 0) {
+    tmem_alloc(smem_u32(&tmem_slot), kCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tm = tmem_slot;
+  const uint32_t tm_lane = tm + ((uint32_t)(warp * 32) << 16);
+
+  const int G = P.G, QT = kRows / G;
+  const int q_local = tid / G, g = tid - q_local * G;
+  uint32_t ph_kv = 0, ph_1 = 0, ph_2 = 0;
+  constexpr uint32_t idS = instr_desc_bf16(128, 64, false, false);    // S, dP : K-major A and B
+  constexpr uint32_t idDQ = instr_desc_bf16(128, D, false, true);     // dQ = dS K    : B MN-major
+  constexpr uint32_t idKV = instr_desc_bf16(64, D, true, true);       // dK, dV       : A and B MN-major
+
+  for (int it = blockIdx.x; it < nitems; it += gridDim.x) {
+    const int4 item = P.items[it];
+    const int list = item.x, j = list % P.nfb, bh = list / P.nfb, h = bh % P.Hkv, b = bh / P.Hkv;
+    if (tid == 0) {
+      mbar_arrive_expect_tx(bar_kv, 2 * NC * 8192);
+#pragma unroll
+      for (int c = 0; c < NC; ++c) {
+        tma_load_4d(sK + c * 8192, &tmK, bar_kv, c * 64, j * kBlock, h, b);
+        tma_load_4d(sV + c * 8192, &tmV, bar_kv, c * 64, j * kBlock, h, b);
+      }
+    }
+    for (int c = 0; c < item.z; ++c) {
+      const uint32_t e = P.entries[item.w + c * QT + q_local];
+      const RowInfo r = decode_row(e, j, P.nsel, P.diag);
+      const int64_t hq = (int64_t)h * G + g;
+      const int64_t row_global = ((int64_t)b * P.Hq + hq) * P.N + r.i;
+      gather_row<D>(sQ, tid, P.q + b * P.q_sb + hq * P.q_sh + (int64_t)r.i * P.q_sn, r.valid);
+      gather_row<D>(sDO, tid, P.dout + b * P.do_sb + hq * P.do_sh + (int64_t)r.i * P.do_sn, r.valid);
+      const float lse2 = r.valid ? P.lse[row_global] * kLog2e : 0.f;
+      const float delta = r.valid ? P.delta[row_global] : 0.f;
+      fence_proxy_async_smem();
+      __syncthreads();
+      if (tid == 0) {
+        if (c == 0) mbar_wait_bounded(bar_kv, ph_kv, &abort_flag);
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t ch = k / 4, in = (k % 4) * 32;
+          mma_bf16(tm + tS, smem_desc_sw128(sQ + ch * 16384 + in, 16), smem_desc_sw128(sK + ch * 8192 + in, 16), idS,
+                   k > 0);
+        }
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t ch = k / 4, in = (k % 4) * 32;
+          mma_bf16(tm + tDP, smem_desc_sw128(sDO + ch * 16384 + in, 16), smem_desc_sw128(sV + ch * 8192 + in, 16), idS,
+                   k > 0);
+        }
+        mma_commit(bar_1);
+      }
+      __syncwarp();
+      mbar_wait_bounded(bar_1, ph_1, &abort_flag);
+      ph_1 ^= 1;
+      tc_fence_after_sync();
+      __syncwarp();
+      float p[64], ds[64];
+      {
+        float t[32];
+        tmem_ld32(tm_lane + tS, t);
+        tmem_ld_wait();
+#pragma unroll
+        for (int x = 0; x < 32; ++x) p[x] = t[x];
+        tmem_ld32(tm_lane + tS + 32, t);
+        tmem_ld_wait();
+#pragma unroll
+        for (int x = 0; x < 32; ++x) p[32 + x] = t[x];
+        tmem_ld32(tm_lane + tDP, t);
+        tmem_ld_wait();
+#pragma unroll
+        for (int x = 0; x < 32; ++x) ds[x] = t[x];
+        tmem_ld32(tm_lane + tDP + 32, t);
+        tmem_ld_wait();
+#pragma unroll
+        for (int x = 0; x < 32; ++x) ds[32 + x] = t[x];
+      }
+      float slot_part = 0.f;
+#pragma unroll
+      for (int x = 0; x < 64; ++x) {
+        const float sx = p[x];
+        const float px = x <= r.lim ? ex2(sx * P.scale_log2 - lse2) : 0.f;
+        const float dsx = px * (ds[x] - delta);
+        slot_part = fmaf(dsx, sx * P.scale, slot_part);
+        p[x] = px;
+        ds[x] = dsx * P.scale;
+      }
+      store_row_bf16(sP, tid, p);
+      store_row_bf16(sDS, tid, ds);
+      if (P.slot_grads != nullptr) {
+        for (int o = G / 2; o > 0; o >>= 1) slot_part += __shfl_xor_sync(kFullMask, slot_part, o);
+        if (r.valid && g == 0 && r.slot < P.nsel)
+          P.slot_grads[(((int64_t)b * P.Hkv + h) * P.N + r.i) * P.nsel + r.slot] = slot_part;
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      __syncthreads();
+      if (tid == 0) {
+        tc_fence_after_sync();
+        // dV += P^T dO, dK += dS^T Q over the 128 rows of the chunk (8 steps of 16 rows)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          mma_bf16(tm + tDV, smem_desc_sw128(sP + k * 2048, 16384), smem_desc_sw128(sDO + k * 2048, 16384), idKV,
+                   c > 0 || k > 0);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          mma_bf16(tm + tDK, smem_desc_sw128(sDS + k * 2048, 16384), smem_desc_sw128(sQ + k * 2048, 16384), idKV,
+                   c > 0 || k > 0);
+        }
+        // dQ_chunk = dS K over the 64 keys (4 steps of 16 keys)
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          mma_bf16(tm + tDQ, smem_desc_sw128(sDS + k * 32, 16), smem_desc_sw128(sK + k * 2048, 8192), idDQ, k > 0);
+        mma_commit(bar_2);
+      }
+      __syncwarp();
+      mbar_wait_bounded(bar_2, ph_2, &abort_flag);
+      ph_2 ^= 1;
+      tc_fence_after_sync();
+      __syncwarp();
+#pragma unroll
+      for (int c2 = 0; c2 < D / 32; ++c2) {
+        float t[32];
+        tmem_ld32(tm_lane + tDQ + c2 * 32, t);
+        tmem_ld_wait();
+        if (r.valid) {
+          float* dst = P.dq + row_global * D + c2 * 32;
+#pragma unroll
+          for (int x = 0; x < 8; ++x) red_add_v4(dst + x * 4, t[x * 4], t[x * 4 + 1], t[x * 4 + 2], t[x * 4 + 3]);
+        }
+      }
+      tc_fence_before_sync();
+    }
+    // flush dK, dV of this item: accumulator rows 16w..16w+15 live in lanes 0..15 of warp w
+    {
+      const int key = j * kBlock + warp * 16 + lane;
+      const bool ok = lane < 16 && key < P.N;
+      float* dkp = P.dk + (((int64_t)b * P.Hkv + h) * P.N + key) * D;
+      float* dvp = P.dv + (((int64_t)b * P.Hkv + h) * P.N + key) * D;
+#pragma unroll
+      for (int c2 = 0; c2 < D / 32; ++c2) {
+        float t[32];
+        tmem_ld32(tm_lane + tDK + c2 * 32, t);
+        tmem_ld_wait();
+        if (ok) {
+#pragma unroll
+          for (int x = 0; x < 8; ++x) red_add_v4(dkp + c2 * 32 + x * 4, t[x * 4], t[x * 4 + 1], t[x * 4 + 2], t[x * 4 + 3]);
+        }
+        tmem_ld32(tm_lane + tDV + c2 * 32, t);
+        tmem_ld_wait();
+        if (ok) {
+#pragma unroll
+          for (int x = 0; x < 8; ++x) red_add_v4(dvp + c2 * 32 + x * 4, t[x * 4], t[x * 4 + 1], t[x * 4 + 2], t[x * 4 + 3]);
+        }
+      }
+      tc_fence_before_sync();
+    }
+    ph_kv ^= 1;
+    __syncthreads();
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tm, kCols);
+  if (tid == 0 && abort_flag) atomicExch(P.status, 1);
+}
+
+// ---- host ----------------------------------------------------------------------------------
+
+static int64_t align_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
+
+// Shapes served by this family; everything else goes to the generic kernels.
+static bool supported(const nsa_sel_fwd_args& a) {
+  if (a.dtype != NSA_BF16 || a.block != kBlock) return false;
+  if (a.dim_head != 64 && a.dim_head != 128) return false;
+  if (a.sel_heads != a.kv_heads || a.diag == NSA_DIAG_NONE) return false;
+  const int G = a.q_heads / a.kv_heads;
+  if (G != 1 && G != 2 && G != 4 && G != 8 && G != 16) return false;
+  if (a.seq < 1 || a.seq >= (1 << 24) || a.nsel > 254 || a.batch < 1) return false;
+  const int64_t nfb = (a.seq + kBlock - 1) / kBlock;
+  if (nfb > 8192) return false;
+  const int64_t lists = (int64_t)a.batch * a.kv_heads * nfb;
+  if (lists * nfb > (1ll << 31) - 1) return false;
+  if ((int64_t)a.batch * a.kv_heads * ((int64_t)a.seq * (a.nsel + 1) + nfb * kRows) > (1ll << 31) - 1) return false;
+  // TMA needs 16-byte aligned bases and strides
+  if (a.k.stride_n < a.dim_head || a.v.stride_n < a.dim_head) return false;
+  return true;
+}
+
+static SelPlan make_plan(const nsa_sel_fwd_args& a, bool backward) {
+  SelPlan p;
+  p.nfb = (a.seq + kBlock - 1) / kBlock;
+  p.G = a.q_heads / a.kv_heads;
+  p.QT = kRows / p.G;
+  p.nlists = a.batch * a.kv_heads * p.nfb;
+  p.entries_cap = (int64_t)a.batch * a.kv_heads * (int64_t)a.seq * (a.nsel + 1) + (int64_t)p.nlists * p.QT;
+  p.items_cap = p.entries_cap / p.QT / kChunksPerItem + p.nlists + 1;
+  int64_t off = 0;
+  p.off_status = off; off += 256;
+  p.off_num_items = p.off_status + 128;
+  p.off_counts = off; off = align_up(off + (int64_t)p.nlists * p.nfb * 4, 256);
+  p.off_totals = off; off = align_up(off + (int64_t)p.nlists * 4, 256);
+  p.off_list_base = off; off = align_up(off + (int64_t)p.nlists * 4, 256);
+  p.off_items = off; off = align_up(off + p.items_cap * 16, 256);
+  p.off_entries = off; off = align_up(off + p.entries_cap * 4, 256);
+  const int64_t rows = (int64_t)a.batch * a.q_heads * a.seq;
+  p.off_partial = p.off_stats = p.off_delta = off;
+  if (!backward) {
+    p.off_partial = off; off = align_up(off + rows * (a.nsel + 1) * a.dim_head * 2, 256);
+    p.off_stats = off; off = align_up(off + rows * (a.nsel + 1) * 8, 256);
+  } else {
+    p.off_delta = off; off = align_up(off + rows * 4, 256);
+  }
+  p.total_bytes = off;
+  return p;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// Tensor map over a [B, H, N, d] bf16 view; one box is a [64 rows x 64 columns] tile of one head.
+static int make_kv_map(CUtensorMap* map, const nsa_tensor& t, int B, int H, int N, int d) {
+  EncodeTiledFn enc = encode_fn();
+  if (enc == nullptr) return fail(NSA_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)N, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)t.stride_n * 2, (cuuint64_t)(H > 1 ? t.stride_h : t.stride_n * N) * 2,
+                           (cuuint64_t)(B > 1 ? t.stride_b : (H > 1 ? t.stride_h * H : t.stride_n * N)) * 2};
+  cuuint32_t box[4] = {64, 64, 1, 1}, es[4] = {1, 1, 1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, t.ptr, dims, strides, box, es,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return NSA_ERR_UNSUPPORTED;   // strides the tiled format cannot express
+  return NSA_OK;
+}
+
+#define CUDA_TRY(expr)                                                        \
+  do {                                                                        \
+    const cudaError_t e_ = (expr);                                            \
+    if (e_ != cudaSuccess) return fail((int)e_, cudaGetErrorString(e_));     \
+  } while (0)
+
+static int build_index(const nsa_sel_fwd_args& a, const SelPlan& p, uint8_t* ws, cudaStream_t st) {
+  int* counts = reinterpret_cast<int*>(ws + p.off_counts);
+  int* totals = reinterpret_cast<int*>(ws + p.off_totals);
+  int* list_base = reinterpret_cast<int*>(ws + p.off_list_base);
+  int4* items = reinterpret_cast<int4*>(ws + p.off_items);
+  int* num_items = reinterpret_cast<int*>(ws + p.off_num_items);
+  uint32_t* entries = reinterpret_cast<uint32_t*>(ws + p.off_entries);
+  CUDA_TRY(cudaMemsetAsync(ws + p.off_status, 0, 256, st));
+  CUDA_TRY(cudaMemsetAsync(entries, 0xff, (size_t)p.entries_cap * 4, st));
+  const dim3 grid(p.nfb, a.batch, a.kv_heads);
+  const size_t hist_smem = (size_t)p.nfb * sizeof(int);
+  sel_hist_kernel<<<grid, kBlock, hist_smem, st>>>(a.idx, a.mask, counts, a.seq, a.nsel, p.nfb, a.diag);
+  sel_scan_kernel<<<(p.nlists + 127) / 128, 128, 0, st>>>(counts, totals, p.nlists, p.nfb);
+  sel_items_kernel<<<1, 1024, 0, st>>>(totals, list_base, items, num_items, p.nlists, p.QT);
+  sel_fill_kernel<<<grid, kBlock, hist_smem, st>>>(a.idx, a.mask, counts, list_base, entries, a.seq, a.nsel, p.nfb,
+                                                    a.diag);
+  CUDA_TRY(cudaGetLastError());
+  return NSA_OK;
+}
+
+static void fill_params(SelParams& P, const nsa_sel_fwd_args& a, const SelPlan& p, uint8_t* ws) {
+  memset(&P, 0, sizeof(P));
+  P.q = (const __nv_bfloat16*)a.q.ptr; P.q_sb = a.q.stride_b; P.q_sh = a.q.stride_h; P.q_sn = a.q.stride_n;
+  P.out = (__nv_bfloat16*)a.out.ptr; P.o_sb = a.out.stride_b; P.o_sh = a.out.stride_h; P.o_sn = a.out.stride_n;
+  P.idx = a.idx; P.mask = a.mask;
+  P.entries = reinterpret_cast<const uint32_t*>(ws + p.off_entries);
+  P.items = reinterpret_cast<const int4*>(ws + p.off_items);
+  P.num_items = reinterpret_cast<const int*>(ws + p.off_num_items);
+  P.status = reinterpret_cast<int*>(ws + p.off_status);
+  P.lse = a.lse;
+  P.B = a.batch; P.Hq = a.q_heads; P.Hkv = a.kv_heads; P.N = a.seq; P.G = p.G; P.nsel = a.nsel; P.nfb = p.nfb;
+  P.diag = a.diag; P.scale = a.scale; P.scale_log2 = a.scale * kLog2e;
+}
+
+static int num_sms() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+int64_t sm100_sel_workspace_bytes(const nsa_sel_fwd_args& a, bool backward) {
+  if (!supported(a)) return NSA_ERR_UNSUPPORTED;
+  if (a.batch == 0 || a.seq == 0) return 0;
+  return make_plan(a, backward).total_bytes;
+}
+
+template <int D>
+static int run_fwd(const nsa_sel_fwd_args& a, const SelPlan& p, uint8_t* ws, cudaStream_t st) {
+  CUtensorMap tmK, tmV;
+  int rc = make_kv_map(&tmK, a.k, a.batch, a.kv_heads, a.seq, D);
+  if (rc != NSA_OK) return rc;
+  rc = make_kv_map(&tmV, a.v, a.batch, a.kv_heads, a.seq, D);
+  if (rc != NSA_OK) return rc;
+  rc = build_index(a, p, ws, st);
+  if (rc != NSA_OK) return rc;
+  SelParams P;
+  fill_params(P, a, p, ws);
+  P.partial = reinterpret_cast<__nv_bfloat16*>(ws + p.off_partial);
+  P.stats = reinterpret_cast<float2*>(ws + p.off_stats);
+  constexpr int NC = D / 64;
+  const int smem = 1024 + NC * (16384 + 8192 + 8192) + 16384;
+  const int per_sm = D == 64 ? 4 : 2;
+  CUDA_TRY(cudaFuncSetAttribute(sel_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  sel_fwd_kernel<D><<<num_sms() * per_sm, kRows, smem, st>>>(tmK, tmV, P);
+  const int64_t threads = (int64_t)a.batch * a.q_heads * a.seq * (D / 8);
+  sel_merge_kernel<D><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(P);
+  CUDA_TRY(cudaGetLastError());
+  return NSA_OK;
+}
+
+template <int D>
+static int run_bwd(const nsa_sel_bwd_args& b, const SelPlan& p, uint8_t* ws, cudaStream_t st) {
+  const nsa_sel_fwd_args& a = b.fwd;
+  CUtensorMap tmK, tmV;
+  int rc = make_kv_map(&tmK, a.k, a.batch, a.kv_heads, a.seq, D);
+  if (rc != NSA_OK) return rc;
+  rc = make_kv_map(&tmV, a.v, a.batch, a.kv_heads, a.seq, D);
+  if (rc != NSA_OK) return rc;
+  rc = build_index(a, p, ws, st);
+  if (rc != NSA_OK) return rc;
+  SelParams P;
+  fill_params(P, a, p, ws);
+  P.dout = (const __nv_bfloat16*)b.dout.ptr; P.do_sb = b.dout.stride_b; P.do_sh = b.dout.stride_h; P.do_sn = b.dout.stride_n;
+  float* delta = reinterpret_cast<float*>(ws + p.off_delta);
+  P.delta = delta;
+  P.dq = b.dq; P.dk = b.dk; P.dv = b.dv; P.slot_grads = b.slot_grads;
+  const int64_t threads = (int64_t)a.batch * a.q_heads * a.seq * (D / 8);
+  sel_delta_kernel<D><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(P, delta);
+  constexpr int NC = D / 64;
+  const int smem = 1024 + NC * (2 * 16384 + 2 * 8192) + 2 * 16384;
+  const int per_sm = D == 64 ? 2 : 1;
+  CUDA_TRY(cudaFuncSetAttribute(sel_bwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  sel_bwd_kernel<D><<<num_sms() * per_sm, kRows, smem, st>>>(tmK, tmV, P);
+  CUDA_TRY(cudaGetLastError());
+  return NSA_OK;
+}
+
+int sm100_sel_fwd(const nsa_sel_fwd_args& a, cudaStream_t st) {
+  if (!supported(a)) return NSA_ERR_UNSUPPORTED;
+  if (a.batch == 0 || a.seq == 0) return NSA_OK;
+  const SelPlan p = make_plan(a, false);
+  if (a.workspace == nullptr || a.workspace_bytes < p.total_bytes)
+    return fail(NSA_ERR_WORKSPACE, "selected-block forward: work buffer missing or smaller than nsa_sel_workspace_bytes");
+  uint8_t* ws = static_cast<uint8_t*>(a.workspace);
+  if (reinterpret_cast<uintptr_t>(ws) & 255) return fail(NSA_ERR_ALIGN, "work buffer must be 256-byte aligned");
+  return a.dim_head == 64 ? run_fwd<64>(a, p, ws, st) : run_fwd<128>(a, p, ws, st);
+}
+
+int sm100_sel_bwd(const nsa_sel_bwd_args& b, cudaStream_t st) {
+  const nsa_sel_fwd_args& a = b.fwd;
+  if (!supported(a)) return NSA_ERR_UNSUPPORTED;
+  if (a.batch == 0 || a.seq == 0) return NSA_OK;
+  const SelPlan p = make_plan(a, true);
+  if (a.workspace == nullptr || a.workspace_bytes < p.total_bytes)
+    return fail(NSA_ERR_WORKSPACE, "selected-block backward: work buffer missing or smaller than nsa_sel_workspace_bytes");
+  uint8_t* ws = static_cast<uint8_t*>(a.workspace);
+  if (reinterpret_cast<uintptr_t>(ws) & 255) return fail(NSA_ERR_ALIGN, "work buffer must be 256-byte aligned");
+  return a.dim_head == 64 ? run_bwd<64>(b, p, ws, st) : run_bwd<128>(b, p, ws, st);
+}
 
 }  // namespace nsa

@@ -30,6 +30,9 @@ def _sel_args(q, k, v, out, idx, mask, lse, block, diag, impl, scale):
                         workspace=None, workspace_bytes=0)
 
 
+_status_words = []
+
+
 def _with_workspace(args, backward, device):
     lib = L.load()
     need = lib.nsa_sel_workspace_bytes(C.byref(args), int(backward))
@@ -40,6 +43,22 @@ def _with_workspace(args, backward, device):
         ws = torch.empty(need, dtype=torch.uint8, device=device)
         args.workspace, args.workspace_bytes = ws.data_ptr(), need
     return ws
+
+
+def _keep_status(ws):
+    """The tensor-core kernels report a bounded wait that ran out through the first word of their work
+    buffer; keep a 4-byte device copy so it can be read later without holding the buffer."""
+    if ws is not None:
+        _status_words.append(ws[:4].clone())
+        del _status_words[:-64]
+
+
+def check_device_status():
+    """Synchronise and raise if any tensor-core kernel launched since the last call gave up on a wait."""
+    words, _status_words[:] = list(_status_words), []
+    for w in words:
+        if w.view(torch.int32).item() != 0:
+            raise L.NsaError('a tensor-core kernel gave up on a bounded wait; its results are invalid')
 
 
 class SelectedAttention(Function):
@@ -61,6 +80,7 @@ class SelectedAttention(Function):
             args = _sel_args(q, k, v, out, idx, mask, lse, block, diag, impl, scale)
             ws = _with_workspace(args, False, q.device)
             L.check(lib.nsa_sel_fwd(C.byref(args), L.stream_of(q)))
+        _keep_status(ws)
         del ws
         ctx.save_for_backward(q, k, v, idx, mask, out, lse)
         ctx.cfg = (block, diag, impl, scale, None if slot_scale is None else slot_scale.dtype)
@@ -84,6 +104,7 @@ class SelectedAttention(Function):
             args = L.SelBwdArgs(fwd=fwd, dout=L.t4(dout), dq=L.ptr(dq), dk=L.ptr(dk), dv=L.ptr(dv),
                                 slot_grads=L.ptr(slot))
             L.check(lib.nsa_sel_bwd(C.byref(args), L.stream_of(q)))
+        _keep_status(ws)
         del ws
         return (dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), None, None,
                 None if slot is None else slot.to(slot_dtype), None, None, None)
