@@ -129,6 +129,35 @@ int nsa_sel_bwd(const nsa_sel_bwd_args* args, void* stream);
 int64_t nsa_sel_workspace_bytes(const nsa_sel_fwd_args* args, int backward);
 
 /* ------------------------------------------------------------------------
+ * Selected-block attention, forward, on the library's built-in scratch area.
+ * (No counterpart in upstream: there PyTorch's allocator provides every
+ * buffer.)
+ *
+ * For callers that cannot allocate device memory at the point of the call --
+ * a serving loop that must not enter the CUDA allocator, a host application
+ * whose memory pool is closed to plug-ins, an embedder that forbids
+ * cudaMalloc after start-up.  Same arguments, results and error codes as
+ * nsa_sel_fwd with the tensor-core kernels (impl is ignored; `workspace` and
+ * `workspace_bytes` are ignored), but the work buffer is a fixed area of
+ * nsa_sel_static_scratch_bytes() bytes inside the library image, which every
+ * GPU that loads the library keeps reserved until the process exits.
+ *   - Only shapes the tensor-core family serves are accepted (bf16, block 64,
+ *     dim_head 64 or 128, sel_heads == kv_heads, diag != NSA_DIAG_NONE);
+ *     others return NSA_ERR_UNSUPPORTED.
+ *   - A problem whose work buffer (nsa_sel_workspace_bytes(args, 0)) exceeds
+ *     the area returns NSA_ERR_WORKSPACE; nothing is launched.
+ *   - The call itself allocates nothing and frees nothing.  The first call on
+ *     a device looks up the area's device address; make that first call
+ *     outside any stream capture.
+ *   - All calls on a device share the one area and it keeps the previous
+ *     call's contents; the call re-initialises what it needs.  Two calls that
+ *     overlap on the GPU (different streams, or the same stream before the
+ *     first has finished being consumed) race on it: keep them ordered.
+ * ---------------------------------------------------------------------- */
+int nsa_sel_fwd_static(const nsa_sel_fwd_args* args, void* stream);
+int64_t nsa_sel_static_scratch_bytes(void);
+
+/* ------------------------------------------------------------------------
  * Compressed-KV attention with the importance reduction fused in.
  * Replaces NSA:621-639 + attend NSA:153-184 and the first half of the
  * selection chain NSA:652-680, without materialising the logits tensor.

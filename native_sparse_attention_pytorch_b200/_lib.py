@@ -73,7 +73,8 @@ class CombineBwdArgs(C.Structure):
 _STRUCTS = [Tensor4, SelFwdArgs, SelBwdArgs, CmpFwdArgs, CmpBwdArgs, SelectArgs, SwaFwdArgs, SwaBwdArgs,
             CombineFwdArgs, CombineBwdArgs]
 
-ENTRY_POINTS = ['nsa_sel_fwd', 'nsa_sel_bwd', 'nsa_sel_workspace_bytes', 'nsa_cmp_fwd', 'nsa_cmp_bwd', 'nsa_select',
+ENTRY_POINTS = ['nsa_sel_fwd', 'nsa_sel_bwd', 'nsa_sel_workspace_bytes', 'nsa_sel_fwd_static',
+                'nsa_sel_static_scratch_bytes', 'nsa_cmp_fwd', 'nsa_cmp_bwd', 'nsa_select',
                 'nsa_swa_fwd', 'nsa_swa_bwd', 'nsa_combine_fwd', 'nsa_combine_bwd', 'nsa_last_error',
                 'nsa_abi_version', 'nsa_struct_size']
 
@@ -96,6 +97,7 @@ def load():
     lib = C.CDLL(LIB_PATH)
     lib.nsa_last_error.restype = C.c_char_p
     lib.nsa_sel_workspace_bytes.restype = i64
+    lib.nsa_sel_static_scratch_bytes.restype = i64
     for which, st in enumerate(_STRUCTS):
         if lib.nsa_struct_size(which) != C.sizeof(st):
             raise NsaError(f'struct layout mismatch for {st.__name__}: library {lib.nsa_struct_size(which)} '

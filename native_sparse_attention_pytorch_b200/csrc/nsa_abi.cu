@@ -136,6 +136,15 @@ int nsa_sel_fwd(const nsa_sel_fwd_args* a, void* stream) {
   return simt_attend(P, BR_SEL, a->dtype, false, st);
 }
 
+int nsa_sel_fwd_static(const nsa_sel_fwd_args* a, void* stream) {
+  if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
+  AttnParams P;
+  NSA_TRY(fill_sel(P, *a));
+  return sm100_sel_fwd_static(*a, (cudaStream_t)stream);
+}
+
+int64_t nsa_sel_static_scratch_bytes(void) { return sm100_static_scratch_bytes(); }
+
 int nsa_sel_bwd(const nsa_sel_bwd_args* a, void* stream) {
   if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
   AttnParams P;

@@ -67,5 +67,7 @@ int launch_combine(const CombineParams& P, int dtype, bool backward, cudaStream_
 int64_t sm100_sel_workspace_bytes(const nsa_sel_fwd_args& a, bool backward);
 int sm100_sel_fwd(const nsa_sel_fwd_args& a, cudaStream_t stream);
 int sm100_sel_bwd(const nsa_sel_bwd_args& a, cudaStream_t stream);
+int sm100_sel_fwd_static(const nsa_sel_fwd_args& a, cudaStream_t stream);
+int64_t sm100_static_scratch_bytes();
 
 }  // namespace nsa

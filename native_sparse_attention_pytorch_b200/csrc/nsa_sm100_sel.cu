@@ -26,6 +26,7 @@
 // tensor memory.
 
 #include <cuda_bf16.h>
+#include <stdio.h>
 #include <string.h>
 
 #include "nsa_common.cuh"
@@ -872,5 +873,52 @@ int sm100_sel_bwd(const nsa_sel_bwd_args& b, cudaStream_t st) {
   if (reinterpret_cast<uintptr_t>(ws) & 255) return fail(NSA_ERR_ALIGN, "work buffer must be 256-byte aligned");
   return a.dim_head == 64 ? run_bwd<64>(b, p, ws, st) : run_bwd<128>(b, p, ws, st);
 }
+
+// ---- forward without a caller-provided work buffer ---------------------------------------------
+//
+// Some callers cannot hand over device memory for the work buffer: code that runs where the CUDA
+// allocator must not be entered (a serving loop holding an allocator lock, a plug-in host whose
+// memory pool is closed to extensions, an embedder that forbids cudaMalloc after start-up).  For
+// them the forward pass can run on a fixed scratch area that is part of the library image.  Every
+// device that loads the library reserves kStaticScratchBytes for it until the process ends.
+constexpr int64_t kStaticScratchBytes = 32ll << 20;
+static __device__ __align__(256) unsigned char g_sel_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static unsigned char* g_scratch_ptr[kMaxDevices] = {nullptr};
+
+// The device address of the scratch array for the current device.  In host code the array's name
+// is only a handle; the address a kernel can use comes from cudaGetSymbolAddress, asked once per
+// device while that device is current.
+static int static_scratch(unsigned char** out) {
+  int dev = -1;
+  CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(NSA_ERR_UNSUPPORTED, "device ordinal beyond the scratch table");
+  if (g_scratch_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    CUDA_TRY(cudaGetSymbolAddress(&p, g_sel_scratch));
+    g_scratch_ptr[dev] = static_cast<unsigned char*>(p);
+  }
+  *out = g_scratch_ptr[dev];
+  return NSA_OK;
+}
+
+int sm100_sel_fwd_static(const nsa_sel_fwd_args& a, cudaStream_t st) {
+  if (!supported(a)) return fail(NSA_ERR_UNSUPPORTED, "nsa_sel_fwd_static: shape outside the tensor-core family (bf16, block 64, dim_head 64/128, shared selection, own block included)");
+  if (a.batch == 0 || a.seq == 0) return NSA_OK;
+  const SelPlan p = make_plan(a, false);
+  if (p.total_bytes > kStaticScratchBytes) {
+    static thread_local char msg[160];
+    snprintf(msg, sizeof(msg), "nsa_sel_fwd_static: this problem needs %lld bytes of scratch, the built-in area holds %lld",
+             (long long)p.total_bytes, (long long)kStaticScratchBytes);
+    return fail(NSA_ERR_WORKSPACE, msg);
+  }
+  unsigned char* ws = nullptr;
+  const int rc = static_scratch(&ws);
+  if (rc != NSA_OK) return rc;
+  return a.dim_head == 64 ? run_fwd<64>(a, p, ws, st) : run_fwd<128>(a, p, ws, st);
+}
+
+int64_t sm100_static_scratch_bytes() { return kStaticScratchBytes; }
 
 }  // namespace nsa
