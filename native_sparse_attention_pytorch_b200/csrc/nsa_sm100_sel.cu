@@ -27,6 +27,7 @@
 
 #include <cuda_bf16.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "nsa_common.cuh"
@@ -200,14 +201,29 @@ __device__ __forceinline__ RowInfo decode_row(uint32_t e, int j, int nsel, int d
   return r;
 }
 
-// copies one row of D bf16 from global memory into swizzled [128 x 128 B] tiles (one tile per 64 columns)
+// All 128 threads copy the 128 rows of a chunk (D bf16 each) from global memory into swizzled [128 x 128 B]
+// tiles, one tile per 64 columns.  D/8 neighbouring threads share a row, so a warp reads whole 128-byte lines.
+// `base` points at batch element b; row r of the tile is query entries[r / G], head h*G + r % G.
 template <int D>
-__device__ __forceinline__ void gather_row(uint32_t tile, int row, const __nv_bfloat16* src, bool valid) {
+__device__ __forceinline__ void gather_tile(uint32_t tile, const __nv_bfloat16* base, int64_t stride_h, int64_t stride_n,
+                                            const uint32_t* entries, int g_shift, int h, int tid) {
+  constexpr int CH = D / 8;         // 16-byte pieces per row
+  constexpr int RPP = kRows / CH;   // rows covered by one pass of the 128 threads
+  const int sub = tid % CH, r0 = tid / CH;
+  uint4 v[CH];
 #pragma unroll
-  for (int c = 0; c < D / 8; ++c) {
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (valid) v = ldg_nc_v4(src + c * 8);
-    sts_v4(tile + (c / 8) * (kRows * 128) + sw128_offset(row, c % 8), v);
+  for (int it = 0; it < CH; ++it) {
+    const int row = r0 + it * RPP;
+    const int ql = row >> g_shift, g = row - (ql << g_shift);
+    const uint32_t e = __ldg(entries + ql);
+    v[it] = make_uint4(0u, 0u, 0u, 0u);
+    if (e != kInvalidEntry)
+      v[it] = ldg_nc_v4(base + (int64_t)((h << g_shift) + g) * stride_h + (int64_t)(e & 0xffffffu) * stride_n + sub * 8);
+  }
+#pragma unroll
+  for (int it = 0; it < CH; ++it) {
+    const int row = r0 + it * RPP;
+    sts_v4(tile + (sub / 8) * (kRows * 128) + sw128_offset(row, sub % 8), v[it]);
   }
 }
 
@@ -223,6 +239,31 @@ __device__ __forceinline__ void store_row_bf16(uint32_t tile, int row, const flo
   }
 }
 
+
+// Ships the 128 rows of a staging area (ROW_BYTES each, padded to `stride`) to scattered global rows.  Row r goes to
+// gbase + dst[r] * ROW_BYTES (skipped when dst[r] < 0); ROW_BYTES/16 neighbouring threads share a row, so every
+// store instruction writes whole 128-byte lines.  `t` is the thread's index among the 128 callers, which must have
+// synchronised after filling the staging area and dst[].  (One bulk copy per row would be simpler, but an SM issues
+// only about one bulk copy per 20 cycles, which made that the slowest step of a chunk.)
+template <int ROW_BYTES>
+__device__ __forceinline__ void store_rows_coalesced(uint32_t stage, uint32_t stride, const int* dst,
+                                                     uint8_t* gbase, int t) {
+  constexpr int TPR = ROW_BYTES / 16;
+  constexpr int RPP = kRows / TPR;
+  const int sub = t % TPR, r0 = t / TPR;
+  uint4 v[TPR];
+  int d[TPR];
+#pragma unroll
+  for (int k = 0; k < TPR; ++k) {
+    const int row = r0 + k * RPP;
+    d[k] = dst[row];
+    v[k] = lds_v4(stage + row * stride + sub * 16);
+  }
+#pragma unroll
+  for (int k = 0; k < TPR; ++k)
+    if (d[k] >= 0) *reinterpret_cast<uint4*>(gbase + (int64_t)d[k] * ROW_BYTES + sub * 16) = v[k];
+}
+
 // ---- forward -------------------------------------------------------------------------
 
 template <int D>
@@ -233,11 +274,15 @@ sel_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   __shared__ int abort_flag;
   __shared__ uint32_t tmem_slot;
   __shared__ __align__(8) uint64_t bars[3];
+  __shared__ int row_dst[kRows];
   const int nitems = *P.num_items;
   if ((int)blockIdx.x >= nitems) return;
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sQ = base, sK = sQ + NC * 16384, sV = sK + NC * 8192, sP = sV + NC * 8192;
+  // the P tile doubles as the staging area of the partial-output rows (one padded row per thread)
+  constexpr uint32_t kStageStride = D * 2 + 16;
+  const uint32_t sStage = sP;
   const uint32_t bar_kv = smem_u32(&bars[0]), bar_s = smem_u32(&bars[1]), bar_o = smem_u32(&bars[2]);
   const int tid = threadIdx.x, warp = tid >> 5;
   constexpr uint32_t kCols = D == 64 ? 128 : 256;
@@ -263,7 +308,7 @@ sel_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   const uint32_t tm_lane = tm + ((uint32_t)(warp * 32) << 16);
   const uint32_t tS = 0, tO = 64;
 
-  const int G = P.G, QT = kRows / G;
+  const int G = P.G, QT = kRows / G, g_shift = 31 - __clz(G);
   const int q_local = tid / G, g = tid - q_local * G;
   uint32_t ph_kv = 0, ph_s = 0, ph_o = 0;
   constexpr uint32_t idS = instr_desc_bf16(128, 64, false, false);
@@ -281,10 +326,11 @@ sel_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       }
     }
     for (int c = 0; c < item.z; ++c) {
-      const uint32_t e = P.entries[item.w + c * QT + q_local];
+      const uint32_t* chunk_entries = P.entries + item.w + c * QT;
+      const uint32_t e = chunk_entries[q_local];
       const RowInfo r = decode_row(e, j, P.nsel, P.diag);
       const int64_t hq = (int64_t)h * G + g;
-      gather_row<D>(sQ, tid, P.q + b * P.q_sb + hq * P.q_sh + (int64_t)r.i * P.q_sn, r.valid);
+      gather_tile<D>(sQ, P.q + b * P.q_sb, P.q_sh, P.q_sn, chunk_entries, g_shift, h, tid);
       fence_proxy_async_smem();
       __syncthreads();
       if (tid == 0) {
@@ -352,19 +398,19 @@ sel_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         float t[32];
         tmem_ld32(tm_lane + tO + c2 * 32, t);
         tmem_ld_wait();
-        if (r.valid) {
-          uint4* dst = reinterpret_cast<uint4*>(P.partial + pslot * D + c2 * 32);
 #pragma unroll
-          for (int x = 0; x < 4; ++x) {
-            uint4 v;
-            v.x = pack_bf16(t[x * 8 + 0] * inv, t[x * 8 + 1] * inv);
-            v.y = pack_bf16(t[x * 8 + 2] * inv, t[x * 8 + 3] * inv);
-            v.z = pack_bf16(t[x * 8 + 4] * inv, t[x * 8 + 5] * inv);
-            v.w = pack_bf16(t[x * 8 + 6] * inv, t[x * 8 + 7] * inv);
-            dst[x] = v;
-          }
+        for (int x = 0; x < 4; ++x) {
+          uint4 v;
+          v.x = pack_bf16(t[x * 8 + 0] * inv, t[x * 8 + 1] * inv);
+          v.y = pack_bf16(t[x * 8 + 2] * inv, t[x * 8 + 3] * inv);
+          v.z = pack_bf16(t[x * 8 + 4] * inv, t[x * 8 + 5] * inv);
+          v.w = pack_bf16(t[x * 8 + 6] * inv, t[x * 8 + 7] * inv);
+          sts_v4(sStage + tid * kStageStride + c2 * 64 + x * 16, v);
         }
       }
+      row_dst[tid] = r.valid ? (int)pslot : -1;
+      __syncthreads();
+      store_rows_coalesced<D * 2>(sStage, kStageStride, row_dst, reinterpret_cast<uint8_t*>(P.partial), tid);
       if (r.valid) P.stats[pslot] = make_float2(m2, l);
       tc_fence_before_sync();
     }
@@ -460,6 +506,22 @@ __global__ void __launch_bounds__(256) sel_delta_kernel(const SelParams P, float
   if (row < nrows && part == 0) delta[row] = acc;
 }
 
+#ifdef NSA_PHASE_TIMING
+#define WT(i, expr) { const long long t0_ = clock64(); expr; wt_[i] += clock64() - t0_; }
+#define WT_DECL long long wt_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long wt_start = clock64();
+#define WT_REPORT(name, cond, nchunks) if (cond) printf("%s total %lld per-chunk: w0 %lld w1 %lld w2 %lld w3 %lld w4 %lld w5 %lld w6 %lld\n", name, (clock64() - wt_start) / max(1, nchunks), wt_[0] / max(1, nchunks), wt_[1] / max(1, nchunks), wt_[2] / max(1, nchunks), wt_[3] / max(1, nchunks), wt_[4] / max(1, nchunks), wt_[5] / max(1, nchunks), wt_[6] / max(1, nchunks));
+#define PT_DECL long long pt_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long pt_last = clock64(); int pt_chunks = 0;
+#define PT_MARK(i) { const long long now_ = clock64(); pt_[i] += now_ - pt_last; pt_last = now_; }
+#define PT_REPORT(name) if (threadIdx.x == 0 && blockIdx.x == 0) printf("%s chunks %d: gather %lld mma1 %lld softmax %lld mma2 %lld out %lld flush %lld item %lld (cycles per chunk)\n", name, pt_chunks, pt_[0]/pt_chunks, pt_[1]/pt_chunks, pt_[2]/pt_chunks, pt_[3]/pt_chunks, pt_[4]/pt_chunks, pt_[5]/pt_chunks, pt_[6]/pt_chunks);
+#else
+#define WT(i, expr) expr;
+#define WT_DECL
+#define WT_REPORT(name, cond, nchunks)
+#define PT_DECL
+#define PT_MARK(i)
+#define PT_REPORT(name)
+#endif
+
 template <int D>
 __global__ void __launch_bounds__(kRows, D == 64 ? 2 : 1)
 sel_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const SelParams P) {
@@ -474,6 +536,9 @@ sel_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sQ = base, sDO = sQ + NC * 16384, sK = sDO + NC * 16384, sV = sK + NC * 8192;
   const uint32_t sP = sV + NC * 8192, sDS = sP + 16384;
+  // the P and dS tiles (plus a tail) double as the staging area of the dQ rows (one padded fp32 row per thread)
+  constexpr uint32_t kStageStride = D * 4 + 16;
+  const uint32_t sStage = sP;
   const uint32_t bar_kv = smem_u32(&bars[0]), bar_1 = smem_u32(&bars[1]), bar_2 = smem_u32(&bars[2]);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   constexpr uint32_t kCols = D == 64 ? 256 : 512;
@@ -500,13 +565,14 @@ sel_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   const uint32_t tm = tmem_slot;
   const uint32_t tm_lane = tm + ((uint32_t)(warp * 32) << 16);
 
-  const int G = P.G, QT = kRows / G;
+  const int G = P.G, QT = kRows / G, g_shift = 31 - __clz(G);
   const int q_local = tid / G, g = tid - q_local * G;
   uint32_t ph_kv = 0, ph_1 = 0, ph_2 = 0;
   constexpr uint32_t idS = instr_desc_bf16(128, 64, false, false);    // S, dP : K-major A and B
   constexpr uint32_t idDQ = instr_desc_bf16(128, D, false, true);     // dQ = dS K    : B MN-major
   constexpr uint32_t idKV = instr_desc_bf16(64, D, true, true);       // dK, dV       : A and B MN-major
 
+  PT_DECL
   for (int it = blockIdx.x; it < nitems; it += gridDim.x) {
     const int4 item = P.items[it];
     const int list = item.x, j = list % P.nfb, bh = list / P.nfb, h = bh % P.Hkv, b = bh / P.Hkv;
@@ -519,16 +585,19 @@ sel_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       }
     }
     for (int c = 0; c < item.z; ++c) {
-      const uint32_t e = P.entries[item.w + c * QT + q_local];
+      const uint32_t* chunk_entries = P.entries + item.w + c * QT;
+      const uint32_t e = chunk_entries[q_local];
       const RowInfo r = decode_row(e, j, P.nsel, P.diag);
       const int64_t hq = (int64_t)h * G + g;
       const int64_t row_global = ((int64_t)b * P.Hq + hq) * P.N + r.i;
-      gather_row<D>(sQ, tid, P.q + b * P.q_sb + hq * P.q_sh + (int64_t)r.i * P.q_sn, r.valid);
-      gather_row<D>(sDO, tid, P.dout + b * P.do_sb + hq * P.do_sh + (int64_t)r.i * P.do_sn, r.valid);
+      gather_tile<D>(sQ, P.q + b * P.q_sb, P.q_sh, P.q_sn, chunk_entries, g_shift, h, tid);
+      gather_tile<D>(sDO, P.dout + b * P.do_sb, P.do_sh, P.do_sn, chunk_entries, g_shift, h, tid);
       const float lse2 = r.valid ? P.lse[row_global] * kLog2e : 0.f;
       const float delta = r.valid ? P.delta[row_global] : 0.f;
       fence_proxy_async_smem();
+      bulk_wait_read();   // the previous chunk's dQ rows have left the staging area (= the P and dS tiles)
       __syncthreads();
+      PT_MARK(0)
       if (tid == 0) {
         if (c == 0) mbar_wait_bounded(bar_kv, ph_kv, &abort_flag);
         tc_fence_after_sync();
@@ -549,6 +618,7 @@ sel_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       __syncwarp();
       mbar_wait_bounded(bar_1, ph_1, &abort_flag);
       ph_1 ^= 1;
+      PT_MARK(1)
       tc_fence_after_sync();
       __syncwarp();
       float p[64], ds[64];
@@ -591,6 +661,7 @@ sel_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       fence_proxy_async_smem();
       tc_fence_before_sync();
       __syncthreads();
+      PT_MARK(2)
       if (tid == 0) {
         tc_fence_after_sync();
         // dV += P^T dO, dK += dS^T Q over the 128 rows of the chunk (8 steps of 16 rows)
@@ -613,6 +684,7 @@ sel_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       __syncwarp();
       mbar_wait_bounded(bar_2, ph_2, &abort_flag);
       ph_2 ^= 1;
+      PT_MARK(3)
       tc_fence_after_sync();
       __syncwarp();
 #pragma unroll
@@ -620,13 +692,19 @@ sel_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         float t[32];
         tmem_ld32(tm_lane + tDQ + c2 * 32, t);
         tmem_ld_wait();
-        if (r.valid) {
-          float* dst = P.dq + row_global * D + c2 * 32;
 #pragma unroll
-          for (int x = 0; x < 8; ++x) red_add_v4(dst + x * 4, t[x * 4], t[x * 4 + 1], t[x * 4 + 2], t[x * 4 + 3]);
-        }
+        for (int x = 0; x < 8; ++x)
+          sts_v4f(sStage + tid * kStageStride + c2 * 128 + x * 16, t[x * 4], t[x * 4 + 1], t[x * 4 + 2], t[x * 4 + 3]);
       }
+      // each thread adds its own dQ row into global memory with one bulk reduction
+      fence_proxy_async_smem();
+      if (r.valid) bulk_reduce_add_f32(P.dq + row_global * D, sStage + tid * kStageStride, D * 4);
+      bulk_commit();
       tc_fence_before_sync();
+      PT_MARK(4)
+#ifdef NSA_PHASE_TIMING
+      ++pt_chunks;
+#endif
     }
     // flush dK, dV of this item: accumulator rows 16w..16w+15 live in lanes 0..15 of warp w
     {
@@ -654,12 +732,458 @@ sel_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     }
     ph_kv ^= 1;
     __syncthreads();
+    PT_MARK(5)
   }
+  PT_REPORT("bwd")
 
+  bulk_wait_read();
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tm, kCols);
   if (tid == 0 && abort_flag) atomicExch(P.status, 1);
+}
+
+
+// ---- backward, warp-specialised ---------------------------------------------------------------
+//
+// One CTA per SM, 13 warps with fixed roles, so that the gathers, the tensor-core work and the per-row
+// arithmetic of different chunks overlap instead of taking turns:
+//   warps 0-3, 4-7  two softmax groups; chunk n (counted per CTA) belongs to group n % 2.  A thread owns one row:
+//                   it reads S and dP from tensor memory, writes P and dS (bf16) for the second set of MMAs and
+//                   later reduces its dQ row into global memory.  Group t % 2 also flushes dK/dV of item t.
+//   warp 8          one thread issues every tcgen05.mma: S/dP of chunk n+1 before dV/dK/dQ of chunk n.
+//   warps 9-12      gather the Q and dO rows with 16-byte cp.async into a ring of kStages stages; a stage announces
+//                   itself (cp.async.mbarrier.arrive) when the copies have landed, the threads never wait for data.
+//   warp 13         one thread requests the K/V tiles of each item by TMA (double buffered).  It is a role of its
+//                   own because it waits for the consumer: a gathering thread that did so would hold back the
+//                   announcements the consumer is waiting for.
+// Tensor memory (512 columns): two S/dP/dQ buffers of 128 columns, two dK/dV accumulators of 128 columns.
+// Every hand-over is an mbarrier; every wait is bounded.
+namespace ws {
+constexpr int kStages = 3;
+constexpr uint32_t kMetaBytes = 3 * kRows * 4;   // per stage: entry, lse, delta of every row of the chunk
+constexpr uint32_t kPBytes = 32768;   // P and dS tiles; afterwards the staging area of the bf16 dQ rows (144-byte rows)
+constexpr int kThreads = 14 * 32;
+constexpr int kLoaderThreads = 128;
+
+struct Bars {
+  uint64_t q_full[kStages], q_free[kStages];
+  uint64_t s_full[2], p_full[2], mma2_done[2], t_free[2];
+  uint64_t kv_full[2], kv_free[2], acc_full[2], acc_free[2];
+  uint64_t drain;
+};
+}  // namespace ws
+
+__global__ void __launch_bounds__(ws::kThreads, 1)
+sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const SelParams P) {
+  using namespace ws;
+  constexpr int D = 64;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ int abort_flag;
+  __shared__ uint32_t tmem_slot;
+  __shared__ __align__(8) Bars bars;
+  __shared__ int row_dst[2][kRows];
+  const int nitems = *P.num_items;
+  if ((int)blockIdx.x >= nitems) return;
+
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  // stage s: Q tile then dO tile (16 KB each); buffer b: P tile then dS tile; KV buffer: K tile then V tile (8 KB each)
+  const uint32_t sQ0 = base, sP0 = sQ0 + kStages * 32768, sKV0 = sP0 + 2 * kPBytes, sMeta0 = sKV0 + 2 * 16384;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  if (tid == 0) {
+    abort_flag = 0;
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(smem_u32(&bars.q_full[i]), kLoaderThreads);
+      mbar_init(smem_u32(&bars.q_free[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&bars.s_full[i]), 1);
+      mbar_init(smem_u32(&bars.p_full[i]), kRows);
+      mbar_init(smem_u32(&bars.mma2_done[i]), 1);
+      mbar_init(smem_u32(&bars.t_free[i]), kRows);
+      mbar_init(smem_u32(&bars.kv_full[i]), 1);
+      mbar_init(smem_u32(&bars.kv_free[i]), 1);
+      mbar_init(smem_u32(&bars.acc_full[i]), 1);
+      mbar_init(smem_u32(&bars.acc_free[i]), kRows);
+    }
+    mbar_init(smem_u32(&bars.drain), 1);
+    fence_mbar_init();
+    prefetch_tensormap(&tmK);
+    prefetch_tensormap(&tmV);
+  }
+  __syncthreads();
+  if (warp == 0) {
+    tmem_alloc(smem_u32(&tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tm = tmem_slot;
+  const int G = P.G, QT = kRows / G, g_shift = 31 - __clz(G);
+
+  if (warp < 8) {
+    // ------------------------------------------------------------------ softmax groups
+    const int wg = warp >> 2, r_tid = tid & 127;
+    const uint32_t tm_lane = tm + ((uint32_t)((warp & 3) * 32) << 16);
+    const int q_local = r_tid >> g_shift, g = r_tid - (q_local << g_shift);
+    WT_DECL
+    // one chunk of this group; the thread's entry and its row's statistics come from the stage's metadata, which
+    // the loaders fetched together with the rows
+    auto process_chunk = [&](const int4 item, const int n) {
+      {
+        const int list = item.x, j = list % P.nfb, bh = list / P.nfb, h = bh % P.Hkv, b = bh / P.Hkv;
+        const int buf = n & 1;
+        const uint32_t use = (uint32_t)(n >> 1);   // how many times this buffer has been used before
+        const uint32_t sMeta = sMeta0 + (n % kStages) * kMetaBytes + r_tid * 4;
+        WT(0, mbar_wait_bounded(smem_u32(&bars.s_full[buf]), use & 1, &abort_flag))
+        tc_fence_after_sync();
+        const uint32_t e = lds_u32(sMeta);
+        const float lse2 = __uint_as_float(lds_u32(sMeta + kRows * 4)) * kLog2e;
+        const float delta = __uint_as_float(lds_u32(sMeta + 2 * kRows * 4));
+        const RowInfo r = decode_row(e, j, P.nsel, P.diag);
+        const int64_t hq = (int64_t)h * G + g;
+        const int64_t row_global = ((int64_t)b * P.Hq + hq) * P.N + r.i;
+        const uint32_t tS = buf * 128, tDP = buf * 128 + 64, tDQ = buf * 128;
+        const uint32_t sP = sP0 + buf * kPBytes, sDS = sP + 16384;
+        // rows of other threads overlap this thread's P/dS bytes: every thread must be done reading the dQ rows
+        WT(6, asm volatile("bar.sync %0, 128;" ::"r"(1 + wg) : "memory"))
+#ifdef NSA_PHASE_TIMING
+        const long long tc0_ = clock64();
+#endif
+        float slot_part = 0.f;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          float sv[32], dv[32];
+          tmem_ld32(tm_lane + tS + half * 32, sv);
+          tmem_ld32(tm_lane + tDP + half * 32, dv);
+          tmem_ld_wait();
+#pragma unroll
+          for (int x = 0; x < 32; ++x) {
+            const float sx = sv[x];
+            const float px = (half * 32 + x) <= r.lim ? ex2(sx * P.scale_log2 - lse2) : 0.f;
+            const float dsx = px * (dv[x] - delta);
+            slot_part = fmaf(dsx, sx * P.scale, slot_part);
+            sv[x] = px;
+            dv[x] = dsx * P.scale;
+          }
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            uint4 pv, dsv;
+            pv.x = pack_bf16(sv[x * 8 + 0], sv[x * 8 + 1]); pv.y = pack_bf16(sv[x * 8 + 2], sv[x * 8 + 3]);
+            pv.z = pack_bf16(sv[x * 8 + 4], sv[x * 8 + 5]); pv.w = pack_bf16(sv[x * 8 + 6], sv[x * 8 + 7]);
+            dsv.x = pack_bf16(dv[x * 8 + 0], dv[x * 8 + 1]); dsv.y = pack_bf16(dv[x * 8 + 2], dv[x * 8 + 3]);
+            dsv.z = pack_bf16(dv[x * 8 + 4], dv[x * 8 + 5]); dsv.w = pack_bf16(dv[x * 8 + 6], dv[x * 8 + 7]);
+            sts_v4(sP + sw128_offset(r_tid, half * 4 + x), pv);
+            sts_v4(sDS + sw128_offset(r_tid, half * 4 + x), dsv);
+          }
+        }
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        mbar_arrive(smem_u32(&bars.p_full[buf]));
+        if (P.slot_grads != nullptr) {
+          for (int o = G / 2; o > 0; o >>= 1) slot_part += __shfl_xor_sync(kFullMask, slot_part, o);
+          if (r.valid && g == 0 && r.slot < P.nsel)
+            P.slot_grads[(((int64_t)b * P.Hkv + h) * P.N + r.i) * P.nsel + r.slot] = slot_part;
+        }
+
+#ifdef NSA_PHASE_TIMING
+        wt_[2] += clock64() - tc0_;
+#endif
+        WT(1, mbar_wait_bounded(smem_u32(&bars.mma2_done[buf]), use & 1, &abort_flag))
+        tc_fence_after_sync();
+        __syncwarp();
+#ifdef NSA_PHASE_TIMING
+        const long long tc1_ = clock64();
+#endif
+        // The P/dS tiles of this buffer are free now: park the dQ row there as bf16 (padded rows, conflict-free) and
+        // ship it with one bulk copy as the partial result of (row, slot).  Partials are summed by sel_dq_merge_kernel:
+        // plain stores run at memory speed, whereas fp32 reductions into dq are limited by the L2 atomic units.
+        const uint32_t stage_row = sP + r_tid * (D * 2 + 16);
+#pragma unroll
+        for (int c2 = 0; c2 < D / 32; ++c2) {
+          float tq[32];
+          tmem_ld32(tm_lane + tDQ + c2 * 32, tq);
+          tmem_ld_wait();
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            uint4 v;
+            v.x = pack_bf16(tq[x * 8 + 0], tq[x * 8 + 1]); v.y = pack_bf16(tq[x * 8 + 2], tq[x * 8 + 3]);
+            v.z = pack_bf16(tq[x * 8 + 4], tq[x * 8 + 5]); v.w = pack_bf16(tq[x * 8 + 6], tq[x * 8 + 7]);
+            sts_v4(stage_row + c2 * 64 + x * 16, v);
+          }
+        }
+        row_dst[wg][r_tid] = r.valid ? (int)(row_global * (P.nsel + 1) + r.slot) : -1;
+        tc_fence_before_sync();
+        mbar_arrive(smem_u32(&bars.t_free[buf]));   // tensor memory of this buffer is free again
+        asm volatile("bar.sync %0, 128;" ::"r"(1 + wg) : "memory");
+        store_rows_coalesced<D * 2>(sP, D * 2 + 16, row_dst[wg], reinterpret_cast<uint8_t*>(P.partial), r_tid);
+#ifdef NSA_PHASE_TIMING
+        wt_[3] += clock64() - tc1_;
+#endif
+      }
+    };
+    auto flush_item = [&](const int4 item, const int t) {
+      const int list = item.x, j = list % P.nfb, bh = list / P.nfb, h = bh % P.Hkv, b = bh / P.Hkv;
+      {
+        // flush dK/dV of this item: accumulator rows 16w..16w+15 live in lanes 0..15 of warp w of the group
+        const int ab = t & 1;
+        const uint32_t use = (uint32_t)(t >> 1);
+        mbar_wait_bounded(smem_u32(&bars.acc_full[ab]), use & 1, &abort_flag);
+        tc_fence_after_sync();
+        __syncwarp();
+        const int key = j * kBlock + (warp & 3) * 16 + lane;
+        const bool ok = lane < 16 && key < P.N;
+        float* dkp = P.dk + (((int64_t)b * P.Hkv + h) * P.N + key) * D;
+        float* dvp = P.dv + (((int64_t)b * P.Hkv + h) * P.N + key) * D;
+        const uint32_t tDK = 256 + ab * 128, tDV = tDK + 64;
+#pragma unroll
+        for (int c2 = 0; c2 < D / 32; ++c2) {
+          float tk[32];
+          tmem_ld32(tm_lane + tDK + c2 * 32, tk);
+          tmem_ld_wait();
+          if (ok) {
+#pragma unroll
+            for (int x = 0; x < 8; ++x) red_add_v4(dkp + c2 * 32 + x * 4, tk[x * 4], tk[x * 4 + 1], tk[x * 4 + 2], tk[x * 4 + 3]);
+          }
+          tmem_ld32(tm_lane + tDV + c2 * 32, tk);
+          tmem_ld_wait();
+          if (ok) {
+#pragma unroll
+            for (int x = 0; x < 8; ++x) red_add_v4(dvp + c2 * 32 + x * 4, tk[x * 4], tk[x * 4 + 1], tk[x * 4 + 2], tk[x * 4 + 3]);
+          }
+        }
+        tc_fence_before_sync();
+        mbar_arrive(smem_u32(&bars.acc_free[ab]));
+      }
+    };
+    // dK/dV of item t are flushed by group t % 2, one own chunk late, so that the group does not sit waiting for the
+    // item's last MMAs while it has work
+    int n = 0, t = 0, own_chunks = 0, pend_t = -1;
+    int4 pend_item = make_int4(0, 0, 0, 0);
+    for (int it = blockIdx.x; it < nitems; it += gridDim.x, ++t) {
+      const int4 item = P.items[it];
+      for (int c = 0; c < item.z; ++c, ++n) {
+        if ((n & 1) != wg) continue;
+        if (pend_t >= 0 && t >= pend_t + 2) {   // this item reuses the pending accumulator: it must be free first
+          flush_item(pend_item, pend_t);
+          pend_t = -1;
+        }
+        process_chunk(item, n);
+        ++own_chunks;
+        if (pend_t >= 0) {
+          flush_item(pend_item, pend_t);
+          pend_t = -1;
+        }
+      }
+      if ((t & 1) == wg) {
+        if (pend_t >= 0) flush_item(pend_item, pend_t);
+        pend_t = t;
+        pend_item = item;
+      }
+    }
+    if (pend_t >= 0) flush_item(pend_item, pend_t);
+    WT_REPORT("softmax: w0 s_full, w1 mma2_done, w2 math, w3 dq out, w6 group barrier;", blockIdx.x == 0 && r_tid == 0, own_chunks)
+  } else if (warp == 8) {
+    // ------------------------------------------------------------------ MMA issuer
+    constexpr uint32_t idS = instr_desc_bf16(128, 64, false, false);
+    constexpr uint32_t idDQ = instr_desc_bf16(128, D, false, true);
+    constexpr uint32_t idKV = instr_desc_bf16(64, D, true, true);
+    int n = 0, t = 0;
+    WT_DECL
+    // state of the chunk whose second set of MMAs is still to be issued
+    bool pending = false;
+    int p_n = 0, p_t = 0, p_c = 0;
+    bool p_last = false;
+    auto issue_mma2 = [&](int pn, int pt, int pc, bool last) {
+      const int buf = pn & 1, stage = pn % kStages, kb = pt & 1, ab = pt & 1;
+      const uint32_t sQ = sQ0 + stage * 32768, sDO = sQ + 16384;
+      const uint32_t sP = sP0 + buf * kPBytes, sDS = sP + 16384;
+      const uint32_t sK = sKV0 + kb * 16384;
+      WT(3, mbar_wait_bounded(smem_u32(&bars.p_full[buf]), (uint32_t)(pn >> 1) & 1, &abort_flag))
+      if (pc == 0 && pt >= 2) WT(4, mbar_wait_bounded(smem_u32(&bars.acc_free[ab]), (uint32_t)((pt >> 1) - 1) & 1, &abort_flag))
+      tc_fence_after_sync();
+      if (lane == 0) {
+        const uint32_t tDK = 256 + ab * 128, tDV = tDK + 64, tDQ = buf * 128;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          mma_bf16(tm + tDV, smem_desc_sw128(sP + k * 2048, 16384), smem_desc_sw128(sDO + k * 2048, 16384), idKV,
+                   pc > 0 || k > 0);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          mma_bf16(tm + tDK, smem_desc_sw128(sDS + k * 2048, 16384), smem_desc_sw128(sQ + k * 2048, 16384), idKV,
+                   pc > 0 || k > 0);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          mma_bf16(tm + tDQ, smem_desc_sw128(sDS + k * 32, 16), smem_desc_sw128(sK + k * 2048, 8192), idDQ, k > 0);
+        mma_commit(smem_u32(&bars.mma2_done[buf]));
+        mma_commit(smem_u32(&bars.q_free[stage]));
+        if (last) {
+          mma_commit(smem_u32(&bars.kv_free[kb]));
+          mma_commit(smem_u32(&bars.acc_full[ab]));
+        }
+      }
+      __syncwarp();
+    };
+    for (int it = blockIdx.x; it < nitems; it += gridDim.x, ++t) {
+      const int4 item = P.items[it];
+      const int kb = t & 1;
+      for (int c = 0; c < item.z; ++c, ++n) {
+        const int buf = n & 1, stage = n % kStages;
+        const uint32_t sQ = sQ0 + stage * 32768, sDO = sQ + 16384;
+        const uint32_t sK = sKV0 + kb * 16384, sV = sK + 8192;
+        WT(0, mbar_wait_bounded(smem_u32(&bars.q_full[stage]), (uint32_t)(n / kStages) & 1, &abort_flag))
+        if (n >= 2) WT(1, mbar_wait_bounded(smem_u32(&bars.t_free[buf]), (uint32_t)((n >> 1) - 1) & 1, &abort_flag))
+        if (c == 0) WT(2, mbar_wait_bounded(smem_u32(&bars.kv_full[kb]), (uint32_t)(t >> 1) & 1, &abort_flag))
+        tc_fence_after_sync();
+        if (lane == 0) {
+          const uint32_t tS = buf * 128, tDP = tS + 64;
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            mma_bf16(tm + tS, smem_desc_sw128(sQ + k * 32, 16), smem_desc_sw128(sK + k * 32, 16), idS, k > 0);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            mma_bf16(tm + tDP, smem_desc_sw128(sDO + k * 32, 16), smem_desc_sw128(sV + k * 32, 16), idS, k > 0);
+          mma_commit(smem_u32(&bars.s_full[buf]));
+        }
+        __syncwarp();
+        if (pending) issue_mma2(p_n, p_t, p_c, p_last);
+        pending = true;
+        p_n = n; p_t = t; p_c = c; p_last = (c == item.z - 1);
+      }
+    }
+    if (pending) issue_mma2(p_n, p_t, p_c, p_last);
+    // nothing of this block may still be running on the tensor cores when tensor memory is freed
+    if (lane == 0) mma_commit(smem_u32(&bars.drain));
+    __syncwarp();
+    mbar_wait_drain(smem_u32(&bars.drain), 0);
+    WT_REPORT("mma: w0 q_full, w1 t_free, w2 kv_full, w3 p_full, w4 acc_free;", blockIdx.x == 0 && lane == 0, n)
+  } else if (warp == 13) {
+    // ------------------------------------------------------------------ K/V tiles
+    if (lane == 0) {
+      int t = 0;
+      for (int it = blockIdx.x; it < nitems; it += gridDim.x, ++t) {
+        const int4 item = P.items[it];
+        const int list = item.x, j = list % P.nfb, bh = list / P.nfb, h = bh % P.Hkv, b = bh / P.Hkv;
+        const int kb = t & 1;
+        if (t >= 2) mbar_wait_bounded(smem_u32(&bars.kv_free[kb]), (uint32_t)((t >> 1) - 1) & 1, &abort_flag);
+        const uint32_t sK = sKV0 + kb * 16384, sV = sK + 8192;
+        const uint32_t bar = smem_u32(&bars.kv_full[kb]);
+        mbar_arrive_expect_tx(bar, 2 * 8192);
+        tma_load_4d(sK, &tmK, bar, 0, j * kBlock, h, b);
+        tma_load_4d(sV, &tmV, bar, 0, j * kBlock, h, b);
+      }
+      // the last two requests must have landed before the block may exit
+      for (int back = 1; back <= 2 && t - back >= 0; ++back) {
+        const int tt = t - back;
+        mbar_wait_drain(smem_u32(&bars.kv_full[tt & 1]), (uint32_t)(tt >> 1) & 1);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ loaders
+    const int lt = tid - 9 * 32;           // 0..127
+    const int sub = lt & 7, r0 = lt >> 3;  // 16-byte piece of a row, first row (rows r0 + 16*k)
+    int n = 0, t = 0;
+    WT_DECL
+    for (int it = blockIdx.x; it < nitems; it += gridDim.x, ++t) {
+      const int4 item = P.items[it];
+      const int list = item.x, bh = list / P.nfb, h = bh % P.Hkv, b = bh / P.Hkv;
+      const __nv_bfloat16* qb = P.q + b * P.q_sb;
+      const __nv_bfloat16* dob = P.dout + b * P.do_sb;
+      for (int c = 0; c < item.z; ++c, ++n) {
+        const int stage = n % kStages;
+        if (n >= kStages) WT(0, mbar_wait_bounded(smem_u32(&bars.q_free[stage]), (uint32_t)(n / kStages - 1) & 1, &abort_flag))
+        const uint32_t sQ = sQ0 + stage * 32768, sDO = sQ + 16384;
+        const uint32_t* chunk_entries = P.entries + item.w + c * QT;
+        // read the entries first: the copies below are compiler barriers, a load placed between them would be
+        // waited for eight times per chunk
+        uint32_t ev[8];
+#ifdef NSA_PHASE_TIMING
+        const long long tl0_ = clock64();
+#endif
+#pragma unroll
+        for (int k = 0; k < 8; ++k) ev[k] = __ldg(chunk_entries + ((r0 + k * 16) >> g_shift));
+#ifdef NSA_PHASE_TIMING
+        if (ev[0] == 0x12345678u) ++t;   // keeps the loads before the timestamp
+        const long long tl1_ = clock64();
+        wt_[2] += tl1_ - tl0_;
+#endif
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int row = r0 + k * 16;
+          const int g = row & ((1 << g_shift) - 1);
+          const uint32_t e = ev[k];
+          const bool valid = e != kInvalidEntry;
+          const int64_t i = valid ? (int64_t)(e & 0xffffffu) : 0;
+          const int64_t hq = (int64_t)((h << g_shift) + g);
+          const uint32_t off = sw128_offset(row, sub);
+          cp_async16(sQ + off, qb + hq * P.q_sh + i * P.q_sn + sub * 8, valid ? 16u : 0u);
+          cp_async16(sDO + off, dob + hq * P.do_sh + i * P.do_sn + sub * 8, valid ? 16u : 0u);
+        }
+        {
+          // metadata of row lt: its entry and the statistics of its (query, head)
+          const uint32_t e = __ldg(chunk_entries + (lt >> g_shift));
+          const bool valid = e != kInvalidEntry;
+          const int64_t row = ((int64_t)b * P.Hq + (int64_t)((h << g_shift) + (lt & ((1 << g_shift) - 1)))) * P.N +
+                              (valid ? (int64_t)(e & 0xffffffu) : 0);
+          const uint32_t sMeta = sMeta0 + stage * kMetaBytes + lt * 4;
+          cp_async4(sMeta, chunk_entries + (lt >> g_shift), 4u);
+          cp_async4(sMeta + kRows * 4, P.lse + row, valid ? 4u : 0u);
+          cp_async4(sMeta + 2 * kRows * 4, P.delta + row, valid ? 4u : 0u);
+        }
+        // the stage announces itself when this thread's copies have landed; the thread moves on at once
+        cp_async_arrive_noinc(smem_u32(&bars.q_full[stage]));
+#ifdef NSA_PHASE_TIMING
+        wt_[3] += clock64() - tl1_;
+#endif
+      }
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    WT_REPORT("loader: w0 q_free, w1 cp.async wait, w2 entries, w3 cp.async issue, w4 fence;", blockIdx.x == 0 && lt == 0, n)
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tm, 512);
+  if (tid == 0 && abort_flag) atomicExch(P.status, 1);
+}
+
+
+// sums the bf16 dQ partials of every (batch, query head, query) into the fp32 dq row: D/8 threads per row
+template <int D>
+__global__ void __launch_bounds__(256) sel_dq_merge_kernel(const SelParams P) {
+  constexpr int TPR = D / 8;
+  const int64_t row = ((int64_t)blockIdx.x * 256 + threadIdx.x) / TPR;
+  const int part = threadIdx.x % TPR;
+  const int64_t nrows = (int64_t)P.B * P.Hq * P.N;
+  if (row >= nrows) return;
+  const int i = (int)(row % P.N);
+  const int hq = (int)((row / P.N) % P.Hq);
+  const int b = (int)(row / ((int64_t)P.N * P.Hq));
+  const int h = hq / P.G;
+  const int64_t sbase = (((int64_t)b * P.Hkv + h) * P.N + i) * P.nsel;
+  const int ns = P.nsel + 1;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int s = 0; s < ns; ++s) {
+    bool ok = s == P.nsel ? P.diag != NSA_DIAG_NONE : false;
+    if (s < P.nsel) {
+      const int64_t blk = P.idx[sbase + s];
+      ok = P.mask[sbase + s] != 0 && blk >= 0 && blk < P.nfb;
+    }
+    if (!ok) continue;
+    const uint4 v = *reinterpret_cast<const uint4*>(P.partial + (row * ns + s) * D + part * 8);
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      acc[2 * x] += __uint_as_float(u[x] << 16);
+      acc[2 * x + 1] += __uint_as_float(u[x] & 0xffff0000u);
+    }
+  }
+  float4* dst = reinterpret_cast<float4*>(P.dq + row * D + part * 8);
+  dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+  dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
 }
 
 // ---- host ----------------------------------------------------------------------------------
@@ -679,6 +1203,7 @@ static bool supported(const nsa_sel_fwd_args& a) {
   const int64_t lists = (int64_t)a.batch * a.kv_heads * nfb;
   if (lists * nfb > (1ll << 31) - 1) return false;
   if ((int64_t)a.batch * a.kv_heads * ((int64_t)a.seq * (a.nsel + 1) + nfb * kRows) > (1ll << 31) - 1) return false;
+  if ((int64_t)a.batch * a.q_heads * (int64_t)a.seq * (a.nsel + 1) > (1ll << 31) - 1) return false;   // (row, slot) ids are 32-bit
   // TMA needs 16-byte aligned bases and strides
   if (a.k.stride_n < a.dim_head || a.v.stride_n < a.dim_head) return false;
   return true;
@@ -707,6 +1232,7 @@ static SelPlan make_plan(const nsa_sel_fwd_args& a, bool backward) {
     p.off_stats = off; off = align_up(off + rows * (a.nsel + 1) * 8, 256);
   } else {
     p.off_delta = off; off = align_up(off + rows * 4, 256);
+    if (a.dim_head == 64) { p.off_partial = off; off = align_up(off + rows * (a.nsel + 1) * a.dim_head * 2, 256); }
   }
   p.total_bytes = off;
   return p;
@@ -814,7 +1340,7 @@ static int run_fwd(const nsa_sel_fwd_args& a, const SelPlan& p, uint8_t* ws, cud
   P.partial = reinterpret_cast<__nv_bfloat16*>(ws + p.off_partial);
   P.stats = reinterpret_cast<float2*>(ws + p.off_stats);
   constexpr int NC = D / 64;
-  const int smem = 1024 + NC * (16384 + 8192 + 8192) + 16384;
+  const int smem = 1024 + NC * (16384 + 8192 + 8192) + kRows * (D * 2 + 16);
   const int per_sm = D == 64 ? 4 : 2;
   CUDA_TRY(cudaFuncSetAttribute(sel_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   sel_fwd_kernel<D><<<num_sms() * per_sm, kRows, smem, st>>>(tmK, tmV, P);
@@ -842,8 +1368,18 @@ static int run_bwd(const nsa_sel_bwd_args& b, const SelPlan& p, uint8_t* ws, cud
   P.dq = b.dq; P.dk = b.dk; P.dv = b.dv; P.slot_grads = b.slot_grads;
   const int64_t threads = (int64_t)a.batch * a.q_heads * a.seq * (D / 8);
   sel_delta_kernel<D><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(P, delta);
+  static const bool use_ws = []() { const char* e = getenv("NSA_SEL_BWD"); return e != nullptr && strcmp(e, "ws") == 0; }();
+  if (D == 64 && use_ws) {
+    const int smem = 1024 + ws::kStages * 32768 + 2 * ws::kPBytes + 2 * 16384 + ws::kStages * ws::kMetaBytes;
+    CUDA_TRY(cudaFuncSetAttribute(sel_bwd_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    P.partial = reinterpret_cast<__nv_bfloat16*>(ws + p.off_partial);
+    sel_bwd_ws_kernel<<<num_sms(), ws::kThreads, smem, st>>>(tmK, tmV, P);
+    sel_dq_merge_kernel<64><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(P);
+    CUDA_TRY(cudaGetLastError());
+    return NSA_OK;
+  }
   constexpr int NC = D / 64;
-  const int smem = 1024 + NC * (2 * 16384 + 2 * 8192) + 2 * 16384;
+  const int smem = 1024 + NC * (2 * 16384 + 2 * 8192) + kRows * (D * 4 + 16);
   const int per_sm = D == 64 ? 2 : 1;
   CUDA_TRY(cudaFuncSetAttribute(sel_bwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   sel_bwd_kernel<D><<<num_sms() * per_sm, kRows, smem, st>>>(tmK, tmV, P);
