@@ -45,15 +45,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // can run to its end, free its tensor memory and report through a status word.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (*abort_flag) return false;
+  if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
-  while (!mbar_try_wait(bar, parity)) {
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
     if (clock64() - t0 > 2000000000LL) {
       *abort_flag = 1;
       return false;
     }
   }
-  return true;
+}
+
+// The same for a whole warp: one lane polls, the others sleep at the warp barrier and then observe the completed
+// phase themselves (one probe), so that 32 lanes do not poll side by side.
+__device__ __forceinline__ void mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if ((threadIdx.x & 31) == 0) mbar_wait_bounded(bar, parity, abort_flag);
+  __syncwarp();
+  while (!mbar_try_wait(bar, parity)) {
+    if (*abort_flag) break;
+  }
 }
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
@@ -152,6 +163,9 @@ __host__ __device__ constexpr uint32_t instr_desc_bf16(int m, int n, bool a_mn_m
          (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
+// A descriptor moved by `bytes` inside its tile (a multiple of 16; the address field counts 16-byte units).
+__device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes) { return desc + (bytes >> 4); }
+
 // D[tmem] (+)= A[smem] * B[smem]; one thread issues.
 __device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                          bool accumulate) {
@@ -183,6 +197,19 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
       : "memory");
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+// The same for 16 columns.
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");

@@ -601,15 +601,12 @@ sel_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       if (tid == 0) {
         if (c == 0) mbar_wait_bounded(bar_kv, ph_kv, &abort_flag);
         tc_fence_after_sync();
+        // (an MMA that accumulates into the previous one's tile waits for it, so independent chains are interleaved)
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t ch = k / 4, in = (k % 4) * 32;
           mma_bf16(tm + tS, smem_desc_sw128(sQ + ch * 16384 + in, 16), smem_desc_sw128(sK + ch * 8192 + in, 16), idS,
                    k > 0);
-        }
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t ch = k / 4, in = (k % 4) * 32;
           mma_bf16(tm + tDP, smem_desc_sw128(sDO + ch * 16384 + in, 16), smem_desc_sw128(sV + ch * 8192 + in, 16), idS,
                    k > 0);
         }
@@ -664,21 +661,17 @@ sel_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       PT_MARK(2)
       if (tid == 0) {
         tc_fence_after_sync();
-        // dV += P^T dO, dK += dS^T Q over the 128 rows of the chunk (8 steps of 16 rows)
+        // dV += P^T dO, dK += dS^T Q over the 128 rows of the chunk (8 steps of 16 rows) and dQ_chunk = dS K over
+        // the 64 keys (4 steps of 16 keys), the three chains interleaved
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           mma_bf16(tm + tDV, smem_desc_sw128(sP + k * 2048, 16384), smem_desc_sw128(sDO + k * 2048, 16384), idKV,
                    c > 0 || k > 0);
-        }
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
           mma_bf16(tm + tDK, smem_desc_sw128(sDS + k * 2048, 16384), smem_desc_sw128(sQ + k * 2048, 16384), idKV,
                    c > 0 || k > 0);
+          if (k < 4)
+            mma_bf16(tm + tDQ, smem_desc_sw128(sDS + k * 32, 16), smem_desc_sw128(sK + k * 2048, 8192), idDQ, k > 0);
         }
-        // dQ_chunk = dS K over the 64 keys (4 steps of 16 keys)
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          mma_bf16(tm + tDQ, smem_desc_sw128(sDS + k * 32, 16), smem_desc_sw128(sK + k * 2048, 8192), idDQ, k > 0);
         mma_commit(bar_2);
       }
       __syncwarp();
@@ -750,8 +743,9 @@ sel_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 // arithmetic of different chunks overlap instead of taking turns:
 //   warps 0-3, 4-7  two softmax groups; chunk n (counted per CTA) belongs to group n % 2.  A thread owns one row:
 //                   it reads S and dP from tensor memory, writes P and dS (bf16) for the second set of MMAs and
-//                   later reduces its dQ row into global memory.  Group t % 2 also flushes dK/dV of item t.
-//   warp 8          one thread issues every tcgen05.mma: S/dP of chunk n+1 before dV/dK/dQ of chunk n.
+//                   later stores its dQ row as a bf16 partial result (summed by sel_dq_merge_kernel).  Group t % 2
+//                   also flushes dK/dV of item t with fp32 reductions.
+//   warp 8          one thread issues every tcgen05.mma: S/dP of chunk n+1 before dQ/dV/dK of chunk n.
 //   warps 9-12      gather the Q and dO rows with 16-byte cp.async into a ring of kStages stages; a stage announces
 //                   itself (cp.async.mbarrier.arrive) when the copies have landed, the threads never wait for data.
 //   warp 13         one thread requests the K/V tiles of each item by TMA (double buffered).  It is a role of its
@@ -759,6 +753,12 @@ sel_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 //                   announcements the consumer is waiting for.
 // Tensor memory (512 columns): two S/dP/dQ buffers of 128 columns, two dK/dV accumulators of 128 columns.
 // Every hand-over is an mbarrier; every wait is bounded.
+#ifdef NSA_PHASE_TIMING
+__device__ long long g_trace[4][64][8];
+#define TR(role, n, k) if (blockIdx.x == 0 && (n) < 64) g_trace[role][n][k] = clock64();
+#else
+#define TR(role, n, k) ;
+#endif
 namespace ws {
 constexpr int kStages = 3;
 constexpr uint32_t kMetaBytes = 3 * kRows * 4;   // per stage: entry, lse, delta of every row of the chunk
@@ -782,7 +782,6 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
   __shared__ int abort_flag;
   __shared__ uint32_t tmem_slot;
   __shared__ __align__(8) Bars bars;
-  __shared__ int row_dst[2][kRows];
   const int nitems = *P.num_items;
   if ((int)blockIdx.x >= nitems) return;
 
@@ -837,7 +836,9 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         const int buf = n & 1;
         const uint32_t use = (uint32_t)(n >> 1);   // how many times this buffer has been used before
         const uint32_t sMeta = sMeta0 + (n % kStages) * kMetaBytes + r_tid * 4;
-        WT(0, mbar_wait_bounded(smem_u32(&bars.s_full[buf]), use & 1, &abort_flag))
+        if (r_tid == 0) TR(wg, n, 0)
+        WT(0, mbar_wait_warp(smem_u32(&bars.s_full[buf]), use & 1, &abort_flag))
+        if (r_tid == 0) TR(wg, n, 1)
         tc_fence_after_sync();
         const uint32_t e = lds_u32(sMeta);
         const float lse2 = __uint_as_float(lds_u32(sMeta + kRows * 4)) * kLog2e;
@@ -847,78 +848,110 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         const int64_t row_global = ((int64_t)b * P.Hq + hq) * P.N + r.i;
         const uint32_t tS = buf * 128, tDP = buf * 128 + 64, tDQ = buf * 128;
         const uint32_t sP = sP0 + buf * kPBytes, sDS = sP + 16384;
-        // rows of other threads overlap this thread's P/dS bytes: every thread must be done reading the dQ rows
-        WT(6, asm volatile("bar.sync %0, 128;" ::"r"(1 + wg) : "memory"))
 #ifdef NSA_PHASE_TIMING
         const long long tc0_ = clock64();
 #endif
         float slot_part = 0.f;
+        const bool want_slot = P.slot_grads != nullptr;
+        // rows that see the whole block need no per-column test; only own-block (causal) and padding rows do
+        const bool all_full = __all_sync(kFullMask, r.lim == kBlock - 1);
+        // 16 columns at a time in a rolled loop: the body stays small enough for the instruction cache, which four
+        // roles share
+        auto math16 = [&](float (&sv)[16], float (&dv)[16], const int q4) {
+          const int rem = r.lim - q4 * 16;   // columns 0..rem of this group are visible
+          if (all_full) {
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          float sv[32], dv[32];
-          tmem_ld32(tm_lane + tS + half * 32, sv);
-          tmem_ld32(tm_lane + tDP + half * 32, dv);
-          tmem_ld_wait();
+            for (int x = 0; x < 16; ++x) {
+              const float sx = sv[x];
+              const float px = ex2(sx * P.scale_log2 - lse2);
+              const float dsx = px * (dv[x] - delta);
+              if (want_slot) slot_part = fmaf(dsx, sx, slot_part);
+              sv[x] = px;
+              dv[x] = dsx;
+            }
+          } else {
 #pragma unroll
-          for (int x = 0; x < 32; ++x) {
-            const float sx = sv[x];
-            const float px = (half * 32 + x) <= r.lim ? ex2(sx * P.scale_log2 - lse2) : 0.f;
-            const float dsx = px * (dv[x] - delta);
-            slot_part = fmaf(dsx, sx * P.scale, slot_part);
-            sv[x] = px;
-            dv[x] = dsx * P.scale;
+            for (int x = 0; x < 16; ++x) {
+              const float sx = sv[x];
+              const float px = x <= rem ? ex2(sx * P.scale_log2 - lse2) : 0.f;
+              const float dsx = px * (dv[x] - delta);
+              if (want_slot) slot_part = fmaf(dsx, sx, slot_part);
+              sv[x] = px;
+              dv[x] = dsx;
+            }
           }
 #pragma unroll
-          for (int x = 0; x < 4; ++x) {
+          for (int x = 0; x < 2; ++x) {
             uint4 pv, dsv;
             pv.x = pack_bf16(sv[x * 8 + 0], sv[x * 8 + 1]); pv.y = pack_bf16(sv[x * 8 + 2], sv[x * 8 + 3]);
             pv.z = pack_bf16(sv[x * 8 + 4], sv[x * 8 + 5]); pv.w = pack_bf16(sv[x * 8 + 6], sv[x * 8 + 7]);
             dsv.x = pack_bf16(dv[x * 8 + 0], dv[x * 8 + 1]); dsv.y = pack_bf16(dv[x * 8 + 2], dv[x * 8 + 3]);
             dsv.z = pack_bf16(dv[x * 8 + 4], dv[x * 8 + 5]); dsv.w = pack_bf16(dv[x * 8 + 6], dv[x * 8 + 7]);
-            sts_v4(sP + sw128_offset(r_tid, half * 4 + x), pv);
-            sts_v4(sDS + sw128_offset(r_tid, half * 4 + x), dsv);
+            sts_v4(sP + sw128_offset(r_tid, q4 * 2 + x), pv);
+            sts_v4(sDS + sw128_offset(r_tid, q4 * 2 + x), dsv);
+          }
+        };
+        {
+          float sa[16], da[16], sb[16], db[16];
+          tmem_ld16(tm_lane + tS, sa);
+          tmem_ld16(tm_lane + tDP, da);
+          tmem_ld_wait();
+#pragma unroll 1
+          for (int q2 = 0; q2 < 2; ++q2) {
+            tmem_ld16(tm_lane + tS + q2 * 32 + 16, sb);
+            tmem_ld16(tm_lane + tDP + q2 * 32 + 16, db);
+            math16(sa, da, q2 * 2);
+            tmem_ld_wait();
+            if (q2 == 0) {
+              tmem_ld16(tm_lane + tS + 32, sa);
+              tmem_ld16(tm_lane + tDP + 32, da);
+            }
+            math16(sb, db, q2 * 2 + 1);
+            tmem_ld_wait();
           }
         }
         fence_proxy_async_smem();
         tc_fence_before_sync();
         mbar_arrive(smem_u32(&bars.p_full[buf]));
+        if (r_tid == 0) TR(wg, n, 2)
         if (P.slot_grads != nullptr) {
           for (int o = G / 2; o > 0; o >>= 1) slot_part += __shfl_xor_sync(kFullMask, slot_part, o);
           if (r.valid && g == 0 && r.slot < P.nsel)
-            P.slot_grads[(((int64_t)b * P.Hkv + h) * P.N + r.i) * P.nsel + r.slot] = slot_part;
+            P.slot_grads[(((int64_t)b * P.Hkv + h) * P.N + r.i) * P.nsel + r.slot] = slot_part * P.scale;
         }
 
 #ifdef NSA_PHASE_TIMING
         wt_[2] += clock64() - tc0_;
 #endif
-        WT(1, mbar_wait_bounded(smem_u32(&bars.mma2_done[buf]), use & 1, &abort_flag))
+        WT(1, mbar_wait_warp(smem_u32(&bars.mma2_done[buf]), use & 1, &abort_flag))
+        if (r_tid == 0) TR(wg, n, 3)
         tc_fence_after_sync();
         __syncwarp();
 #ifdef NSA_PHASE_TIMING
         const long long tc1_ = clock64();
 #endif
-        // The P/dS tiles of this buffer are free now: park the dQ row there as bf16 (padded rows, conflict-free) and
-        // ship it with one bulk copy as the partial result of (row, slot).  Partials are summed by sel_dq_merge_kernel:
-        // plain stores run at memory speed, whereas fp32 reductions into dq are limited by the L2 atomic units.
-        const uint32_t stage_row = sP + r_tid * (D * 2 + 16);
-#pragma unroll
-        for (int c2 = 0; c2 < D / 32; ++c2) {
-          float tq[32];
-          tmem_ld32(tm_lane + tDQ + c2 * 32, tq);
+        // The dQ row goes out as the bf16 partial result of (row, slot), straight from registers (the P/dS tiles are
+        // still being read by the dV/dK MMAs).  Partials are summed by sel_dq_merge_kernel: plain stores run at
+        // memory speed, whereas fp32 reductions into dq are limited by the L2 atomic units.
+        uint4* part_row = reinterpret_cast<uint4*>(P.partial + (row_global * (P.nsel + 1) + r.slot) * D);
+#pragma unroll 1
+        for (int c2 = 0; c2 < D / 16; ++c2) {
+          float tq[16];
+          tmem_ld16(tm_lane + tDQ + c2 * 16, tq);
           tmem_ld_wait();
+          if (r.valid) {
 #pragma unroll
-          for (int x = 0; x < 4; ++x) {
-            uint4 v;
-            v.x = pack_bf16(tq[x * 8 + 0], tq[x * 8 + 1]); v.y = pack_bf16(tq[x * 8 + 2], tq[x * 8 + 3]);
-            v.z = pack_bf16(tq[x * 8 + 4], tq[x * 8 + 5]); v.w = pack_bf16(tq[x * 8 + 6], tq[x * 8 + 7]);
-            sts_v4(stage_row + c2 * 64 + x * 16, v);
+            for (int x = 0; x < 2; ++x) {
+              uint4 v;
+              v.x = pack_bf16(tq[x * 8 + 0], tq[x * 8 + 1]); v.y = pack_bf16(tq[x * 8 + 2], tq[x * 8 + 3]);
+              v.z = pack_bf16(tq[x * 8 + 4], tq[x * 8 + 5]); v.w = pack_bf16(tq[x * 8 + 6], tq[x * 8 + 7]);
+              part_row[c2 * 2 + x] = v;
+            }
           }
         }
-        row_dst[wg][r_tid] = r.valid ? (int)(row_global * (P.nsel + 1) + r.slot) : -1;
         tc_fence_before_sync();
         mbar_arrive(smem_u32(&bars.t_free[buf]));   // tensor memory of this buffer is free again
-        asm volatile("bar.sync %0, 128;" ::"r"(1 + wg) : "memory");
-        store_rows_coalesced<D * 2>(sP, D * 2 + 16, row_dst[wg], reinterpret_cast<uint8_t*>(P.partial), r_tid);
+        if (r_tid == 0) TR(wg, n, 4)
 #ifdef NSA_PHASE_TIMING
         wt_[3] += clock64() - tc1_;
 #endif
@@ -930,7 +963,7 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         // flush dK/dV of this item: accumulator rows 16w..16w+15 live in lanes 0..15 of warp w of the group
         const int ab = t & 1;
         const uint32_t use = (uint32_t)(t >> 1);
-        mbar_wait_bounded(smem_u32(&bars.acc_full[ab]), use & 1, &abort_flag);
+        mbar_wait_warp(smem_u32(&bars.acc_full[ab]), use & 1, &abort_flag);
         tc_fence_after_sync();
         __syncwarp();
         const int key = j * kBlock + (warp & 3) * 16 + lane;
@@ -945,7 +978,8 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
           tmem_ld_wait();
           if (ok) {
 #pragma unroll
-            for (int x = 0; x < 8; ++x) red_add_v4(dkp + c2 * 32 + x * 4, tk[x * 4], tk[x * 4 + 1], tk[x * 4 + 2], tk[x * 4 + 3]);
+            for (int x = 0; x < 8; ++x)
+              red_add_v4(dkp + c2 * 32 + x * 4, tk[x * 4] * P.scale, tk[x * 4 + 1] * P.scale, tk[x * 4 + 2] * P.scale, tk[x * 4 + 3] * P.scale);
           }
           tmem_ld32(tm_lane + tDV + c2 * 32, tk);
           tmem_ld_wait();
@@ -967,13 +1001,15 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
       for (int c = 0; c < item.z; ++c, ++n) {
         if ((n & 1) != wg) continue;
         if (pend_t >= 0 && t >= pend_t + 2) {   // this item reuses the pending accumulator: it must be free first
-          flush_item(pend_item, pend_t);
+          WT(4, flush_item(pend_item, pend_t))
           pend_t = -1;
         }
-        process_chunk(item, n);
+        if (r_tid == 0) TR(wg, n, 6)
+        WT(5, process_chunk(item, n))
+        if (r_tid == 0) TR(wg, n, 5)
         ++own_chunks;
         if (pend_t >= 0) {
-          flush_item(pend_item, pend_t);
+          WT(4, flush_item(pend_item, pend_t))
           pend_t = -1;
         }
       }
@@ -984,9 +1020,11 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
       }
     }
     if (pend_t >= 0) flush_item(pend_item, pend_t);
-    WT_REPORT("softmax: w0 s_full, w1 mma2_done, w2 math, w3 dq out, w6 group barrier;", blockIdx.x == 0 && r_tid == 0, own_chunks)
+    WT_REPORT("softmax: w0 s_full, w1 mma2_done, w2 math, w3 dq out, w4 flush, w5 whole chunk, w6 group barrier;", blockIdx.x == 0 && r_tid == 0, own_chunks)
   } else if (warp == 8) {
-    // ------------------------------------------------------------------ MMA issuer
+    // ------------------------------------------------------------------ MMA issuer (one thread; the other lanes
+    // of the warp go straight to the final barrier and take no issue slots)
+    if (lane == 0) {
     constexpr uint32_t idS = instr_desc_bf16(128, 64, false, false);
     constexpr uint32_t idDQ = instr_desc_bf16(128, D, false, true);
     constexpr uint32_t idKV = instr_desc_bf16(64, D, true, true);
@@ -1002,29 +1040,35 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
       const uint32_t sP = sP0 + buf * kPBytes, sDS = sP + 16384;
       const uint32_t sK = sKV0 + kb * 16384;
       WT(3, mbar_wait_bounded(smem_u32(&bars.p_full[buf]), (uint32_t)(pn >> 1) & 1, &abort_flag))
+      if (lane == 0) TR(2, pn, 2)
       if (pc == 0 && pt >= 2) WT(4, mbar_wait_bounded(smem_u32(&bars.acc_free[ab]), (uint32_t)((pt >> 1) - 1) & 1, &abort_flag))
       tc_fence_after_sync();
       if (lane == 0) {
         const uint32_t tDK = 256 + ab * 128, tDV = tDK + 64, tDQ = buf * 128;
-#pragma unroll
-        for (int k = 0; k < 8; ++k)
-          mma_bf16(tm + tDV, smem_desc_sw128(sP + k * 2048, 16384), smem_desc_sw128(sDO + k * 2048, 16384), idKV,
-                   pc > 0 || k > 0);
-#pragma unroll
-        for (int k = 0; k < 8; ++k)
-          mma_bf16(tm + tDK, smem_desc_sw128(sDS + k * 2048, 16384), smem_desc_sw128(sQ + k * 2048, 16384), idKV,
-                   pc > 0 || k > 0);
+        // One descriptor per tile (the leading-offset field is unused for 64-wide tiles, so the same descriptor
+        // serves the K-major and the MN-major reading of a tile); every MMA then costs one 64-bit add to issue.
+        const uint64_t dQt = smem_desc_sw128(sQ, 16), dDOt = smem_desc_sw128(sDO, 16), dPt = smem_desc_sw128(sP, 16),
+                       dDSt = smem_desc_sw128(sDS, 16), dKt = smem_desc_sw128(sK, 16);
+        // dQ first, and its own commit: the softmax group can read it out while dV and dK are still being computed.
+        // (Measured: a small MMA costs about 50 cycles to issue whatever its shape, so the count matters, not the
+        // order; interleaving the accumulation chains brought nothing.)
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          mma_bf16(tm + tDQ, smem_desc_sw128(sDS + k * 32, 16), smem_desc_sw128(sK + k * 2048, 8192), idDQ, k > 0);
+          mma_bf16(tm + tDQ, desc_advance(dDSt, k * 32), desc_advance(dKt, k * 2048), idDQ, k > 0);
         mma_commit(smem_u32(&bars.mma2_done[buf]));
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          mma_bf16(tm + tDV, desc_advance(dPt, k * 2048), desc_advance(dDOt, k * 2048), idKV, pc > 0 || k > 0);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          mma_bf16(tm + tDK, desc_advance(dDSt, k * 2048), desc_advance(dQt, k * 2048), idKV, pc > 0 || k > 0);
         mma_commit(smem_u32(&bars.q_free[stage]));
+        TR(2, pn, 3)
         if (last) {
           mma_commit(smem_u32(&bars.kv_free[kb]));
           mma_commit(smem_u32(&bars.acc_full[ab]));
         }
       }
-      __syncwarp();
     };
     for (int it = blockIdx.x; it < nitems; it += gridDim.x, ++t) {
       const int4 item = P.items[it];
@@ -1033,22 +1077,25 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         const int buf = n & 1, stage = n % kStages;
         const uint32_t sQ = sQ0 + stage * 32768, sDO = sQ + 16384;
         const uint32_t sK = sKV0 + kb * 16384, sV = sK + 8192;
+        if (lane == 0) TR(2, n, 0)
         WT(0, mbar_wait_bounded(smem_u32(&bars.q_full[stage]), (uint32_t)(n / kStages) & 1, &abort_flag))
+        if (lane == 0) TR(2, n, 4)
         if (n >= 2) WT(1, mbar_wait_bounded(smem_u32(&bars.t_free[buf]), (uint32_t)((n >> 1) - 1) & 1, &abort_flag))
         if (c == 0) WT(2, mbar_wait_bounded(smem_u32(&bars.kv_full[kb]), (uint32_t)(t >> 1) & 1, &abort_flag))
         tc_fence_after_sync();
         if (lane == 0) {
           const uint32_t tS = buf * 128, tDP = tS + 64;
+          const uint64_t dQt = smem_desc_sw128(sQ, 16), dDOt = smem_desc_sw128(sDO, 16), dKt = smem_desc_sw128(sK, 16),
+                         dVt = smem_desc_sw128(sV, 16);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            mma_bf16(tm + tS, smem_desc_sw128(sQ + k * 32, 16), smem_desc_sw128(sK + k * 32, 16), idS, k > 0);
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            mma_bf16(tm + tDP, smem_desc_sw128(sDO + k * 32, 16), smem_desc_sw128(sV + k * 32, 16), idS, k > 0);
+          for (int k = 0; k < 4; ++k) {
+            mma_bf16(tm + tS, desc_advance(dQt, k * 32), desc_advance(dKt, k * 32), idS, k > 0);
+            mma_bf16(tm + tDP, desc_advance(dDOt, k * 32), desc_advance(dVt, k * 32), idS, k > 0);
+          }
           mma_commit(smem_u32(&bars.s_full[buf]));
+          TR(2, n, 1)
         }
-        __syncwarp();
-        if (pending) issue_mma2(p_n, p_t, p_c, p_last);
+          if (pending) issue_mma2(p_n, p_t, p_c, p_last);
         pending = true;
         p_n = n; p_t = t; p_c = c; p_last = (c == item.z - 1);
       }
@@ -1056,9 +1103,9 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     if (pending) issue_mma2(p_n, p_t, p_c, p_last);
     // nothing of this block may still be running on the tensor cores when tensor memory is freed
     if (lane == 0) mma_commit(smem_u32(&bars.drain));
-    __syncwarp();
     mbar_wait_drain(smem_u32(&bars.drain), 0);
     WT_REPORT("mma: w0 q_full, w1 t_free, w2 kv_full, w3 p_full, w4 acc_free;", blockIdx.x == 0 && lane == 0, n)
+    }
   } else if (warp == 13) {
     // ------------------------------------------------------------------ K/V tiles
     if (lane == 0) {
@@ -1093,7 +1140,8 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
       const __nv_bfloat16* dob = P.dout + b * P.do_sb;
       for (int c = 0; c < item.z; ++c, ++n) {
         const int stage = n % kStages;
-        if (n >= kStages) WT(0, mbar_wait_bounded(smem_u32(&bars.q_free[stage]), (uint32_t)(n / kStages - 1) & 1, &abort_flag))
+        if (n >= kStages) WT(0, mbar_wait_warp(smem_u32(&bars.q_free[stage]), (uint32_t)(n / kStages - 1) & 1, &abort_flag))
+        if (lt == 0) TR(3, n, 0)
         const uint32_t sQ = sQ0 + stage * 32768, sDO = sQ + 16384;
         const uint32_t* chunk_entries = P.entries + item.w + c * QT;
         // read the entries first: the copies below are compiler barriers, a load placed between them would be
@@ -1134,6 +1182,7 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         }
         // the stage announces itself when this thread's copies have landed; the thread moves on at once
         cp_async_arrive_noinc(smem_u32(&bars.q_full[stage]));
+        if (lt == 0) TR(3, n, 1)
 #ifdef NSA_PHASE_TIMING
         wt_[3] += clock64() - tl1_;
 #endif
@@ -1148,6 +1197,18 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
   __syncthreads();
   if (warp == 0) tmem_dealloc(tm, 512);
   if (tid == 0 && abort_flag) atomicExch(P.status, 1);
+#ifdef NSA_PHASE_TIMING
+  if (tid == 0 && blockIdx.x == 0) {
+    const long long z = g_trace[3][0][0];
+    for (int n = 8; n < 28; ++n) {
+      const int w = n & 1;
+      printf("TRACE n %2d wg%d: call %6lld enter %6lld s_full %6lld p_arrive %6lld mma2_done %6lld end %6lld ret %6lld | mma: wait_q %6lld got_q %6lld mma1 %6lld got_p %6lld mma2 %6lld\n", n, w,
+             g_trace[w][n][6] - z, g_trace[w][n][0] - z, g_trace[w][n][1] - z, g_trace[w][n][2] - z, g_trace[w][n][3] - z,
+             g_trace[w][n][4] - z, g_trace[w][n][5] - z, g_trace[2][n][0] - z, g_trace[2][n][4] - z, g_trace[2][n][1] - z,
+             g_trace[2][n][2] - z, g_trace[2][n][3] - z);
+    }
+  }
+#endif
 }
 
 
@@ -1182,8 +1243,9 @@ __global__ void __launch_bounds__(256) sel_dq_merge_kernel(const SelParams P) {
     }
   }
   float4* dst = reinterpret_cast<float4*>(P.dq + row * D + part * 8);
-  dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-  dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+  // the partials hold dS K without the logit scale
+  dst[0] = make_float4(acc[0] * P.scale, acc[1] * P.scale, acc[2] * P.scale, acc[3] * P.scale);
+  dst[1] = make_float4(acc[4] * P.scale, acc[5] * P.scale, acc[6] * P.scale, acc[7] * P.scale);
 }
 
 // ---- host ----------------------------------------------------------------------------------
@@ -1368,7 +1430,7 @@ static int run_bwd(const nsa_sel_bwd_args& b, const SelPlan& p, uint8_t* ws, cud
   P.dq = b.dq; P.dk = b.dk; P.dv = b.dv; P.slot_grads = b.slot_grads;
   const int64_t threads = (int64_t)a.batch * a.q_heads * a.seq * (D / 8);
   sel_delta_kernel<D><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(P, delta);
-  static const bool use_ws = []() { const char* e = getenv("NSA_SEL_BWD"); return e != nullptr && strcmp(e, "ws") == 0; }();
+  static const bool use_ws = []() { const char* e = getenv("NSA_SEL_BWD"); return e == nullptr || strcmp(e, "v1") != 0; }();
   if (D == 64 && use_ws) {
     const int smem = 1024 + ws::kStages * 32768 + 2 * ws::kPBytes + 2 * 16384 + ws::kStages * ws::kMetaBytes;
     CUDA_TRY(cudaFuncSetAttribute(sel_bwd_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
