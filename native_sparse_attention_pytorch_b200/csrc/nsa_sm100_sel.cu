@@ -227,6 +227,29 @@ __device__ __forceinline__ void gather_tile(uint32_t tile, const __nv_bfloat16* 
   }
 }
 
+// The same gather with 16-byte cp.async: returns at once, the rows land later (cp_async_wait).  Padding rows are
+// zero-filled.
+template <int D>
+__device__ __forceinline__ void gather_tile_async(uint32_t tile, const __nv_bfloat16* base, int64_t stride_h,
+                                                  int64_t stride_n, const uint32_t* entries, int g_shift, int h,
+                                                  int tid) {
+  constexpr int CH = D / 8;
+  constexpr int RPP = kRows / CH;
+  const int sub = tid % CH, r0 = tid / CH;
+  uint32_t ev[CH];
+#pragma unroll
+  for (int it = 0; it < CH; ++it) ev[it] = __ldg(entries + ((r0 + it * RPP) >> g_shift));
+#pragma unroll
+  for (int it = 0; it < CH; ++it) {
+    const int row = r0 + it * RPP;
+    const int g = row & ((1 << g_shift) - 1);
+    const bool valid = ev[it] != kInvalidEntry;
+    const int64_t i = valid ? (int64_t)(ev[it] & 0xffffffu) : 0;
+    cp_async16(tile + (sub / 8) * (kRows * 128) + sw128_offset(row, sub % 8),
+               base + (int64_t)((h << g_shift) + g) * stride_h + i * stride_n + sub * 8, valid ? 16u : 0u);
+  }
+}
+
 __device__ __forceinline__ void store_row_bf16(uint32_t tile, int row, const float (&x)[64]) {
 #pragma unroll
   for (int c = 0; c < 8; ++c) {
@@ -325,12 +348,15 @@ sel_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         tma_load_4d(sV + c * 8192, &tmV, bar_kv, c * 64, j * kBlock, h, b);
       }
     }
+    bool prefetched = false;
     for (int c = 0; c < item.z; ++c) {
       const uint32_t* chunk_entries = P.entries + item.w + c * QT;
       const uint32_t e = chunk_entries[q_local];
       const RowInfo r = decode_row(e, j, P.nsel, P.diag);
       const int64_t hq = (int64_t)h * G + g;
-      gather_tile<D>(sQ, P.q + b * P.q_sb, P.q_sh, P.q_sn, chunk_entries, g_shift, h, tid);
+      if (!prefetched) gather_tile_async<D>(sQ, P.q + b * P.q_sb, P.q_sh, P.q_sn, chunk_entries, g_shift, h, tid);
+      cp_async_commit();
+      cp_async_wait<0>();
       fence_proxy_async_smem();
       __syncthreads();
       if (tid == 0) {
@@ -347,9 +373,14 @@ sel_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         mma_commit(bar_s);
       }
       __syncwarp();
-      mbar_wait_bounded(bar_s, ph_s, &abort_flag);
+      mbar_wait_warp(bar_s, ph_s, &abort_flag);
       ph_s ^= 1;
       tc_fence_after_sync();
+      // S is complete, so the Q tile is free: request the next chunk's rows now; they travel while this chunk's
+      // softmax, second MMA and output run
+      prefetched = c + 1 < item.z;
+      if (prefetched)
+        gather_tile_async<D>(sQ, P.q + b * P.q_sb, P.q_sh, P.q_sn, chunk_entries + QT, g_shift, h, tid);
       __syncwarp();
       float s[64];
       {
@@ -386,7 +417,7 @@ sel_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         mma_commit(bar_o);
       }
       __syncwarp();
-      mbar_wait_bounded(bar_o, ph_o, &abort_flag);
+      mbar_wait_warp(bar_o, ph_o, &abort_flag);
       ph_o ^= 1;
       tc_fence_after_sync();
       __syncwarp();
