@@ -190,6 +190,7 @@ def main():
     ap.add_argument('--workload', default=DEFAULT_WORKLOAD, choices=list(WORKLOADS))
     ap.add_argument('--kernels', default='auto', choices=['auto', 'simt', 'sm100'])
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--rows', action='store_true', help='also time the other kernels of the hot path (N=1 only)')
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
     if args.impl == 'reference':
@@ -301,6 +302,9 @@ def main():
     }
     from native_sparse_attention_pytorch_b200 import _lib
     line['gpu_launches'] = launches_per_step(args.kernels, w) * args.steps
+    if args.rows and world == 1:
+        del q, k, v, idx, mask, do
+        line['rows'] = measure_rows(dev, flush)
     if not args.no_cpu_baseline and world == 1:
         val, sample = time_cpu_port(w, host)
         line['cpu_baseline'] = {'value': val, 'unit': 'tokens/s', 'cores': os.cpu_count(), 'kind': 'port',
@@ -310,12 +314,100 @@ def main():
         dist.destroy_process_group()
 
 
+def measure_rows(dev, flush, iters=5):
+    """Times every other kernel of the hot path (compressed attention, block selection, sliding window, gated
+    combine, and the selected-block kernels at the layer's head grouping) at the shapes of the full-layer
+    configuration: batch 2, 16384 tokens, 16 query / 4 KV heads, dim_head 64, compress stride 16, block 64,
+    16 selected blocks, window 512, bf16.  Returns {row: {ms, achieved, unit, peak, frac, bound}}."""
+    import native_sparse_attention_pytorch_b200 as nsa
+    b, hq, hkv, n, d, st, blk, nsel, win = 2, 16, 4, 16384, 64, 16, 64, 16, 512
+    g = hq // hkv
+    ncb = n // st
+    gen = torch.Generator('cpu').manual_seed(1)
+    rnd = lambda *shape: torch.randn(*shape, generator=gen).bfloat16().to(dev)
+    q, k, v, do = rnd(b, hq, n, d), rnd(b, hkv, n, d), rnd(b, hkv, n, d), rnd(b, hq, n, d)
+    ck, cv = rnd(b, hkv, 1 + ncb, d), rnd(b, hkv, 1 + ncb, d)
+    gates = torch.sigmoid(rnd(b, n, hq * 3)).view(b, n, hq, 3).transpose(1, 2)
+    tf_peak, _, _ = peaks()
+    hbm_peak = json.load(open(os.path.join(ROOT, 'MEASURED_PEAKS.json')))['hbm_gbs'] if os.path.exists(
+        os.path.join(ROOT, 'MEASURED_PEAKS.json')) else 6650.0
+
+    def timed(fn):
+        for _ in range(2):
+            fn()
+        evs = []
+        for i in range(iters):
+            flush.fill_(i)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            evs.append((e0, e1))
+        torch.cuda.synchronize()
+        return sum(a.elapsed_time(c) for a, c in evs) / iters
+
+    rows = {}
+
+    def add(name, ms, work, bound):
+        if bound == 'tensor':
+            ach, peak, unit = work / (ms / 1e3) / 1e12, tf_peak, 'TFLOP/s'
+        else:
+            ach, peak, unit = work / (ms / 1e3) / 1e9, hbm_peak, 'GB/s'
+        rows[name] = {'ms': ms, 'achieved': ach, 'unit': unit, 'peak': peak, 'frac': ach / peak, 'bound': bound}
+
+    i = torch.arange(n)
+    # compressed attention (+ importance)
+    pairs = float(((i // st).clamp(max=ncb) + 1).sum()) * b * hq
+    qd, ckd, cvd = (t.detach().requires_grad_() for t in (q, ck, cv))
+    holder = {}
+    def cmp_fwd():
+        holder['o'], holder['imp'] = nsa.compressed_attend(qd, ckd, cvd, 1, st, True)
+    add('compressed_fwd', timed(cmp_fwd), 4 * d * pairs, 'tensor')
+    add('compressed_bwd', timed(lambda: torch.autograd.grad(holder['o'], (qd, ckd, cvd), do, retain_graph=True)),
+        10 * d * pairs, 'tensor')
+    imp = holder['imp']
+    # block selection
+    def select():
+        holder['vals'], holder['idx'] = nsa.select_blocks(imp, blk, st, nsel, dtype=torch.bfloat16)
+    ms = timed(select)
+    add('select', ms, imp.numel() * 4 + b * hkv * n * nsel * 12, 'hbm')
+    idx, mask = holder['idx'], holder['vals'] > 1e-10
+    # selected-block attention at this head grouping
+    keys = (mask.sum(dim=-1).cpu() * blk + (i % blk + 1).view(1, 1, n)).sum().item() * g
+    qd2, kd2, vd2 = (t.detach().requires_grad_() for t in (q, k, v))
+    def sel_fwd():
+        holder['os'] = nsa.native_sparse_attend(qd2, kd2, vd2, blk, idx, mask)
+    add('selected_fwd', timed(sel_fwd), 4 * d * keys, 'tensor')
+    add('selected_bwd', timed(lambda: torch.autograd.grad(holder['os'], (qd2, kd2, vd2), do, retain_graph=True)),
+        10 * d * keys, 'tensor')
+    # sliding window
+    pairs = float((i.clamp(max=win) + 1).sum()) * b * hq
+    qd3, kd3, vd3 = (t.detach().requires_grad_() for t in (q, k, v))
+    def swa_fwd():
+        holder['ow'] = nsa.sliding_window_attend(qd3, kd3, vd3, win, True)
+    add('sliding_fwd', timed(swa_fwd), 4 * d * pairs, 'tensor')
+    add('sliding_bwd', timed(lambda: torch.autograd.grad(holder['ow'], (qd3, kd3, vd3), do, retain_graph=True)),
+        10 * d * pairs, 'tensor')
+    # gated combine
+    o1, o2, o3 = (t.detach().requires_grad_() for t in (holder['o'], holder['os'], holder['ow']))
+    gd = gates.detach().requires_grad_()
+    def comb_fwd():
+        holder['m'] = nsa.gated_combine(o1, o2, o3, gd)
+    act = b * hq * n * d * 2
+    add('combine_fwd', timed(comb_fwd), 4 * act + gates.numel() * 2, 'hbm')
+    dm = torch.randn_like(holder['m'])
+    add('combine_bwd', timed(lambda: torch.autograd.grad(holder['m'], (o1, o2, o3, gd), dm, retain_graph=True)),
+        7 * act + gates.numel() * 6, 'hbm')
+    return rows
+
+
 def launches_per_step(kernels, w):
     """Kernels of this library launched by one forward+backward of the operator."""
     if kernels == 'simt':
         return 2   # one forward kernel, one backward kernel (gradient buffers are cleared by memset)
-    # tensor-core family: index pre-pass (4 kernels) + main + merge forward; pre-pass + delta + main backward
-    return 6 + 6
+    # tensor-core family: index pre-pass (4 kernels) + main + merge forward;
+    # index pre-pass + delta + main + dq merge backward
+    return 6 + 7
 
 
 if __name__ == '__main__':

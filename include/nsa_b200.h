@@ -9,7 +9,7 @@
  * Conventions
  *   - All pointers are DEVICE pointers owned by the caller.  Nothing here
  *     allocates or frees; work buffers are passed in and sized with
- *     nsa_sel_workspace_bytes().
+ *     nsa_sel_workspace_bytes() / nsa_cmp_workspace_bytes() / nsa_swa_workspace_bytes().
  *   - Every call is asynchronous on the given CUDA stream (a cudaStream_t
  *     passed as void*, NULL = default stream).
  *   - Return value: 0 on success; a negative NSA_ERR_* for an argument the
@@ -186,9 +186,17 @@ typedef struct {
   int32_t impl;
   float scale;
   float sentinel;        /* value an invisible logit is replaced by            */
+  void* workspace;       /* nsa_cmp_workspace_bytes(args, 0) bytes, may be NULL if that is 0 */
+  int64_t workspace_bytes;
 } nsa_cmp_fwd_args;
 
 int nsa_cmp_fwd(const nsa_cmp_fwd_args* args, void* stream);
+
+/* Bytes of work buffer nsa_cmp_fwd (backward != 0: nsa_cmp_bwd) needs; 0 when
+ * the SIMT family serves the problem.  The tensor-core family serves bf16,
+ * causal, dim_head 64/128, sel_heads == kv_heads, q_heads/kv_heads a power of
+ * two up to 16. */
+int64_t nsa_cmp_workspace_bytes(const nsa_cmp_fwd_args* args, int backward);
 
 /* Backward of the compressed branch (autograd of NSA:621-639 in upstream).
  * dq [B,q_heads,N,d], dck, dcv [B,kv_heads,num_mem+ncb,d] contiguous fp32,
@@ -243,9 +251,16 @@ typedef struct {
   int32_t batch, q_heads, kv_heads, seq, dim_head;
   int32_t window, causal, dtype, impl;
   float scale;
+  void* workspace;       /* nsa_swa_workspace_bytes(args, 0) bytes, may be NULL if that is 0 */
+  int64_t workspace_bytes;
 } nsa_swa_fwd_args;
 
 int nsa_swa_fwd(const nsa_swa_fwd_args* args, void* stream);
+
+/* Bytes of work buffer nsa_swa_fwd (backward != 0: nsa_swa_bwd) needs; 0 when
+ * the SIMT family serves the problem (tensor-core family: bf16, causal,
+ * dim_head 64/128, q_heads/kv_heads a power of two up to 16). */
+int64_t nsa_swa_workspace_bytes(const nsa_swa_fwd_args* args, int backward);
 
 typedef struct {
   nsa_swa_fwd_args fwd;

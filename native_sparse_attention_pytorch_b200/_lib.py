@@ -39,7 +39,7 @@ class CmpFwdArgs(C.Structure):
     _fields_ = [('q', Tensor4), ('ck', Tensor4), ('cv', Tensor4), ('out', Tensor4), ('lse', vp), ('importance', vp),
                 ('batch', i32), ('q_heads', i32), ('kv_heads', i32), ('sel_heads', i32), ('seq', i32), ('dim_head', i32),
                 ('num_mem', i32), ('ncb', i32), ('stride', i32), ('causal', i32), ('dtype', i32), ('impl', i32),
-                ('scale', f32), ('sentinel', f32)]
+                ('scale', f32), ('sentinel', f32), ('workspace', vp), ('workspace_bytes', i64)]
 
 
 class CmpBwdArgs(C.Structure):
@@ -54,7 +54,8 @@ class SelectArgs(C.Structure):
 class SwaFwdArgs(C.Structure):
     _fields_ = [('q', Tensor4), ('k', Tensor4), ('v', Tensor4), ('out', Tensor4), ('lse', vp),
                 ('batch', i32), ('q_heads', i32), ('kv_heads', i32), ('seq', i32), ('dim_head', i32),
-                ('window', i32), ('causal', i32), ('dtype', i32), ('impl', i32), ('scale', f32)]
+                ('window', i32), ('causal', i32), ('dtype', i32), ('impl', i32), ('scale', f32),
+                ('workspace', vp), ('workspace_bytes', i64)]
 
 
 class SwaBwdArgs(C.Structure):
@@ -74,7 +75,7 @@ _STRUCTS = [Tensor4, SelFwdArgs, SelBwdArgs, CmpFwdArgs, CmpBwdArgs, SelectArgs,
             CombineFwdArgs, CombineBwdArgs]
 
 ENTRY_POINTS = ['nsa_sel_fwd', 'nsa_sel_bwd', 'nsa_sel_workspace_bytes', 'nsa_sel_fwd_static',
-                'nsa_sel_static_scratch_bytes', 'nsa_cmp_fwd', 'nsa_cmp_bwd', 'nsa_select',
+                'nsa_sel_static_scratch_bytes', 'nsa_cmp_workspace_bytes', 'nsa_swa_workspace_bytes', 'nsa_cmp_fwd', 'nsa_cmp_bwd', 'nsa_select',
                 'nsa_swa_fwd', 'nsa_swa_bwd', 'nsa_combine_fwd', 'nsa_combine_bwd', 'nsa_last_error',
                 'nsa_abi_version', 'nsa_struct_size']
 
@@ -98,6 +99,8 @@ def load():
     lib.nsa_last_error.restype = C.c_char_p
     lib.nsa_sel_workspace_bytes.restype = i64
     lib.nsa_sel_static_scratch_bytes.restype = i64
+    lib.nsa_cmp_workspace_bytes.restype = i64
+    lib.nsa_swa_workspace_bytes.restype = i64
     for which, st in enumerate(_STRUCTS):
         if lib.nsa_struct_size(which) != C.sizeof(st):
             raise NsaError(f'struct layout mismatch for {st.__name__}: library {lib.nsa_struct_size(which)} '

@@ -188,11 +188,23 @@ static int fill_cmp(AttnParams& P, const nsa_cmp_fwd_args& a) {
   return NSA_OK;
 }
 
+int64_t nsa_cmp_workspace_bytes(const nsa_cmp_fwd_args* a, int backward) {
+  if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
+  if (a->impl == NSA_IMPL_SIMT) return 0;
+  const int64_t need = sm100_cmp_workspace_bytes(*a, backward != 0);
+  if (need < 0) return a->impl == NSA_IMPL_SM100 ? need : 0;
+  return need;
+}
+
 int nsa_cmp_fwd(const nsa_cmp_fwd_args* a, void* stream) {
   if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
   AttnParams P;
   NSA_TRY(fill_cmp(P, *a));
-  if (a->impl == NSA_IMPL_SM100) return fail(NSA_ERR_UNSUPPORTED, "compressed branch: only the SIMT family is built");
+  if (a->impl != NSA_IMPL_SIMT) {
+    const int rc = sm100_cmp_fwd(*a, (cudaStream_t)stream);
+    if (rc != NSA_ERR_UNSUPPORTED) return rc;
+    if (a->impl == NSA_IMPL_SM100) return fail(NSA_ERR_UNSUPPORTED, "compressed branch: shape outside the tensor-core family");
+  }
   return simt_attend(P, BR_CMP, a->dtype, false, (cudaStream_t)stream);
 }
 
@@ -202,12 +214,16 @@ int nsa_cmp_bwd(const nsa_cmp_bwd_args* a, void* stream) {
   NSA_TRY(fill_cmp(P, a->fwd));
   NSA_TRY(check_tensor(a->dout, a->fwd.dtype, "dout"));
   if (!a->dq || !a->dck || !a->dcv) return fail(NSA_ERR_NULL, "dq/dck/dcv: NULL pointer");
-  if (a->fwd.impl == NSA_IMPL_SM100) return fail(NSA_ERR_UNSUPPORTED, "compressed branch: only the SIMT family is built");
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t d = a->fwd.dim_head, rows = a->fwd.num_mem + a->fwd.ncb, b = a->fwd.batch;
   NSA_TRY(zero_async(a->dq, b * a->fwd.q_heads * a->fwd.seq * d, st));
   NSA_TRY(zero_async(a->dck, b * a->fwd.kv_heads * rows * d, st));
   NSA_TRY(zero_async(a->dcv, b * a->fwd.kv_heads * rows * d, st));
+  if (a->fwd.impl != NSA_IMPL_SIMT) {
+    const int rc = sm100_cmp_bwd(*a, st);
+    if (rc != NSA_ERR_UNSUPPORTED) return rc;
+    if (a->fwd.impl == NSA_IMPL_SM100) return fail(NSA_ERR_UNSUPPORTED, "compressed branch: shape outside the tensor-core family");
+  }
   set_dout(P, a->dout);
   P.importance = nullptr;
   P.dq = a->dq; P.dk = a->dck; P.dv = a->dcv;
@@ -253,11 +269,23 @@ static int fill_swa(AttnParams& P, const nsa_swa_fwd_args& a) {
   return NSA_OK;
 }
 
+int64_t nsa_swa_workspace_bytes(const nsa_swa_fwd_args* a, int backward) {
+  if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
+  if (a->impl == NSA_IMPL_SIMT) return 0;
+  const int64_t need = sm100_swa_workspace_bytes(*a, backward != 0);
+  if (need < 0) return a->impl == NSA_IMPL_SM100 ? need : 0;
+  return need;
+}
+
 int nsa_swa_fwd(const nsa_swa_fwd_args* a, void* stream) {
   if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
   AttnParams P;
   NSA_TRY(fill_swa(P, *a));
-  if (a->impl == NSA_IMPL_SM100) return fail(NSA_ERR_UNSUPPORTED, "sliding branch: only the SIMT family is built");
+  if (a->impl != NSA_IMPL_SIMT) {
+    const int rc = sm100_swa_fwd(*a, (cudaStream_t)stream);
+    if (rc != NSA_ERR_UNSUPPORTED) return rc;
+    if (a->impl == NSA_IMPL_SM100) return fail(NSA_ERR_UNSUPPORTED, "sliding branch: shape outside the tensor-core family");
+  }
   return simt_attend(P, BR_SWA, a->dtype, false, (cudaStream_t)stream);
 }
 
@@ -267,12 +295,16 @@ int nsa_swa_bwd(const nsa_swa_bwd_args* a, void* stream) {
   NSA_TRY(fill_swa(P, a->fwd));
   NSA_TRY(check_tensor(a->dout, a->fwd.dtype, "dout"));
   if (!a->dq || !a->dk || !a->dv) return fail(NSA_ERR_NULL, "dq/dk/dv: NULL pointer");
-  if (a->fwd.impl == NSA_IMPL_SM100) return fail(NSA_ERR_UNSUPPORTED, "sliding branch: only the SIMT family is built");
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t d = a->fwd.dim_head, n = a->fwd.seq, b = a->fwd.batch;
   NSA_TRY(zero_async(a->dq, b * a->fwd.q_heads * n * d, st));
   NSA_TRY(zero_async(a->dk, b * a->fwd.kv_heads * n * d, st));
   NSA_TRY(zero_async(a->dv, b * a->fwd.kv_heads * n * d, st));
+  if (a->fwd.impl != NSA_IMPL_SIMT) {
+    const int rc = sm100_swa_bwd(*a, st);
+    if (rc != NSA_ERR_UNSUPPORTED) return rc;
+    if (a->fwd.impl == NSA_IMPL_SM100) return fail(NSA_ERR_UNSUPPORTED, "sliding branch: shape outside the tensor-core family");
+  }
   set_dout(P, a->dout);
   P.dq = a->dq; P.dk = a->dk; P.dv = a->dv;
   return simt_attend(P, BR_SWA, a->fwd.dtype, true, st);

@@ -68,6 +68,12 @@ int64_t sm100_sel_workspace_bytes(const nsa_sel_fwd_args& a, bool backward);
 int sm100_sel_fwd(const nsa_sel_fwd_args& a, cudaStream_t stream);
 int sm100_sel_bwd(const nsa_sel_bwd_args& a, cudaStream_t stream);
 int sm100_sel_fwd_static(const nsa_sel_fwd_args& a, cudaStream_t stream);
+int64_t sm100_swa_workspace_bytes(const nsa_swa_fwd_args& a, bool backward);
+int sm100_swa_fwd(const nsa_swa_fwd_args& a, cudaStream_t stream);
+int sm100_swa_bwd(const nsa_swa_bwd_args& a, cudaStream_t stream);
+int64_t sm100_cmp_workspace_bytes(const nsa_cmp_fwd_args& a, bool backward);
+int sm100_cmp_fwd(const nsa_cmp_fwd_args& a, cudaStream_t stream);
+int sm100_cmp_bwd(const nsa_cmp_bwd_args& a, cudaStream_t stream);
 int64_t sm100_static_scratch_bytes();
 
 }  // namespace nsa

@@ -43,8 +43,45 @@ constexpr int kRows = 128;           // rows of a chunk tile (queries x heads of
 constexpr int kChunksPerItem = 16;   // chunks a CTA processes per resident K/V tile
 constexpr uint32_t kInvalidEntry = 0xffffffffu;
 
+// Which keys a query attends.  The three NSA branches differ only in this rule; everything after the index pre-pass
+// (lists of (query, slot) per key block, dense 128-row chunks) is shared.
+//   kModeSel : the blocks named by idx/mask plus the own block as `diag` says         (slot = position in idx; own = nsel)
+//   kModeSwa : causal window, keys i-window..i                                         (slot = own block - key block)
+//   kModeCmp : compressed keys, rows 0 .. num_mem + i/stride - 1 of a [num_mem + ncb]-row key tensor (slot = key block)
+enum { kModeSel = 0, kModeSwa = 1, kModeCmp = 2 };
+
+struct BlockRule {
+  const int64_t* idx;
+  const uint8_t* mask;
+  int N;        // queries
+  int nkb;      // key blocks of 64 rows
+  int nsel;     // slots in idx (kModeSel)
+  int ns;       // slots a query can have: the partial results of a query are indexed 0..ns-1
+  int diag, mode, window, stride, num_mem;
+};
+
+// Slot s of query i (selection head bh): does it exist, and which key block is it?
+__device__ __forceinline__ bool slot_block(const BlockRule& R, int bh, int i, int s, int* blk) {
+  if (R.mode == kModeSel) {
+    if (s == R.nsel) {
+      *blk = i / 64;
+      return R.diag != NSA_DIAG_NONE;
+    }
+    const int64_t at = ((int64_t)bh * R.N + i) * R.nsel + s;
+    const int64_t b = R.idx[at];
+    *blk = (int)b;
+    return R.mask[at] != 0 && b >= 0 && b < R.nkb;
+  }
+  if (R.mode == kModeSwa) {
+    *blk = i / 64 - s;
+    return *blk >= 0 && *blk * 64 + 63 >= i - R.window;
+  }
+  *blk = s;
+  return s * 64 < R.num_mem + i / R.stride;
+}
+
 struct SelPlan {
-  int nfb, G, QT, nlists;
+  int nqb, nkb, ns, G, QT, nlists;
   int64_t entries_cap, items_cap;
   // byte offsets into the work buffer
   int64_t off_status, off_num_items, off_counts, off_totals, off_list_base, off_items, off_entries;
@@ -67,41 +104,43 @@ struct SelParams {
   const float* delta;
   float *dq, *dk, *dv, *slot_grads;
   int* status;
-  int B, Hq, Hkv, N, G, nsel, nfb, diag;
+  int B, Hq, Hkv, N, Nk, G, nsel, nfb, diag;   // nfb = key blocks (lists per head); N queries, Nk key rows
+  int ns;                                       // slots per query in the partial buffers
   float scale, scale_log2;
+  BlockRule rule;
+  // compressed branch only: the head-averaged logits of every compressed block column, [B, Hkv, N, ncb] fp32
+  float* importance;
+  int ncb, round_bf16;
 };
 
 // ---- index pre-pass --------------------------------------------------------------
 
-// counts[(bh*nfb + qb)*nfb + j] = entries that the queries of block qb contribute to list (bh, j)
-__global__ void __launch_bounds__(kBlock) sel_hist_kernel(const int64_t* idx, const uint8_t* mask, int* counts, int N,
-                                                          int nsel, int nfb, int diag) {
+// counts[(bh*nqb + qb)*nkb + j] = entries that the queries of block qb contribute to list (bh, j)
+__global__ void __launch_bounds__(kBlock) sel_hist_kernel(const BlockRule R, int* counts) {
   extern __shared__ int hist[];
-  const int qb = blockIdx.x, bh = blockIdx.y * gridDim.z + blockIdx.z;  // gridDim = (nfb, B, Hkv) -> bh = b*Hkv + h
-  for (int j = threadIdx.x; j < nfb; j += kBlock) hist[j] = 0;
+  const int qb = blockIdx.x, nqb = gridDim.x, bh = blockIdx.y * gridDim.z + blockIdx.z;  // bh = b*Hkv + h
+  for (int j = threadIdx.x; j < R.nkb; j += kBlock) hist[j] = 0;
   __syncthreads();
   const int i = qb * kBlock + threadIdx.x;
-  if (i < N) {
-    const int64_t base = ((int64_t)bh * N + i) * nsel;
-    for (int s = 0; s < nsel; ++s) {
-      const int64_t blk = idx[base + s];
-      if (mask[base + s] != 0 && blk >= 0 && blk < nfb) atomicAdd(&hist[(int)blk], 1);
+  if (i < R.N) {
+    for (int s = 0; s < R.ns; ++s) {
+      int blk;
+      if (slot_block(R, bh, i, s, &blk)) atomicAdd(&hist[blk], 1);
     }
-    if (diag != NSA_DIAG_NONE) atomicAdd(&hist[qb], 1);
   }
   __syncthreads();
-  int* row = counts + ((int64_t)bh * nfb + qb) * nfb;
-  for (int j = threadIdx.x; j < nfb; j += kBlock) row[j] = hist[j];
+  int* row = counts + ((int64_t)bh * nqb + qb) * R.nkb;
+  for (int j = threadIdx.x; j < R.nkb; j += kBlock) row[j] = hist[j];
 }
 
 // per list: exclusive prefix over the contributing query blocks, and the list total
-__global__ void sel_scan_kernel(int* counts, int* totals, int nlists, int nfb) {
+__global__ void sel_scan_kernel(int* counts, int* totals, int nlists, int nqb, int nkb) {
   const int l = blockIdx.x * blockDim.x + threadIdx.x;
   if (l >= nlists) return;
-  const int bh = l / nfb, j = l - bh * nfb;
+  const int bh = l / nkb, j = l - bh * nkb;
   int running = 0;
-  for (int qb = 0; qb < nfb; ++qb) {
-    int* c = counts + ((int64_t)bh * nfb + qb) * nfb + j;
+  for (int qb = 0; qb < nqb; ++qb) {
+    int* c = counts + ((int64_t)bh * nqb + qb) * nkb + j;
     const int v = *c;
     *c = running;
     running += v;
@@ -149,31 +188,29 @@ __global__ void __launch_bounds__(1024) sel_items_kernel(const int* totals, int*
 }
 
 // writes the entries (query | slot << 24) in a fixed order: by query block, then slot, then query
-__global__ void __launch_bounds__(kBlock) sel_fill_kernel(const int64_t* idx, const uint8_t* mask, const int* counts,
-                                                          const int* list_base, uint32_t* entries, int N, int nsel,
-                                                          int nfb, int diag) {
+__global__ void __launch_bounds__(kBlock) sel_fill_kernel(const BlockRule R, const int* counts, const int* list_base,
+                                                          uint32_t* entries) {
   extern __shared__ int cursor[];
-  const int qb = blockIdx.x, bh = blockIdx.y * gridDim.z + blockIdx.z;
-  const int* row = counts + ((int64_t)bh * nfb + qb) * nfb;
-  for (int j = threadIdx.x; j < nfb; j += kBlock) cursor[j] = list_base[bh * nfb + j] + row[j];
+  const int qb = blockIdx.x, nqb = gridDim.x, bh = blockIdx.y * gridDim.z + blockIdx.z;
+  const int* row = counts + ((int64_t)bh * nqb + qb) * R.nkb;
+  for (int j = threadIdx.x; j < R.nkb; j += kBlock) cursor[j] = list_base[bh * R.nkb + j] + row[j];
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int i = qb * kBlock + threadIdx.x;
-  const int64_t base = ((int64_t)bh * N + min(i, N - 1)) * nsel;
-  for (int s = 0; s < nsel; ++s) {
-    const int64_t blk = idx[base + s];
-    const bool valid = i < N && mask[base + s] != 0 && blk >= 0 && blk < nfb;
+  for (int s = 0; s < R.ns; ++s) {
+    int blk = 0;
+    const bool valid = i < R.N && slot_block(R, bh, i, s, &blk);
     for (int w = 0; w < 2; ++w) {
       if (warp == w) {
         const unsigned vm = __ballot_sync(kFullMask, valid);
         if (valid) {
-          const unsigned peers = __match_any_sync(vm, (int)blk);
+          const unsigned peers = __match_any_sync(vm, blk);
           const int rank = __popc(peers & ((1u << lane) - 1u));
           const int leader = __ffs(peers) - 1;
           int pos = 0;
           if (lane == leader) {
-            pos = cursor[(int)blk];
-            cursor[(int)blk] = pos + __popc(peers);
+            pos = cursor[blk];
+            cursor[blk] = pos + __popc(peers);
           }
           pos = __shfl_sync(peers, pos, leader);
           entries[pos + rank] = (uint32_t)i | ((uint32_t)s << 24);
@@ -182,22 +219,32 @@ __global__ void __launch_bounds__(kBlock) sel_fill_kernel(const int64_t* idx, co
       __syncthreads();
     }
   }
-  if (diag != NSA_DIAG_NONE && i < N) entries[cursor[qb] + threadIdx.x] = (uint32_t)i | ((uint32_t)nsel << 24);
 }
 
 // ---- shared pieces of the two main kernels -----------------------------------------
 
 struct RowInfo {
-  int i, slot, lim;   // query position, slot, last visible key column of the block (-1: row is padding)
+  int i, slot;
+  int lo, lim;   // first and last visible key column of the block (lim = -1: the row is padding)
   bool valid;
 };
 
-__device__ __forceinline__ RowInfo decode_row(uint32_t e, int j, int nsel, int diag) {
+__device__ __forceinline__ RowInfo decode_row(uint32_t e, int j, const BlockRule& R) {
   RowInfo r;
   r.valid = e != kInvalidEntry;
   r.i = (int)(e & 0xffffffu);
   r.slot = (int)(e >> 24);
-  r.lim = !r.valid ? -1 : ((r.slot == nsel && diag == NSA_DIAG_CAUSAL) ? r.i - j * kBlock : kBlock - 1);
+  r.lo = 0;
+  r.lim = kBlock - 1;
+  if (R.mode == kModeSel) {
+    if (r.slot == R.nsel && R.diag == NSA_DIAG_CAUSAL) r.lim = r.i - j * kBlock;
+  } else if (R.mode == kModeSwa) {
+    r.lim = min(kBlock - 1, r.i - j * kBlock);
+    r.lo = max(0, r.i - R.window - j * kBlock);
+  } else {
+    r.lim = min(kBlock - 1, R.num_mem + r.i / R.stride - 1 - j * kBlock);
+  }
+  if (!r.valid) r.lim = -1;
   return r;
 }
 
@@ -352,7 +399,7 @@ sel_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     for (int c = 0; c < item.z; ++c) {
       const uint32_t* chunk_entries = P.entries + item.w + c * QT;
       const uint32_t e = chunk_entries[q_local];
-      const RowInfo r = decode_row(e, j, P.nsel, P.diag);
+      const RowInfo r = decode_row(e, j, P.rule);
       const int64_t hq = (int64_t)h * G + g;
       if (!prefetched) gather_tile_async<D>(sQ, P.q + b * P.q_sb, P.q_sh, P.q_sn, chunk_entries, g_shift, h, tid);
       cp_async_commit();
@@ -394,14 +441,27 @@ sel_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 #pragma unroll
         for (int x = 0; x < 32; ++x) s[32 + x] = t[x];
       }
+      if (P.importance != nullptr) {
+        // compressed branch: the scaled logit of every visible block column, averaged over the G heads of the query
+        // (neighbouring lanes), as the tensor of that dtype would hold it upstream: product, scaled logit and mean
+        // each rounded to bf16
+        float* imp_row = P.importance + (((int64_t)b * P.Hkv + h) * P.N + r.i) * P.ncb;
+#pragma unroll
+        for (int x = 0; x < 64; ++x) {
+          float logit = round_bf16(round_bf16(s[x]) * P.scale);
+          for (int o = G / 2; o > 0; o >>= 1) logit += __shfl_xor_sync(kFullMask, logit, o);
+          const int col = j * kBlock + x - P.rule.num_mem;
+          if (r.valid && g == 0 && x <= r.lim && col >= 0 && col < P.ncb) imp_row[col] = round_bf16(logit / (float)G);
+        }
+      }
       float m = -INFINITY;
 #pragma unroll
-      for (int x = 0; x < 64; ++x) m = x <= r.lim ? fmaxf(m, s[x]) : m;
+      for (int x = 0; x < 64; ++x) m = (x >= r.lo && x <= r.lim) ? fmaxf(m, s[x]) : m;
       const float m2 = r.valid ? m * P.scale_log2 : 0.f;
       float l = 0.f;
 #pragma unroll
       for (int x = 0; x < 64; ++x) {
-        const float p = x <= r.lim ? ex2(s[x] * P.scale_log2 - m2) : 0.f;
+        const float p = (x >= r.lo && x <= r.lim) ? ex2(s[x] * P.scale_log2 - m2) : 0.f;
         s[x] = p;
         l += p;   // the fp32 sum: the log-sum-exp stays exact although P is rounded to bf16 for the MMA
       }
@@ -422,7 +482,7 @@ sel_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       tc_fence_after_sync();
       __syncwarp();
       const int64_t row_global = ((int64_t)b * P.Hq + hq) * P.N + r.i;
-      const int64_t pslot = r.valid ? row_global * (P.nsel + 1) + r.slot : 0;
+      const int64_t pslot = r.valid ? row_global * P.ns + r.slot : 0;
       const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
       for (int c2 = 0; c2 < D / 32; ++c2) {
@@ -467,26 +527,19 @@ __global__ void __launch_bounds__(256) sel_merge_kernel(const SelParams P) {
   const int hq = (int)((row / P.N) % P.Hq);
   const int b = (int)(row / ((int64_t)P.N * P.Hq));
   const int h = hq / P.G;
-  const int64_t sbase = (((int64_t)b * P.Hkv + h) * P.N + i) * P.nsel;
-  const int ns = P.nsel + 1;
+  const int ns = P.ns;
   const float2* st = P.stats + row * ns;
   float M = -INFINITY;
   for (int s = 0; s < ns; ++s) {
-    bool ok = s == P.nsel ? P.diag != NSA_DIAG_NONE : false;
-    if (s < P.nsel) {
-      const int64_t blk = P.idx[sbase + s];
-      ok = P.mask[sbase + s] != 0 && blk >= 0 && blk < P.nfb;
-    }
+    int blk_;
+    const bool ok = slot_block(P.rule, b * P.Hkv + h, i, s, &blk_);
     if (ok) M = fmaxf(M, st[s].x);
   }
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   float L = 0.f;
   for (int s = 0; s < ns; ++s) {
-    bool ok = s == P.nsel ? P.diag != NSA_DIAG_NONE : false;
-    if (s < P.nsel) {
-      const int64_t blk = P.idx[sbase + s];
-      ok = P.mask[sbase + s] != 0 && blk >= 0 && blk < P.nfb;
-    }
+    int blk_;
+    const bool ok = slot_block(P.rule, b * P.Hkv + h, i, s, &blk_);
     if (!ok) continue;
     const float2 ml = st[s];
     const float w = ex2(ml.x - M) * ml.y;
@@ -618,7 +671,7 @@ sel_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     for (int c = 0; c < item.z; ++c) {
       const uint32_t* chunk_entries = P.entries + item.w + c * QT;
       const uint32_t e = chunk_entries[q_local];
-      const RowInfo r = decode_row(e, j, P.nsel, P.diag);
+      const RowInfo r = decode_row(e, j, P.rule);
       const int64_t hq = (int64_t)h * G + g;
       const int64_t row_global = ((int64_t)b * P.Hq + hq) * P.N + r.i;
       gather_tile<D>(sQ, P.q + b * P.q_sb, P.q_sh, P.q_sn, chunk_entries, g_shift, h, tid);
@@ -673,7 +726,7 @@ sel_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 #pragma unroll
       for (int x = 0; x < 64; ++x) {
         const float sx = p[x];
-        const float px = x <= r.lim ? ex2(sx * P.scale_log2 - lse2) : 0.f;
+        const float px = (x >= r.lo && x <= r.lim) ? ex2(sx * P.scale_log2 - lse2) : 0.f;
         const float dsx = px * (ds[x] - delta);
         slot_part = fmaf(dsx, sx * P.scale, slot_part);
         p[x] = px;
@@ -733,9 +786,9 @@ sel_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     // flush dK, dV of this item: accumulator rows 16w..16w+15 live in lanes 0..15 of warp w
     {
       const int key = j * kBlock + warp * 16 + lane;
-      const bool ok = lane < 16 && key < P.N;
-      float* dkp = P.dk + (((int64_t)b * P.Hkv + h) * P.N + key) * D;
-      float* dvp = P.dv + (((int64_t)b * P.Hkv + h) * P.N + key) * D;
+      const bool ok = lane < 16 && key < P.Nk;
+      float* dkp = P.dk + (((int64_t)b * P.Hkv + h) * P.Nk + key) * D;
+      float* dvp = P.dv + (((int64_t)b * P.Hkv + h) * P.Nk + key) * D;
 #pragma unroll
       for (int c2 = 0; c2 < D / 32; ++c2) {
         float t[32];
@@ -874,7 +927,7 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         const uint32_t e = lds_u32(sMeta);
         const float lse2 = __uint_as_float(lds_u32(sMeta + kRows * 4)) * kLog2e;
         const float delta = __uint_as_float(lds_u32(sMeta + 2 * kRows * 4));
-        const RowInfo r = decode_row(e, j, P.nsel, P.diag);
+        const RowInfo r = decode_row(e, j, P.rule);
         const int64_t hq = (int64_t)h * G + g;
         const int64_t row_global = ((int64_t)b * P.Hq + hq) * P.N + r.i;
         const uint32_t tS = buf * 128, tDP = buf * 128 + 64, tDQ = buf * 128;
@@ -885,11 +938,11 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         float slot_part = 0.f;
         const bool want_slot = P.slot_grads != nullptr;
         // rows that see the whole block need no per-column test; only own-block (causal) and padding rows do
-        const bool all_full = __all_sync(kFullMask, r.lim == kBlock - 1);
+        const bool all_full = __all_sync(kFullMask, r.lim == kBlock - 1 && r.lo == 0);
         // 16 columns at a time in a rolled loop: the body stays small enough for the instruction cache, which four
         // roles share
         auto math16 = [&](float (&sv)[16], float (&dv)[16], const int q4) {
-          const int rem = r.lim - q4 * 16;   // columns 0..rem of this group are visible
+          const int rem = r.lim - q4 * 16, rlo = r.lo - q4 * 16;   // columns rlo..rem of this group are visible
           if (all_full) {
 #pragma unroll
             for (int x = 0; x < 16; ++x) {
@@ -904,7 +957,7 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
 #pragma unroll
             for (int x = 0; x < 16; ++x) {
               const float sx = sv[x];
-              const float px = x <= rem ? ex2(sx * P.scale_log2 - lse2) : 0.f;
+              const float px = (x >= rlo && x <= rem) ? ex2(sx * P.scale_log2 - lse2) : 0.f;
               const float dsx = px * (dv[x] - delta);
               if (want_slot) slot_part = fmaf(dsx, sx, slot_part);
               sv[x] = px;
@@ -964,7 +1017,7 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         // The dQ row goes out as the bf16 partial result of (row, slot), straight from registers (the P/dS tiles are
         // still being read by the dV/dK MMAs).  Partials are summed by sel_dq_merge_kernel: plain stores run at
         // memory speed, whereas fp32 reductions into dq are limited by the L2 atomic units.
-        uint4* part_row = reinterpret_cast<uint4*>(P.partial + (row_global * (P.nsel + 1) + r.slot) * D);
+        uint4* part_row = reinterpret_cast<uint4*>(P.partial + (row_global * P.ns + r.slot) * D);
 #pragma unroll 1
         for (int c2 = 0; c2 < D / 16; ++c2) {
           float tq[16];
@@ -998,9 +1051,9 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         tc_fence_after_sync();
         __syncwarp();
         const int key = j * kBlock + (warp & 3) * 16 + lane;
-        const bool ok = lane < 16 && key < P.N;
-        float* dkp = P.dk + (((int64_t)b * P.Hkv + h) * P.N + key) * D;
-        float* dvp = P.dv + (((int64_t)b * P.Hkv + h) * P.N + key) * D;
+        const bool ok = lane < 16 && key < P.Nk;
+        float* dkp = P.dk + (((int64_t)b * P.Hkv + h) * P.Nk + key) * D;
+        float* dvp = P.dv + (((int64_t)b * P.Hkv + h) * P.Nk + key) * D;
         const uint32_t tDK = 256 + ab * 128, tDV = tDK + 64;
 #pragma unroll
         for (int c2 = 0; c2 < D / 32; ++c2) {
@@ -1255,15 +1308,11 @@ __global__ void __launch_bounds__(256) sel_dq_merge_kernel(const SelParams P) {
   const int hq = (int)((row / P.N) % P.Hq);
   const int b = (int)(row / ((int64_t)P.N * P.Hq));
   const int h = hq / P.G;
-  const int64_t sbase = (((int64_t)b * P.Hkv + h) * P.N + i) * P.nsel;
-  const int ns = P.nsel + 1;
+  const int ns = P.ns;
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   for (int s = 0; s < ns; ++s) {
-    bool ok = s == P.nsel ? P.diag != NSA_DIAG_NONE : false;
-    if (s < P.nsel) {
-      const int64_t blk = P.idx[sbase + s];
-      ok = P.mask[sbase + s] != 0 && blk >= 0 && blk < P.nfb;
-    }
+    int blk_;
+    const bool ok = slot_block(P.rule, b * P.Hkv + h, i, s, &blk_);
     if (!ok) continue;
     const uint4 v = *reinterpret_cast<const uint4*>(P.partial + (row * ns + s) * D + part * 8);
     const uint32_t u[4] = {v.x, v.y, v.z, v.w};
@@ -1279,53 +1328,80 @@ __global__ void __launch_bounds__(256) sel_dq_merge_kernel(const SelParams P) {
   dst[1] = make_float4(acc[4] * P.scale, acc[5] * P.scale, acc[6] * P.scale, acc[7] * P.scale);
 }
 
+__global__ void fill_kernel(float* dst, float value, int64_t count) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (int64_t)gridDim.x * blockDim.x) dst[i] = value;
+}
+
 // ---- host ----------------------------------------------------------------------------------
 
 static int64_t align_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
 
+// One problem of any of the three branches, as the host code sees it.
+struct SelProblem {
+  nsa_tensor q, k, v, out, dout;
+  const int64_t* idx;
+  const uint8_t* mask;
+  float* lse;
+  float *dq, *dk, *dv, *slot_grads;
+  float* importance;
+  void* workspace;
+  int64_t workspace_bytes;
+  int B, Hq, Hkv, N, Nk, D;
+  int nsel, diag, mode, window, stride, num_mem, ncb, round_bf16;
+  float scale;
+};
+
+static int slots_per_query(const SelProblem& a) {
+  if (a.mode == kModeSel) return a.nsel + 1;
+  if (a.mode == kModeSwa) return a.window / kBlock + 2;   // own block + every older block the window can touch
+  return (a.Nk + kBlock - 1) / kBlock;
+}
+
 // Shapes served by this family; everything else goes to the generic kernels.
-static bool supported(const nsa_sel_fwd_args& a) {
-  if (a.dtype != NSA_BF16 || a.block != kBlock) return false;
-  if (a.dim_head != 64 && a.dim_head != 128) return false;
-  if (a.sel_heads != a.kv_heads || a.diag == NSA_DIAG_NONE) return false;
-  const int G = a.q_heads / a.kv_heads;
+static bool supported(const SelProblem& a) {
+  if (a.D != 64 && a.D != 128) return false;
+  const int G = a.Hq / a.Hkv;
   if (G != 1 && G != 2 && G != 4 && G != 8 && G != 16) return false;
-  if (a.seq < 1 || a.seq >= (1 << 24) || a.nsel > 254 || a.batch < 1) return false;
-  const int64_t nfb = (a.seq + kBlock - 1) / kBlock;
-  if (nfb > 8192) return false;
-  const int64_t lists = (int64_t)a.batch * a.kv_heads * nfb;
-  if (lists * nfb > (1ll << 31) - 1) return false;
-  if ((int64_t)a.batch * a.kv_heads * ((int64_t)a.seq * (a.nsel + 1) + nfb * kRows) > (1ll << 31) - 1) return false;
-  if ((int64_t)a.batch * a.q_heads * (int64_t)a.seq * (a.nsel + 1) > (1ll << 31) - 1) return false;   // (row, slot) ids are 32-bit
-  // TMA needs 16-byte aligned bases and strides
-  if (a.k.stride_n < a.dim_head || a.v.stride_n < a.dim_head) return false;
+  if (a.N < 1 || a.N >= (1 << 24) || a.Nk < 1 || a.B < 1) return false;
+  if (a.mode == kModeSel && a.diag == NSA_DIAG_NONE) return false;   // a query must see at least one key
+  const int64_t ns = slots_per_query(a);
+  if (ns > 255) return false;
+  const int64_t nqb = (a.N + kBlock - 1) / kBlock, nkb = (a.Nk + kBlock - 1) / kBlock;
+  if (nkb > 8192) return false;
+  const int64_t lists = (int64_t)a.B * a.Hkv * nkb;
+  if (lists * nqb > (1ll << 31) - 1) return false;
+  if ((int64_t)a.B * a.Hkv * ((int64_t)a.N * ns + nkb * kRows) > (1ll << 31) - 1) return false;
+  if ((int64_t)a.B * a.Hq * (int64_t)a.N * ns > (1ll << 31) - 1) return false;   // (row, slot) ids are 32-bit
+  if (a.k.stride_n < a.D || a.v.stride_n < a.D) return false;
   return true;
 }
 
-static SelPlan make_plan(const nsa_sel_fwd_args& a, bool backward) {
+static SelPlan make_plan(const SelProblem& a, bool backward) {
   SelPlan p;
-  p.nfb = (a.seq + kBlock - 1) / kBlock;
-  p.G = a.q_heads / a.kv_heads;
+  p.nqb = (a.N + kBlock - 1) / kBlock;
+  p.nkb = (a.Nk + kBlock - 1) / kBlock;
+  p.ns = slots_per_query(a);
+  p.G = a.Hq / a.Hkv;
   p.QT = kRows / p.G;
-  p.nlists = a.batch * a.kv_heads * p.nfb;
-  p.entries_cap = (int64_t)a.batch * a.kv_heads * (int64_t)a.seq * (a.nsel + 1) + (int64_t)p.nlists * p.QT;
+  p.nlists = a.B * a.Hkv * p.nkb;
+  p.entries_cap = (int64_t)a.B * a.Hkv * (int64_t)a.N * p.ns + (int64_t)p.nlists * p.QT;
   p.items_cap = p.entries_cap / p.QT / kChunksPerItem + p.nlists + 1;
   int64_t off = 0;
   p.off_status = off; off += 256;
   p.off_num_items = p.off_status + 128;
-  p.off_counts = off; off = align_up(off + (int64_t)p.nlists * p.nfb * 4, 256);
+  p.off_counts = off; off = align_up(off + (int64_t)a.B * a.Hkv * p.nqb * p.nkb * 4, 256);
   p.off_totals = off; off = align_up(off + (int64_t)p.nlists * 4, 256);
   p.off_list_base = off; off = align_up(off + (int64_t)p.nlists * 4, 256);
   p.off_items = off; off = align_up(off + p.items_cap * 16, 256);
   p.off_entries = off; off = align_up(off + p.entries_cap * 4, 256);
-  const int64_t rows = (int64_t)a.batch * a.q_heads * a.seq;
+  const int64_t rows = (int64_t)a.B * a.Hq * a.N;
   p.off_partial = p.off_stats = p.off_delta = off;
   if (!backward) {
-    p.off_partial = off; off = align_up(off + rows * (a.nsel + 1) * a.dim_head * 2, 256);
-    p.off_stats = off; off = align_up(off + rows * (a.nsel + 1) * 8, 256);
+    p.off_partial = off; off = align_up(off + rows * p.ns * a.D * 2, 256);
+    p.off_stats = off; off = align_up(off + rows * p.ns * 8, 256);
   } else {
     p.off_delta = off; off = align_up(off + rows * 4, 256);
-    if (a.dim_head == 64) { p.off_partial = off; off = align_up(off + rows * (a.nsel + 1) * a.dim_head * 2, 256); }
+    if (a.D == 64) { p.off_partial = off; off = align_up(off + rows * p.ns * a.D * 2, 256); }
   }
   p.total_bytes = off;
   return p;
@@ -1368,7 +1444,15 @@ static int make_kv_map(CUtensorMap* map, const nsa_tensor& t, int B, int H, int 
     if (e_ != cudaSuccess) return fail((int)e_, cudaGetErrorString(e_));     \
   } while (0)
 
-static int build_index(const nsa_sel_fwd_args& a, const SelPlan& p, uint8_t* ws, cudaStream_t st) {
+static BlockRule make_rule(const SelProblem& a, const SelPlan& p) {
+  BlockRule R;
+  R.idx = a.idx; R.mask = a.mask;
+  R.N = a.N; R.nkb = p.nkb; R.nsel = a.nsel; R.ns = p.ns;
+  R.diag = a.diag; R.mode = a.mode; R.window = a.window; R.stride = a.stride > 0 ? a.stride : 1; R.num_mem = a.num_mem;
+  return R;
+}
+
+static int build_index(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaStream_t st) {
   int* counts = reinterpret_cast<int*>(ws + p.off_counts);
   int* totals = reinterpret_cast<int*>(ws + p.off_totals);
   int* list_base = reinterpret_cast<int*>(ws + p.off_list_base);
@@ -1377,18 +1461,18 @@ static int build_index(const nsa_sel_fwd_args& a, const SelPlan& p, uint8_t* ws,
   uint32_t* entries = reinterpret_cast<uint32_t*>(ws + p.off_entries);
   CUDA_TRY(cudaMemsetAsync(ws + p.off_status, 0, 256, st));
   CUDA_TRY(cudaMemsetAsync(entries, 0xff, (size_t)p.entries_cap * 4, st));
-  const dim3 grid(p.nfb, a.batch, a.kv_heads);
-  const size_t hist_smem = (size_t)p.nfb * sizeof(int);
-  sel_hist_kernel<<<grid, kBlock, hist_smem, st>>>(a.idx, a.mask, counts, a.seq, a.nsel, p.nfb, a.diag);
-  sel_scan_kernel<<<(p.nlists + 127) / 128, 128, 0, st>>>(counts, totals, p.nlists, p.nfb);
+  const BlockRule R = make_rule(a, p);
+  const dim3 grid(p.nqb, a.B, a.Hkv);
+  const size_t hist_smem = (size_t)p.nkb * sizeof(int);
+  sel_hist_kernel<<<grid, kBlock, hist_smem, st>>>(R, counts);
+  sel_scan_kernel<<<(p.nlists + 127) / 128, 128, 0, st>>>(counts, totals, p.nlists, p.nqb, p.nkb);
   sel_items_kernel<<<1, 1024, 0, st>>>(totals, list_base, items, num_items, p.nlists, p.QT);
-  sel_fill_kernel<<<grid, kBlock, hist_smem, st>>>(a.idx, a.mask, counts, list_base, entries, a.seq, a.nsel, p.nfb,
-                                                    a.diag);
+  sel_fill_kernel<<<grid, kBlock, hist_smem, st>>>(R, counts, list_base, entries);
   CUDA_TRY(cudaGetLastError());
   return NSA_OK;
 }
 
-static void fill_params(SelParams& P, const nsa_sel_fwd_args& a, const SelPlan& p, uint8_t* ws) {
+static void fill_params(SelParams& P, const SelProblem& a, const SelPlan& p, uint8_t* ws) {
   memset(&P, 0, sizeof(P));
   P.q = (const __nv_bfloat16*)a.q.ptr; P.q_sb = a.q.stride_b; P.q_sh = a.q.stride_h; P.q_sn = a.q.stride_n;
   P.out = (__nv_bfloat16*)a.out.ptr; P.o_sb = a.out.stride_b; P.o_sh = a.out.stride_h; P.o_sn = a.out.stride_n;
@@ -1398,8 +1482,11 @@ static void fill_params(SelParams& P, const nsa_sel_fwd_args& a, const SelPlan& 
   P.num_items = reinterpret_cast<const int*>(ws + p.off_num_items);
   P.status = reinterpret_cast<int*>(ws + p.off_status);
   P.lse = a.lse;
-  P.B = a.batch; P.Hq = a.q_heads; P.Hkv = a.kv_heads; P.N = a.seq; P.G = p.G; P.nsel = a.nsel; P.nfb = p.nfb;
+  P.B = a.B; P.Hq = a.Hq; P.Hkv = a.Hkv; P.N = a.N; P.Nk = a.Nk; P.G = p.G; P.nsel = a.nsel; P.nfb = p.nkb;
+  P.ns = p.ns;
   P.diag = a.diag; P.scale = a.scale; P.scale_log2 = a.scale * kLog2e;
+  P.rule = make_rule(a, p);
+  P.importance = a.importance; P.ncb = a.ncb; P.round_bf16 = a.round_bf16;
 }
 
 static int num_sms() {
@@ -1413,18 +1500,12 @@ static int num_sms() {
   return n;
 }
 
-int64_t sm100_sel_workspace_bytes(const nsa_sel_fwd_args& a, bool backward) {
-  if (!supported(a)) return NSA_ERR_UNSUPPORTED;
-  if (a.batch == 0 || a.seq == 0) return 0;
-  return make_plan(a, backward).total_bytes;
-}
-
 template <int D>
-static int run_fwd(const nsa_sel_fwd_args& a, const SelPlan& p, uint8_t* ws, cudaStream_t st) {
+static int run_fwd(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaStream_t st) {
   CUtensorMap tmK, tmV;
-  int rc = make_kv_map(&tmK, a.k, a.batch, a.kv_heads, a.seq, D);
+  int rc = make_kv_map(&tmK, a.k, a.B, a.Hkv, a.Nk, D);
   if (rc != NSA_OK) return rc;
-  rc = make_kv_map(&tmV, a.v, a.batch, a.kv_heads, a.seq, D);
+  rc = make_kv_map(&tmV, a.v, a.B, a.Hkv, a.Nk, D);
   if (rc != NSA_OK) return rc;
   rc = build_index(a, p, ws, st);
   if (rc != NSA_OK) return rc;
@@ -1437,29 +1518,28 @@ static int run_fwd(const nsa_sel_fwd_args& a, const SelPlan& p, uint8_t* ws, cud
   const int per_sm = D == 64 ? 4 : 2;
   CUDA_TRY(cudaFuncSetAttribute(sel_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   sel_fwd_kernel<D><<<num_sms() * per_sm, kRows, smem, st>>>(tmK, tmV, P);
-  const int64_t threads = (int64_t)a.batch * a.q_heads * a.seq * (D / 8);
+  const int64_t threads = (int64_t)a.B * a.Hq * a.N * (D / 8);
   sel_merge_kernel<D><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(P);
   CUDA_TRY(cudaGetLastError());
   return NSA_OK;
 }
 
 template <int D>
-static int run_bwd(const nsa_sel_bwd_args& b, const SelPlan& p, uint8_t* ws, cudaStream_t st) {
-  const nsa_sel_fwd_args& a = b.fwd;
+static int run_bwd(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaStream_t st) {
   CUtensorMap tmK, tmV;
-  int rc = make_kv_map(&tmK, a.k, a.batch, a.kv_heads, a.seq, D);
+  int rc = make_kv_map(&tmK, a.k, a.B, a.Hkv, a.Nk, D);
   if (rc != NSA_OK) return rc;
-  rc = make_kv_map(&tmV, a.v, a.batch, a.kv_heads, a.seq, D);
+  rc = make_kv_map(&tmV, a.v, a.B, a.Hkv, a.Nk, D);
   if (rc != NSA_OK) return rc;
   rc = build_index(a, p, ws, st);
   if (rc != NSA_OK) return rc;
   SelParams P;
   fill_params(P, a, p, ws);
-  P.dout = (const __nv_bfloat16*)b.dout.ptr; P.do_sb = b.dout.stride_b; P.do_sh = b.dout.stride_h; P.do_sn = b.dout.stride_n;
+  P.dout = (const __nv_bfloat16*)a.dout.ptr; P.do_sb = a.dout.stride_b; P.do_sh = a.dout.stride_h; P.do_sn = a.dout.stride_n;
   float* delta = reinterpret_cast<float*>(ws + p.off_delta);
   P.delta = delta;
-  P.dq = b.dq; P.dk = b.dk; P.dv = b.dv; P.slot_grads = b.slot_grads;
-  const int64_t threads = (int64_t)a.batch * a.q_heads * a.seq * (D / 8);
+  P.dq = a.dq; P.dk = a.dk; P.dv = a.dv; P.slot_grads = a.slot_grads;
+  const int64_t threads = (int64_t)a.B * a.Hq * a.N * (D / 8);
   sel_delta_kernel<D><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(P, delta);
   static const bool use_ws = []() { const char* e = getenv("NSA_SEL_BWD"); return e == nullptr || strcmp(e, "v1") != 0; }();
   if (D == 64 && use_ws) {
@@ -1480,27 +1560,124 @@ static int run_bwd(const nsa_sel_bwd_args& b, const SelPlan& p, uint8_t* ws, cud
   return NSA_OK;
 }
 
-int sm100_sel_fwd(const nsa_sel_fwd_args& a, cudaStream_t st) {
-  if (!supported(a)) return NSA_ERR_UNSUPPORTED;
-  if (a.batch == 0 || a.seq == 0) return NSA_OK;
-  const SelPlan p = make_plan(a, false);
-  if (a.workspace == nullptr || a.workspace_bytes < p.total_bytes)
-    return fail(NSA_ERR_WORKSPACE, "selected-block forward: work buffer missing or smaller than nsa_sel_workspace_bytes");
-  uint8_t* ws = static_cast<uint8_t*>(a.workspace);
-  if (reinterpret_cast<uintptr_t>(ws) & 255) return fail(NSA_ERR_ALIGN, "work buffer must be 256-byte aligned");
-  return a.dim_head == 64 ? run_fwd<64>(a, p, ws, st) : run_fwd<128>(a, p, ws, st);
+// ---- the three branches as problems ------------------------------------------------------------
+
+static void problem_base(SelProblem& x) { memset(&x, 0, sizeof(x)); x.stride = 1; }
+
+static bool sel_problem(SelProblem& x, const nsa_sel_fwd_args& a) {
+  problem_base(x);
+  if (a.dtype != NSA_BF16 || a.block != kBlock || a.sel_heads != a.kv_heads || a.nsel > 254) return false;
+  x.q = a.q; x.k = a.k; x.v = a.v; x.out = a.out; x.idx = a.idx; x.mask = a.mask; x.lse = a.lse;
+  x.workspace = a.workspace; x.workspace_bytes = a.workspace_bytes;
+  x.B = a.batch; x.Hq = a.q_heads; x.Hkv = a.kv_heads; x.N = a.seq; x.Nk = a.seq; x.D = a.dim_head;
+  x.nsel = a.nsel; x.diag = a.diag; x.mode = kModeSel; x.scale = a.scale;
+  return supported(x);
 }
 
+static bool swa_problem(SelProblem& x, const nsa_swa_fwd_args& a) {
+  problem_base(x);
+  if (a.dtype != NSA_BF16 || !a.causal) return false;
+  x.q = a.q; x.k = a.k; x.v = a.v; x.out = a.out; x.lse = a.lse;
+  x.workspace = a.workspace; x.workspace_bytes = a.workspace_bytes;
+  x.B = a.batch; x.Hq = a.q_heads; x.Hkv = a.kv_heads; x.N = a.seq; x.Nk = a.seq; x.D = a.dim_head;
+  x.mode = kModeSwa; x.window = a.window; x.scale = a.scale;
+  return supported(x);
+}
+
+static bool cmp_problem(SelProblem& x, const nsa_cmp_fwd_args& a) {
+  problem_base(x);
+  if (a.dtype != NSA_BF16 || !a.causal || a.sel_heads != a.kv_heads) return false;
+  x.q = a.q; x.k = a.ck; x.v = a.cv; x.out = a.out; x.lse = a.lse;
+  x.workspace = a.workspace; x.workspace_bytes = a.workspace_bytes;
+  x.B = a.batch; x.Hq = a.q_heads; x.Hkv = a.kv_heads; x.N = a.seq; x.Nk = a.num_mem + a.ncb; x.D = a.dim_head;
+  x.mode = kModeCmp; x.stride = a.stride; x.num_mem = a.num_mem; x.ncb = a.ncb; x.round_bf16 = 1;
+  x.importance = a.importance; x.scale = a.scale;
+  return supported(x);
+}
+
+static int check_ws(const SelProblem& x, const SelPlan& p, uint8_t** ws) {
+  if (x.workspace == nullptr || x.workspace_bytes < p.total_bytes)
+    return fail(NSA_ERR_WORKSPACE, "work buffer missing or smaller than the matching *_workspace_bytes says");
+  *ws = static_cast<uint8_t*>(x.workspace);
+  if (reinterpret_cast<uintptr_t>(*ws) & 255) return fail(NSA_ERR_ALIGN, "work buffer must be 256-byte aligned");
+  return NSA_OK;
+}
+
+static int problem_fwd(const SelProblem& x, cudaStream_t st) {
+  const SelPlan p = make_plan(x, false);
+  uint8_t* ws = nullptr;
+  const int rc = check_ws(x, p, &ws);
+  if (rc != NSA_OK) return rc;
+  return x.D == 64 ? run_fwd<64>(x, p, ws, st) : run_fwd<128>(x, p, ws, st);
+}
+
+static int problem_bwd(const SelProblem& x, cudaStream_t st) {
+  const SelPlan p = make_plan(x, true);
+  uint8_t* ws = nullptr;
+  const int rc = check_ws(x, p, &ws);
+  if (rc != NSA_OK) return rc;
+  return x.D == 64 ? run_bwd<64>(x, p, ws, st) : run_bwd<128>(x, p, ws, st);
+}
+
+int64_t sm100_sel_workspace_bytes(const nsa_sel_fwd_args& a, bool backward) {
+  SelProblem x;
+  if (!sel_problem(x, a)) return NSA_ERR_UNSUPPORTED;
+  return make_plan(x, backward).total_bytes;
+}
+int sm100_sel_fwd(const nsa_sel_fwd_args& a, cudaStream_t st) {
+  SelProblem x;
+  if (!sel_problem(x, a)) return NSA_ERR_UNSUPPORTED;
+  return problem_fwd(x, st);
+}
 int sm100_sel_bwd(const nsa_sel_bwd_args& b, cudaStream_t st) {
-  const nsa_sel_fwd_args& a = b.fwd;
-  if (!supported(a)) return NSA_ERR_UNSUPPORTED;
-  if (a.batch == 0 || a.seq == 0) return NSA_OK;
-  const SelPlan p = make_plan(a, true);
-  if (a.workspace == nullptr || a.workspace_bytes < p.total_bytes)
-    return fail(NSA_ERR_WORKSPACE, "selected-block backward: work buffer missing or smaller than nsa_sel_workspace_bytes");
-  uint8_t* ws = static_cast<uint8_t*>(a.workspace);
-  if (reinterpret_cast<uintptr_t>(ws) & 255) return fail(NSA_ERR_ALIGN, "work buffer must be 256-byte aligned");
-  return a.dim_head == 64 ? run_bwd<64>(b, p, ws, st) : run_bwd<128>(b, p, ws, st);
+  SelProblem x;
+  if (!sel_problem(x, b.fwd)) return NSA_ERR_UNSUPPORTED;
+  x.dout = b.dout; x.dq = b.dq; x.dk = b.dk; x.dv = b.dv; x.slot_grads = b.slot_grads;
+  return problem_bwd(x, st);
+}
+
+int64_t sm100_swa_workspace_bytes(const nsa_swa_fwd_args& a, bool backward) {
+  SelProblem x;
+  if (!swa_problem(x, a)) return NSA_ERR_UNSUPPORTED;
+  return make_plan(x, backward).total_bytes;
+}
+int sm100_swa_fwd(const nsa_swa_fwd_args& a, cudaStream_t st) {
+  SelProblem x;
+  if (!swa_problem(x, a)) return NSA_ERR_UNSUPPORTED;
+  return problem_fwd(x, st);
+}
+int sm100_swa_bwd(const nsa_swa_bwd_args& b, cudaStream_t st) {
+  SelProblem x;
+  if (!swa_problem(x, b.fwd)) return NSA_ERR_UNSUPPORTED;
+  x.dout = b.dout; x.dq = b.dq; x.dk = b.dk; x.dv = b.dv;
+  return problem_bwd(x, st);
+}
+
+int64_t sm100_cmp_workspace_bytes(const nsa_cmp_fwd_args& a, bool backward) {
+  SelProblem x;
+  if (!cmp_problem(x, a)) return NSA_ERR_UNSUPPORTED;
+  return make_plan(x, backward).total_bytes;
+}
+int sm100_cmp_fwd(const nsa_cmp_fwd_args& a, cudaStream_t st) {
+  SelProblem x;
+  if (!cmp_problem(x, a)) return NSA_ERR_UNSUPPORTED;
+  if (x.importance != nullptr) {
+    // columns a query cannot see carry the head mean of the sentinel; the kernel overwrites the visible ones
+    float fill = 0.f;
+    const int G = x.Hq / x.Hkv;
+    for (int g = 0; g < G; ++g) fill += a.sentinel;
+    fill = __bfloat162float(__float2bfloat16_rn(fill / (float)G));
+    const int64_t count = (int64_t)x.B * x.Hkv * x.N * x.ncb;
+    fill_kernel<<<(unsigned)((count + 1023) / 1024 < 148 * 16 ? (count + 1023) / 1024 : 148 * 16), 256, 0, st>>>(x.importance, fill, count);
+  }
+  return problem_fwd(x, st);
+}
+int sm100_cmp_bwd(const nsa_cmp_bwd_args& b, cudaStream_t st) {
+  SelProblem x;
+  if (!cmp_problem(x, b.fwd)) return NSA_ERR_UNSUPPORTED;
+  x.importance = nullptr;
+  x.dout = b.dout; x.dq = b.dq; x.dk = b.dck; x.dv = b.dcv;
+  return problem_bwd(x, st);
 }
 
 // ---- forward without a caller-provided work buffer ---------------------------------------------
@@ -1533,9 +1710,9 @@ static int static_scratch(unsigned char** out) {
 }
 
 int sm100_sel_fwd_static(const nsa_sel_fwd_args& a, cudaStream_t st) {
-  if (!supported(a)) return fail(NSA_ERR_UNSUPPORTED, "nsa_sel_fwd_static: shape outside the tensor-core family (bf16, block 64, dim_head 64/128, shared selection, own block included)");
-  if (a.batch == 0 || a.seq == 0) return NSA_OK;
-  const SelPlan p = make_plan(a, false);
+  SelProblem x;
+  if (!sel_problem(x, a)) return fail(NSA_ERR_UNSUPPORTED, "nsa_sel_fwd_static: shape outside the tensor-core family (bf16, block 64, dim_head 64/128, shared selection, own block included)");
+  const SelPlan p = make_plan(x, false);
   if (p.total_bytes > kStaticScratchBytes) {
     static thread_local char msg[160];
     snprintf(msg, sizeof(msg), "nsa_sel_fwd_static: this problem needs %lld bytes of scratch, the built-in area holds %lld",
@@ -1545,7 +1722,7 @@ int sm100_sel_fwd_static(const nsa_sel_fwd_args& a, cudaStream_t st) {
   unsigned char* ws = nullptr;
   const int rc = static_scratch(&ws);
   if (rc != NSA_OK) return rc;
-  return a.dim_head == 64 ? run_fwd<64>(a, p, ws, st) : run_fwd<128>(a, p, ws, st);
+  return x.D == 64 ? run_fwd<64>(x, p, ws, st) : run_fwd<128>(x, p, ws, st);
 }
 
 int64_t sm100_static_scratch_bytes() { return kStaticScratchBytes; }

@@ -33,9 +33,9 @@ def _sel_args(q, k, v, out, idx, mask, lse, block, diag, impl, scale):
 _status_words = []
 
 
-def _with_workspace(args, backward, device):
+def _with_workspace(args, backward, device, sizer='nsa_sel_workspace_bytes'):
     lib = L.load()
-    need = lib.nsa_sel_workspace_bytes(C.byref(args), int(backward))
+    need = getattr(lib, sizer)(C.byref(args), int(backward))
     if need < 0:
         L.check(int(need))
     ws = None
@@ -153,7 +153,8 @@ def _cmp_args(q, ck, cv, out, lse, imp, sel_heads, num_mem, stride, causal, impl
     return L.CmpFwdArgs(q=L.t4(q), ck=L.t4(ck), cv=L.t4(cv), out=L.t4(out), lse=L.ptr(lse), importance=L.ptr(imp),
                         batch=b, q_heads=hq, kv_heads=ck.shape[1], sel_heads=sel_heads, seq=n, dim_head=d,
                         num_mem=num_mem, ncb=ck.shape[2] - num_mem, stride=stride, causal=int(causal),
-                        dtype=L.dtype_code(q), impl=impl, scale=scale, sentinel=mask_sentinel(q.dtype))
+                        dtype=L.dtype_code(q), impl=impl, scale=scale, sentinel=mask_sentinel(q.dtype), workspace=None,
+                        workspace_bytes=0)
 
 
 class CompressedAttention(Function):
@@ -173,7 +174,10 @@ class CompressedAttention(Function):
         scale = d ** -0.5
         with torch.cuda.device(q.device):
             args = _cmp_args(q, ck, cv, out, lse, imp, sel_heads, num_mem, stride, causal, impl, scale)
+            ws = _with_workspace(args, False, q.device, 'nsa_cmp_workspace_bytes')
             L.check(lib.nsa_cmp_fwd(C.byref(args), L.stream_of(q)))
+            _keep_status(ws)
+            del ws
         ctx.save_for_backward(q, ck, cv, out, lse)
         ctx.cfg = (num_mem, stride, causal, sel_heads, impl, scale)
         if imp is None:
@@ -192,8 +196,11 @@ class CompressedAttention(Function):
         dcv = torch.empty(cv.shape, dtype=torch.float32, device=q.device)
         with torch.cuda.device(q.device):
             fwd = _cmp_args(q, ck, cv, out, lse, None, sel_heads, num_mem, stride, causal, impl, scale)
+            ws = _with_workspace(fwd, True, q.device, 'nsa_cmp_workspace_bytes')
             args = L.CmpBwdArgs(fwd=fwd, dout=L.t4(dout), dq=L.ptr(dq), dck=L.ptr(dck), dcv=L.ptr(dcv))
             L.check(lib.nsa_cmp_bwd(C.byref(args), L.stream_of(q)))
+            _keep_status(ws)
+            del ws
         return dq.to(q.dtype), dck.to(ck.dtype), dcv.to(cv.dtype), None, None, None, None, None, None
 
 
@@ -239,7 +246,7 @@ def _swa_args(q, k, v, out, lse, window, causal, impl, scale):
     b, hq, n, d = q.shape
     return L.SwaFwdArgs(q=L.t4(q), k=L.t4(k), v=L.t4(v), out=L.t4(out), lse=L.ptr(lse), batch=b, q_heads=hq,
                         kv_heads=k.shape[1], seq=n, dim_head=d, window=window, causal=int(causal),
-                        dtype=L.dtype_code(q), impl=impl, scale=scale)
+                        dtype=L.dtype_code(q), impl=impl, scale=scale, workspace=None, workspace_bytes=0)
 
 
 class SlidingAttention(Function):
@@ -254,7 +261,10 @@ class SlidingAttention(Function):
         scale = d ** -0.5
         with torch.cuda.device(q.device):
             args = _swa_args(q, k, v, out, lse, window, causal, impl, scale)
+            ws = _with_workspace(args, False, q.device, 'nsa_swa_workspace_bytes')
             L.check(lib.nsa_swa_fwd(C.byref(args), L.stream_of(q)))
+            _keep_status(ws)
+            del ws
         ctx.save_for_backward(q, k, v, out, lse)
         ctx.cfg = (window, causal, impl, scale)
         return out
@@ -270,8 +280,11 @@ class SlidingAttention(Function):
         dv = torch.empty(v.shape, dtype=torch.float32, device=q.device)
         with torch.cuda.device(q.device):
             fwd = _swa_args(q, k, v, out, lse, window, causal, impl, scale)
+            ws = _with_workspace(fwd, True, q.device, 'nsa_swa_workspace_bytes')
             args = L.SwaBwdArgs(fwd=fwd, dout=L.t4(dout), dq=L.ptr(dq), dk=L.ptr(dk), dv=L.ptr(dv))
             L.check(lib.nsa_swa_bwd(C.byref(args), L.stream_of(q)))
+            _keep_status(ws)
+            del ws
         return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), None, None, None
 
 

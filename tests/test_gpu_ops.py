@@ -170,9 +170,12 @@ def test_compressed_matches_oracle(case, dtype):
     close = closeness(dtype)
     close(out, ref, 'out')
     close(dq, rdq, 'dq')
-    close(dck, rdck, 'dck')
-    close(dcv, rdcv, 'dcv')
-    close(dmem, rdmem, 'dmem')
+    # a compressed key (above all a memory slot) collects gradient from every later query of every head; in bf16
+    # allow 0.5 % of the largest value on those sums
+    wide = dict(rel_to_max=5e-3) if dtype == torch.bfloat16 else {}
+    close(dck, rdck, 'dck', **wide)
+    close(dcv, rdcv, 'dcv', **wide)
+    close(dmem, rdmem, 'dmem', **wide)
     # importance = head-mean of the block logits, the sentinel where invisible
     ref_imp = csim[..., m:]
     if share:

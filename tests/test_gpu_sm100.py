@@ -121,3 +121,92 @@ def test_sm100_refuses_shapes_it_does_not_serve():
     q, k, v, idx, mask, up = make_case(1, 4, 2, 100, 32, 2, seed=1)
     with pytest.raises(RuntimeError):
         nsa.native_sparse_attend(q.to(DEV), k.to(DEV), v.to(DEV), BLOCK, idx.to(DEV), mask.to(DEV), impl='sm100')
+
+
+# ---- the compressed and the sliding branch on the same tensor-core kernels ---------------------------------------
+
+SWA_CASES = [
+    # b, hq, hkv, n, d, window
+    (2, 8, 2, 300, 64, 100),
+    (1, 4, 1, 515, 64, 512),
+    (1, 16, 1, 200, 128, 64),
+    (1, 2, 2, 130, 64, 0),
+    (1, 8, 1, 97, 64, 1000),
+]
+
+
+@pytest.mark.parametrize('case', SWA_CASES)
+def test_sm100_sliding_matches_oracle(case):
+    b, hq, hkv, n, d, win = case
+    q = recipe.randn((b, hq, n, d), 1).bfloat16()
+    k = recipe.randn((b, hkv, n, d), 2).bfloat16()
+    v = recipe.randn((b, hkv, n, d), 3).bfloat16()
+    up = recipe.randn((b, hq, n, d), 4).bfloat16()
+    qo, ko, vo = (t.float().requires_grad_() for t in (q, k, v))
+    ref = O.sliding_attend(qo, ko, vo, win, True)
+    rd = torch.autograd.grad((ref * up.float()).sum(), (qo, ko, vo))
+    qg, kg, vg = (t.to(DEV).requires_grad_() for t in (q, k, v))
+    out = nsa.sliding_window_attend(qg, kg, vg, win, True, impl='sm100')
+    gd = torch.autograd.grad((out * up.to(DEV)).sum(), (qg, kg, vg))
+    ops.check_device_status()
+    for g, r, w in zip((out, *gd), (ref, *rd), ('out', 'dq', 'dk', 'dv')):
+        assert_close_bf16(g, r, w)
+
+
+CMP_CASES = [
+    # b, hq, hkv, n, d, stride, num_mem
+    (2, 8, 2, 300, 64, 4, 1),
+    (1, 4, 1, 1000, 64, 16, 2),
+    (1, 8, 1, 260, 128, 2, 1),
+    (1, 2, 2, 70, 64, 1, 1),
+]
+
+
+@pytest.mark.parametrize('case', CMP_CASES)
+def test_sm100_compressed_matches_oracle(case):
+    b, hq, hkv, n, d, st, m = case
+    ncb = n // st
+    q = recipe.randn((b, hq, n, d), 1).bfloat16()
+    ck = recipe.randn((b, hkv, ncb, d), 2).bfloat16()
+    cv = recipe.randn((b, hkv, ncb, d), 3).bfloat16()
+    mem = recipe.randn((2, hkv, m, d), 4).bfloat16()
+    up = recipe.randn((b, hq, n, d), 5).bfloat16()
+    qo, cko, cvo, memo = (t.float().requires_grad_() for t in (q, ck, cv, mem))
+    ref, csim = O.compressed_attend(qo, cko, cvo, memo[0], memo[1], st, True)
+    rd = torch.autograd.grad((ref * up.float()).sum(), (qo, cko, cvo, memo))
+    qg, ckg, cvg, memg = (t.to(DEV).requires_grad_() for t in (q, ck, cv, mem))
+    ckf = torch.cat((memg[0].expand(b, -1, -1, -1), ckg), dim=-2)
+    cvf = torch.cat((memg[1].expand(b, -1, -1, -1), cvg), dim=-2)
+    out, imp = nsa.compressed_attend(qg, ckf, cvf, m, st, True, impl='sm100')
+    gd = torch.autograd.grad((out * up.to(DEV)).sum(), (qg, ckg, cvg, memg))
+    ops.check_device_status()
+    for g, r, w in zip((out, *gd), (ref, *rd), ('out', 'dq', 'dck', 'dcv', 'dmem')):
+        # a compressed key (and above all a memory slot) collects gradient from every later query of every head:
+        # allow 0.5 % of the largest value on those sums
+        assert_close_bf16(g, r, w, rel_to_max=5e-3 if w in ('dck', 'dcv', 'dmem') else 0.0)
+    ref_imp = csim[..., m:].reshape(b, hkv, hq // hkv, n, ncb).mean(dim=2)
+    vis = ref_imp > -1e30
+    assert torch.equal(vis, imp.cpu() > -1e30)
+    assert_close_bf16(torch.where(vis, imp.cpu(), 0), torch.where(vis, ref_imp, 0), 'importance', tol=6e-2)
+    # the generic kernels write the same importance values (same rounding chain, other summation order)
+    _, imp_simt = nsa.compressed_attend(qg, ckf, cvf, m, st, True, impl='simt')
+    assert torch.equal(imp.cpu()[~vis], imp_simt.cpu()[~vis])
+    assert_close_bf16(torch.where(vis, imp.cpu(), 0), torch.where(vis, imp_simt.cpu(), 0), 'importance vs simt', tol=6e-2)
+
+
+def test_sm100_layer_bf16_uses_tensor_core_branches():
+    # a whole layer at a shape all three branches serve on tensor cores, against the fp32 oracle
+    from native_sparse_attention_pytorch_b200 import SparseAttention
+    kw = dict(dim=128, dim_head=64, heads=4, kv_heads=2, causal=True, sliding_window_size=70, compress_block_size=16,
+              compress_block_sliding_stride=8, selection_block_size=64, num_selected_blocks=2)
+    attn = SparseAttention(**kw, use_triton_kernel=True, kernel_impl='sm100')
+    recipe.fill_weights(attn, seed=7)
+    attn = attn.to(DEV).bfloat16()
+    ref = O.OracleSparseAttention(**kw)
+    ref.load_state_dict({k_: v_.float().cpu() for k_, v_ in attn.state_dict().items()})
+    x = recipe.randn((2, 300, 128), 11).bfloat16()
+    out, mid = attn(x.to(DEV), return_intermediates=True)
+    rout, rmid = ref(x.float(), return_intermediates=True)
+    ops.check_device_status()
+    assert_close_bf16(mid['o_cmp'], rmid['o_cmp'], 'compressed branch')
+    assert_close_bf16(mid['o_swa'], rmid['o_swa'], 'sliding branch')
