@@ -61,8 +61,9 @@ struct BlockRule {
 };
 
 // Slot s of query i (selection head bh): does it exist, and which key block is it?
+template <int MODE>
 __device__ __forceinline__ bool slot_block(const BlockRule& R, int bh, int i, int s, int* blk) {
-  if (R.mode == kModeSel) {
+  if (MODE == kModeSel) {
     if (s == R.nsel) {
       *blk = i / 64;
       return R.diag != NSA_DIAG_NONE;
@@ -72,7 +73,7 @@ __device__ __forceinline__ bool slot_block(const BlockRule& R, int bh, int i, in
     *blk = (int)b;
     return R.mask[at] != 0 && b >= 0 && b < R.nkb;
   }
-  if (R.mode == kModeSwa) {
+  if (MODE == kModeSwa) {
     *blk = i / 64 - s;
     return *blk >= 0 && *blk * 64 + 63 >= i - R.window;
   }
@@ -116,6 +117,7 @@ struct SelParams {
 // ---- index pre-pass --------------------------------------------------------------
 
 // counts[(bh*nqb + qb)*nkb + j] = entries that the queries of block qb contribute to list (bh, j)
+template <int MODE>
 __global__ void __launch_bounds__(kBlock) sel_hist_kernel(const BlockRule R, int* counts) {
   extern __shared__ int hist[];
   const int qb = blockIdx.x, nqb = gridDim.x, bh = blockIdx.y * gridDim.z + blockIdx.z;  // bh = b*Hkv + h
@@ -125,7 +127,7 @@ __global__ void __launch_bounds__(kBlock) sel_hist_kernel(const BlockRule R, int
   if (i < R.N) {
     for (int s = 0; s < R.ns; ++s) {
       int blk;
-      if (slot_block(R, bh, i, s, &blk)) atomicAdd(&hist[blk], 1);
+      if (slot_block<MODE>(R, bh, i, s, &blk)) atomicAdd(&hist[blk], 1);
     }
   }
   __syncthreads();
@@ -188,6 +190,7 @@ __global__ void __launch_bounds__(1024) sel_items_kernel(const int* totals, int*
 }
 
 // writes the entries (query | slot << 24) in a fixed order: by query block, then slot, then query
+template <int MODE>
 __global__ void __launch_bounds__(kBlock) sel_fill_kernel(const BlockRule R, const int* counts, const int* list_base,
                                                           uint32_t* entries) {
   extern __shared__ int cursor[];
@@ -199,7 +202,7 @@ __global__ void __launch_bounds__(kBlock) sel_fill_kernel(const BlockRule R, con
   const int i = qb * kBlock + threadIdx.x;
   for (int s = 0; s < R.ns; ++s) {
     int blk = 0;
-    const bool valid = i < R.N && slot_block(R, bh, i, s, &blk);
+    const bool valid = i < R.N && slot_block<MODE>(R, bh, i, s, &blk);
     for (int w = 0; w < 2; ++w) {
       if (warp == w) {
         const unsigned vm = __ballot_sync(kFullMask, valid);
@@ -336,7 +339,7 @@ __device__ __forceinline__ void store_rows_coalesced(uint32_t stage, uint32_t st
 
 // ---- forward -------------------------------------------------------------------------
 
-template <int D>
+template <int D, bool IMP, bool LO>   // IMP: also write the compressed branch's importance; LO: rows may have a first visible column > 0
 __global__ void __launch_bounds__(kRows, D == 64 ? 4 : 2)
 sel_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const SelParams P) {
   constexpr int NC = D / 64;
@@ -441,27 +444,51 @@ sel_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 #pragma unroll
         for (int x = 0; x < 32; ++x) s[32 + x] = t[x];
       }
-      if (P.importance != nullptr) {
-        // compressed branch: the scaled logit of every visible block column, averaged over the G heads of the query
-        // (neighbouring lanes), as the tensor of that dtype would hold it upstream: product, scaled logit and mean
-        // each rounded to bf16
+      if constexpr (IMP) {
+        // Compressed branch: the scaled logit of every visible block column, averaged over the G heads of the query
+        // (G neighbouring lanes), as the tensor of that dtype would hold it upstream: product, scaled logit and mean
+        // each rounded to bf16.  The G lanes reduce-scatter: every step a lane hands half of its columns to its
+        // partner and keeps the other half, so that it ends with 64/G fully summed columns, which it stores.
+        float v[64];
+#pragma unroll
+        for (int x = 0; x < 64; ++x) v[x] = round_bf16(round_bf16(s[x]) * P.scale);
+        int first = 0;   // first block column this lane ends up owning
+#pragma unroll
+        for (int step = 0; step < 4; ++step) {
+          const int width = 32 >> step;          // columns kept after this step
+          if ((1 << step) < G) {
+            const bool upper = (g >> step) & 1;  // this lane keeps the upper half
+#pragma unroll
+            for (int x = 0; x < 32; ++x) {
+              if (x < width) {
+                const float give = upper ? v[x] : v[x + width];
+                const float keep = upper ? v[x + width] : v[x];
+                v[x] = keep + __shfl_xor_sync(kFullMask, give, 1 << step);
+              }
+            }
+            first += upper ? width : 0;
+          }
+        }
+        const int owned = kBlock / G;
         float* imp_row = P.importance + (((int64_t)b * P.Hkv + h) * P.N + r.i) * P.ncb;
+        const float inv_g = 1.f / (float)G;
 #pragma unroll
         for (int x = 0; x < 64; ++x) {
-          float logit = round_bf16(round_bf16(s[x]) * P.scale);
-          for (int o = G / 2; o > 0; o >>= 1) logit += __shfl_xor_sync(kFullMask, logit, o);
-          const int col = j * kBlock + x - P.rule.num_mem;
-          if (r.valid && g == 0 && x <= r.lim && col >= 0 && col < P.ncb) imp_row[col] = round_bf16(logit / (float)G);
+          if (x < owned) {
+            const int col_in_block = first + x;
+            const int col = j * kBlock + col_in_block - P.rule.num_mem;
+            if (r.valid && col_in_block <= r.lim && col >= 0 && col < P.ncb) imp_row[col] = round_bf16(v[x] * inv_g);
+          }
         }
       }
       float m = -INFINITY;
 #pragma unroll
-      for (int x = 0; x < 64; ++x) m = (x >= r.lo && x <= r.lim) ? fmaxf(m, s[x]) : m;
+      for (int x = 0; x < 64; ++x) m = ((!LO || x >= r.lo) && x <= r.lim) ? fmaxf(m, s[x]) : m;
       const float m2 = r.valid ? m * P.scale_log2 : 0.f;
       float l = 0.f;
 #pragma unroll
       for (int x = 0; x < 64; ++x) {
-        const float p = (x >= r.lo && x <= r.lim) ? ex2(s[x] * P.scale_log2 - m2) : 0.f;
+        const float p = ((!LO || x >= r.lo) && x <= r.lim) ? ex2(s[x] * P.scale_log2 - m2) : 0.f;
         s[x] = p;
         l += p;   // the fp32 sum: the log-sum-exp stays exact although P is rounded to bf16 for the MMA
       }
@@ -516,7 +543,7 @@ sel_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 }
 
 // merges the partial results of every (batch, query head, query): one group of D/8 threads per row
-template <int D>
+template <int D, int MODE>
 __global__ void __launch_bounds__(256) sel_merge_kernel(const SelParams P) {
   constexpr int TPR = D / 8;
   const int64_t row = ((int64_t)blockIdx.x * 256 + threadIdx.x) / TPR;
@@ -532,14 +559,14 @@ __global__ void __launch_bounds__(256) sel_merge_kernel(const SelParams P) {
   float M = -INFINITY;
   for (int s = 0; s < ns; ++s) {
     int blk_;
-    const bool ok = slot_block(P.rule, b * P.Hkv + h, i, s, &blk_);
+    const bool ok = slot_block<MODE>(P.rule, b * P.Hkv + h, i, s, &blk_);
     if (ok) M = fmaxf(M, st[s].x);
   }
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   float L = 0.f;
   for (int s = 0; s < ns; ++s) {
     int blk_;
-    const bool ok = slot_block(P.rule, b * P.Hkv + h, i, s, &blk_);
+    const bool ok = slot_block<MODE>(P.rule, b * P.Hkv + h, i, s, &blk_);
     if (!ok) continue;
     const float2 ml = st[s];
     const float w = ex2(ml.x - M) * ml.y;
@@ -1297,7 +1324,7 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
 
 
 // sums the bf16 dQ partials of every (batch, query head, query) into the fp32 dq row: D/8 threads per row
-template <int D>
+template <int D, int MODE>
 __global__ void __launch_bounds__(256) sel_dq_merge_kernel(const SelParams P) {
   constexpr int TPR = D / 8;
   const int64_t row = ((int64_t)blockIdx.x * 256 + threadIdx.x) / TPR;
@@ -1312,7 +1339,7 @@ __global__ void __launch_bounds__(256) sel_dq_merge_kernel(const SelParams P) {
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   for (int s = 0; s < ns; ++s) {
     int blk_;
-    const bool ok = slot_block(P.rule, b * P.Hkv + h, i, s, &blk_);
+    const bool ok = slot_block<MODE>(P.rule, b * P.Hkv + h, i, s, &blk_);
     if (!ok) continue;
     const uint4 v = *reinterpret_cast<const uint4*>(P.partial + (row * ns + s) * D + part * 8);
     const uint32_t u[4] = {v.x, v.y, v.z, v.w};
@@ -1464,10 +1491,14 @@ static int build_index(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaS
   const BlockRule R = make_rule(a, p);
   const dim3 grid(p.nqb, a.B, a.Hkv);
   const size_t hist_smem = (size_t)p.nkb * sizeof(int);
-  sel_hist_kernel<<<grid, kBlock, hist_smem, st>>>(R, counts);
+  if (a.mode == kModeSel) sel_hist_kernel<kModeSel><<<grid, kBlock, hist_smem, st>>>(R, counts);
+  else if (a.mode == kModeSwa) sel_hist_kernel<kModeSwa><<<grid, kBlock, hist_smem, st>>>(R, counts);
+  else sel_hist_kernel<kModeCmp><<<grid, kBlock, hist_smem, st>>>(R, counts);
   sel_scan_kernel<<<(p.nlists + 127) / 128, 128, 0, st>>>(counts, totals, p.nlists, p.nqb, p.nkb);
   sel_items_kernel<<<1, 1024, 0, st>>>(totals, list_base, items, num_items, p.nlists, p.QT);
-  sel_fill_kernel<<<grid, kBlock, hist_smem, st>>>(R, counts, list_base, entries);
+  if (a.mode == kModeSel) sel_fill_kernel<kModeSel><<<grid, kBlock, hist_smem, st>>>(R, counts, list_base, entries);
+  else if (a.mode == kModeSwa) sel_fill_kernel<kModeSwa><<<grid, kBlock, hist_smem, st>>>(R, counts, list_base, entries);
+  else sel_fill_kernel<kModeCmp><<<grid, kBlock, hist_smem, st>>>(R, counts, list_base, entries);
   CUDA_TRY(cudaGetLastError());
   return NSA_OK;
 }
@@ -1516,10 +1547,21 @@ static int run_fwd(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaStrea
   constexpr int NC = D / 64;
   const int smem = 1024 + NC * (16384 + 8192 + 8192) + kRows * (D * 2 + 16);
   const int per_sm = D == 64 ? 4 : 2;
-  CUDA_TRY(cudaFuncSetAttribute(sel_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  sel_fwd_kernel<D><<<num_sms() * per_sm, kRows, smem, st>>>(tmK, tmV, P);
+  if (P.importance != nullptr) {
+    CUDA_TRY(cudaFuncSetAttribute(sel_fwd_kernel<D, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    sel_fwd_kernel<D, true, false><<<num_sms() * per_sm, kRows, smem, st>>>(tmK, tmV, P);
+  } else if (a.mode == kModeSwa) {
+    CUDA_TRY(cudaFuncSetAttribute(sel_fwd_kernel<D, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    sel_fwd_kernel<D, false, true><<<num_sms() * per_sm, kRows, smem, st>>>(tmK, tmV, P);
+  } else {
+    CUDA_TRY(cudaFuncSetAttribute(sel_fwd_kernel<D, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    sel_fwd_kernel<D, false, false><<<num_sms() * per_sm, kRows, smem, st>>>(tmK, tmV, P);
+  }
   const int64_t threads = (int64_t)a.B * a.Hq * a.N * (D / 8);
-  sel_merge_kernel<D><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(P);
+  const unsigned mblocks = (unsigned)((threads + 255) / 256);
+  if (a.mode == kModeSel) sel_merge_kernel<D, kModeSel><<<mblocks, 256, 0, st>>>(P);
+  else if (a.mode == kModeSwa) sel_merge_kernel<D, kModeSwa><<<mblocks, 256, 0, st>>>(P);
+  else sel_merge_kernel<D, kModeCmp><<<mblocks, 256, 0, st>>>(P);
   CUDA_TRY(cudaGetLastError());
   return NSA_OK;
 }
@@ -1547,7 +1589,10 @@ static int run_bwd(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaStrea
     CUDA_TRY(cudaFuncSetAttribute(sel_bwd_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     P.partial = reinterpret_cast<__nv_bfloat16*>(ws + p.off_partial);
     sel_bwd_ws_kernel<<<num_sms(), ws::kThreads, smem, st>>>(tmK, tmV, P);
-    sel_dq_merge_kernel<64><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(P);
+    const unsigned mblocks = (unsigned)((threads + 255) / 256);
+    if (a.mode == kModeSel) sel_dq_merge_kernel<64, kModeSel><<<mblocks, 256, 0, st>>>(P);
+    else if (a.mode == kModeSwa) sel_dq_merge_kernel<64, kModeSwa><<<mblocks, 256, 0, st>>>(P);
+    else sel_dq_merge_kernel<64, kModeCmp><<<mblocks, 256, 0, st>>>(P);
     CUDA_TRY(cudaGetLastError());
     return NSA_OK;
   }
