@@ -44,6 +44,15 @@ WORKLOADS = {
 DEFAULT_WORKLOAD = 'sel_fwd_bwd_b4_n8192_h32kv4_d64_blk64_top16'
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the main backward kernel, from an ncu capture of this
+# command (profiles/tcgen05_selected_attention_b4_n8192_h32kv4_d64.md, profiles/simt_selected_attention_...md).
+NCU_TRAFFIC = {
+    (DEFAULT_WORKLOAD, 'auto'): 602.3e6 + 2188.4e6,
+    (DEFAULT_WORKLOAD, 'sm100'): 602.3e6 + 2188.4e6,
+    (DEFAULT_WORKLOAD, 'simt'): 531.8e6 + 300.4e6,
+}
+
+
 def make_inputs(w, seed, dtype=torch.bfloat16):
     """Seeded host tensors: q,k,v,do ~ N(0,1); block scores ~ N(0,1) with the own and future
     blocks excluded; the top `nsel` scores give the selected blocks, slots with no valid block are masked."""
@@ -294,7 +303,7 @@ def main():
         'tensor_frac_fwd_bwd': (f_fwd + f_bwd) / (ms_per_step / 1e3) / 1e12 / burst,
         'roofline': {'bound': 'tensor', 'kernel': 'selected-block backward', 'achieved': achieved, 'peak': burst,
                      'unit': 'TFLOP/s', 'frac': achieved / burst, 'peak_source': src, 'peak_sustained': sustained,
-                     'flops_per_launch': f_bwd, 'traffic': None},
+                     'flops_per_launch': f_bwd, 'traffic': NCU_TRAFFIC.get((args.workload, args.kernels))},
         'e2e': {'value': tokens_per_step / (e2e_ms / e2e_steps / 1e3), 'unit': 'tokens/s',
                 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h, 'steps': e2e_steps},
         'gpu_launches': None,
