@@ -256,21 +256,42 @@ def main():
     bwd_ms = [e[1].elapsed_time(e[2]) for e in events]
     total_ms = sum(fwd_ms) + sum(bwd_ms)
 
-    # end to end: pinned host buffers in, results back to the host, every step
+    # end to end: every step copies its inputs from pinned host buffers and its results (out, dq, dk, dv) back to
+    # the host.  The copies run on their own streams, double buffered, so that step i+1's inputs travel while step i
+    # computes and step i-1's results travel back; every step's copies are inside the timed region.
     h_out = [torch.empty_like(t).pin_memory() for t in (host[0], host[0], host[1], host[2])]
-    def e2e_step():
-        dev_in = [t.to(dev, non_blocking=True) for t in pinned]
-        out, grads = step(*dev_in)
-        for dst, src in zip(h_out, (out, *grads)):
-            dst.copy_(src, non_blocking=True)
-    for _ in range(2):
-        e2e_step()
+    s_in, s_out, s_main = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
+    dev_in = [[torch.empty_like(t, device=dev) for t in host] for _ in range(2)]
+    in_ready = [torch.cuda.Event() for _ in range(2)]
+    in_free = [torch.cuda.Event() for _ in range(2)]
+
+    def e2e_run(steps):
+        for i in range(steps):
+            b = i & 1
+            with torch.cuda.stream(s_in):
+                if i >= 2:
+                    s_in.wait_event(in_free[b])
+                for d, src in zip(dev_in[b], pinned):
+                    d.copy_(src, non_blocking=True)
+                in_ready[b].record(s_in)
+            s_main.wait_event(in_ready[b])
+            out, grads = step(*dev_in[b])
+            in_free[b].record(s_main)
+            done = torch.cuda.Event()
+            done.record(s_main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                for dst, src in zip(h_out, (out, *grads)):
+                    dst.copy_(src, non_blocking=True)
+                    src.record_stream(s_out)
+        s_main.wait_stream(s_out)
+
+    e2e_run(2)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e2e_steps = max(3, min(args.steps, 10))
     e0.record()
-    for _ in range(e2e_steps):
-        e2e_step()
+    e2e_run(e2e_steps)
     e1.record()
     torch.cuda.synchronize()
     e2e_ms = e0.elapsed_time(e1)

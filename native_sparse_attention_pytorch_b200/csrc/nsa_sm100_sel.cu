@@ -542,8 +542,11 @@ sel_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   if (tid == 0 && abort_flag) atomicExch(P.status, 1);
 }
 
-// merges the partial results of every (batch, query head, query): one group of D/8 threads per row
-template <int D, int MODE>
+// merges the partial results of every (batch, query head, query): one group of D/8 threads per row.
+// The statistics were cleared before the forward kernel ran, so a slot the query does not have reads (0, 0) and needs
+// no look-up in the index; its partial row was never written and is not read.  Loads are issued eight slots at a time
+// with nothing depending on them in between: the kernel is a stream over the partial buffer.
+template <int D>
 __global__ void __launch_bounds__(256) sel_merge_kernel(const SelParams P) {
   constexpr int TPR = D / 8;
   const int64_t row = ((int64_t)blockIdx.x * 256 + threadIdx.x) / TPR;
@@ -553,30 +556,37 @@ __global__ void __launch_bounds__(256) sel_merge_kernel(const SelParams P) {
   const int i = (int)(row % P.N);
   const int hq = (int)((row / P.N) % P.Hq);
   const int b = (int)(row / ((int64_t)P.N * P.Hq));
-  const int h = hq / P.G;
   const int ns = P.ns;
   const float2* st = P.stats + row * ns;
+  const __nv_bfloat16* prow = P.partial + row * ns * D + part * 8;
   float M = -INFINITY;
+#pragma unroll 4
   for (int s = 0; s < ns; ++s) {
-    int blk_;
-    const bool ok = slot_block<MODE>(P.rule, b * P.Hkv + h, i, s, &blk_);
-    if (ok) M = fmaxf(M, st[s].x);
+    const float2 ml = st[s];
+    if (ml.y > 0.f) M = fmaxf(M, ml.x);
   }
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   float L = 0.f;
-  for (int s = 0; s < ns; ++s) {
-    int blk_;
-    const bool ok = slot_block<MODE>(P.rule, b * P.Hkv + h, i, s, &blk_);
-    if (!ok) continue;
-    const float2 ml = st[s];
-    const float w = ex2(ml.x - M) * ml.y;
-    L += w;
-    const uint4 v = *reinterpret_cast<const uint4*>(P.partial + (row * ns + s) * D + part * 8);
-    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+  for (int s0 = 0; s0 < ns; s0 += 8) {
+    float w[8];
+    uint4 v[8];
 #pragma unroll
-    for (int x = 0; x < 4; ++x) {
-      acc[2 * x] = fmaf(w, __uint_as_float(u[x] << 16), acc[2 * x]);
-      acc[2 * x + 1] = fmaf(w, __uint_as_float(u[x] & 0xffff0000u), acc[2 * x + 1]);
+    for (int u = 0; u < 8; ++u) {
+      const bool in = s0 + u < ns;
+      const float2 ml = in ? st[s0 + u] : make_float2(0.f, 0.f);
+      const bool ok = ml.y > 0.f;
+      w[u] = ok ? ex2(ml.x - M) * ml.y : 0.f;
+      v[u] = ok ? *reinterpret_cast<const uint4*>(prow + (int64_t)(s0 + u) * D) : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      L += w[u];
+      const uint32_t q[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        acc[2 * x] = fmaf(w[u], __uint_as_float(q[x] << 16), acc[2 * x]);
+        acc[2 * x + 1] = fmaf(w[u], __uint_as_float(q[x] & 0xffff0000u), acc[2 * x + 1]);
+      }
     }
   }
   const float inv = L > 0.f ? 1.f / L : 0.f;
@@ -1337,16 +1347,27 @@ __global__ void __launch_bounds__(256) sel_dq_merge_kernel(const SelParams P) {
   const int h = hq / P.G;
   const int ns = P.ns;
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  for (int s = 0; s < ns; ++s) {
-    int blk_;
-    const bool ok = slot_block<MODE>(P.rule, b * P.Hkv + h, i, s, &blk_);
-    if (!ok) continue;
-    const uint4 v = *reinterpret_cast<const uint4*>(P.partial + (row * ns + s) * D + part * 8);
-    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+  const __nv_bfloat16* prow = P.partial + row * ns * D + part * 8;
+  // eight slots at a time: first which of them the query has, then their loads together, then the sums
+  for (int s0 = 0; s0 < ns; s0 += 8) {
+    bool ok[8];
+    uint4 v[8];
 #pragma unroll
-    for (int x = 0; x < 4; ++x) {
-      acc[2 * x] += __uint_as_float(u[x] << 16);
-      acc[2 * x + 1] += __uint_as_float(u[x] & 0xffff0000u);
+    for (int u = 0; u < 8; ++u) {
+      int blk_;
+      ok[u] = s0 + u < ns && slot_block<MODE>(P.rule, b * P.Hkv + h, i, s0 + u, &blk_);
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      v[u] = ok[u] ? *reinterpret_cast<const uint4*>(prow + (int64_t)(s0 + u) * D) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const uint32_t q[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        acc[2 * x] += __uint_as_float(q[x] << 16);
+        acc[2 * x + 1] += __uint_as_float(q[x] & 0xffff0000u);
+      }
     }
   }
   float4* dst = reinterpret_cast<float4*>(P.dq + row * D + part * 8);
@@ -1544,6 +1565,8 @@ static int run_fwd(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaStrea
   fill_params(P, a, p, ws);
   P.partial = reinterpret_cast<__nv_bfloat16*>(ws + p.off_partial);
   P.stats = reinterpret_cast<float2*>(ws + p.off_stats);
+  // a slot that no list holds keeps (0, 0): the merge reads the statistics of every slot and skips those
+  CUDA_TRY(cudaMemsetAsync(P.stats, 0, (size_t)a.B * a.Hq * a.N * p.ns * sizeof(float2), st));
   constexpr int NC = D / 64;
   const int smem = 1024 + NC * (16384 + 8192 + 8192) + kRows * (D * 2 + 16);
   const int per_sm = D == 64 ? 4 : 2;
@@ -1559,9 +1582,7 @@ static int run_fwd(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaStrea
   }
   const int64_t threads = (int64_t)a.B * a.Hq * a.N * (D / 8);
   const unsigned mblocks = (unsigned)((threads + 255) / 256);
-  if (a.mode == kModeSel) sel_merge_kernel<D, kModeSel><<<mblocks, 256, 0, st>>>(P);
-  else if (a.mode == kModeSwa) sel_merge_kernel<D, kModeSwa><<<mblocks, 256, 0, st>>>(P);
-  else sel_merge_kernel<D, kModeCmp><<<mblocks, 256, 0, st>>>(P);
+  sel_merge_kernel<D><<<mblocks, 256, 0, st>>>(P);
   CUDA_TRY(cudaGetLastError());
   return NSA_OK;
 }
