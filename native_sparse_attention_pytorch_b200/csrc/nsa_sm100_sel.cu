@@ -872,7 +872,9 @@ sel_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 //   warp 13         one thread requests the K/V tiles of each item by TMA (double buffered).  It is a role of its
 //                   own because it waits for the consumer: a gathering thread that did so would hold back the
 //                   announcements the consumer is waiting for.
-// Tensor memory (512 columns): two S/dP/dQ buffers of 128 columns, two dK/dV accumulators of 128 columns.
+// Tensor memory (512 columns): per softmax group S, dP and dQ (64 columns each), then dK and dV (64 each).  dQ has
+// columns of its own so that a group can go on to the S/dP of its next chunk and read dQ of the previous one out
+// afterwards, while the tensor cores are busy with the other group's chunk.
 // Every hand-over is an mbarrier; every wait is bounded.
 #ifdef NSA_PHASE_TIMING
 __device__ long long g_trace[4][64][8];
@@ -889,8 +891,8 @@ constexpr int kLoaderThreads = 128;
 
 struct Bars {
   uint64_t q_full[kStages], q_free[kStages];
-  uint64_t s_full[2], p_full[2], mma2_done[2], t_free[2];
-  uint64_t kv_full[2], kv_free[2], acc_full[2], acc_free[2];
+  uint64_t s_full[2], p_full[2], mma2_done[2], dq_free[2];
+  uint64_t kv_full[2], kv_free[2], acc_full, acc_free;
   uint64_t drain;
 };
 }  // namespace ws
@@ -921,12 +923,12 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
       mbar_init(smem_u32(&bars.s_full[i]), 1);
       mbar_init(smem_u32(&bars.p_full[i]), kRows);
       mbar_init(smem_u32(&bars.mma2_done[i]), 1);
-      mbar_init(smem_u32(&bars.t_free[i]), kRows);
+      mbar_init(smem_u32(&bars.dq_free[i]), kRows);
       mbar_init(smem_u32(&bars.kv_full[i]), 1);
       mbar_init(smem_u32(&bars.kv_free[i]), 1);
-      mbar_init(smem_u32(&bars.acc_full[i]), 1);
-      mbar_init(smem_u32(&bars.acc_free[i]), kRows);
     }
+    mbar_init(smem_u32(&bars.acc_full), 1);
+    mbar_init(smem_u32(&bars.acc_free), kRows);
     mbar_init(smem_u32(&bars.drain), 1);
     fence_mbar_init();
     prefetch_tensormap(&tmK);
@@ -949,16 +951,47 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     const uint32_t tm_lane = tm + ((uint32_t)((warp & 3) * 32) << 16);
     const int q_local = r_tid >> g_shift, g = r_tid - (q_local << g_shift);
     WT_DECL
+    const uint32_t tS = wg * 192, tDP = tS + 64, tDQ = tS + 128;
+    const uint32_t sP = sP0 + wg * kPBytes, sDS = sP + 16384;
+    // dQ row of the group's previous chunk, still to be read out of tensor memory
+    uint4* prev_row = nullptr;
+    bool prev_valid = false, have_prev = false;
+    uint32_t prev_use = 0;
+    // The dQ row goes out as the bf16 partial result of (row, slot), straight from registers.  Partials are summed by
+    // sel_dq_merge_kernel: plain stores run at memory speed, whereas fp32 reductions into dq are limited by the L2
+    // atomic units.
+    auto dq_out = [&]() {
+      WT(1, mbar_wait_warp(smem_u32(&bars.mma2_done[wg]), prev_use & 1, &abort_flag))
+      tc_fence_after_sync();
+      __syncwarp();
+#pragma unroll 1
+      for (int c2 = 0; c2 < D / 16; ++c2) {
+        float tq[16];
+        tmem_ld16(tm_lane + tDQ + c2 * 16, tq);
+        tmem_ld_wait();
+        if (prev_valid) {
+#pragma unroll
+          for (int x = 0; x < 2; ++x) {
+            uint4 v;
+            v.x = pack_bf16(tq[x * 8 + 0], tq[x * 8 + 1]); v.y = pack_bf16(tq[x * 8 + 2], tq[x * 8 + 3]);
+            v.z = pack_bf16(tq[x * 8 + 4], tq[x * 8 + 5]); v.w = pack_bf16(tq[x * 8 + 6], tq[x * 8 + 7]);
+            prev_row[c2 * 2 + x] = v;
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(&bars.dq_free[wg]));   // the dQ columns of this group may be overwritten
+      have_prev = false;
+    };
     // one chunk of this group; the thread's entry and its row's statistics come from the stage's metadata, which
     // the loaders fetched together with the rows
     auto process_chunk = [&](const int4 item, const int n) {
       {
         const int list = item.x, j = list % P.nfb, bh = list / P.nfb, h = bh % P.Hkv, b = bh / P.Hkv;
-        const int buf = n & 1;
-        const uint32_t use = (uint32_t)(n >> 1);   // how many times this buffer has been used before
+        const uint32_t use = (uint32_t)(n >> 1);   // how many chunks this group has had before
         const uint32_t sMeta = sMeta0 + (n % kStages) * kMetaBytes + r_tid * 4;
         if (r_tid == 0) TR(wg, n, 0)
-        WT(0, mbar_wait_warp(smem_u32(&bars.s_full[buf]), use & 1, &abort_flag))
+        WT(0, mbar_wait_warp(smem_u32(&bars.s_full[wg]), use & 1, &abort_flag))
         if (r_tid == 0) TR(wg, n, 1)
         tc_fence_after_sync();
         const uint32_t e = lds_u32(sMeta);
@@ -967,8 +1000,6 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         const RowInfo r = decode_row(e, j, P.rule);
         const int64_t hq = (int64_t)h * G + g;
         const int64_t row_global = ((int64_t)b * P.Hq + hq) * P.N + r.i;
-        const uint32_t tS = buf * 128, tDP = buf * 128 + 64, tDQ = buf * 128;
-        const uint32_t sP = sP0 + buf * kPBytes, sDS = sP + 16384;
 #ifdef NSA_PHASE_TIMING
         const long long tc0_ = clock64();
 #endif
@@ -1033,46 +1064,24 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         }
         fence_proxy_async_smem();
         tc_fence_before_sync();
-        mbar_arrive(smem_u32(&bars.p_full[buf]));
+        mbar_arrive(smem_u32(&bars.p_full[wg]));
         if (r_tid == 0) TR(wg, n, 2)
         if (P.slot_grads != nullptr) {
           for (int o = G / 2; o > 0; o >>= 1) slot_part += __shfl_xor_sync(kFullMask, slot_part, o);
           if (r.valid && g == 0 && r.slot < P.nsel)
             P.slot_grads[(((int64_t)b * P.Hkv + h) * P.N + r.i) * P.nsel + r.slot] = slot_part * P.scale;
         }
-
 #ifdef NSA_PHASE_TIMING
         wt_[2] += clock64() - tc0_;
-#endif
-        WT(1, mbar_wait_warp(smem_u32(&bars.mma2_done[buf]), use & 1, &abort_flag))
-        if (r_tid == 0) TR(wg, n, 3)
-        tc_fence_after_sync();
-        __syncwarp();
-#ifdef NSA_PHASE_TIMING
         const long long tc1_ = clock64();
 #endif
-        // The dQ row goes out as the bf16 partial result of (row, slot), straight from registers (the P/dS tiles are
-        // still being read by the dV/dK MMAs).  Partials are summed by sel_dq_merge_kernel: plain stores run at
-        // memory speed, whereas fp32 reductions into dq are limited by the L2 atomic units.
-        uint4* part_row = reinterpret_cast<uint4*>(P.partial + (row_global * P.ns + r.slot) * D);
-#pragma unroll 1
-        for (int c2 = 0; c2 < D / 16; ++c2) {
-          float tq[16];
-          tmem_ld16(tm_lane + tDQ + c2 * 16, tq);
-          tmem_ld_wait();
-          if (r.valid) {
-#pragma unroll
-            for (int x = 0; x < 2; ++x) {
-              uint4 v;
-              v.x = pack_bf16(tq[x * 8 + 0], tq[x * 8 + 1]); v.y = pack_bf16(tq[x * 8 + 2], tq[x * 8 + 3]);
-              v.z = pack_bf16(tq[x * 8 + 4], tq[x * 8 + 5]); v.w = pack_bf16(tq[x * 8 + 6], tq[x * 8 + 7]);
-              part_row[c2 * 2 + x] = v;
-            }
-          }
-        }
-        tc_fence_before_sync();
-        mbar_arrive(smem_u32(&bars.t_free[buf]));   // tensor memory of this buffer is free again
+        // while the tensor cores work on this chunk's P and dS, read out dQ of the previous chunk of the group
+        if (have_prev) dq_out();
         if (r_tid == 0) TR(wg, n, 4)
+        prev_row = reinterpret_cast<uint4*>(P.partial + (row_global * P.ns + r.slot) * D);
+        prev_valid = r.valid;
+        prev_use = use;
+        have_prev = true;
 #ifdef NSA_PHASE_TIMING
         wt_[3] += clock64() - tc1_;
 #endif
@@ -1082,16 +1091,14 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
       const int list = item.x, j = list % P.nfb, bh = list / P.nfb, h = bh % P.Hkv, b = bh / P.Hkv;
       {
         // flush dK/dV of this item: accumulator rows 16w..16w+15 live in lanes 0..15 of warp w of the group
-        const int ab = t & 1;
-        const uint32_t use = (uint32_t)(t >> 1);
-        mbar_wait_warp(smem_u32(&bars.acc_full[ab]), use & 1, &abort_flag);
+        mbar_wait_warp(smem_u32(&bars.acc_full), (uint32_t)t & 1, &abort_flag);
         tc_fence_after_sync();
         __syncwarp();
         const int key = j * kBlock + (warp & 3) * 16 + lane;
         const bool ok = lane < 16 && key < P.Nk;
         float* dkp = P.dk + (((int64_t)b * P.Hkv + h) * P.Nk + key) * D;
         float* dvp = P.dv + (((int64_t)b * P.Hkv + h) * P.Nk + key) * D;
-        const uint32_t tDK = 256 + ab * 128, tDV = tDK + 64;
+        const uint32_t tDK = 384, tDV = 448;
 #pragma unroll
         for (int c2 = 0; c2 < D / 32; ++c2) {
           float tk[32];
@@ -1110,42 +1117,29 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
           }
         }
         tc_fence_before_sync();
-        mbar_arrive(smem_u32(&bars.acc_free[ab]));
+        mbar_arrive(smem_u32(&bars.acc_free));
       }
     };
-    // dK/dV of item t are flushed by group t % 2, one own chunk late, so that the group does not sit waiting for the
-    // item's last MMAs while it has work
-    int n = 0, t = 0, own_chunks = 0, pend_t = -1;
-    int4 pend_item = make_int4(0, 0, 0, 0);
+    // dK/dV of an item are flushed by the group that had the item's last chunk, as soon as the tensor cores are done
+    // with it: the next item's dV/dK MMAs wait for the accumulator
+    int n = 0, t = 0, own_chunks = 0;
     for (int it = blockIdx.x; it < nitems; it += gridDim.x, ++t) {
       const int4 item = P.items[it];
       for (int c = 0; c < item.z; ++c, ++n) {
         if ((n & 1) != wg) continue;
-        if (pend_t >= 0 && t >= pend_t + 2) {   // this item reuses the pending accumulator: it must be free first
-          WT(4, flush_item(pend_item, pend_t))
-          pend_t = -1;
-        }
         if (r_tid == 0) TR(wg, n, 6)
         WT(5, process_chunk(item, n))
         if (r_tid == 0) TR(wg, n, 5)
         ++own_chunks;
-        if (pend_t >= 0) {
-          WT(4, flush_item(pend_item, pend_t))
-          pend_t = -1;
-        }
-      }
-      if ((t & 1) == wg) {
-        if (pend_t >= 0) flush_item(pend_item, pend_t);
-        pend_t = t;
-        pend_item = item;
+        if (c == item.z - 1) WT(4, flush_item(item, t))
       }
     }
-    if (pend_t >= 0) flush_item(pend_item, pend_t);
+    if (have_prev) dq_out();
     WT_REPORT("softmax: w0 s_full, w1 mma2_done, w2 math, w3 dq out, w4 flush, w5 whole chunk, w6 group barrier;", blockIdx.x == 0 && r_tid == 0, own_chunks)
   } else if (warp == 8) {
-    // ------------------------------------------------------------------ MMA issuer (one thread; the other lanes
-    // of the warp go straight to the final barrier and take no issue slots)
-    if (lane == 0) {
+    // ------------------------------------------------------------------ MMA issuer: the whole warp runs the loop
+    // (so that its state lives in uniform registers), one elected lane issues
+    {
     constexpr uint32_t idS = instr_desc_bf16(128, 64, false, false);
     constexpr uint32_t idDQ = instr_desc_bf16(128, D, false, true);
     constexpr uint32_t idKV = instr_desc_bf16(64, D, true, true);
@@ -1156,74 +1150,80 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     int p_n = 0, p_t = 0, p_c = 0;
     bool p_last = false;
     auto issue_mma2 = [&](int pn, int pt, int pc, bool last) {
-      const int buf = pn & 1, stage = pn % kStages, kb = pt & 1, ab = pt & 1;
+      const int grp = pn & 1, stage = pn % kStages, kb = pt & 1;
       const uint32_t sQ = sQ0 + stage * 32768, sDO = sQ + 16384;
-      const uint32_t sP = sP0 + buf * kPBytes, sDS = sP + 16384;
+      const uint32_t sP = sP0 + grp * kPBytes, sDS = sP + 16384;
       const uint32_t sK = sKV0 + kb * 16384;
-      WT(3, mbar_wait_bounded(smem_u32(&bars.p_full[buf]), (uint32_t)(pn >> 1) & 1, &abort_flag))
+      WT(3, mbar_wait_bounded(smem_u32(&bars.p_full[grp]), (uint32_t)(pn >> 1) & 1, &abort_flag))
       if (lane == 0) TR(2, pn, 2)
-      if (pc == 0 && pt >= 2) WT(4, mbar_wait_bounded(smem_u32(&bars.acc_free[ab]), (uint32_t)((pt >> 1) - 1) & 1, &abort_flag))
+      // the accumulators are single: the first chunk of an item waits until the previous item has been flushed
+      if (pc == 0 && pt >= 1) WT(4, mbar_wait_bounded(smem_u32(&bars.acc_free), (uint32_t)(pt - 1) & 1, &abort_flag))
+      __syncwarp();
       tc_fence_after_sync();
-      if (lane == 0) {
-        const uint32_t tDK = 256 + ab * 128, tDV = tDK + 64, tDQ = buf * 128;
-        // One descriptor per tile (the leading-offset field is unused for 64-wide tiles, so the same descriptor
-        // serves the K-major and the MN-major reading of a tile); every MMA then costs one 64-bit add to issue.
-        const uint64_t dQt = smem_desc_sw128(sQ, 16), dDOt = smem_desc_sw128(sDO, 16), dPt = smem_desc_sw128(sP, 16),
-                       dDSt = smem_desc_sw128(sDS, 16), dKt = smem_desc_sw128(sK, 16);
-        // dQ first, and its own commit: the softmax group can read it out while dV and dK are still being computed.
-        // (Measured: a small MMA costs about 50 cycles to issue whatever its shape, so the count matters, not the
-        // order; interleaving the accumulation chains brought nothing.)
+      const uint32_t tDK = 384, tDV = 448, tDQ = grp * 192 + 128;
+      // One descriptor per tile (the leading-offset field is unused for 64-wide tiles, so the same descriptor
+      // serves the K-major and the MN-major reading of a tile); every MMA then costs one 64-bit add to issue.
+      const uint64_t dQt = smem_desc_sw128(sQ, 16), dDOt = smem_desc_sw128(sDO, 16), dPt = smem_desc_sw128(sP, 16),
+                     dDSt = smem_desc_sw128(sDS, 16), dKt = smem_desc_sw128(sK, 16);
+      // dV and dK first: the group reads dQ of its previous chunk out right after it has handed P and dS over, and
+      // is done with it by the time these sixteen MMAs have been issued.
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          mma_bf16(tm + tDQ, desc_advance(dDSt, k * 32), desc_advance(dKt, k * 2048), idDQ, k > 0);
-        mma_commit(smem_u32(&bars.mma2_done[buf]));
+      for (int k = 0; k < 8; ++k)
+        mma_bf16_elect(tm + tDV, desc_advance(dPt, k * 2048), desc_advance(dDOt, k * 2048), idKV, pc > 0 || k > 0);
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          mma_bf16(tm + tDV, desc_advance(dPt, k * 2048), desc_advance(dDOt, k * 2048), idKV, pc > 0 || k > 0);
+      for (int k = 0; k < 8; ++k)
+        mma_bf16_elect(tm + tDK, desc_advance(dDSt, k * 2048), desc_advance(dQt, k * 2048), idKV, pc > 0 || k > 0);
+      if (pn >= 2) {
+        WT(1, mbar_wait_bounded(smem_u32(&bars.dq_free[grp]), (uint32_t)((pn >> 1) - 1) & 1, &abort_flag))
+        __syncwarp();
+        tc_fence_after_sync();
+      }
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          mma_bf16(tm + tDK, desc_advance(dDSt, k * 2048), desc_advance(dQt, k * 2048), idKV, pc > 0 || k > 0);
-        mma_commit(smem_u32(&bars.q_free[stage]));
-        TR(2, pn, 3)
-        if (last) {
-          mma_commit(smem_u32(&bars.kv_free[kb]));
-          mma_commit(smem_u32(&bars.acc_full[ab]));
-        }
+      for (int k = 0; k < 4; ++k)
+        mma_bf16_elect(tm + tDQ, desc_advance(dDSt, k * 32), desc_advance(dKt, k * 2048), idDQ, k > 0);
+      mma_commit_elect(smem_u32(&bars.mma2_done[grp]));
+      mma_commit_elect(smem_u32(&bars.q_free[stage]));
+      if (lane == 0) TR(2, pn, 3)
+      if (last) {
+        mma_commit_elect(smem_u32(&bars.kv_free[kb]));
+        mma_commit_elect(smem_u32(&bars.acc_full));
       }
     };
     for (int it = blockIdx.x; it < nitems; it += gridDim.x, ++t) {
       const int4 item = P.items[it];
       const int kb = t & 1;
       for (int c = 0; c < item.z; ++c, ++n) {
-        const int buf = n & 1, stage = n % kStages;
+        const int grp = n & 1, stage = n % kStages;
         const uint32_t sQ = sQ0 + stage * 32768, sDO = sQ + 16384;
         const uint32_t sK = sKV0 + kb * 16384, sV = sK + 8192;
         if (lane == 0) TR(2, n, 0)
         WT(0, mbar_wait_bounded(smem_u32(&bars.q_full[stage]), (uint32_t)(n / kStages) & 1, &abort_flag))
         if (lane == 0) TR(2, n, 4)
-        if (n >= 2) WT(1, mbar_wait_bounded(smem_u32(&bars.t_free[buf]), (uint32_t)((n >> 1) - 1) & 1, &abort_flag))
         if (c == 0) WT(2, mbar_wait_bounded(smem_u32(&bars.kv_full[kb]), (uint32_t)(t >> 1) & 1, &abort_flag))
+        __syncwarp();
         tc_fence_after_sync();
-        if (lane == 0) {
-          const uint32_t tS = buf * 128, tDP = tS + 64;
+        {
+          // S and dP of the group are free: the group handed P and dS of its previous chunk over (waited for in
+          // issue_mma2 of that chunk, which ran before this point) only after reading them
+          const uint32_t tS = grp * 192, tDP = tS + 64;
           const uint64_t dQt = smem_desc_sw128(sQ, 16), dDOt = smem_desc_sw128(sDO, 16), dKt = smem_desc_sw128(sK, 16),
                          dVt = smem_desc_sw128(sV, 16);
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            mma_bf16(tm + tS, desc_advance(dQt, k * 32), desc_advance(dKt, k * 32), idS, k > 0);
-            mma_bf16(tm + tDP, desc_advance(dDOt, k * 32), desc_advance(dVt, k * 32), idS, k > 0);
+            mma_bf16_elect(tm + tS, desc_advance(dQt, k * 32), desc_advance(dKt, k * 32), idS, k > 0);
+            mma_bf16_elect(tm + tDP, desc_advance(dDOt, k * 32), desc_advance(dVt, k * 32), idS, k > 0);
           }
-          mma_commit(smem_u32(&bars.s_full[buf]));
-          TR(2, n, 1)
+          mma_commit_elect(smem_u32(&bars.s_full[grp]));
+          if (lane == 0) TR(2, n, 1)
         }
-          if (pending) issue_mma2(p_n, p_t, p_c, p_last);
+        if (pending) issue_mma2(p_n, p_t, p_c, p_last);
         pending = true;
         p_n = n; p_t = t; p_c = c; p_last = (c == item.z - 1);
       }
     }
     if (pending) issue_mma2(p_n, p_t, p_c, p_last);
     // nothing of this block may still be running on the tensor cores when tensor memory is freed
-    if (lane == 0) mma_commit(smem_u32(&bars.drain));
+    mma_commit_elect(smem_u32(&bars.drain));
     mbar_wait_drain(smem_u32(&bars.drain), 0);
     WT_REPORT("mma: w0 q_full, w1 t_free, w2 kv_full, w3 p_full, w4 acc_free;", blockIdx.x == 0 && lane == 0, n)
     }
