@@ -11,13 +11,14 @@
 // MMAs against the resident tiles:
 //
 //   forward : S = Q K^T -> per-row softmax of that block -> O_part = P V.
-//             Every (row, slot) writes a normalised partial output and its
-//             (max, sum); a second kernel merges the <= nsel+1 partials of a
-//             row into the output and the log-sum-exp.
+//             Every (row, slot) writes its partial output (sum of p v, bf16)
+//             and its (max, sum); a second kernel merges the partials of a row
+//             into the output and the log-sum-exp.
 //   backward: S = Q K^T and dP = dO V^T -> P = exp(S - lse), dS = P (dP - delta)
 //             -> dV += P^T dO and dK += dS^T Q stay in tensor memory across the
 //             chunks of the item (flushed once with fp32 reductions), and
-//             dQ_chunk = dS K is reduced into dq row by row.
+//             dQ_chunk = dS K goes out as a bf16 partial per (row, slot) that a
+//             last kernel sums into dq.
 //
 // All operand tiles are [rows x 64 columns] bf16 with 128-byte rows and the
 // 128-byte swizzle, which serves both as a K-major and as an MN-major operand.
@@ -409,18 +410,19 @@ sel_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       cp_async_wait<0>();
       fence_proxy_async_smem();
       __syncthreads();
-      if (tid == 0) {
+      if (warp == 0) {   // the whole warp runs the issue code, one elected lane issues
         if (c == 0) {
           mbar_wait_bounded(bar_kv, ph_kv, &abort_flag);
+          __syncwarp();
         }
         tc_fence_after_sync();
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t ch = k / 4, in = (k % 4) * 32;
-          mma_bf16(tm + tS, smem_desc_sw128(sQ + ch * 16384 + in, 16), smem_desc_sw128(sK + ch * 8192 + in, 16), idS,
-                   k > 0);
+          mma_bf16_elect(tm + tS, smem_desc_sw128(sQ + ch * 16384 + in, 16), smem_desc_sw128(sK + ch * 8192 + in, 16),
+                         idS, k > 0);
         }
-        mma_commit(bar_s);
+        mma_commit_elect(bar_s);
       }
       __syncwarp();
       mbar_wait_warp(bar_s, ph_s, &abort_flag);
@@ -496,12 +498,12 @@ sel_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       fence_proxy_async_smem();
       tc_fence_before_sync();
       __syncthreads();
-      if (tid == 0) {
+      if (warp == 0) {
         tc_fence_after_sync();
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          mma_bf16(tm + tO, smem_desc_sw128(sP + k * 32, 16), smem_desc_sw128(sV + k * 2048, 8192), idO, k > 0);
-        mma_commit(bar_o);
+          mma_bf16_elect(tm + tO, smem_desc_sw128(sP + k * 32, 16), smem_desc_sw128(sV + k * 2048, 8192), idO, k > 0);
+        mma_commit_elect(bar_o);
       }
       __syncwarp();
       mbar_wait_warp(bar_o, ph_o, &abort_flag);
@@ -510,7 +512,7 @@ sel_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       __syncwarp();
       const int64_t row_global = ((int64_t)b * P.Hq + hq) * P.N + r.i;
       const int64_t pslot = r.valid ? row_global * P.ns + r.slot : 0;
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+      // the partial row stays unnormalised (sum of p * v, at most 64 max|v|): the merge divides once per row
 #pragma unroll
       for (int c2 = 0; c2 < D / 32; ++c2) {
         float t[32];
@@ -519,10 +521,10 @@ sel_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
           uint4 v;
-          v.x = pack_bf16(t[x * 8 + 0] * inv, t[x * 8 + 1] * inv);
-          v.y = pack_bf16(t[x * 8 + 2] * inv, t[x * 8 + 3] * inv);
-          v.z = pack_bf16(t[x * 8 + 4] * inv, t[x * 8 + 5] * inv);
-          v.w = pack_bf16(t[x * 8 + 6] * inv, t[x * 8 + 7] * inv);
+          v.x = pack_bf16(t[x * 8 + 0], t[x * 8 + 1]);
+          v.y = pack_bf16(t[x * 8 + 2], t[x * 8 + 3]);
+          v.z = pack_bf16(t[x * 8 + 4], t[x * 8 + 5]);
+          v.w = pack_bf16(t[x * 8 + 6], t[x * 8 + 7]);
           sts_v4(sStage + tid * kStageStride + c2 * 64 + x * 16, v);
         }
       }
@@ -575,12 +577,12 @@ __global__ void __launch_bounds__(256) sel_merge_kernel(const SelParams P) {
       const bool in = s0 + u < ns;
       const float2 ml = in ? st[s0 + u] : make_float2(0.f, 0.f);
       const bool ok = ml.y > 0.f;
-      w[u] = ok ? ex2(ml.x - M) * ml.y : 0.f;
+      w[u] = ok ? ex2(ml.x - M) : 0.f;
+      L = fmaf(w[u], ml.y, L);
       v[u] = ok ? *reinterpret_cast<const uint4*>(prow + (int64_t)(s0 + u) * D) : make_uint4(0u, 0u, 0u, 0u);
     }
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
-      L += w[u];
       const uint32_t q[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
 #pragma unroll
       for (int x = 0; x < 4; ++x) {

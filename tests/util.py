@@ -12,6 +12,11 @@ BF16_ABS = 2e-2     # bf16: |a-b| <= BF16_ABS + 2^-8 |b| elementwise; the second
                     # bf16 numbers at |b| (a stored bf16 value cannot be closer), it is below 2e-2 for |b| < 5
 
 
+# dk and dv (and the slot gradients) sum thousands of bf16-rounded terms per element, over every query and head that
+# attends the key; their bound gets a stated share of the tensor's largest value on top of BF16_ABS
+SUM_REL = {'dk': 2e-3, 'dv': 2e-3, 'dscale': 5e-3}
+
+
 def load_golden(name):
     z = np.load(os.path.join(GOLDEN, name + '.npz'))
     return {k: torch.from_numpy(z[k]) for k in z.files}
