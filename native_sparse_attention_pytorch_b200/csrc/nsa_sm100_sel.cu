@@ -887,7 +887,9 @@ __device__ long long g_trace[4][64][8];
 namespace ws {
 constexpr int kStages = 3;
 constexpr uint32_t kMetaBytes = 3 * kRows * 4;   // per stage: entry, lse, delta of every row of the chunk
-constexpr uint32_t kPBytes = 32768;   // P and dS tiles; afterwards the staging area of the bf16 dQ rows (144-byte rows)
+constexpr uint32_t kPBytes = 32768;   // P and dS tiles
+constexpr uint32_t kDqRow = 80;       // staged half dQ row: 64 bytes + 16 of padding (conflict-free 16-byte stores)
+constexpr uint32_t kDqStage = 32 * kDqRow;   // per softmax warp
 constexpr int kThreads = 14 * 32;
 constexpr int kLoaderThreads = 128;
 
@@ -912,7 +914,8 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   // stage s: Q tile then dO tile (16 KB each); buffer b: P tile then dS tile; KV buffer: K tile then V tile (8 KB each)
-  const uint32_t sQ0 = base, sP0 = sQ0 + kStages * 32768, sKV0 = sP0 + 2 * kPBytes, sMeta0 = sKV0 + 2 * 16384;
+  const uint32_t sQ0 = base, sP0 = sQ0 + kStages * 32768, sKV0 = sP0 + 2 * kPBytes, sMeta0 = sKV0 + 2 * 16384,
+                 sDq0 = sMeta0 + kStages * kMetaBytes;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   if (tid == 0) {
@@ -955,31 +958,42 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     WT_DECL
     const uint32_t tS = wg * 192, tDP = tS + 64, tDQ = tS + 128;
     const uint32_t sP = sP0 + wg * kPBytes, sDS = sP + 16384;
-    // dQ row of the group's previous chunk, still to be read out of tensor memory
-    uint4* prev_row = nullptr;
-    bool prev_valid = false, have_prev = false;
+    // dQ row of the group's previous chunk, still to be read out of tensor memory: index of its (row, slot) partial
+    int prev_dst = -1;
+    bool have_prev = false;
     uint32_t prev_use = 0;
-    // The dQ row goes out as the bf16 partial result of (row, slot), straight from registers.  Partials are summed by
-    // sel_dq_merge_kernel: plain stores run at memory speed, whereas fp32 reductions into dq are limited by the L2
-    // atomic units.
+    const uint32_t sDq = sDq0 + warp * kDqStage;
+    // The dQ rows go out as the bf16 partial results of their (row, slot); sel_dq_merge_kernel sums them (plain stores
+    // run at memory speed, fp32 reductions into dq are limited by the L2 atomic units).  A thread that stored its own
+    // 128-byte row would make every store instruction touch 32 lines; the warp stages half rows in shared memory
+    // instead and stores them eight rows per instruction.
     auto dq_out = [&]() {
       WT(1, mbar_wait_warp(smem_u32(&bars.mma2_done[wg]), prev_use & 1, &abort_flag))
       tc_fence_after_sync();
       __syncwarp();
+      uint8_t* const pbase = reinterpret_cast<uint8_t*>(P.partial);
 #pragma unroll 1
-      for (int c2 = 0; c2 < D / 16; ++c2) {
-        float tq[16];
-        tmem_ld16(tm_lane + tDQ + c2 * 16, tq);
+      for (int half = 0; half < 2; ++half) {
+        float tq[32];
+        tmem_ld32(tm_lane + tDQ + half * 32, tq);
         tmem_ld_wait();
-        if (prev_valid) {
 #pragma unroll
-          for (int x = 0; x < 2; ++x) {
-            uint4 v;
-            v.x = pack_bf16(tq[x * 8 + 0], tq[x * 8 + 1]); v.y = pack_bf16(tq[x * 8 + 2], tq[x * 8 + 3]);
-            v.z = pack_bf16(tq[x * 8 + 4], tq[x * 8 + 5]); v.w = pack_bf16(tq[x * 8 + 6], tq[x * 8 + 7]);
-            prev_row[c2 * 2 + x] = v;
-          }
+        for (int x = 0; x < 4; ++x) {
+          uint4 v;
+          v.x = pack_bf16(tq[x * 8 + 0], tq[x * 8 + 1]); v.y = pack_bf16(tq[x * 8 + 2], tq[x * 8 + 3]);
+          v.z = pack_bf16(tq[x * 8 + 4], tq[x * 8 + 5]); v.w = pack_bf16(tq[x * 8 + 6], tq[x * 8 + 7]);
+          sts_v4(sDq + lane * kDqRow + x * 16, v);
         }
+        __syncwarp();
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int rr = k * 8 + (lane >> 2);
+          const int dst = __shfl_sync(kFullMask, prev_dst, rr);
+          const uint4 v = lds_v4(sDq + rr * kDqRow + (lane & 3) * 16);
+          if (dst >= 0)
+            *reinterpret_cast<uint4*>(pbase + (int64_t)dst * (D * 2) + half * 64 + (lane & 3) * 16) = v;
+        }
+        __syncwarp();
       }
       tc_fence_before_sync();
       mbar_arrive(smem_u32(&bars.dq_free[wg]));   // the dQ columns of this group may be overwritten
@@ -1080,8 +1094,7 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         // while the tensor cores work on this chunk's P and dS, read out dQ of the previous chunk of the group
         if (have_prev) dq_out();
         if (r_tid == 0) TR(wg, n, 4)
-        prev_row = reinterpret_cast<uint4*>(P.partial + (row_global * P.ns + r.slot) * D);
-        prev_valid = r.valid;
+        prev_dst = r.valid ? (int)(row_global * P.ns + r.slot) : -1;
         prev_use = use;
         have_prev = true;
 #ifdef NSA_PHASE_TIMING
@@ -1608,7 +1621,8 @@ static int run_bwd(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaStrea
   sel_delta_kernel<D><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(P, delta);
   static const bool use_ws = []() { const char* e = getenv("NSA_SEL_BWD"); return e == nullptr || strcmp(e, "v1") != 0; }();
   if (D == 64 && use_ws) {
-    const int smem = 1024 + ws::kStages * 32768 + 2 * ws::kPBytes + 2 * 16384 + ws::kStages * ws::kMetaBytes;
+    const int smem = 1024 + ws::kStages * 32768 + 2 * ws::kPBytes + 2 * 16384 + ws::kStages * ws::kMetaBytes +
+                     8 * ws::kDqStage;
     CUDA_TRY(cudaFuncSetAttribute(sel_bwd_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     P.partial = reinterpret_cast<__nv_bfloat16*>(ws + p.off_partial);
     sel_bwd_ws_kernel<<<num_sms(), ws::kThreads, smem, st>>>(tmK, tmV, P);
