@@ -43,6 +43,23 @@ WORKLOADS = {
 }
 DEFAULT_WORKLOAD = 'sel_fwd_bwd_b4_n8192_h32kv4_d64_blk64_top16'
 
+# Two more workloads of the baseline (not the default line): the full layer forward+backward and the long-context
+# prefill that is sharded over the GPUs by KV-head group with the output all-gathered.
+LAYER_WORKLOADS = {
+    'layer_fwd_bwd_b2_n16384_dim1024_h16kv4_d64': dict(
+        batch=2, seq=16384, dim=1024, heads=16, kv_heads=4, dim_head=64, sliding_window_size=512,
+        compress_block_size=32, compress_block_sliding_stride=16, selection_block_size=64, num_selected_blocks=16),
+    'layer_small': dict(batch=1, seq=1024, dim=256, heads=4, kv_heads=2, dim_head=64, sliding_window_size=128,
+                        compress_block_size=32, compress_block_sliding_stride=16, selection_block_size=64,
+                        num_selected_blocks=4),
+}
+PREFILL_WORKLOADS = {
+    'prefill_b1_n65536_h64kv8_d128': dict(batch=1, seq=65536, q_heads=64, kv_heads=8, dim_head=128,
+                                          compress_block_size=32, stride=16, block=64, nsel=16, window=512, num_mem=1),
+    'prefill_small': dict(batch=1, seq=4096, q_heads=16, kv_heads=2, dim_head=128, compress_block_size=32, stride=16,
+                          block=64, nsel=16, window=512, num_mem=1),
+}
+
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the main backward kernel, from an ncu capture of this
 # command (profiles/tcgen05_selected_attention_b4_n8192_h32kv4_d64.md, profiles/simt_selected_attention_...md).
@@ -196,11 +213,16 @@ def main():
     ap.add_argument('--steps', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
-    ap.add_argument('--workload', default=DEFAULT_WORKLOAD, choices=list(WORKLOADS))
+    ap.add_argument('--workload', default=DEFAULT_WORKLOAD,
+                    choices=list(WORKLOADS) + list(LAYER_WORKLOADS) + list(PREFILL_WORKLOADS))
     ap.add_argument('--kernels', default='auto', choices=['auto', 'simt', 'sm100'])
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--rows', action='store_true', help='also time the other kernels of the hot path (N=1 only)')
     args = ap.parse_args()
+    if args.workload in LAYER_WORKLOADS:
+        return run_layer(args, LAYER_WORKLOADS[args.workload])
+    if args.workload in PREFILL_WORKLOADS:
+        return run_prefill(args, PREFILL_WORKLOADS[args.workload])
     w = WORKLOADS[args.workload]
     if args.impl == 'reference':
         return run_reference(args, w, args.workload)
@@ -429,6 +451,348 @@ def measure_rows(dev, flush, iters=5):
     add('combine_bwd', timed(lambda: torch.autograd.grad(holder['m'], (o1, o2, o3, gd), dm, retain_graph=True)),
         7 * act + gates.numel() * 6, 'hbm')
     return rows
+
+
+def _dist_setup():
+    import torch.distributed as dist
+    rank = int(os.environ.get('RANK', '0'))
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    torch.cuda.set_device(local)
+    dev = torch.device('cuda', local)
+    if world > 1:
+        dist.init_process_group('nccl', device_id=dev)
+    return dist, rank, world, local, dev
+
+
+def _timed_steps(step, steps, warmup, flush, dist, world, rank, local):
+    """`warmup` untimed steps, then `steps` steps timed one by one with CUDA events (L2 flushed outside the events);
+    returns (total ms as the max over ranks, clocks of rank 0)."""
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    evs = []
+    for i in range(steps):
+        flush.fill_(i & 0xff)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        step()
+        e1.record()
+        evs.append((e0, e1))
+    torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([sum(a.elapsed_time(b) for a, b in evs)], dtype=torch.float64, device=flush.device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item(), clocks
+
+
+def hot_path_flops(n, d, g, units, stride, ncb, num_mem, block, window, visible_slots):
+    """Forward FLOPs (4*d per attended pair) of the three branches for `units` (batch, KV head) pairs of `g` heads;
+    `visible_slots` = number of selected blocks summed over all (batch, KV head, query)."""
+    i = torch.arange(n, dtype=torch.float64)
+    cmp_pairs = (torch.clamp((i // stride), max=ncb) + num_mem).sum().item() * units * g
+    swa_pairs = (torch.clamp(i, max=window) + 1).sum().item() * units * g
+    sel_pairs = (visible_slots * block + (i % block + 1).sum().item() * units) * g
+    return {k: 4 * d * v for k, v in (('compressed', cmp_pairs), ('selected', sel_pairs), ('sliding', swa_pairs))}
+
+
+def run_layer(args, w):
+    """Full SparseAttention layer forward+backward in bf16 (the baseline's third configuration): every rank runs the
+    layer on its own batch (weak scaling)."""
+    import native_sparse_attention_pytorch_b200 as nsa
+    kw = {k: v for k, v in w.items() if k not in ('batch', 'seq')}
+    if args.impl == 'reference':
+        return run_layer_reference(args, w, kw)
+    dist, rank, world, local, dev = _dist_setup()
+    warmup = max(args.warmup, 3)
+    torch.manual_seed(0)
+    layer = nsa.SparseAttention(causal=True, use_triton_kernel=True, **kw).to(dev).bfloat16()
+    gen = torch.Generator('cpu').manual_seed(100 + rank)
+    x_host = torch.randn(w['batch'], w['seq'], w['dim'], generator=gen).bfloat16().pin_memory()
+    g_host = torch.randn(w['batch'], w['seq'], w['dim'], generator=gen).bfloat16().pin_memory()
+    x, up = x_host.to(dev).requires_grad_(), g_host.to(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def step():
+        layer.zero_grad(set_to_none=True)
+        x.grad = None
+        out = layer(x)
+        out.backward(up)
+        return out
+
+    with torch.no_grad():
+        _, mid = layer(x, return_intermediates=True)
+    n, d, hkv = w['seq'], w['dim_head'], w['kv_heads']
+    st = w['compress_block_sliding_stride']
+    flops = hot_path_flops(n, d, w['heads'] // hkv, w['batch'] * hkv, st, n // st, 1, w['selection_block_size'],
+                           w['sliding_window_size'], mid['fmask'].sum().item())
+    del mid
+    total_ms, clocks = _timed_steps(step, args.steps, warmup, flush, dist, world, rank, local)
+
+    # end to end: the input arrives from pinned host memory, the output and the input gradient go back
+    h_out, h_dx = torch.empty_like(x_host).pin_memory(), torch.empty_like(x_host).pin_memory()
+    def e2e_step():
+        x.data.copy_(x_host, non_blocking=True)
+        up.copy_(g_host, non_blocking=True)
+        out = step()
+        h_out.copy_(out.detach(), non_blocking=True)
+        h_dx.copy_(x.grad, non_blocking=True)
+    e2e_step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_steps = max(3, min(args.steps, 10))
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    ms = total_ms / args.steps
+    tokens = w['batch'] * w['seq'] * world
+    burst, sustained, src = peaks()
+    f_step = 3.5 * sum(flops.values())
+    line = {
+        'metric': 'nsa_layer_fwd_bwd_tokens_per_s', 'value': tokens / (ms / 1e3), 'unit': 'tokens/s', 'n_gpus': world,
+        'steps': args.steps, 'warmup': warmup, 'ms_per_step': ms, 'higher_is_better': True, 'scaling': 'weak',
+        'vs_baseline': None, 'dtype': 'bf16', 'data': 'synthetic',
+        'config': {'workload': args.workload, **w, 'l2': 'flushed between timed steps',
+                   'per_rank': 'each rank runs the layer on its own seeded batch'},
+        'roofline': {'bound': 'tensor', 'kernel': 'whole layer step; FLOPs of the three attention branches only',
+                     'achieved': f_step / (ms / 1e3) / 1e12, 'peak': burst, 'unit': 'TFLOP/s',
+                     'frac': f_step / (ms / 1e3) / 1e12 / burst, 'peak_source': src, 'peak_sustained': sustained,
+                     'flops_per_step': f_step, 'flops_fwd_by_branch': flops, 'traffic': None},
+        'e2e': {'value': tokens / (t.item() / e2e_steps / 1e3), 'unit': 'tokens/s',
+                'h2d_bytes_per_step': 2 * x_host.numel() * 2, 'd2h_bytes_per_step': 2 * x_host.numel() * 2,
+                'steps': e2e_steps},
+        'gpu_launches': None, 'clocks': clocks,
+    }
+    # kernels of this library per step: three branches forward and backward (13 + 13 + 13 with the tensor-core
+    # family), selection, combine forward and backward
+    line['gpu_launches'] = (3 * 13 + 3) * args.steps
+    if not args.no_cpu_baseline and world == 1:
+        line['cpu_baseline'] = layer_cpu_sample(kw)
+    print(json.dumps(line))
+
+
+def layer_cpu_sample(kw, n=1024, budget_s=15.0):
+    """The CPU oracle of the layer (a port of upstream's PyTorch path), forward+backward in fp32 at a sequence length
+    whose gathered keys fit host memory."""
+    from oracle import nsa_oracle as O
+    torch.set_num_threads(os.cpu_count())
+    torch.manual_seed(0)
+    layer = O.OracleSparseAttention(causal=True, **kw)
+    x = torch.randn(1, n, kw['dim'], generator=torch.Generator('cpu').manual_seed(1)).requires_grad_()
+    layer(x).sum().backward()
+    t0, reps = time.perf_counter(), 0
+    while True:
+        layer.zero_grad()
+        layer(x).sum().backward()
+        reps += 1
+        el = time.perf_counter() - t0
+        if el > budget_s or reps >= 20:
+            break
+    return {'value': reps * n / el, 'unit': 'tokens/s', 'cores': os.cpu_count(), 'kind': 'port',
+            'sample': f'batch 1, {n} tokens (upstream\'s gather formulation does not fit host memory at the full length), '
+                      f'fp32, {reps} repetitions'}
+
+
+def run_layer_reference(args, w, kw):
+    if int(os.environ.get('RANK', '0')) != 0:
+        return
+    base = layer_cpu_sample(kw, budget_s=max(5.0, min(60.0, 3.0 * args.steps)))
+    print(json.dumps({
+        'impl': 'reference', 'metric': 'nsa_layer_fwd_bwd_tokens_per_s', 'value': base['value'], 'unit': 'tokens/s',
+        'n_gpus': args.gpus, 'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': 1e3 * 1024 / base['value'],
+        'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
+        'config': {'workload': args.workload, **w}, 'cpu_baseline': base,
+        'e2e': {'value': base['value'], 'unit': 'tokens/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0}}))
+
+
+def prefill_inputs(w, heads, dev, host=False):
+    """Seeded inputs of the KV heads in `heads` (a range) and their query heads; the same values whatever the rank
+    that asks.  q, k, v ~ N(0,1) bf16; compressed keys / values from the default compress network (a two-layer MLP
+    over each window of `compress_block_size` rows, default init) on the un-rotated keys / values; rotary on q and k
+    for the selected and sliding branches; gates = sigmoid(N(0,1))."""
+    from native_sparse_attention_pytorch_b200.rotary import RotaryEmbedding
+    b, n, d, hkv = w['batch'], w['seq'], w['dim_head'], w['kv_heads']
+    g = w['q_heads'] // hkv
+    cbs, st = w['compress_block_size'], w['stride']
+    ncb = n // st
+    torch.manual_seed(0)
+    mlp = torch.nn.Sequential(torch.nn.Flatten(-2), torch.nn.Linear(cbs * d, cbs * d), torch.nn.ReLU(),
+                              torch.nn.Linear(cbs * d, d)).to(dev).bfloat16()
+    rot = RotaryEmbedding(d).to(dev)
+    outs = {k: [] for k in ('q', 'qr', 'kr', 'v', 'ck', 'cv', 'gates')}
+    with torch.no_grad():
+        for h in heads:
+            gen = torch.Generator(dev).manual_seed(1000 + h)
+            q = torch.randn(b, g, n, d, generator=gen, device=dev).bfloat16()
+            k = torch.randn(b, 1, n, d, generator=gen, device=dev).bfloat16()
+            v = torch.randn(b, 1, n, d, generator=gen, device=dev).bfloat16()
+            gates = torch.sigmoid(torch.randn(b, g, n, 3, generator=gen, device=dev)).bfloat16()
+            pad = cbs - st
+            def compress(t):
+                tp = torch.nn.functional.pad(t, (0, 0, pad, 0))[..., : (ncb - 1) * st + cbs, :]
+                win = tp.unfold(-2, cbs, st).transpose(-1, -2)          # [b, 1, ncb, cbs, d]
+                c = torch.cat([mlp(win[:, :, a:a + 512]) for a in range(0, ncb, 512)], dim=2)
+                return torch.cat((c.new_zeros(b, 1, w['num_mem'], d), c), dim=2)
+            qr, kr = rot.rotate_queries_with_cached_keys(q, k)
+            for name, t in (('q', q), ('qr', qr), ('kr', kr), ('v', v), ('ck', compress(k)), ('cv', compress(v)),
+                            ('gates', gates)):
+                outs[name].append(t.cpu().pin_memory() if host else t)
+    return {k: torch.cat(v, dim=1) for k, v in outs.items()}
+
+
+def run_prefill(args, w):
+    """Long-context prefill (forward only) of the hot path, KV-head groups split over the ranks, output all-gathered
+    (the baseline's fifth configuration).  Total work is fixed: strong scaling."""
+    from native_sparse_attention_pytorch_b200 import sharding
+    if args.impl == 'reference':
+        return run_prefill_reference(args, w)
+    dist, rank, world, local, dev = _dist_setup()
+    warmup = max(args.warmup, 3)
+    h0, h1 = sharding.kv_head_range(w['kv_heads'], world, rank)
+    t = prefill_inputs(w, range(h0, h1), dev)
+    cfg = dict(num_mem=w['num_mem'], stride=w['stride'], block=w['block'], num_selected=w['nsel'], window=w['window'],
+               causal=True, impl=args.kernels, local=True)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    keep = {}
+
+    def step():
+        keep['out'] = sharding.sharded_attend_core(t['q'], t['qr'], t['kr'], t['v'], t['ck'], t['cv'], t['gates'], **cfg)
+
+    total_ms, clocks = _timed_steps(step, args.steps, warmup, flush, dist, world, rank, local)
+
+    # end to end: this rank's inputs arrive from pinned host memory every step, rank 0 reads the gathered output back
+    host = {k: v.cpu().pin_memory() for k, v in t.items()}
+    h_out = torch.empty_like(keep['out'], device='cpu').pin_memory() if rank == 0 else None
+    def e2e_step():
+        for k in t:
+            t[k].copy_(host[k], non_blocking=True)
+        step()
+        if rank == 0:
+            h_out.copy_(keep['out'], non_blocking=True)
+    e2e_step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_steps = max(2, min(args.steps, 5))
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    te = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    # selected blocks actually visible, for the FLOP count (one more untimed pass of the selection on this rank)
+    from native_sparse_attention_pytorch_b200 import ops
+    vis = 0
+    g = w['q_heads'] // w['kv_heads']
+    with torch.no_grad():
+        for a in range(h1 - h0):
+            _, imp = ops.compressed_attend(t['q'][:, a * g:(a + 1) * g], t['ck'][:, a:a + 1], t['cv'][:, a:a + 1],
+                                           w['num_mem'], w['stride'], True, sel_heads=1, want_importance=True)
+            vals, _ = ops.select_blocks(imp, w['block'], w['stride'], w['nsel'], dtype=torch.bfloat16)
+            vis += int((vals > 1e-10).sum().item())
+            del imp
+    tv = torch.tensor([float(vis)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tv)
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    ms = total_ms / args.steps
+    n = w['seq']
+    tokens = w['batch'] * n
+    flops = hot_path_flops(n, w['dim_head'], g, w['batch'] * w['kv_heads'], w['stride'], n // w['stride'], w['num_mem'],
+                           w['block'], w['window'], tv.item())
+    f_step = sum(flops.values())
+    burst, sustained, src = peaks()
+    in_bytes = sum(v.numel() * v.element_size() for v in host.values())
+    line = {
+        'metric': 'nsa_prefill_tokens_per_s', 'value': tokens / (ms / 1e3), 'unit': 'tokens/s', 'n_gpus': world,
+        'steps': args.steps, 'warmup': warmup, 'ms_per_step': ms, 'higher_is_better': True, 'scaling': 'strong',
+        'vs_baseline': None, 'dtype': 'bf16', 'data': 'synthetic',
+        'config': {'workload': args.workload, **w, 'kernels': args.kernels, 'l2': 'flushed between timed steps',
+                   'sharding': f'{w["kv_heads"] // world} KV-head group(s) per rank, output all-gathered (NCCL)'},
+        'roofline': {'bound': 'tensor', 'kernel': 'whole forward step of all branches (per GPU)',
+                     'achieved': f_step / world / (ms / 1e3) / 1e12, 'peak': burst, 'unit': 'TFLOP/s',
+                     'frac': f_step / world / (ms / 1e3) / 1e12 / burst, 'peak_source': src,
+                     'peak_sustained': sustained, 'flops_per_step': f_step, 'flops_fwd_by_branch': flops,
+                     'traffic': None},
+        'e2e': {'value': tokens / (te.item() / e2e_steps / 1e3), 'unit': 'tokens/s',
+                'h2d_bytes_per_step': in_bytes * world, 'd2h_bytes_per_step': keep['out'].numel() * 2,
+                'steps': e2e_steps},
+        'gpu_launches': (3 * 6 + 2) * (h1 - h0) * args.steps, 'clocks': clocks,
+    }
+    if not args.no_cpu_baseline and world == 1:
+        line['cpu_baseline'] = prefill_cpu_sample(w)
+    print(json.dumps(line))
+
+
+def oracle_core_fns(num_mem):
+    """The CPU oracle's functions behind the argument lists of the CUDA operators (for the CPU baseline only)."""
+    from oracle import nsa_oracle as O
+
+    def compressed(q, ck, cv, nm, stride, causal, sel_heads=None, want_importance=True):
+        out, csim = O.compressed_attend(q, ck[:, :, nm:], cv[:, :, nm:], ck[0, :, :nm], cv[0, :, :nm], stride, causal)
+        return out, (csim, ck.shape[1])
+
+    def select(importance, block, stride, nsel, dtype=None):
+        csim, hkv = importance
+        return O.select_blocks(O.importance_scores(csim, num_mem, hkv, stride, block), nsel)
+
+    def selected(q, k, v, block, idx, mask, include_block_causal=True):
+        return O.selected_attend(q, k, v, block, idx, mask, include_block_causal)
+
+    return dict(compressed=compressed, select=select, selected=selected, sliding=O.sliding_attend, combine=O.combine)
+
+
+def prefill_cpu_sample(w, n=2048, budget_s=15.0):
+    from native_sparse_attention_pytorch_b200 import sharding
+    torch.set_num_threads(os.cpu_count())
+    ws = dict(w, seq=n)
+    t = {k: v.float() for k, v in prefill_inputs(ws, range(1), torch.device('cpu')).items()}
+    cfg = dict(num_mem=w['num_mem'], stride=w['stride'], block=w['block'], num_selected=w['nsel'], window=w['window'],
+               causal=True, attend_fns=oracle_core_fns(w['num_mem']))
+    run = lambda: sharding.attend_core(t['q'], t['qr'], t['kr'], t['v'], t['ck'], t['cv'], t['gates'], **cfg)
+    with torch.no_grad():
+        run()
+        t0, reps = time.perf_counter(), 0
+        while True:
+            run()
+            reps += 1
+            el = time.perf_counter() - t0
+            if el > budget_s or reps >= 20:
+                break
+    return {'value': reps * n / w['kv_heads'] / el, 'unit': 'tokens/s', 'cores': os.cpu_count(), 'kind': 'port',
+            'sample': f'{n} tokens, 1 of {w["kv_heads"]} KV-head groups (a token counts 1/{w["kv_heads"]} per group), '
+                      f'fp32, forward only, {reps} repetitions'}
+
+
+def run_prefill_reference(args, w):
+    if int(os.environ.get('RANK', '0')) != 0:
+        return
+    base = prefill_cpu_sample(w, budget_s=max(5.0, min(60.0, 3.0 * args.steps)))
+    print(json.dumps({
+        'impl': 'reference', 'metric': 'nsa_prefill_tokens_per_s', 'value': base['value'], 'unit': 'tokens/s',
+        'n_gpus': args.gpus, 'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': None,
+        'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
+        'config': {'workload': args.workload, **w}, 'cpu_baseline': base,
+        'e2e': {'value': base['value'], 'unit': 'tokens/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0}}))
 
 
 def launches_per_step(kernels, w):

@@ -70,3 +70,71 @@ def sharded_selected_attend(fq, fk, fv, block_size, idx, fmask, include_block_ca
         return torch.cat(parts, dim=0)
     rows = [torch.cat(parts[i * n:(i + 1) * n], dim=1) for i in range(b)]
     return torch.cat(rows, dim=0)
+
+
+def attend_core(q, qr, kr, v, ck, cv, gates, *, num_mem, stride, block, num_selected, window, causal=True,
+                impl='auto', attend_fns=None):
+    """The hot path between the projections (upstream NSA:621-860) for the heads it is given: compressed attention with
+    the importance by-product, block selection, selected-block attention, sliding window, gated combine.
+
+    q: un-rotated queries [B, Hq, N, d]; qr, kr: rotated queries / keys; v: values [B, Hkv, N, d]; ck, cv: compressed
+    keys / values with the `num_mem` memory slots in front [B, Hkv, num_mem + ncb, d]; gates [B, Hq, N, 3] (order:
+    compressed, selected, sliding).  Returns the merged output [B, N, Hq * d].  `attend_fns` replaces the CUDA operators
+    (a dict with the keys used below); the CPU tests pass the oracle's functions."""
+    if attend_fns is None:
+        from . import ops
+        attend_fns = dict(compressed=ops.compressed_attend, select=ops.select_blocks,
+                          selected=ops.native_sparse_attend, sliding=ops.sliding_window_attend,
+                          combine=ops.gated_combine)
+        kw = dict(impl=impl)
+    else:
+        kw = {}
+    hkv = v.shape[1]
+    o_cmp, importance = attend_fns['compressed'](q, ck, cv, num_mem, stride, causal, sel_heads=hkv,
+                                                 want_importance=True, **kw)
+    vals, idx = attend_fns['select'](importance, block, stride, num_selected, dtype=q.dtype)
+    fmask = vals > 1e-10
+    o_sel = attend_fns['selected'](qr, kr, v, block, idx, fmask, include_block_causal=causal, **kw)
+    o_swa = attend_fns['sliding'](qr, kr, v, window, causal, **kw)
+    return attend_fns['combine'](o_cmp, o_sel, o_swa, gates)
+
+
+def kv_head_range(kv_heads, world, rank):
+    """KV heads owned by `rank` when the heads of one batch element are dealt out over `world` ranks."""
+    if kv_heads % world != 0:
+        raise ValueError(f'{kv_heads} KV heads do not split evenly over {world} ranks')
+    per = kv_heads // world
+    return rank * per, (rank + 1) * per
+
+
+def gather_heads(merged_local, group=None):
+    """All-gather of the merged output along the head axis: every rank contributes [B, N, Hl * d] (its own heads, in
+    rank order) and receives [B, N, world * Hl * d].  The one collective of the sharded path."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if world == 1:
+        return merged_local
+    b, n, f = merged_local.shape
+    parts = torch.empty(world * b, n, f, dtype=merged_local.dtype, device=merged_local.device)
+    dist.all_gather_into_tensor(parts, merged_local.contiguous(), group=group)
+    return parts.view(world, b, n, f).permute(1, 2, 0, 3).reshape(b, n, world * f)
+
+
+def sharded_attend_core(q, qr, kr, v, ck, cv, gates, *, group=None, heads_per_pass=1, **cfg):
+    """`attend_core` with the KV-head groups split over the ranks of `group` (long-context prefill: batch 1, one or a
+    few KV heads per GPU).  Every rank passes tensors that hold (at least) its own heads -- either the full tensors or
+    already the local slices (`local=True` in cfg) -- and receives the full merged output [B, N, Hq * d].  The local
+    heads are processed `heads_per_pass` KV heads at a time to bound the work buffers."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    local = cfg.pop('local', False)
+    hkv_total = v.shape[1] * (world if local else 1)
+    g = q.shape[1] // v.shape[1]
+    h0, h1 = (0, v.shape[1]) if local else kv_head_range(hkv_total, world, rank)
+    b, _, n, d = q.shape
+    merged = torch.empty(b, n, (h1 - h0) * g * d, dtype=q.dtype, device=q.device)
+    for a in range(h0, h1, heads_per_pass):
+        z = min(a + heads_per_pass, h1)
+        hs, qs = slice(a, z), slice(a * g, z * g)
+        part = attend_core(q[:, qs], qr[:, qs], kr[:, hs], v[:, hs], ck[:, hs], cv[:, hs], gates[:, qs], **cfg)
+        merged[..., (a - h0) * g * d:(z - h0) * g * d] = part
+    return gather_heads(merged, group)

@@ -59,3 +59,75 @@ def test_sharded_attend_equals_unsharded(world, batch, hkv):
     ret = mp.Manager().dict()
     mp.spawn(worker, args=(world, port, batch, hkv, ret), nprocs=world, join=True)
     assert len(ret) == world and all(e < 1e-6 for e in ret.values()), dict(ret)
+
+
+# ---- the whole hot path, KV-head groups split over the ranks, output all-gathered --------------------------------
+
+NUM_MEM, STRIDE, BLOCK, NSEL, WINDOW = 1, 4, 8, 2, 6
+
+
+def _oracle_fns():
+    def compressed(q, ck, cv, num_mem, stride, causal, sel_heads=None, want_importance=True):
+        hkv = ck.shape[1]
+        zero = ck.new_zeros(hkv, 0, ck.shape[-1])
+        out, csim = O.compressed_attend(q, ck, cv, zero, zero, stride, causal) if num_mem == 0 else \
+            _compressed_with_mem(q, ck, cv, num_mem, stride, causal)
+        return out, (csim, hkv)
+
+    def _compressed_with_mem(q, ck, cv, num_mem, stride, causal):
+        # the operator takes the memory slots in front of ck / cv; the oracle takes them apart (batch 1 per call)
+        outs, sims = [], []
+        for b in range(q.shape[0]):
+            o, s = O.compressed_attend(q[b:b + 1], ck[b:b + 1, :, num_mem:], cv[b:b + 1, :, num_mem:],
+                                       ck[b, :, :num_mem], cv[b, :, :num_mem], stride, causal)
+            outs.append(o)
+            sims.append(s)
+        return torch.cat(outs), torch.cat(sims)
+
+    def select(importance, block, stride, nsel, dtype=None):
+        csim, hkv = importance
+        return O.select_blocks(O.importance_scores(csim, NUM_MEM, hkv, stride, block), nsel)
+
+    def selected(q, k, v, block, idx, mask, include_block_causal=True):
+        return O.selected_attend(q, k, v, block, idx, mask, include_block_causal)
+
+    return dict(compressed=compressed, select=select, selected=selected, sliding=O.sliding_attend, combine=O.combine)
+
+
+def core_worker(rank, world, port, ret):
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    try:
+        b, hkv, g, n, d = 1, 4, 2, 50, 16
+        ncb = n // STRIDE
+        q = recipe.randn((b, hkv * g, n, d), 11)
+        k = recipe.randn((b, hkv, n, d), 12)
+        v = recipe.randn((b, hkv, n, d), 13)
+        qr, kr = O.rotary(q), O.rotary(k)
+        ck = recipe.randn((b, hkv, NUM_MEM + ncb, d), 14)
+        cv = recipe.randn((b, hkv, NUM_MEM + ncb, d), 15)
+        gates = torch.sigmoid(recipe.randn((b, hkv * g, n, 3), 16))
+        cfg = dict(num_mem=NUM_MEM, stride=STRIDE, block=BLOCK, num_selected=NSEL, window=WINDOW, causal=True,
+                   attend_fns=_oracle_fns())
+        out = sharding.sharded_attend_core(q, qr, kr, v, ck, cv, gates, **cfg)
+        full = sharding.attend_core(q, qr, kr, v, ck, cv, gates, **cfg)
+        ret[rank] = (tuple(out.shape), float((out - full).abs().max()))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize('world', [2, 4])
+def test_head_sharded_hot_path_equals_unsharded(world):
+    port = 31500 + (os.getpid() % 2000) + world * 11
+    ret = mp.Manager().dict()
+    mp.spawn(core_worker, args=(world, port, ret), nprocs=world, join=True)
+    assert len(ret) == world
+    for shape, err in ret.values():
+        assert shape == (1, 50, 4 * 2 * 16) and err < 1e-6, dict(ret)
+
+
+def test_kv_head_range():
+    assert [sharding.kv_head_range(8, 4, r) for r in range(4)] == [(0, 2), (2, 4), (4, 6), (6, 8)]
+    with pytest.raises(ValueError):
+        sharding.kv_head_range(8, 3, 0)
