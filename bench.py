@@ -217,6 +217,8 @@ def main():
                     choices=list(WORKLOADS) + list(LAYER_WORKLOADS) + list(PREFILL_WORKLOADS))
     ap.add_argument('--kernels', default='auto', choices=['auto', 'simt', 'sm100'])
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--gather', default='fused', choices=['fused', 'nccl'],
+                    help='prefill workloads, N > 1: combine kernel stores into every rank (fused) or NCCL all-gather')
     ap.add_argument('--rows', action='store_true', help='also time the other kernels of the hot path (N=1 only)')
     args = ap.parse_args()
     if args.workload in LAYER_WORKLOADS:
@@ -669,9 +671,12 @@ def run_prefill(args, w):
                causal=True, impl=args.kernels, local=True)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     keep = {}
+    fused = world > 1 and args.gather == 'fused'
+    peer = sharding.PeerOutput(w['batch'], w['seq'], w['q_heads'] * w['dim_head'], torch.bfloat16, dev) if fused else None
 
     def step():
-        keep['out'] = sharding.sharded_attend_core(t['q'], t['qr'], t['kr'], t['v'], t['ck'], t['cv'], t['gates'], **cfg)
+        keep['out'] = sharding.sharded_attend_core(t['q'], t['qr'], t['kr'], t['v'], t['ck'], t['cv'], t['gates'],
+                                                   peer_output=peer, **cfg)
 
     total_ms, clocks = _timed_steps(step, args.steps, warmup, flush, dist, world, rank, local)
 
@@ -727,7 +732,8 @@ def run_prefill(args, w):
         'steps': args.steps, 'warmup': warmup, 'ms_per_step': ms, 'higher_is_better': True, 'scaling': 'strong',
         'vs_baseline': None, 'dtype': 'bf16', 'data': 'synthetic',
         'config': {'workload': args.workload, **w, 'kernels': args.kernels, 'l2': 'flushed between timed steps',
-                   'sharding': f'{w["kv_heads"] // world} KV-head group(s) per rank, output all-gathered (NCCL)'},
+                   'sharding': f'{w["kv_heads"] // world} KV-head group(s) per rank, output gathered by '
+                               + ('the combine kernel storing into every rank' if fused else 'NCCL all-gather')},
         'roofline': {'bound': 'tensor', 'kernel': 'whole forward step of all branches (per GPU)',
                      'achieved': f_step / world / (ms / 1e3) / 1e12, 'peak': burst, 'unit': 'TFLOP/s',
                      'frac': f_step / world / (ms / 1e3) / 1e12 / burst, 'peak_source': src,

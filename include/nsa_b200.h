@@ -298,9 +298,29 @@ typedef struct {
 
 int nsa_combine_bwd(const nsa_combine_bwd_args* args, void* stream);
 
+/* Gated combine fused with the all-gather of the head-sharded layout.  Replaces the same upstream lines as
+ * nsa_combine_fwd (NSA:854-860) for a rank that holds only its own heads: the merged rows of these heads are written
+ * at `feature_offset` into every buffer of `outs`, each a [B, N, total_features] tensor -- this GPU's own and the
+ * peers' (their device memory mapped into this process, e.g. CUDA IPC or symmetric memory), so no local copy of the
+ * merged rows and no separate collective are needed.  Upstream runs on one GPU and has no counterpart of the gather;
+ * the partition (KV-head groups per GPU, output all-gathered) is the one this library is specified with.
+ * The caller orders the call against the other ranks (a barrier before the buffers are reused, one after the call
+ * before they are read).  Pointers, strides and dim_head must keep 16-byte pieces aligned. */
+#define NSA_MAX_GATHER 8
+typedef struct {
+  nsa_combine_fwd_args fwd;       /* fwd.out is not used                      */
+  void* outs[NSA_MAX_GATHER];     /* destinations, own buffer included        */
+  int32_t num_outs;               /* 1 .. NSA_MAX_GATHER                      */
+  int32_t reserved;
+  int64_t total_features;         /* features per position in the destinations */
+  int64_t feature_offset;         /* first feature of this rank's heads       */
+} nsa_combine_gather_args;
+
+int nsa_combine_fwd_gather(const nsa_combine_gather_args* args, void* stream);
+
 /* Library information.  nsa_struct_size(i) is sizeof() of the i-th argument
  * struct in declaration order (0 nsa_tensor, 1 sel_fwd, 2 sel_bwd, 3 cmp_fwd,
- * 4 cmp_bwd, 5 select, 6 swa_fwd, 7 swa_bwd, 8 combine_fwd, 9 combine_bwd), so
+ * 4 cmp_bwd, 5 select, 6 swa_fwd, 7 swa_bwd, 8 combine_fwd, 9 combine_bwd, 10 combine_gather), so
  * a foreign-function binding can verify its own layout; -1 for other i. */
 const char* nsa_last_error(void);
 int nsa_abi_version(void);

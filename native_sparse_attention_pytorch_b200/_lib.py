@@ -71,12 +71,20 @@ class CombineBwdArgs(C.Structure):
     _fields_ = [('fwd', CombineFwdArgs), ('dout', vp), ('d_cmp', vp), ('d_sel', vp), ('d_swa', vp), ('d_gates', vp)]
 
 
+MAX_GATHER = 8
+
+
+class CombineGatherArgs(C.Structure):
+    _fields_ = [('fwd', CombineFwdArgs), ('outs', vp * MAX_GATHER), ('num_outs', i32), ('reserved', i32),
+                ('total_features', i64), ('feature_offset', i64)]
+
+
 _STRUCTS = [Tensor4, SelFwdArgs, SelBwdArgs, CmpFwdArgs, CmpBwdArgs, SelectArgs, SwaFwdArgs, SwaBwdArgs,
-            CombineFwdArgs, CombineBwdArgs]
+            CombineFwdArgs, CombineBwdArgs, CombineGatherArgs]
 
 ENTRY_POINTS = ['nsa_sel_fwd', 'nsa_sel_bwd', 'nsa_sel_workspace_bytes', 'nsa_sel_fwd_static',
                 'nsa_sel_static_scratch_bytes', 'nsa_cmp_workspace_bytes', 'nsa_swa_workspace_bytes', 'nsa_cmp_fwd', 'nsa_cmp_bwd', 'nsa_select',
-                'nsa_swa_fwd', 'nsa_swa_bwd', 'nsa_combine_fwd', 'nsa_combine_bwd', 'nsa_last_error',
+                'nsa_swa_fwd', 'nsa_swa_bwd', 'nsa_combine_fwd', 'nsa_combine_bwd', 'nsa_combine_fwd_gather', 'nsa_last_error',
                 'nsa_abi_version', 'nsa_struct_size']
 
 _lib = None

@@ -109,6 +109,7 @@ int nsa_struct_size(int which) {
     case 7: return (int)sizeof(nsa_swa_bwd_args);
     case 8: return (int)sizeof(nsa_combine_fwd_args);
     case 9: return (int)sizeof(nsa_combine_bwd_args);
+    case 10: return (int)sizeof(nsa_combine_gather_args);
     default: return -1;
   }
 }
@@ -336,7 +337,51 @@ int nsa_combine_fwd(const nsa_combine_fwd_args* a, void* stream) {
   NSA_TRY(fill_combine(P, *a));
   if (a->out == nullptr) return fail(NSA_ERR_NULL, "out: NULL pointer");
   P.out = a->out;
+  // 16-byte pieces when everything is aligned for them (the usual case), feature pairs otherwise
+  const int V = a->dtype == NSA_F32 ? 4 : 8;
+  bool vec = a->dim_head % V == 0 && (reinterpret_cast<uintptr_t>(a->out) & 15u) == 0;
+  const nsa_tensor* o[3] = {&a->o_cmp, &a->o_sel, &a->o_swa};
+  for (int s = 0; s < 3; ++s)
+    vec = vec && (reinterpret_cast<uintptr_t>(o[s]->ptr) & 15u) == 0 && o[s]->stride_b % V == 0 &&
+          o[s]->stride_h % V == 0 && o[s]->stride_n % V == 0;
+  if (vec) {
+    GatherTargets Gt;
+    memset(&Gt, 0, sizeof(Gt));
+    Gt.outs[0] = a->out;
+    Gt.num_outs = 1;
+    Gt.total_features = (int64_t)a->q_heads * a->dim_head;
+    Gt.feature_offset = 0;
+    return launch_combine_gather(P, Gt, a->dtype, (cudaStream_t)stream);
+  }
   return launch_combine(P, a->dtype, false, (cudaStream_t)stream);
+}
+
+int nsa_combine_fwd_gather(const nsa_combine_gather_args* a, void* stream) {
+  if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
+  CombineParams P;
+  NSA_TRY(fill_combine(P, a->fwd));
+  const nsa_combine_fwd_args& f = a->fwd;
+  const int V = f.dtype == NSA_F32 ? 4 : 8;
+  if (a->num_outs < 1 || a->num_outs > NSA_MAX_GATHER) return fail(NSA_ERR_SHAPE, "num_outs must be 1..NSA_MAX_GATHER");
+  if (f.dim_head % V) return fail(NSA_ERR_ALIGN, "dim_head must be a multiple of 16 bytes");
+  if (a->feature_offset < 0 || a->feature_offset % V || a->total_features % V ||
+      a->feature_offset + (int64_t)f.q_heads * f.dim_head > a->total_features)
+    return fail(NSA_ERR_SHAPE, "feature_offset / total_features do not hold these heads in 16-byte pieces");
+  const nsa_tensor* o[3] = {&f.o_cmp, &f.o_sel, &f.o_swa};
+  for (int s = 0; s < 3; ++s)
+    if ((reinterpret_cast<uintptr_t>(o[s]->ptr) & 15u) || o[s]->stride_b % V || o[s]->stride_h % V || o[s]->stride_n % V)
+      return fail(NSA_ERR_ALIGN, "branch outputs must keep 16-byte pieces aligned");
+  GatherTargets Gt;
+  memset(&Gt, 0, sizeof(Gt));
+  for (int r = 0; r < a->num_outs; ++r) {
+    if (a->outs[r] == nullptr) return fail(NSA_ERR_NULL, "outs: NULL pointer");
+    if (reinterpret_cast<uintptr_t>(a->outs[r]) & 15u) return fail(NSA_ERR_ALIGN, "outs must be 16-byte aligned");
+    Gt.outs[r] = a->outs[r];
+  }
+  Gt.num_outs = a->num_outs;
+  Gt.total_features = a->total_features;
+  Gt.feature_offset = a->feature_offset;
+  return launch_combine_gather(P, Gt, f.dtype, (cudaStream_t)stream);
 }
 
 int nsa_combine_bwd(const nsa_combine_bwd_args* a, void* stream) {

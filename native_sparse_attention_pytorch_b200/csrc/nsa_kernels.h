@@ -55,11 +55,19 @@ struct CombineParams {
   int batch, q_heads, seq, d;
 };
 
+constexpr int kMaxGather = NSA_MAX_GATHER;
+struct GatherTargets {
+  void* outs[kMaxGather];
+  int num_outs;
+  int64_t total_features, feature_offset;
+};
+
 int fail(int code, const char* msg);
 
 int simt_attend(const AttnParams& P, int branch, int dtype, bool backward, cudaStream_t stream);
 int launch_select(const SelectParams& P, cudaStream_t stream);
 int launch_combine(const CombineParams& P, int dtype, bool backward, cudaStream_t stream);
+int launch_combine_gather(const CombineParams& P, const GatherTargets& Gt, int dtype, cudaStream_t stream);
 
 // Tensor-core family for the selected-block branch.  Each returns
 // NSA_ERR_UNSUPPORTED (without touching the error message state of a later

@@ -340,3 +340,29 @@ class GatedCombine(Function):
 
 def gated_combine(o_cmp, o_sel, o_swa, gates):
     return GatedCombine.apply(o_cmp, o_sel, o_swa, gates)
+
+
+def _vec_ok(t):
+    v = 16 // t.element_size()
+    return t.stride(-1) == 1 and t.data_ptr() % 16 == 0 and all(s % v == 0 for s in t.stride()[:-1])
+
+
+def gated_combine_gather(o_cmp, o_sel, o_swa, gates, out_ptrs, total_features, feature_offset):
+    """Forward-only gated combine of this rank's heads, written at `feature_offset` into every [B, N, total_features]
+    buffer whose device address is listed in `out_ptrs` (own buffer and the peers' mappings): the combine fused with
+    the all-gather of the head-sharded layout.  The caller synchronises the ranks around the call."""
+    L.require_cuda(o_cmp, o_sel, o_swa, gates)
+    lib = L.load()
+    o_cmp, o_sel, o_swa = (t if _vec_ok(t) else t.contiguous() for t in (o_cmp, o_sel, o_swa))
+    if gates.stride(-1) != 1:
+        gates = gates.contiguous()
+    b, h, n, d = o_cmp.shape
+    if not 1 <= len(out_ptrs) <= L.MAX_GATHER:
+        raise ValueError(f'between 1 and {L.MAX_GATHER} destinations, got {len(out_ptrs)}')
+    fwd = L.CombineFwdArgs(o_cmp=L.t4(o_cmp), o_sel=L.t4(o_sel), o_swa=L.t4(o_swa), gates=L.t4(gates), out=None,
+                           batch=b, q_heads=h, seq=n, dim_head=d, dtype=L.dtype_code(o_cmp))
+    outs = (C.c_void_p * L.MAX_GATHER)(*[int(p) for p in out_ptrs])
+    args = L.CombineGatherArgs(fwd=fwd, outs=outs, num_outs=len(out_ptrs), reserved=0,
+                               total_features=total_features, feature_offset=feature_offset)
+    with torch.cuda.device(o_cmp.device):
+        L.check(lib.nsa_combine_fwd_gather(C.byref(args), L.stream_of(o_cmp)))

@@ -73,14 +73,15 @@ def sharded_selected_attend(fq, fk, fv, block_size, idx, fmask, include_block_ca
 
 
 def attend_core(q, qr, kr, v, ck, cv, gates, *, num_mem, stride, block, num_selected, window, causal=True,
-                impl='auto', attend_fns=None):
+                impl='auto', attend_fns=None, combine=None):
     """The hot path between the projections (upstream NSA:621-860) for the heads it is given: compressed attention with
     the importance by-product, block selection, selected-block attention, sliding window, gated combine.
 
     q: un-rotated queries [B, Hq, N, d]; qr, kr: rotated queries / keys; v: values [B, Hkv, N, d]; ck, cv: compressed
     keys / values with the `num_mem` memory slots in front [B, Hkv, num_mem + ncb, d]; gates [B, Hq, N, 3] (order:
     compressed, selected, sliding).  Returns the merged output [B, N, Hq * d].  `attend_fns` replaces the CUDA operators
-    (a dict with the keys used below); the CPU tests pass the oracle's functions."""
+    (a dict with the keys used below); the CPU tests pass the oracle's functions.  `combine` replaces the last step
+    only (the fused combine + gather of the sharded path) and its result is returned."""
     if attend_fns is None:
         from . import ops
         attend_fns = dict(compressed=ops.compressed_attend, select=ops.select_blocks,
@@ -96,7 +97,7 @@ def attend_core(q, qr, kr, v, ck, cv, gates, *, num_mem, stride, block, num_sele
     fmask = vals > 1e-10
     o_sel = attend_fns['selected'](qr, kr, v, block, idx, fmask, include_block_causal=causal, **kw)
     o_swa = attend_fns['sliding'](qr, kr, v, window, causal, **kw)
-    return attend_fns['combine'](o_cmp, o_sel, o_swa, gates)
+    return (combine or attend_fns['combine'])(o_cmp, o_sel, o_swa, gates)
 
 
 def kv_head_range(kv_heads, world, rank):
@@ -119,7 +120,31 @@ def gather_heads(merged_local, group=None):
     return parts.view(world, b, n, f).permute(1, 2, 0, 3).reshape(b, n, world * f)
 
 
-def sharded_attend_core(q, qr, kr, v, ck, cv, gates, *, group=None, heads_per_pass=1, **cfg):
+class PeerOutput:
+    """The gathered output [B, N, features] of every rank in symmetric memory, so that each rank's combine kernel can
+    store its heads straight into all of them (`ops.gated_combine_gather`): the all-gather without a collective call
+    and without a local copy of the merged rows.  `begin()` / `end()` order one step against the other ranks: nobody
+    stores into a buffer that a peer may still be reading, nobody reads before every peer's stores have landed."""
+
+    def __init__(self, batch, seq, features, dtype, device, group=None):
+        import torch.distributed._symmetric_memory as symm
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.buffer = symm.empty(batch, seq, features, dtype=dtype, device=device)
+        self.handle = symm.rendezvous(self.buffer, self.group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.features = features
+
+    def begin(self):
+        self.handle.barrier(channel=0)
+
+    def end(self):
+        self.handle.barrier(channel=1)
+        return self.buffer
+
+
+def sharded_attend_core(q, qr, kr, v, ck, cv, gates, *, group=None, heads_per_pass=1, peer_output=None, **cfg):
     """`attend_core` with the KV-head groups split over the ranks of `group` (long-context prefill: batch 1, one or a
     few KV heads per GPU).  Every rank passes tensors that hold (at least) its own heads -- either the full tensors or
     already the local slices (`local=True` in cfg) -- and receives the full merged output [B, N, Hq * d].  The local
@@ -131,6 +156,21 @@ def sharded_attend_core(q, qr, kr, v, ck, cv, gates, *, group=None, heads_per_pa
     g = q.shape[1] // v.shape[1]
     h0, h1 = (0, v.shape[1]) if local else kv_head_range(hkv_total, world, rank)
     b, _, n, d = q.shape
+    if peer_output is not None:
+        # fused path: the combine of every pass stores into all ranks' output buffers
+        first = (rank * (h1 - h0) if local else h0) * g * d     # first feature of this rank's heads
+        peer_output.begin()
+        for a in range(h0, h1, heads_per_pass):
+            z = min(a + heads_per_pass, h1)
+            hs, qs = slice(a, z), slice(a * g, z * g)
+
+            def combine_into_peers(o_cmp, o_sel, o_swa, gts, offset=first + (a - h0) * g * d):
+                from . import ops
+                ops.gated_combine_gather(o_cmp, o_sel, o_swa, gts, peer_output.ptrs, peer_output.features, offset)
+
+            attend_core(q[:, qs], qr[:, qs], kr[:, hs], v[:, hs], ck[:, hs], cv[:, hs], gates[:, qs],
+                        combine=combine_into_peers, **cfg)
+        return peer_output.end()
     merged = torch.empty(b, n, (h1 - h0) * g * d, dtype=q.dtype, device=q.device)
     for a in range(h0, h1, heads_per_pass):
         z = min(a + heads_per_pass, h1)

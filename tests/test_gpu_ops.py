@@ -9,6 +9,7 @@ from oracle import nsa_oracle as O
 from util import assert_close_bf16, assert_close_f32, load_golden, same_selection
 
 import native_sparse_attention_pytorch_b200 as nsa
+from native_sparse_attention_pytorch_b200 import _lib as nsa_lib
 
 pytestmark = pytest.mark.gpu
 DEV = 'cuda'
@@ -270,3 +271,23 @@ def test_combine_matches_oracle(dtype):
     close(out, ref, 'out')
     for g, r, w in zip(gd, rd, ('d_cmp', 'd_sel', 'd_swa', 'd_gates')):
         close(g, r, w)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16])
+def test_combine_gather_writes_every_destination(dtype):
+    # the fused combine + all-gather kernel with its destinations on one GPU: two buffers stand for two ranks' outputs
+    from native_sparse_attention_pytorch_b200 import ops
+    b, h, n, d = 2, 4, 37, 32
+    os_ = [recipe.randn((b, h, n, d), s).to(dtype).to(DEV) for s in (1, 2, 3)]
+    gates = torch.sigmoid(recipe.randn((b, n, h * 3), 4)).to(dtype).to(DEV).view(b, n, h, 3).transpose(1, 2)
+    ref = O.combine(*[t.float().cpu() for t in os_], gates.float().cpu())
+    total, offset = 3 * h * d, h * d           # this "rank" owns the middle third of the features
+    outs = [torch.full((b, n, total), 7.0, dtype=dtype, device=DEV) for _ in range(2)]
+    ops.gated_combine_gather(*os_, gates, [t.data_ptr() for t in outs], total, offset)
+    close = closeness(dtype)
+    for t in outs:
+        close(t[..., offset:offset + h * d], ref, 'own features')
+        assert bool((t[..., :offset] == 7).all()) and bool((t[..., offset + h * d:] == 7).all())
+    with pytest.raises(nsa_lib.NsaError):
+        ops.gated_combine_gather(*os_, gates, [outs[0].data_ptr()], total, total - 8)      # heads do not fit
