@@ -601,6 +601,301 @@ __global__ void __launch_bounds__(256) sel_merge_kernel(const SelParams P) {
   if (part == 0) P.lse[row] = L > 0.f ? (M + log2f(L)) * kLn2 : -INFINITY;
 }
 
+// ---- forward of the dense causal branches, query-tile stationary ---------------------------------------------
+//
+// The compressed and the sliding-window branch attend a contiguous range of key blocks per query, the same range for
+// neighbouring queries.  For them the key-block-stationary form above pays for partial results it does not need: one
+// CTA here owns a tile of 128/G consecutive queries (128 rows with the G heads of the group), walks the key blocks
+// the tile can see and keeps the running maximum and sum of every row in registers and the output accumulator in
+// tensor memory, as a flash-attention forward does.  No index, no partial results, no merge.
+//   * S of block t+2 is issued as soon as P of block t has been handed to the PV MMA, so the tensor cores work on
+//     PV(t) and S(t+2) while the threads do the softmax of block t+1 (two S buffers in tensor memory, two K and two V
+//     buffers in shared memory, filled by TMA).
+//   * The accumulator is rescaled lazily: a row keeps its reference maximum until a block exceeds it by more than 2^8;
+//     only then is the O row read from tensor memory, scaled and written back (P stays below 2^8, exact in bf16's
+//     range, and the sum is fp32).
+//   * MODE compressed with IMP also writes the head-averaged logits of the visible columns (the importance).
+template <int D, int MODE, bool IMP>
+__global__ void __launch_bounds__(kRows, 2)
+dense_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const SelParams P) {
+  constexpr int NC = D / 64;
+  constexpr uint32_t kTileQ = NC * 16384, kTileKV = NC * 8192;
+  constexpr uint32_t kStageStride = D * 2 + 16;
+  constexpr uint32_t kCols = 256;
+  // The dynamic segment is declared 1024-byte aligned (the swizzled tiles need it) and holds exactly the tiles: with
+  // dim_head 128 two CTAs then fill an SM's shared memory to the byte.
+  extern __shared__ __align__(1024) uint8_t dense_smem[];
+  __shared__ int abort_flag;
+  __shared__ uint32_t tmem_slot;
+  __shared__ __align__(8) uint64_t bars[8];
+
+  const uint32_t base = smem_u32(dense_smem);
+  const uint32_t sQ = base, sP = sQ + kTileQ, sK0 = sP + 16384, sV0 = sK0 + 2 * kTileKV;
+  // the Q and P tiles become the staging area of the output rows at the end, followed by the rows' destinations
+  const uint32_t sStage = sQ;
+  int* const row_dst = reinterpret_cast<int*>(dense_smem + kRows * kStageStride);
+  // barriers: K buffers full (2), V buffers full (2), S buffers complete (2), PV complete, drain
+  const uint32_t bar0 = smem_u32(&bars[0]), bar_pv = bar0 + 48;
+  auto bar_k = [&](int t) { return bar0 + (uint32_t)(t & 1) * 8; };
+  auto bar_v = [&](int t) { return bar0 + 16 + (uint32_t)(t & 1) * 8; };
+  auto bar_s = [&](int t) { return bar0 + 32 + (uint32_t)(t & 1) * 8; };
+  const int tid = threadIdx.x, warp = tid >> 5;
+
+  if (tid == 0) {
+    abort_flag = 0;
+    for (int i = 0; i < 8; ++i) mbar_init(smem_u32(&bars[i]), 1);
+    if (base & 1023u) abort_flag = 1;   // the tiles would be mis-swizzled: report instead of computing
+    fence_mbar_init();
+    prefetch_tensormap(&tmK);
+    prefetch_tensormap(&tmV);
+  }
+  __syncthreads();
+  if (warp == 0) {
+    tmem_alloc(smem_u32(&tmem_slot), kCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tm = tmem_slot;
+  const uint32_t tm_lane = tm + ((uint32_t)(warp * 32) << 16);
+  const uint32_t tO = 128;
+  constexpr uint32_t idS = instr_desc_bf16(128, 64, false, false);
+  constexpr uint32_t idO = instr_desc_bf16(128, D, false, true);
+
+  // the tile: heavy tiles (late queries) are launched first
+  const int G = P.G, QT = kRows / G, g_shift = 31 - __clz(G);
+  const int tiles_per_head = (P.N + QT - 1) / QT;
+  const int64_t tile = (int64_t)gridDim.x - 1 - blockIdx.x;
+  const int qt = (int)(tile % tiles_per_head), bh = (int)(tile / tiles_per_head), h = bh % P.Hkv, b = bh / P.Hkv;
+  const int i0 = qt * QT, i_last = min(i0 + QT - 1, P.N - 1);
+  const int q_local = tid >> g_shift, g = tid - (q_local << g_shift);
+  const int i = i0 + q_local;
+  const bool valid = i < P.N;
+  const int64_t hq = (int64_t)h * G + g;
+  int jb, je;
+  if (MODE == kModeCmp) {
+    jb = 0;
+    je = min(P.nfb, (P.rule.num_mem + i_last / P.rule.stride + kBlock - 1) / kBlock);
+  } else {
+    jb = max(0, i0 - P.rule.window) / kBlock;
+    je = i_last / kBlock + 1;
+  }
+  const int nb = je - jb;
+
+  // Q rows of the tile (zero rows past the end of the sequence) and the first K/V blocks
+  {
+    constexpr int CH = D / 8, RPP = kRows / CH;
+    const int sub = tid % CH, r0 = tid / CH;
+    const __nv_bfloat16* qb = P.q + b * P.q_sb;
+#pragma unroll
+    for (int it = 0; it < CH; ++it) {
+      const int row = r0 + it * RPP;
+      const int qi = i0 + (row >> g_shift), gg = row & ((1 << g_shift) - 1);
+      const bool ok = qi < P.N;
+      cp_async16(sQ + (sub / 8) * (kRows * 128) + sw128_offset(row, sub % 8),
+                 qb + (int64_t)((h << g_shift) + gg) * P.q_sh + (int64_t)(ok ? qi : 0) * P.q_sn + sub * 8, ok ? 16u : 0u);
+    }
+    cp_async_commit();
+  }
+  auto load_k = [&](int t) {   // thread 0: key block jb + t into K buffer t & 1
+    mbar_arrive_expect_tx(bar_k(t), kTileKV);
+#pragma unroll
+    for (int c = 0; c < NC; ++c) tma_load_4d(sK0 + (t & 1) * kTileKV + c * 8192, &tmK, bar_k(t), c * 64, (jb + t) * kBlock, h, b);
+  };
+  auto load_v = [&](int t) {
+    mbar_arrive_expect_tx(bar_v(t), kTileKV);
+#pragma unroll
+    for (int c = 0; c < NC; ++c) tma_load_4d(sV0 + (t & 1) * kTileKV + c * 8192, &tmV, bar_v(t), c * 64, (jb + t) * kBlock, h, b);
+  };
+  auto issue_s = [&](int t) {   // warp 0, converged: S(t) = Q K(t)^T into S buffer t & 1
+    mbar_wait_bounded(bar_k(t), (uint32_t)(t >> 1) & 1, &abort_flag);
+    __syncwarp();
+    tc_fence_after_sync();
+    const uint32_t sK = sK0 + (t & 1) * kTileKV;
+#pragma unroll
+    for (int k = 0; k < D / 16; ++k) {
+      const uint32_t ch = k / 4, in = (k % 4) * 32;
+      mma_bf16_elect(tm + (t & 1) * 64, smem_desc_sw128(sQ + ch * 16384 + in, 16), smem_desc_sw128(sK + ch * 8192 + in, 16),
+                     idS, k > 0);
+    }
+    mma_commit_elect(bar_s(t));
+  };
+  if (tid == 0) {
+    load_k(0);
+    load_v(0);
+    if (nb > 1) load_k(1);
+  }
+  cp_async_wait<0>();
+  fence_proxy_async_smem();
+  __syncthreads();
+  if (warp == 0) {
+    issue_s(0);
+    if (nb > 1) issue_s(1);
+  }
+
+  float m_ref = -INFINITY, l = 0.f;
+  for (int t = 0; t < nb; ++t) {
+    const int j = jb + t, sb = t & 1;
+    __syncwarp();
+    mbar_wait_warp(bar_s(t), (uint32_t)(t >> 1) & 1, &abort_flag);
+    tc_fence_after_sync();
+    if (tid == 0 && t + 2 < nb) load_k(t + 2);   // S(t) is complete: its K buffer is free
+    __syncwarp();
+    float s[64];
+    {
+      float tt[32];
+      tmem_ld32(tm_lane + sb * 64, tt);
+      tmem_ld_wait();
+#pragma unroll
+      for (int x = 0; x < 32; ++x) s[x] = tt[x];
+      tmem_ld32(tm_lane + sb * 64 + 32, tt);
+      tmem_ld_wait();
+#pragma unroll
+      for (int x = 0; x < 32; ++x) s[32 + x] = tt[x];
+    }
+    // visible columns of this block for this row
+    int lo = 0, lim;
+    if (MODE == kModeCmp) {
+      lim = min(kBlock - 1, P.rule.num_mem + i / P.rule.stride - 1 - j * kBlock);
+    } else {
+      lim = min(kBlock - 1, i - j * kBlock);
+      lo = max(0, i - P.rule.window - j * kBlock);
+    }
+    if (!valid) lim = -1;
+    if constexpr (IMP) {
+      // the scaled logit of every visible block column, averaged over the G heads of the query (G neighbouring
+      // lanes), as the tensor of that dtype would hold it upstream: product, scaled logit and mean each rounded to
+      // bf16.  The G lanes reduce-scatter: every step a lane hands half of its columns to its partner and keeps the
+      // other half, so that it ends with 64/G fully summed columns, which it stores.
+      float v[64];
+#pragma unroll
+      for (int x = 0; x < 64; ++x) v[x] = round_bf16(round_bf16(s[x]) * P.scale);
+      int first = 0;
+#pragma unroll
+      for (int step = 0; step < 4; ++step) {
+        const int width = 32 >> step;
+        if ((1 << step) < G) {
+          const bool upper = (g >> step) & 1;
+#pragma unroll
+          for (int x = 0; x < 32; ++x) {
+            if (x < width) {
+              const float give = upper ? v[x] : v[x + width];
+              const float keep = upper ? v[x + width] : v[x];
+              v[x] = keep + __shfl_xor_sync(kFullMask, give, 1 << step);
+            }
+          }
+          first += upper ? width : 0;
+        }
+      }
+      const int owned = kBlock / G;
+      float* imp_row = P.importance + (((int64_t)b * P.Hkv + h) * P.N + (valid ? i : 0)) * P.ncb;
+      const float inv_g = 1.f / (float)G;
+#pragma unroll
+      for (int x = 0; x < 64; ++x) {
+        if (x < owned) {
+          const int col_in_block = first + x;
+          const int col = j * kBlock + col_in_block - P.rule.num_mem;
+          if (valid && col_in_block <= lim && col >= 0 && col < P.ncb) imp_row[col] = round_bf16(v[x] * inv_g);
+        }
+      }
+    }
+    float m = -INFINITY;
+#pragma unroll
+    for (int x = 0; x < 64; ++x) m = ((MODE == kModeCmp || x >= lo) && x <= lim) ? fmaxf(m, s[x]) : m;
+    const float m_blk2 = m * P.scale_log2;   // -inf when the row sees nothing of this block
+    bool need = false;
+    float alpha = 1.f;
+    if (m_ref == -INFINITY) {
+      m_ref = m_blk2;
+    } else if (m_blk2 > m_ref + 8.f) {
+      alpha = ex2(m_ref - m_blk2);
+      m_ref = m_blk2;
+      l *= alpha;
+      need = true;
+    }
+    if (t > 0 && __any_sync(kFullMask, need)) {
+      // some row of this warp outgrew its reference maximum: scale the accumulator rows (PV(t-1) must be complete)
+      mbar_wait_warp(bar_pv, (uint32_t)(t - 1) & 1, &abort_flag);
+      tc_fence_after_sync();
+#pragma unroll 1
+      for (int c2 = 0; c2 < D / 16; ++c2) {
+        float o[16];
+        tmem_ld16(tm_lane + tO + c2 * 16, o);
+        tmem_ld_wait();
+#pragma unroll
+        for (int x = 0; x < 16; ++x) o[x] *= alpha;
+        tmem_st16(tm_lane + tO + c2 * 16, o);
+      }
+      tmem_st_wait();
+    }
+#pragma unroll
+    for (int x = 0; x < 64; ++x) {
+      const float p = ((MODE == kModeCmp || x >= lo) && x <= lim) ? ex2(s[x] * P.scale_log2 - m_ref) : 0.f;
+      s[x] = p;
+      l += p;
+    }
+    if (t > 0) {   // PV(t-1) is complete: the P tile and V buffer (t-1) & 1 are free
+      mbar_wait_warp(bar_pv, (uint32_t)(t - 1) & 1, &abort_flag);
+      tc_fence_after_sync();
+    }
+    if (tid == 0 && t + 1 < nb) load_v(t + 1);
+    store_row_bf16(sP, tid, s);
+    fence_proxy_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) {
+      mbar_wait_bounded(bar_v(t), (uint32_t)(t >> 1) & 1, &abort_flag);
+      __syncwarp();
+      tc_fence_after_sync();
+      const uint32_t sV = sV0 + sb * kTileKV;
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        mma_bf16_elect(tm + tO, smem_desc_sw128(sP + k * 32, 16), smem_desc_sw128(sV + k * 2048, 8192), idO, t > 0 || k > 0);
+      mma_commit_elect(bar_pv);
+      if (t + 2 < nb) issue_s(t + 2);
+    }
+  }
+
+  // output rows: O / l through the staging area, whole 128-byte lines per store instruction
+  __syncwarp();
+  if (nb > 0) {
+    mbar_wait_warp(bar_pv, (uint32_t)(nb - 1) & 1, &abort_flag);
+    tc_fence_after_sync();
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  const int64_t row_global = ((int64_t)b * P.Hq + hq) * P.N + (valid ? i : 0);
+#pragma unroll
+  for (int c2 = 0; c2 < D / 32; ++c2) {
+    float tt[32];
+    tmem_ld32(tm_lane + tO + c2 * 32, tt);
+    tmem_ld_wait();
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      uint4 v;
+      v.x = pack_bf16(tt[x * 8 + 0] * inv, tt[x * 8 + 1] * inv);
+      v.y = pack_bf16(tt[x * 8 + 2] * inv, tt[x * 8 + 3] * inv);
+      v.z = pack_bf16(tt[x * 8 + 4] * inv, tt[x * 8 + 5] * inv);
+      v.w = pack_bf16(tt[x * 8 + 6] * inv, tt[x * 8 + 7] * inv);
+      sts_v4(sStage + tid * kStageStride + c2 * 64 + x * 16, v);
+    }
+  }
+  row_dst[tid] = valid && nb > 0 ? (int)row_global : -1;
+  __syncthreads();
+  store_rows_coalesced<D * 2>(sStage, kStageStride, row_dst, reinterpret_cast<uint8_t*>(P.out), tid);
+  if (valid) P.lse[row_global] = l > 0.f ? (m_ref + log2f(l)) * kLn2 : -INFINITY;
+
+  // nothing of this CTA may still be running on the tensor cores when tensor memory is freed
+  if (warp == 0) {
+    mma_commit_elect(smem_u32(&bars[7]));
+    mbar_wait_drain(smem_u32(&bars[7]), 0);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tm, kCols);
+  if (tid == 0 && abort_flag) atomicExch(P.status, 1);
+}
+
 // ---- backward --------------------------------------------------------------------------
 
 // delta[row] = sum_c out[row][c] * dout[row][c]; D/8 threads per row
@@ -1439,6 +1734,15 @@ static bool supported(const SelProblem& a) {
   return true;
 }
 
+// The forward of the compressed and the sliding-window branch runs query-tile stationary (dense_fwd_kernel) when the
+// output is a plain contiguous tensor; NSA_DENSE_FWD=0 keeps the key-block-stationary form for comparison.
+static bool dense_forward(const SelProblem& a) {
+  static const bool enabled = []() { const char* e = getenv("NSA_DENSE_FWD"); return e == nullptr || strcmp(e, "0") != 0; }();
+  if (!enabled || a.mode == kModeSel) return false;
+  if (a.mode == kModeCmp && a.num_mem < 1) return false;   // a query must see at least one key
+  return a.out.stride_n == a.D && a.out.stride_h == (int64_t)a.N * a.D && a.out.stride_b == (int64_t)a.Hq * a.N * a.D;
+}
+
 static SelPlan make_plan(const SelProblem& a, bool backward) {
   SelPlan p;
   p.nqb = (a.N + kBlock - 1) / kBlock;
@@ -1452,6 +1756,12 @@ static SelPlan make_plan(const SelProblem& a, bool backward) {
   int64_t off = 0;
   p.off_status = off; off += 256;
   p.off_num_items = p.off_status + 128;
+  if (!backward && dense_forward(a)) {   // only the status word is needed
+    p.off_counts = p.off_totals = p.off_list_base = p.off_items = p.off_entries = off;
+    p.off_partial = p.off_stats = p.off_delta = off;
+    p.total_bytes = off;
+    return p;
+  }
   p.off_counts = off; off = align_up(off + (int64_t)a.B * a.Hkv * p.nqb * p.nkb * 4, 256);
   p.off_totals = off; off = align_up(off + (int64_t)p.nlists * 4, 256);
   p.off_list_base = off; off = align_up(off + (int64_t)p.nlists * 4, 256);
@@ -1574,6 +1884,28 @@ static int run_fwd(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaStrea
   if (rc != NSA_OK) return rc;
   rc = make_kv_map(&tmV, a.v, a.B, a.Hkv, a.Nk, D);
   if (rc != NSA_OK) return rc;
+  if (dense_forward(a)) {
+    CUDA_TRY(cudaMemsetAsync(ws + p.off_status, 0, 256, st));
+    SelParams P;
+    fill_params(P, a, p, ws);
+    const int QT = kRows / p.G;
+    const int64_t tiles = (int64_t)a.B * a.Hkv * ((a.N + QT - 1) / QT);
+    if (tiles > 0x7fffffffLL) return NSA_ERR_UNSUPPORTED;
+    const int smem = (D / 64) * 16384 + 16384 + 4 * (D / 64) * 8192;
+#define NSA_DENSE_LAUNCH(MODE, IMP)                                                                                  \
+    do {                                                                                                              \
+      CUDA_TRY(cudaFuncSetAttribute(dense_fwd_kernel<D, MODE, IMP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
+      CUDA_TRY(cudaFuncSetAttribute(dense_fwd_kernel<D, MODE, IMP>, cudaFuncAttributePreferredSharedMemoryCarveout,   \
+                                    cudaSharedmemCarveoutMaxShared));                                                 \
+      dense_fwd_kernel<D, MODE, IMP><<<(unsigned)tiles, kRows, smem, st>>>(tmK, tmV, P);                              \
+    } while (0)
+    if (a.mode == kModeSwa) NSA_DENSE_LAUNCH(kModeSwa, false);
+    else if (P.importance != nullptr) NSA_DENSE_LAUNCH(kModeCmp, true);
+    else NSA_DENSE_LAUNCH(kModeCmp, false);
+#undef NSA_DENSE_LAUNCH
+    CUDA_TRY(cudaGetLastError());
+    return NSA_OK;
+  }
   rc = build_index(a, p, ws, st);
   if (rc != NSA_OK) return rc;
   SelParams P;
