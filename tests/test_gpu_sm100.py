@@ -193,6 +193,40 @@ def test_sm100_compressed_matches_oracle(case):
     assert_close_bf16(torch.where(vis, imp.cpu(), 0), torch.where(vis, imp_simt.cpu(), 0), 'importance vs simt', tol=6e-2)
 
 
+@pytest.mark.parametrize('d', [64, 128])
+def test_dense_forward_rescales_when_later_keys_dominate(d):
+    # Keys grow with their position, so the running maximum of a row jumps by far more than 2^8 from one key block to
+    # the next: the query-tile-stationary forward must rescale its accumulator (its lazy path), also for rows whose
+    # first blocks hold nothing visible (sliding window) and for both halves of a 128-wide head.
+    b, hq, hkv, n, win, st, m = 1, 8, 2, 700, 200, 2, 1
+    q = recipe.randn((b, hq, n, d), 1).bfloat16()
+    grow = (1.0 + 20.0 * (torch.arange(n) // 64).float() / (n // 64)).view(1, 1, n, 1)
+    k = (recipe.randn((b, hkv, n, d), 2) * grow).bfloat16()
+    v = recipe.randn((b, hkv, n, d), 3).bfloat16()
+    ref = O.sliding_attend(q.float(), k.float(), v.float(), win, True)
+    out = nsa.sliding_window_attend(q.to(DEV), k.to(DEV), v.to(DEV), win, True, impl='sm100')
+    ops.check_device_status()
+    assert_close_bf16(out, ref, 'sliding out')
+    ncb = n // st
+    growc = (1.0 + 20.0 * (torch.arange(ncb) // 64).float() / (ncb // 64)).view(1, 1, ncb, 1)
+    ck = (recipe.randn((b, hkv, ncb, d), 4) * growc).bfloat16()
+    cv = recipe.randn((b, hkv, ncb, d), 5).bfloat16()
+    mem = recipe.randn((2, hkv, m, d), 6).bfloat16()
+    ref, csim = O.compressed_attend(q.float(), ck.float(), cv.float(), mem[0].float(), mem[1].float(), st, True)
+    ckf = torch.cat((mem[0].expand(b, -1, -1, -1), ck), dim=-2).to(DEV)
+    cvf = torch.cat((mem[1].expand(b, -1, -1, -1), cv), dim=-2).to(DEV)
+    out, imp = nsa.compressed_attend(q.to(DEV), ckf, cvf, m, st, True, impl='sm100')
+    ops.check_device_status()
+    assert_close_bf16(out, ref, 'compressed out')
+    ref_imp = csim[..., m:].reshape(b, hkv, hq // hkv, n, ncb).mean(dim=2)
+    vis = ref_imp > -1e30
+    assert torch.equal(vis, imp.cpu() > -1e30)
+    # logits reach a hundred here and a head mean near zero is a sum of such terms, each rounded to bf16 on the way:
+    # compare relative to the largest logit
+    assert_close_bf16(torch.where(vis, imp.cpu(), 0), torch.where(vis, ref_imp, 0), 'importance', tol=6e-2, roundings=2,
+                      rel_to_max=5e-3)
+
+
 def test_sm100_layer_bf16_uses_tensor_core_branches():
     # a whole layer at a shape all three branches serve on tensor cores, against the fp32 oracle
     from native_sparse_attention_pytorch_b200 import SparseAttention
