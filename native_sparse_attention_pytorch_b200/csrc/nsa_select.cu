@@ -85,7 +85,127 @@ __global__ void __launch_bounds__(128) select_kernel(const SelectParams P, int w
   }
 }
 
+// The same selection with the row in registers: lane l holds columns l, l+32, ... (CPL of them), the arithmetic and its
+// order are those of select_kernel (so both pick the same blocks), but every top-k round is a scan of the lane's own
+// live entries, one warp-wide maximum over order-preserving integer keys and one warp-wide minimum over the column
+// indices of the lanes that hold that maximum; the k results are written by k lanes at the end.
+__device__ __forceinline__ unsigned ordered_bits(float v) {
+  const unsigned u = __float_as_uint(v);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float from_ordered_bits(unsigned k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
+template <int CPL>
+__global__ void __launch_bounds__(128) select_reg_kernel(const SelectParams P) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t task = (int64_t)blockIdx.x * 4 + warp;
+  if (task >= (int64_t)P.rows * P.seq) return;
+  const int i = (int)(task % P.seq);
+  const float* src = P.imp + task * P.ncb;
+  const bool vec4 = P.cpf == 4 && (P.ncb & 3) == 0 && (reinterpret_cast<uintptr_t>(P.imp) & 15u) == 0;
+  float v[CPL];
+  unsigned alive = 0;
+#pragma unroll
+  for (int t = 0; t < CPL; ++t) {
+    const int j = lane + 32 * t;
+    v[t] = 0.f;
+    if (j < P.cols) {
+      alive |= 1u << t;
+      float x;
+      if (P.cpf == 1) {
+        x = src[j];
+      } else {
+        float sum = 0.f;
+        if (vec4) {
+          const float4 q = *reinterpret_cast<const float4*>(src + j * 4);
+          sum = ((sum + q.x) + q.y) + q.z + q.w;
+        } else {
+          for (int c = 0; c < P.cpf; ++c) sum += src[j * P.cpf + c];
+        }
+        x = sum / (float)P.cpf;
+        if (P.round_bf16) x = round_bf16(x);
+      }
+      if (!P.input_is_prob && P.exclude_own && j == i / P.block) x = P.neg_max;
+      v[t] = x;
+    }
+  }
+  if (!P.input_is_prob) {
+    float mx = -1000.f;  // the sink logit
+#pragma unroll
+    for (int t = 0; t < CPL; ++t)
+      if (alive >> t & 1) mx = fmaxf(mx, v[t]);
+    mx = warp_max(mx);
+    float part = 0.f;
+#pragma unroll
+    for (int t = 0; t < CPL; ++t) {
+      if (alive >> t & 1) {
+        v[t] = expf(v[t] - mx);
+        part += v[t];
+      }
+    }
+    const float z = warp_sum(part) + expf(-1000.f - mx);
+#pragma unroll
+    for (int t = 0; t < CPL; ++t) {
+      if (alive >> t & 1) {
+        float p = v[t] / z;
+        if (P.round_bf16) p = round_bf16(p);
+        v[t] = p;
+      }
+    }
+  }
+  unsigned key[CPL];
+#pragma unroll
+  for (int t = 0; t < CPL; ++t) key[t] = ordered_bits(v[t]);
+
+  int my_idx = 0;        // lane r ends up with the r-th pick
+  float my_val = 0.f;
+  for (int r = 0; r < P.k; ++r) {
+    unsigned best = 0;
+    int best_t = -1;
+#pragma unroll
+    for (int t = 0; t < CPL; ++t) {
+      if ((alive >> t & 1) && (best_t < 0 || key[t] > best)) {   // strict: the lower column wins a tie
+        best = key[t];
+        best_t = t;
+      }
+    }
+    const unsigned top = __reduce_max_sync(kFullMask, best_t >= 0 ? best : 0u);
+    const unsigned cand = (best_t >= 0 && best == top) ? (unsigned)(lane + 32 * best_t) : 0xffffffffu;
+    const unsigned win = __reduce_min_sync(kFullMask, cand);
+    if (win != 0xffffffffu) {
+      if ((int)(win & 31u) == lane) alive &= ~(1u << (win >> 5));
+      if (lane == r) {
+        my_idx = (int)win;
+        my_val = from_ordered_bits(top);
+      }
+    }
+  }
+  if (lane < P.k) {
+    P.idx[task * P.k + lane] = my_idx;
+    P.vals[task * P.k + lane] = my_val;
+  }
+}
+
 int launch_select(const SelectParams& P, cudaStream_t stream) {
+  {
+    const int64_t tasks = (int64_t)P.rows * P.seq;
+    if (tasks == 0 || P.k == 0) return NSA_OK;
+    const int64_t blocks = (tasks + 3) / 4;
+    if (P.k <= 32 && P.cols <= 1024 && blocks <= 0x7fffffffLL) {
+      const unsigned grid = (unsigned)blocks;
+      if (P.cols <= 32) select_reg_kernel<1><<<grid, 128, 0, stream>>>(P);
+      else if (P.cols <= 64) select_reg_kernel<2><<<grid, 128, 0, stream>>>(P);
+      else if (P.cols <= 128) select_reg_kernel<4><<<grid, 128, 0, stream>>>(P);
+      else if (P.cols <= 256) select_reg_kernel<8><<<grid, 128, 0, stream>>>(P);
+      else if (P.cols <= 512) select_reg_kernel<16><<<grid, 128, 0, stream>>>(P);
+      else select_reg_kernel<32><<<grid, 128, 0, stream>>>(P);
+      const cudaError_t err = cudaGetLastError();
+      if (err != cudaSuccess) return fail((int)err, cudaGetErrorString(err));
+      return NSA_OK;
+    }
+  }
   const int64_t tasks = (int64_t)P.rows * P.seq;
   if (tasks == 0 || P.k == 0) return NSA_OK;
   const size_t per_warp = (size_t)P.cols * sizeof(float);
