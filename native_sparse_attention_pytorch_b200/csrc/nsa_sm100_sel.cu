@@ -1183,7 +1183,7 @@ namespace ws {
 constexpr int kStages = 3;
 constexpr uint32_t kMetaBytes = 3 * kRows * 4;   // per stage: entry, lse, delta of every row of the chunk
 constexpr uint32_t kPBytes = 32768;   // P and dS tiles
-constexpr uint32_t kDqRow = 80;       // staged half dQ row: 64 bytes + 16 of padding (conflict-free 16-byte stores)
+constexpr uint32_t kDqRow = 64;       // staged half dQ row; its 16-byte pieces are swizzled with the row pair's index
 constexpr uint32_t kDqStage = 32 * kDqRow;   // per softmax warp
 constexpr int kThreads = 14 * 32;
 constexpr int kLoaderThreads = 128;
@@ -1277,14 +1277,14 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
           uint4 v;
           v.x = pack_bf16(tq[x * 8 + 0], tq[x * 8 + 1]); v.y = pack_bf16(tq[x * 8 + 2], tq[x * 8 + 3]);
           v.z = pack_bf16(tq[x * 8 + 4], tq[x * 8 + 5]); v.w = pack_bf16(tq[x * 8 + 6], tq[x * 8 + 7]);
-          sts_v4(sDq + lane * kDqRow + x * 16, v);
+          sts_v4(sDq + lane * kDqRow + ((x ^ ((lane >> 1) & 3)) << 4), v);   // conflict-free to write and to read
         }
         __syncwarp();
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const int rr = k * 8 + (lane >> 2);
           const int dst = __shfl_sync(kFullMask, prev_dst, rr);
-          const uint4 v = lds_v4(sDq + rr * kDqRow + (lane & 3) * 16);
+          const uint4 v = lds_v4(sDq + rr * kDqRow + (((lane & 3) ^ ((rr >> 1) & 3)) << 4));
           if (dst >= 0)
             *reinterpret_cast<uint4*>(pbase + (int64_t)dst * (D * 2) + half * 64 + (lane & 3) * 16) = v;
         }
