@@ -64,8 +64,8 @@ PREFILL_WORKLOADS = {
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the main backward kernel, from an ncu capture of this
 # command (profiles/tcgen05_selected_attention_b4_n8192_h32kv4_d64.md, profiles/simt_selected_attention_...md).
 NCU_TRAFFIC = {
-    (DEFAULT_WORKLOAD, 'auto'): 602.3e6 + 2188.4e6,
-    (DEFAULT_WORKLOAD, 'sm100'): 602.3e6 + 2188.4e6,
+    (DEFAULT_WORKLOAD, 'auto'): 703.7e6 + 2202.2e6,
+    (DEFAULT_WORKLOAD, 'sm100'): 703.7e6 + 2202.2e6,
     (DEFAULT_WORKLOAD, 'simt'): 531.8e6 + 300.4e6,
 }
 
@@ -744,9 +744,51 @@ def run_prefill(args, w):
                 'steps': e2e_steps},
         'gpu_launches': (3 * 6 + 2) * (h1 - h0) * args.steps, 'clocks': clocks,
     }
+    if args.rows and world == 1:
+        line['rows'] = prefill_rows(w, t, flush)
     if not args.no_cpu_baseline and world == 1:
         line['cpu_baseline'] = prefill_cpu_sample(w)
     print(json.dumps(line))
+
+
+def prefill_rows(w, t, flush, iters=5):
+    """The five operators of ONE KV head of the prefill workload, timed one by one (ms, CUDA events, L2 flushed)."""
+    from native_sparse_attention_pytorch_b200 import ops
+    g = w['q_heads'] // w['kv_heads']
+    q, qr, kr, v, ck, cv, gates = (t[k][:, :(g if k in ('q', 'qr', 'gates') else 1)]
+                                   for k in ('q', 'qr', 'kr', 'v', 'ck', 'cv', 'gates'))
+    h, rows = {}, {}
+
+    def timed(fn):
+        for _ in range(2):
+            fn()
+        evs = []
+        for i in range(iters):
+            flush.fill_(i)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            evs.append((e0, e1))
+        torch.cuda.synchronize()
+        return sum(a.elapsed_time(b) for a, b in evs) / iters
+
+    def cmp():
+        h['o'], h['imp'] = ops.compressed_attend(q, ck, cv, w['num_mem'], w['stride'], True, sel_heads=1,
+                                                 want_importance=True)
+    rows['compressed_fwd'] = timed(cmp)
+    def sel():
+        h['vals'], h['idx'] = ops.select_blocks(h['imp'], w['block'], w['stride'], w['nsel'], dtype=torch.bfloat16)
+    rows['select'] = timed(sel)
+    mask = h['vals'] > 1e-10
+    def selected():
+        h['os'] = ops.native_sparse_attend(qr, kr, v, w['block'], h['idx'], mask)
+    rows['selected_fwd'] = timed(selected)
+    def swa():
+        h['ow'] = ops.sliding_window_attend(qr, kr, v, w['window'], True)
+    rows['sliding_fwd'] = timed(swa)
+    rows['combine_fwd'] = timed(lambda: ops.gated_combine(h['o'], h['os'], h['ow'], gates))
+    return {k: {'ms': ms} for k, ms in rows.items()}
 
 
 def oracle_core_fns(num_mem):
