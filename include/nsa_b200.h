@@ -318,9 +318,26 @@ typedef struct {
 
 int nsa_combine_fwd_gather(const nsa_combine_gather_args* args, void* stream);
 
+/* Rotary position embedding of the queries / keys that feed the selected and the sliding branch: replaces the calls
+ * into the third-party rotary_embedding_torch package at NSA:643 (rotate_queries_with_cached_keys) and NSA:384-385
+ * (rotate_queries_or_keys).  out[b,h,n,2m]   = x[2m] cos[n,m] - x[2m+1] sin[n,m],
+ *                        out[b,h,n,2m+1] = x[2m+1] cos[n,m] + x[2m] sin[n,m]   (fp32 arithmetic, no contraction);
+ * `inverse` != 0 rotates by the negative angle, which is the backward of the forward rotation.  The tables hold the
+ * angles of the positions the caller wants (an offset for cached keys is the caller's choice of table rows). */
+typedef struct {
+  nsa_tensor x;                   /* [B, H, N, d] view, last axis contiguous, rows 16-byte aligned */
+  void* out;                      /* [B, H, N, d] contiguous, same dtype, written                  */
+  const float* cos_table;         /* [N, d/2] fp32                                                 */
+  const float* sin_table;         /* [N, d/2] fp32                                                 */
+  int32_t batch, heads, seq, dim_head, dtype, inverse;
+} nsa_rotary_args;
+
+int nsa_rotary(const nsa_rotary_args* args, void* stream);
+
 /* Library information.  nsa_struct_size(i) is sizeof() of the i-th argument
  * struct in declaration order (0 nsa_tensor, 1 sel_fwd, 2 sel_bwd, 3 cmp_fwd,
- * 4 cmp_bwd, 5 select, 6 swa_fwd, 7 swa_bwd, 8 combine_fwd, 9 combine_bwd, 10 combine_gather), so
+ * 4 cmp_bwd, 5 select, 6 swa_fwd, 7 swa_bwd, 8 combine_fwd, 9 combine_bwd, 10 combine_gather,
+ * 11 rotary), so
  * a foreign-function binding can verify its own layout; -1 for other i. */
 const char* nsa_last_error(void);
 int nsa_abi_version(void);

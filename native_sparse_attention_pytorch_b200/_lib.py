@@ -79,12 +79,17 @@ class CombineGatherArgs(C.Structure):
                 ('total_features', i64), ('feature_offset', i64)]
 
 
+class RotaryArgs(C.Structure):
+    _fields_ = [('x', Tensor4), ('out', vp), ('cos_table', vp), ('sin_table', vp), ('batch', i32), ('heads', i32),
+                ('seq', i32), ('dim_head', i32), ('dtype', i32), ('inverse', i32)]
+
+
 _STRUCTS = [Tensor4, SelFwdArgs, SelBwdArgs, CmpFwdArgs, CmpBwdArgs, SelectArgs, SwaFwdArgs, SwaBwdArgs,
-            CombineFwdArgs, CombineBwdArgs, CombineGatherArgs]
+            CombineFwdArgs, CombineBwdArgs, CombineGatherArgs, RotaryArgs]
 
 ENTRY_POINTS = ['nsa_sel_fwd', 'nsa_sel_bwd', 'nsa_sel_workspace_bytes', 'nsa_sel_fwd_static',
                 'nsa_sel_static_scratch_bytes', 'nsa_cmp_workspace_bytes', 'nsa_swa_workspace_bytes', 'nsa_cmp_fwd', 'nsa_cmp_bwd', 'nsa_select',
-                'nsa_swa_fwd', 'nsa_swa_bwd', 'nsa_combine_fwd', 'nsa_combine_bwd', 'nsa_combine_fwd_gather', 'nsa_last_error',
+                'nsa_swa_fwd', 'nsa_swa_bwd', 'nsa_combine_fwd', 'nsa_combine_bwd', 'nsa_combine_fwd_gather', 'nsa_rotary', 'nsa_last_error',
                 'nsa_abi_version', 'nsa_struct_size']
 
 _lib = None

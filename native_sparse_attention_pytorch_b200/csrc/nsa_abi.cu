@@ -110,6 +110,7 @@ int nsa_struct_size(int which) {
     case 8: return (int)sizeof(nsa_combine_fwd_args);
     case 9: return (int)sizeof(nsa_combine_bwd_args);
     case 10: return (int)sizeof(nsa_combine_gather_args);
+    case 11: return (int)sizeof(nsa_rotary_args);
     default: return -1;
   }
 }
@@ -393,6 +394,24 @@ int nsa_combine_bwd(const nsa_combine_bwd_args* a, void* stream) {
   P.d_o[0] = a->d_cmp; P.d_o[1] = a->d_sel; P.d_o[2] = a->d_swa;
   P.d_gates = a->d_gates;
   return launch_combine(P, a->fwd.dtype, true, (cudaStream_t)stream);
+}
+
+int nsa_rotary(const nsa_rotary_args* a, void* stream) {
+  if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
+  if (a->dtype != NSA_F32 && a->dtype != NSA_BF16) return fail(NSA_ERR_DTYPE, "dtype must be NSA_F32 or NSA_BF16");
+  const int V = a->dtype == NSA_F32 ? 4 : 8;
+  if (a->batch < 0 || a->heads < 0 || a->seq < 0 || a->dim_head <= 0 || a->dim_head % V)
+    return fail(NSA_ERR_SHAPE, "negative size, or dim_head not a multiple of 16 bytes");
+  if ((int64_t)a->batch * a->heads * a->seq == 0) return NSA_OK;
+  if (!a->x.ptr || !a->out || !a->cos_table || !a->sin_table) return fail(NSA_ERR_NULL, "tensor: NULL pointer");
+  if ((reinterpret_cast<uintptr_t>(a->x.ptr) & 15u) || (reinterpret_cast<uintptr_t>(a->out) & 15u) ||
+      a->x.stride_b % V || a->x.stride_h % V || a->x.stride_n % V)
+    return fail(NSA_ERR_ALIGN, "x and out must keep 16-byte pieces aligned");
+  RotaryParams P;
+  P.x = a->x.ptr; P.out = a->out; P.cos = a->cos_table; P.sin = a->sin_table;
+  P.x_sb = a->x.stride_b; P.x_sh = a->x.stride_h; P.x_sn = a->x.stride_n;
+  P.batch = a->batch; P.heads = a->heads; P.seq = a->seq; P.d = a->dim_head; P.inverse = a->inverse;
+  return launch_rotary(P, a->dtype, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -62,11 +62,20 @@ struct GatherTargets {
   int64_t total_features, feature_offset;
 };
 
+struct RotaryParams {
+  const void* x;
+  void* out;
+  const float *cos, *sin;
+  int64_t x_sb, x_sh, x_sn;
+  int batch, heads, seq, d, inverse;
+};
+
 int fail(int code, const char* msg);
 
 int simt_attend(const AttnParams& P, int branch, int dtype, bool backward, cudaStream_t stream);
 int launch_select(const SelectParams& P, cudaStream_t stream);
 int launch_combine(const CombineParams& P, int dtype, bool backward, cudaStream_t stream);
+int launch_rotary(const RotaryParams& P, int dtype, cudaStream_t stream);
 int launch_combine_gather(const CombineParams& P, const GatherTargets& Gt, int dtype, cudaStream_t stream);
 
 // Tensor-core family for the selected-block branch.  Each returns

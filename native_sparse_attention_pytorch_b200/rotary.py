@@ -1,10 +1,49 @@
 """Rotary position embedding used in front of the selected and sliding
 branches (upstream call sites NSA:238, NSA:643).  Convention: inverse
 frequency theta^(-2m/d) on the adjacent feature pair (2m, 2m+1), angles in
-fp32, result in the input dtype.  Plain PyTorch: it produces inputs of the
-hot path and is not part of it."""
+fp32, result in the input dtype.  On CUDA tensors the rotation is one kernel
+of the library (`nsa_rotary`) over tables of cos / sin built here; CPU tensors
+(host-side tests) take the same formula in plain PyTorch."""
+import ctypes as C
+
 import torch
 from torch import nn
+from torch.autograd import Function
+
+
+def _tables(inv_freq, n, offset, device):
+    pos = torch.arange(n, device=device, dtype=torch.float32) + offset
+    ang = pos[:, None] * inv_freq.to(device)[None, :]
+    return ang.cos().contiguous(), ang.sin().contiguous()
+
+
+class _Rotate(Function):
+    """out = rotation of every feature pair of x [B, H, N, d] by the angles of the tables [N, d/2]."""
+
+    @staticmethod
+    def forward(ctx, x, cos, sin):
+        ctx.save_for_backward(cos, sin)
+        return _launch(x, cos, sin, inverse=False)
+
+    @staticmethod
+    def backward(ctx, grad):
+        cos, sin = ctx.saved_tensors
+        return _launch(grad, cos, sin, inverse=True), None, None
+
+
+def _launch(x, cos, sin, inverse):
+    from . import _lib as L
+    lib = L.load()
+    v = 16 // x.element_size()
+    if x.stride(-1) != 1 or x.data_ptr() % 16 or any(s % v for s in x.stride()[:-1]):
+        x = x.contiguous()
+    b, h, n, d = x.shape
+    out = torch.empty(b, h, n, d, dtype=x.dtype, device=x.device)
+    args = L.RotaryArgs(x=L.t4(x), out=L.ptr(out), cos_table=L.ptr(cos), sin_table=L.ptr(sin), batch=b, heads=h,
+                        seq=n, dim_head=d, dtype=L.dtype_code(x), inverse=1 if inverse else 0)
+    with torch.cuda.device(x.device):
+        L.check(lib.nsa_rotary(C.byref(args), L.stream_of(x)))
+    return out
 
 
 class RotaryEmbedding(nn.Module):
@@ -14,10 +53,11 @@ class RotaryEmbedding(nn.Module):
 
     def rotate_queries_or_keys(self, t, offset=0):
         n = t.shape[-2]
-        pos = torch.arange(n, device=t.device, dtype=torch.float32) + offset
-        ang = pos[:, None] * self.inv_freq.to(t.device)[None, :]
-        cos = ang.cos().repeat_interleave(2, dim=-1)
-        sin = ang.sin().repeat_interleave(2, dim=-1)
+        cos, sin = _tables(self.inv_freq, n, offset, t.device)
+        if t.is_cuda and t.dim() == 4 and t.dtype in (torch.float32, torch.bfloat16) and \
+                t.shape[-1] % (16 // t.element_size()) == 0:
+            return _Rotate.apply(t, cos, sin)
+        cos, sin = cos.repeat_interleave(2, dim=-1), sin.repeat_interleave(2, dim=-1)
         x = t.float()
         even, odd = x[..., 0::2], x[..., 1::2]
         rotated = torch.stack((-odd, even), dim=-1).flatten(-2)

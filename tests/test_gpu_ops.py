@@ -291,3 +291,26 @@ def test_combine_gather_writes_every_destination(dtype):
         assert bool((t[..., :offset] == 7).all()) and bool((t[..., offset + h * d:] == 7).all())
     with pytest.raises(nsa_lib.NsaError):
         ops.gated_combine_gather(*os_, gates, [outs[0].data_ptr()], total, total - 8)      # heads do not fit
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16])
+def test_rotary_kernel_matches_oracle(dtype):
+    from native_sparse_attention_pytorch_b200.rotary import RotaryEmbedding
+    b, h, n, d = 2, 3, 77, 32
+    base = recipe.randn((b, n, h * d), 1).to(dtype)                 # heads as a strided view, as after to_qkv
+    up = recipe.randn((b, h, n, d), 2).to(dtype)
+    for offset in (0, 5):
+        xr = base.float().view(b, n, h, d).transpose(1, 2).requires_grad_()
+        ref = O.rotary(xr, offset=offset)
+        (rg,) = torch.autograd.grad((ref * up.float()).sum(), xr)
+        xg = base.to(DEV).view(b, n, h, d).transpose(1, 2).requires_grad_()
+        out = RotaryEmbedding(d).to(DEV).rotate_queries_or_keys(xg, offset=offset)
+        (gg,) = torch.autograd.grad((out * up.to(DEV)).sum(), xg)
+        assert out.is_contiguous() and out.dtype == dtype
+        if dtype == torch.float32:
+            assert_close_f32(out, ref, 'out', tol=2e-6)              # same fp32 operations; cos/sin tables from the GPU
+            assert_close_f32(gg, rg, 'd x')
+        else:
+            assert_close_bf16(out, ref, 'out')
+            assert_close_bf16(gg, rg, 'd x')
