@@ -136,19 +136,35 @@ __global__ void __launch_bounds__(kBlock) sel_hist_kernel(const BlockRule R, int
   for (int j = threadIdx.x; j < R.nkb; j += kBlock) row[j] = hist[j];
 }
 
-// per list: exclusive prefix over the contributing query blocks, and the list total
-__global__ void sel_scan_kernel(int* counts, int* totals, int nlists, int nqb, int nkb) {
-  const int l = blockIdx.x * blockDim.x + threadIdx.x;
-  if (l >= nlists) return;
-  const int bh = l / nkb, j = l - bh * nkb;
+// per list: exclusive prefix over the contributing query blocks, and the list total.  A block handles 32
+// neighbouring lists (threadIdx.x, so that loads stay coalesced) with kScanSeg threads each (threadIdx.y): every
+// thread sums its segment of query blocks, the segments' sums are prefixed through shared memory, and a second pass
+// over the segment writes the prefixes.
+constexpr int kScanSeg = 8;
+__global__ void __launch_bounds__(32 * kScanSeg) sel_scan_kernel(int* counts, int* totals, int nlists, int nqb, int nkb) {
+  __shared__ int seg_sum[kScanSeg][32];
+  const int l = blockIdx.x * 32 + threadIdx.x, seg = threadIdx.y;
+  const bool live = l < nlists;
+  const int bh = live ? l / nkb : 0, j = live ? l - bh * nkb : 0;
+  const int per = (nqb + kScanSeg - 1) / kScanSeg;
+  const int q0 = min(nqb, seg * per), q1 = min(nqb, q0 + per);
+  int* base = counts + (int64_t)bh * nqb * nkb + j;
+  int sum = 0;
+  if (live)
+    for (int qb = q0; qb < q1; ++qb) sum += base[(int64_t)qb * nkb];
+  seg_sum[seg][threadIdx.x] = sum;
+  __syncthreads();
   int running = 0;
-  for (int qb = 0; qb < nqb; ++qb) {
-    int* c = counts + ((int64_t)bh * nqb + qb) * nkb + j;
-    const int v = *c;
-    *c = running;
-    running += v;
+  for (int k = 0; k < seg; ++k) running += seg_sum[k][threadIdx.x];
+  if (live) {
+    for (int qb = q0; qb < q1; ++qb) {
+      int* c = base + (int64_t)qb * nkb;
+      const int v = *c;
+      *c = running;
+      running += v;
+    }
+    if (seg == kScanSeg - 1) totals[l] = running;
   }
-  totals[l] = running;
 }
 
 // list bases (padded to whole chunks) and the item table; one CTA of 1024 threads
@@ -1840,7 +1856,7 @@ static int build_index(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaS
   if (a.mode == kModeSel) sel_hist_kernel<kModeSel><<<grid, kBlock, hist_smem, st>>>(R, counts);
   else if (a.mode == kModeSwa) sel_hist_kernel<kModeSwa><<<grid, kBlock, hist_smem, st>>>(R, counts);
   else sel_hist_kernel<kModeCmp><<<grid, kBlock, hist_smem, st>>>(R, counts);
-  sel_scan_kernel<<<(p.nlists + 127) / 128, 128, 0, st>>>(counts, totals, p.nlists, p.nqb, p.nkb);
+  sel_scan_kernel<<<(p.nlists + 31) / 32, dim3(32, kScanSeg), 0, st>>>(counts, totals, p.nlists, p.nqb, p.nkb);
   sel_items_kernel<<<1, 1024, 0, st>>>(totals, list_base, items, num_items, p.nlists, p.QT);
   if (a.mode == kModeSel) sel_fill_kernel<kModeSel><<<grid, kBlock, hist_smem, st>>>(R, counts, list_base, entries);
   else if (a.mode == kModeSwa) sel_fill_kernel<kModeSwa><<<grid, kBlock, hist_smem, st>>>(R, counts, list_base, entries);
