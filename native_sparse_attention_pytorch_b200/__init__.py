@@ -1,4 +1,5 @@
 """B200-native Native Sparse Attention hot path (sm_100a CUDA kernels behind a C ABI)."""
+from . import ops
 from .native_sparse_attention import SparseAttention
 from .ops import (
     native_sparse_attend,
