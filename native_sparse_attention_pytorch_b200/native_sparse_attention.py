@@ -132,8 +132,6 @@ class SparseAttention(Module):
                                'use_triton_kernel=True and do not pass disable_triton_kernel')
         if sliding_window_flex_mask is not None or fine_selection_flex_mask is not None:
             raise RuntimeError('flex-attention masks select another backend upstream; this package has one backend')
-        if self.use_diff_topk:
-            raise NotImplementedError('use_diff_topk (gradient through the selection scores) is not built yet')
         if not inp.is_cuda:
             raise RuntimeError('SparseAttention (B200 kernels) needs CUDA tensors; there is no CPU path here')
         assert not (not self.causal and return_cache)
@@ -181,9 +179,14 @@ class SparseAttention(Module):
         # branch 2: block selection, then attention over the selected blocks
         idx = vals = fmask = None
         if num_selected > 0:
-            vals, idx = ops.select_blocks(importance, sel, st, num_selected, dtype=q.dtype)
+            vals, idx = ops.select_blocks(importance if self.use_diff_topk else importance.detach(), sel, st,
+                                          num_selected, dtype=q.dtype)
             fmask = vals > 1e-10
-            o_sel = ops.native_sparse_attend(qr, kr, v, sel, idx, fmask, include_block_causal=self.causal, impl=impl)
+            # differentiable top-k (NSA:715): the slots are scaled by 1 in the forward, the gradient of that scale
+            # reaches the selected probabilities and through them the compressed logits
+            slot_scale = vals + (1. - vals).detach() if self.use_diff_topk else None
+            o_sel = ops.native_sparse_attend(qr, kr, v, sel, idx, fmask, sel_scale=slot_scale,
+                                             include_block_causal=self.causal, impl=impl)
         else:
             o_sel = ops.block_diagonal_attend(qr, kr, v, sel, self.causal, impl=impl)
 

@@ -180,17 +180,18 @@ class CompressedAttention(Function):
             del ws
         ctx.save_for_backward(q, ck, cv, out, lse)
         ctx.cfg = (num_mem, stride, causal, sel_heads, impl, scale)
+        ctx.set_materialize_grads(False)   # no gradient through the importance unless the top-k is differentiable
         if imp is None:
             imp = torch.empty(0, device=q.device)
-        ctx.mark_non_differentiable(imp)
+            ctx.mark_non_differentiable(imp)
         return out, imp
 
     @staticmethod
-    def backward(ctx, dout, _dimp):
+    def backward(ctx, dout, dimp):
         q, ck, cv, out, lse = ctx.saved_tensors
         num_mem, stride, causal, sel_heads, impl, scale = ctx.cfg
         lib = L.load()
-        dout = L.rowwise(dout)
+        dout = torch.zeros_like(out) if dout is None else L.rowwise(dout)
         dq = torch.empty(q.shape, dtype=torch.float32, device=q.device)
         dck = torch.empty(ck.shape, dtype=torch.float32, device=q.device)
         dcv = torch.empty(cv.shape, dtype=torch.float32, device=q.device)
@@ -201,7 +202,32 @@ class CompressedAttention(Function):
             L.check(lib.nsa_cmp_bwd(C.byref(args), L.stream_of(q)))
             _keep_status(ws)
             del ws
+        if dimp is not None and dimp.numel() > 0 and ctx.needs_input_grad[0]:
+            _importance_backward(dimp, q, ck, dq, dck, num_mem, stride, causal, sel_heads, scale)
         return dq.to(q.dtype), dck.to(ck.dtype), dcv.to(cv.dtype), None, None, None, None, None, None
+
+
+def _importance_backward(dimp, q, ck, dq, dck, num_mem, stride, causal, sel_heads, scale):
+    """Adds the gradient that arrives through the importance output (differentiable top-k, upstream NSA:715) to dq and
+    dck.  importance[b,s,i,c] is the mean over the heads of selection head s of the visible logit
+    scale * q[b,h,i] . ck[b,kv(h),num_mem+c]; rounding steps pass the gradient through.  Two plain batched GEMMs per
+    KV head (library GEMMs: this path is off unless use_diff_topk is set)."""
+    b, hq, n, d = q.shape
+    hkv = ck.shape[1]
+    ncb = ck.shape[2] - num_mem
+    g_sel = hq // sel_heads                      # query heads averaged into one importance row
+    dlog = dimp.float() * (scale / g_sel)        # d logit of every head of the selection head, [B, Hs, N, ncb]
+    if causal:
+        visible = torch.arange(ncb, device=q.device)[None, :] < (torch.arange(n, device=q.device) // stride)[:, None]
+        dlog = dlog * visible
+    per_kv = hq // hkv
+    ckc = ck[:, :, num_mem:].float()             # [B, Hkv, ncb, d]
+    # every query head h gets dlog of its selection head times the compressed keys of its KV head
+    dlog_h = dlog.repeat_interleave(g_sel, dim=1) if g_sel > 1 else dlog        # [B, Hq, N, ncb]
+    ck_h = ckc.repeat_interleave(per_kv, dim=1) if per_kv > 1 else ckc          # [B, Hq, ncb, d]
+    dq += torch.matmul(dlog_h, ck_h)
+    dck_part = torch.matmul(dlog_h.transpose(-1, -2), q.float())                # [B, Hq, ncb, d]
+    dck[:, :, num_mem:] += dck_part.view(b, hkv, per_kv, ncb, d).sum(dim=2)
 
 
 def compressed_attend(q, ck, cv, num_mem, stride, causal, sel_heads=None, want_importance=True, impl='auto'):
@@ -215,8 +241,52 @@ def compressed_attend(q, ck, cv, num_mem, stride, causal, sel_heads=None, want_i
 # block selection (replaces NSA:672-713); integer output, no gradient
 # --------------------------------------------------------------------------
 
-@torch.no_grad()
+class _SelectValuesGrad(Function):
+    """Identity on the selected values that carries their gradient back to the importance matrix (the differentiable
+    top-k of upstream NSA:715: the picked probabilities are a gather out of a softmax).  The forward values and
+    indices come from the selection kernel; the backward recomputes the softmax in PyTorch."""
+
+    @staticmethod
+    def forward(ctx, importance, vals, idx, block, stride):
+        ctx.save_for_backward(importance, idx)
+        ctx.cfg = (block, stride)
+        return vals.clone()
+
+    @staticmethod
+    def backward(ctx, dvals):
+        importance, idx = ctx.saved_tensors
+        block, stride = ctx.cfg
+        b, hs, n, ncb = importance.shape
+        cpf = block // stride
+        cols = ncb // cpf
+        x = importance.float()
+        own = None
+        if cpf > 1:
+            x = x[..., : cols * cpf].reshape(b, hs, n, cols, cpf).mean(dim=-1)
+            own = (torch.arange(n, device=x.device) // block)[:, None] == torch.arange(cols, device=x.device)[None, :]
+            x = x.masked_fill(own, -torch.finfo(torch.float32).max)
+        p = torch.nn.functional.pad(x, (1, 0), value=-1e3).softmax(dim=-1)[..., 1:]
+        dp = torch.zeros_like(p).scatter_add_(-1, idx, dvals.float())
+        dx = p * (dp - (p * dp).sum(dim=-1, keepdim=True))        # the sink has no incoming gradient
+        if cpf > 1:
+            dx = dx.masked_fill(own, 0.)
+            dimp = torch.zeros_like(importance, dtype=torch.float32)
+            dimp[..., : cols * cpf] = (dx / cpf).repeat_interleave(cpf, dim=-1)
+        else:
+            dimp = dx
+        return dimp.to(importance.dtype), None, None, None, None
+
+
 def select_blocks(importance, block, stride, nsel, dtype=torch.float32, input_is_prob=False):
+    """As `_select_blocks`; when `importance` requires grad, the returned values carry it (differentiable top-k)."""
+    vals, idx = _select_blocks(importance.detach(), block, stride, nsel, dtype, input_is_prob)
+    if torch.is_grad_enabled() and importance.requires_grad and not input_is_prob and vals.numel() > 0:
+        vals = _SelectValuesGrad.apply(importance, vals, idx, block, stride)
+    return vals, idx
+
+
+@torch.no_grad()
+def _select_blocks(importance, block, stride, nsel, dtype=torch.float32, input_is_prob=False):
     """importance [B, Hs, N, ncb] fp32 -> (values [B,Hs,N,k] in `dtype`, int64 indices [B,Hs,N,k]),
     k = min(nsel, ncb // (block // stride)).  See nsa_select in include/nsa_b200.h."""
     L.require_cuda(importance)

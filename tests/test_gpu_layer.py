@@ -11,7 +11,7 @@ from native_sparse_attention_pytorch_b200 import SparseAttention
 
 pytestmark = pytest.mark.gpu
 DEV = 'cuda'
-LAYER = [n for n in recipe.LAYER_CASES if n != 'causal_diff_topk']
+LAYER = list(recipe.LAYER_CASES)
 
 
 def build(name, dtype=torch.float32):
