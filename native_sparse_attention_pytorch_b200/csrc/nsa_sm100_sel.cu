@@ -631,7 +631,7 @@ __global__ void __launch_bounds__(256) sel_merge_kernel(const SelParams P) {
 //     only then is the O row read from tensor memory, scaled and written back (P stays below 2^8, exact in bf16's
 //     range, and the sum is fp32).
 //   * MODE compressed with IMP also writes the head-averaged logits of the visible columns (the importance).
-template <int D, int MODE, bool IMP>
+template <int D, int MODE, int GI>   // GI: 0 = no importance output, else the number of heads per KV head (importance written)
 __global__ void __launch_bounds__(kRows, 2)
 dense_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const SelParams P) {
   constexpr int NC = D / 64;
@@ -680,7 +680,8 @@ dense_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
   constexpr uint32_t idO = instr_desc_bf16(128, D, false, true);
 
   // the tile: heavy tiles (late queries) are launched first
-  const int G = P.G, QT = kRows / G, g_shift = 31 - __clz(G);
+  constexpr bool IMP = GI > 0;
+  const int G = IMP ? GI : P.G, QT = kRows / G, g_shift = 31 - __clz(G);
   const int tiles_per_head = (P.N + QT - 1) / QT;
   const int64_t tile = (int64_t)gridDim.x - 1 - blockIdx.x;
   const int qt = (int)(tile % tiles_per_head), bh = (int)(tile / tiles_per_head), h = bh % P.Hkv, b = bh / P.Hkv;
@@ -790,8 +791,9 @@ dense_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
       int first = 0;
 #pragma unroll
       for (int step = 0; step < 4; ++step) {
+        constexpr int kG = IMP ? GI : 1;
         const int width = 32 >> step;
-        if ((1 << step) < G) {
+        if ((1 << step) < kG) {
           const bool upper = (g >> step) & 1;
 #pragma unroll
           for (int x = 0; x < 32; ++x) {
@@ -804,21 +806,26 @@ dense_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
           first += upper ? width : 0;
         }
       }
-      const int owned = kBlock / G;
+      constexpr int owned = kBlock / (IMP ? (GI > 16 ? 16 : GI) : 1);
       float* imp_row = P.importance + (((int64_t)b * P.Hkv + h) * P.N + (valid ? i : 0)) * P.ncb;
-      const float inv_g = 1.f / (float)G;
+      constexpr float inv_g = 1.f / (float)(IMP ? GI : 1);
+      const int col0 = j * kBlock + first - P.rule.num_mem;
 #pragma unroll
-      for (int x = 0; x < 64; ++x) {
-        if (x < owned) {
-          const int col_in_block = first + x;
-          const int col = j * kBlock + col_in_block - P.rule.num_mem;
-          if (valid && col_in_block <= lim && col >= 0 && col < P.ncb) imp_row[col] = round_bf16(v[x] * inv_g);
-        }
+      for (int x = 0; x < owned; ++x) {
+        const int col = col0 + x;
+        if (valid && first + x <= lim && col >= 0 && col < P.ncb) imp_row[col] = round_bf16(v[x] * inv_g);
       }
     }
+    // most blocks are fully visible to every row of the warp: they take the loops without per-column tests
+    const bool all_full = __all_sync(kFullMask, lim == kBlock - 1 && lo == 0);
     float m = -INFINITY;
+    if (all_full) {
 #pragma unroll
-    for (int x = 0; x < 64; ++x) m = ((MODE == kModeCmp || x >= lo) && x <= lim) ? fmaxf(m, s[x]) : m;
+      for (int x = 0; x < 64; ++x) m = fmaxf(m, s[x]);
+    } else {
+#pragma unroll
+      for (int x = 0; x < 64; ++x) m = ((MODE == kModeCmp || x >= lo) && x <= lim) ? fmaxf(m, s[x]) : m;
+    }
     const float m_blk2 = m * P.scale_log2;   // -inf when the row sees nothing of this block
     bool need = false;
     float alpha = 1.f;
@@ -845,11 +852,20 @@ dense_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
       }
       tmem_st_wait();
     }
+    if (all_full) {
 #pragma unroll
-    for (int x = 0; x < 64; ++x) {
-      const float p = ((MODE == kModeCmp || x >= lo) && x <= lim) ? ex2(s[x] * P.scale_log2 - m_ref) : 0.f;
-      s[x] = p;
-      l += p;
+      for (int x = 0; x < 64; ++x) {
+        const float p = ex2(s[x] * P.scale_log2 - m_ref);
+        s[x] = p;
+        l += p;
+      }
+    } else {
+#pragma unroll
+      for (int x = 0; x < 64; ++x) {
+        const float p = ((MODE == kModeCmp || x >= lo) && x <= lim) ? ex2(s[x] * P.scale_log2 - m_ref) : 0.f;
+        s[x] = p;
+        l += p;
+      }
     }
     if (t > 0) {   // PV(t-1) is complete: the P tile and V buffer (t-1) & 1 are free
       mbar_wait_warp(bar_pv, (uint32_t)(t - 1) & 1, &abort_flag);
@@ -1908,16 +1924,20 @@ static int run_fwd(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaStrea
     const int64_t tiles = (int64_t)a.B * a.Hkv * ((a.N + QT - 1) / QT);
     if (tiles > 0x7fffffffLL) return NSA_ERR_UNSUPPORTED;
     const int smem = (D / 64) * 16384 + 16384 + 4 * (D / 64) * 8192;
-#define NSA_DENSE_LAUNCH(MODE, IMP)                                                                                  \
+#define NSA_DENSE_LAUNCH(MODE, GI)                                                                                   \
     do {                                                                                                              \
-      CUDA_TRY(cudaFuncSetAttribute(dense_fwd_kernel<D, MODE, IMP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
-      CUDA_TRY(cudaFuncSetAttribute(dense_fwd_kernel<D, MODE, IMP>, cudaFuncAttributePreferredSharedMemoryCarveout,   \
+      CUDA_TRY(cudaFuncSetAttribute(dense_fwd_kernel<D, MODE, GI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
+      CUDA_TRY(cudaFuncSetAttribute(dense_fwd_kernel<D, MODE, GI>, cudaFuncAttributePreferredSharedMemoryCarveout,    \
                                     cudaSharedmemCarveoutMaxShared));                                                 \
-      dense_fwd_kernel<D, MODE, IMP><<<(unsigned)tiles, kRows, smem, st>>>(tmK, tmV, P);                              \
+      dense_fwd_kernel<D, MODE, GI><<<(unsigned)tiles, kRows, smem, st>>>(tmK, tmV, P);                               \
     } while (0)
-    if (a.mode == kModeSwa) NSA_DENSE_LAUNCH(kModeSwa, false);
-    else if (P.importance != nullptr) NSA_DENSE_LAUNCH(kModeCmp, true);
-    else NSA_DENSE_LAUNCH(kModeCmp, false);
+    if (a.mode == kModeSwa) NSA_DENSE_LAUNCH(kModeSwa, 0);
+    else if (P.importance == nullptr) NSA_DENSE_LAUNCH(kModeCmp, 0);
+    else if (p.G == 1) NSA_DENSE_LAUNCH(kModeCmp, 1);
+    else if (p.G == 2) NSA_DENSE_LAUNCH(kModeCmp, 2);
+    else if (p.G == 4) NSA_DENSE_LAUNCH(kModeCmp, 4);
+    else if (p.G == 8) NSA_DENSE_LAUNCH(kModeCmp, 8);
+    else NSA_DENSE_LAUNCH(kModeCmp, 16);
 #undef NSA_DENSE_LAUNCH
     CUDA_TRY(cudaGetLastError());
     return NSA_OK;
