@@ -72,3 +72,48 @@ def test_layer_bf16_boundary_tensors(name):
     if rmid['idx'] is None:
         assert_close_bf16(mid['o_sel'], rmid['o_sel'], 'selected branch')
         assert_close_bf16(out, rout, 'out', tol=4e-2)
+
+
+@pytest.mark.parametrize('seq_len', (2, 8, 16))
+@pytest.mark.parametrize('num_selected_blocks', (0, 2))
+@pytest.mark.parametrize('stride', (2, 4))
+@pytest.mark.parametrize('selection_block_size', (8, 16, 20))
+def test_decoding_with_cache_equals_parallel_forward(seq_len, num_selected_blocks, stride, selection_block_size):
+    """Upstream's own check of its decode path (tests/test_sparse_attn.py:50-86), on the same grid: feeding the tokens
+    one by one with the cache gives the parallel forward's output (atol 1e-5 upstream; 2e-5 here, the parallel side
+    sums in another order)."""
+    torch.manual_seed(0)
+    attn = SparseAttention(dim=512, dim_head=64, heads=8, causal=True, sliding_window_size=2, compress_block_size=5,
+                           selection_block_size=selection_block_size, num_selected_blocks=num_selected_blocks,
+                           compress_block_sliding_stride=stride, use_triton_kernel=True)
+    recipe.fill_weights(attn, seed=3, rich=False)      # memory slots zero, as upstream initialises them (see below)
+    attn = attn.to(DEV)
+    tokens = recipe.randn((2, seq_len, 512), 5).to(DEV)
+    with torch.no_grad():
+        parallel = attn(tokens)
+        cache, steps = None, []
+        for i in range(seq_len):
+            one, cache = attn(tokens[:, i:i + 1], cache=cache, return_cache=True)
+            steps.append(one)
+    sequential = torch.cat(steps, dim=1)
+    assert (parallel - sequential).abs().max().item() <= 2e-5
+
+
+def test_decoding_with_grouped_heads_and_memory_slots():
+    # Upstream's decode step attends the memory slots only once a compressed block exists (NSA:402-406), its parallel
+    # forward always: with non-zero memory slots the two differ for the first `stride` tokens.  This package keeps
+    # both behaviours, so the comparison starts where a compressed block exists.
+    torch.manual_seed(0)
+    attn = SparseAttention(dim=256, dim_head=64, heads=8, kv_heads=2, causal=True, sliding_window_size=5,
+                           compress_block_size=8, compress_block_sliding_stride=4, selection_block_size=8,
+                           num_selected_blocks=2, num_compressed_mem_kv=2, use_triton_kernel=True)
+    recipe.fill_weights(attn, seed=4, rich=True)
+    attn = attn.to(DEV)
+    tokens = recipe.randn((2, 37, 256), 6).to(DEV)
+    with torch.no_grad():
+        parallel = attn(tokens)
+        cache, steps = None, []
+        for i in range(tokens.shape[1]):
+            one, cache = attn(tokens[:, i:i + 1], cache=cache, return_cache=True)
+            steps.append(one)
+    assert (parallel - torch.cat(steps, dim=1))[:, 4:].abs().max().item() <= 2e-5

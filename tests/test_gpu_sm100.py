@@ -158,6 +158,8 @@ CMP_CASES = [
     (1, 4, 1, 1000, 64, 16, 2),
     (1, 8, 1, 260, 128, 2, 1),
     (1, 2, 2, 70, 64, 1, 1),
+    (1, 4, 2, 200, 64, 4, 1),      # two heads per KV head
+    (1, 16, 1, 130, 128, 2, 1),    # sixteen
 ]
 
 
