@@ -510,15 +510,17 @@ sel_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         s[x] = p;
         l += p;   // the fp32 sum: the log-sum-exp stays exact although P is rounded to bf16 for the MMA
       }
-      store_row_bf16(sP, tid, s);
-      fence_proxy_async_smem();
+      // P goes to the tensor cores through tensor memory, over the first half of this row's S columns (which the
+      // thread has read): no shared-memory tile, no proxy fence
+      tmem_st_bf16_row64(tm_lane + tS, s);
+      tmem_st_wait();
       tc_fence_before_sync();
       __syncthreads();
       if (warp == 0) {
         tc_fence_after_sync();
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          mma_bf16_elect(tm + tO, smem_desc_sw128(sP + k * 32, 16), smem_desc_sw128(sV + k * 2048, 8192), idO, k > 0);
+          mma_bf16_tmem_a_elect(tm + tO, tm + tS + k * 8, smem_desc_sw128(sV + k * 2048, 8192), idO, k > 0);
         mma_commit_elect(bar_o);
       }
       __syncwarp();
@@ -872,8 +874,10 @@ dense_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
       tc_fence_after_sync();
     }
     if (tid == 0 && t + 1 < nb) load_v(t + 1);
-    store_row_bf16(sP, tid, s);
-    fence_proxy_async_smem();
+    // P through tensor memory, over the first half of this row's S columns of buffer sb; S(t+2), which is issued
+    // after PV(t) by the same lane, overwrites them only after PV(t) has read them
+    tmem_st_bf16_row64(tm_lane + sb * 64, s);
+    tmem_st_wait();
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 0) {
@@ -883,7 +887,7 @@ dense_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
       const uint32_t sV = sV0 + sb * kTileKV;
 #pragma unroll
       for (int k = 0; k < 4; ++k)
-        mma_bf16_elect(tm + tO, smem_desc_sw128(sP + k * 32, 16), smem_desc_sw128(sV + k * 2048, 8192), idO, t > 0 || k > 0);
+        mma_bf16_tmem_a_elect(tm + tO, tm + sb * 64 + k * 8, smem_desc_sw128(sV + k * 2048, 8192), idO, t > 0 || k > 0);
       mma_commit_elect(bar_pv);
       if (t + 2 < nb) issue_s(t + 2);
     }
