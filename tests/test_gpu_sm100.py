@@ -245,3 +245,34 @@ def test_sm100_layer_bf16_uses_tensor_core_branches():
     ops.check_device_status()
     assert_close_bf16(mid['o_cmp'], rmid['o_cmp'], 'compressed branch')
     assert_close_bf16(mid['o_swa'], rmid['o_swa'], 'sliding branch')
+
+
+def test_full_benchmark_size_properties():
+    """The kernel-level benchmark shape (batch 4, 8192 tokens, 32 / 4 heads, 16 selected blocks + own block) is far too
+    large for the gather formulation of the oracle, so it is checked through what does not depend on size: the output
+    of a sample of query rows against the oracle evaluated on those rows only, and three identities of the backward
+    -- the rows of P sum to one, so  sum_keys dv = sum_(queries, heads) do ;  the rows of dS sum to zero and
+    dq . q and dk . k both total scale * sum(dS * S), so  sum(dq * q) = sum(dk * k)  per KV head."""
+    import bench
+    w = bench.WORKLOADS[bench.DEFAULT_WORKLOAD]
+    q, k, v, idx, mask, do = bench.make_inputs(w, seed=0)
+    qg, kg, vg = (t.to(DEV).requires_grad_() for t in (q, k, v))
+    out = nsa.native_sparse_attend(qg, kg, vg, w['block'], idx.to(DEV), mask.to(DEV), include_block_causal=True,
+                                   impl='sm100')
+    dq, dk, dv = torch.autograd.grad(out, (qg, kg, vg), do.to(DEV))
+    ops.check_device_status()
+    # sampled rows of batch element 1, KV head 2: first blocks, a block boundary, the middle, the end
+    g = w['q_heads'] // w['kv_heads']
+    rows = torch.tensor([0, 1, 63, 64, 65, 127, 128, 1000, 4095, 4096, 8000, 8190, 8191])
+    hs = slice(2 * g, 3 * g)
+    ref = O.selected_attend(q[1:2, hs].float(), k[1:2, 2:3].float(), v[1:2, 2:3].float(), w['block'], idx[1:2, 2:3],
+                            mask[1:2, 2:3], True, rows=rows)
+    assert_close_bf16(out[1:2, hs][:, :, rows.to(DEV)], ref, 'sampled output rows')
+    b, hkv, n, d = k.shape
+    do_sum = do.float().view(b, hkv, g, n, d).sum(dim=(2, 3)).to(DEV)            # [B, Hkv, d]
+    dv_sum = dv.float().sum(dim=2)
+    assert (dv_sum - do_sum).abs().max().item() <= 2e-3 * do_sum.abs().max().item() + 0.5   # sums of 2.6e5 bf16 terms
+    lhs = (dq.float() * qg.float()).view(b, hkv, g, n, d).sum(dim=(2, 3, 4))
+    rhs = (dk.float() * kg.float()).sum(dim=(2, 3))
+    scale_ref = (dq.float() * qg.float()).view(b, hkv, -1).abs().sum(dim=-1)
+    assert ((lhs - rhs).abs() <= 2e-3 * scale_ref).all(), (lhs, rhs)
