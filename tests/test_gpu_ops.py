@@ -314,3 +314,33 @@ def test_rotary_kernel_matches_oracle(dtype):
         else:
             assert_close_bf16(out, ref, 'out')
             assert_close_bf16(gg, rg, 'd x')
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize('shape', [(2, 4, 16384, 16, 64, 16), (1, 1, 65536, 16, 64, 16)])
+def test_selection_at_full_size_equals_the_oracle_steps(shape):
+    """The selection kernel at the row lengths of the full-layer and the long-context configuration (256 and 1024
+    block columns per row), against the oracle's steps evaluated with the same tensor on the GPU.  PyTorch's CUDA
+    softmax and the kernel's differ in the last bit here and there, so two blocks whose probabilities are one ulp apart
+    may swap: the picks must be a top-k of the oracle's probabilities up to that ulp, in non-increasing order, and
+    identical for (nearly) all rows whose k+1 largest values are distinct."""
+    b, hs, n, st, sel, nsel = shape
+    ncb = n // st
+    gen = torch.Generator(DEV).manual_seed(3)
+    imp = torch.randn(b, hs, n, ncb, generator=gen, device=DEV)
+    invisible = torch.arange(ncb, device=DEV)[None, :] >= (torch.arange(n, device=DEV) // st)[:, None]
+    imp = imp.masked_fill(invisible, nsa.ops.mask_sentinel(torch.float32))
+    probs = O.importance_scores(imp, 0, hs, st, sel, True)
+    ref_vals, ref_idx = O.select_blocks(probs, nsel)
+    vals, idx = nsa.select_blocks(imp, sel, st, nsel)
+    assert_close_f32(vals, ref_vals, 'values', tol=1e-6)
+    assert torch.equal(vals > 1e-10, ref_vals > 1e-10)
+    top = probs.topk(nsel + 1, dim=-1).values
+    unique = (top[..., :-1] > top[..., 1:]).all(dim=-1)
+    assert unique.float().mean().item() > 0.5
+    same = (idx == ref_idx).all(dim=-1)
+    assert same[unique].float().mean().item() > 0.999
+    picked = probs.gather(-1, idx)                      # the oracle's probabilities of the kernel's picks
+    ulp = 2e-7 * probs.amax(dim=-1, keepdim=True)
+    assert (picked >= top[..., -1:] - ulp).all()        # none of them is below the (k+1)-th largest
+    assert (picked[..., :-1] >= picked[..., 1:] - ulp).all()
