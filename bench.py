@@ -53,6 +53,17 @@ LAYER_WORKLOADS = {
                         compress_block_size=32, compress_block_sliding_stride=16, selection_block_size=64,
                         num_selected_blocks=4),
 }
+LM_WORKLOADS = {
+    # the language-model training step of the baseline's fourth configuration: 8 pre-norm blocks of
+    # [SparseAttention, feed-forward x4 GELU], byte vocabulary, next-token cross-entropy, forward+backward
+    'lm_step_b8_n8192_dim512_depth8': dict(batch=8, seq=8192, vocab=256, dim=512, depth=8, heads=8, kv_heads=4,
+                                           dim_head=64, sliding_window_size=512, compress_block_size=32,
+                                           compress_block_sliding_stride=16, selection_block_size=64,
+                                           num_selected_blocks=16),
+    'lm_small': dict(batch=2, seq=1024, vocab=256, dim=256, depth=2, heads=4, kv_heads=2, dim_head=64,
+                     sliding_window_size=128, compress_block_size=32, compress_block_sliding_stride=16,
+                     selection_block_size=64, num_selected_blocks=4),
+}
 PREFILL_WORKLOADS = {
     'prefill_b1_n65536_h64kv8_d128': dict(batch=1, seq=65536, q_heads=64, kv_heads=8, dim_head=128,
                                           compress_block_size=32, stride=16, block=64, nsel=16, window=512, num_mem=1),
@@ -214,7 +225,7 @@ def main():
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--workload', default=DEFAULT_WORKLOAD,
-                    choices=list(WORKLOADS) + list(LAYER_WORKLOADS) + list(PREFILL_WORKLOADS))
+                    choices=list(WORKLOADS) + list(LAYER_WORKLOADS) + list(PREFILL_WORKLOADS) + list(LM_WORKLOADS))
     ap.add_argument('--kernels', default='auto', choices=['auto', 'simt', 'sm100'])
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--gather', default='fused', choices=['fused', 'nccl'],
@@ -225,6 +236,8 @@ def main():
         return run_layer(args, LAYER_WORKLOADS[args.workload])
     if args.workload in PREFILL_WORKLOADS:
         return run_prefill(args, PREFILL_WORKLOADS[args.workload])
+    if args.workload in LM_WORKLOADS:
+        return run_lm(args, LM_WORKLOADS[args.workload])
     w = WORKLOADS[args.workload]
     if args.impl == 'reference':
         return run_reference(args, w, args.workload)
@@ -276,6 +289,7 @@ def main():
         step(q, k, v, idx, mask, do, events[i])
     torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
+    nsa.ops.check_device_status()     # a kernel that gave up on a bounded wait makes the whole measurement void
     fwd_ms = [e[0].elapsed_time(e[1]) for e in events]
     bwd_ms = [e[1].elapsed_time(e[2]) for e in events]
     total_ms = sum(fwd_ms) + sum(bwd_ms)
@@ -489,6 +503,8 @@ def _timed_steps(step, steps, warmup, flush, dist, world, rank, local):
         evs.append((e0, e1))
     torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
+    from native_sparse_attention_pytorch_b200 import ops
+    ops.check_device_status()     # a kernel that gave up on a bounded wait makes the whole measurement void
     t = torch.tensor([sum(a.elapsed_time(b) for a, b in evs)], dtype=torch.float64, device=flush.device)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -610,12 +626,15 @@ def layer_cpu_sample(kw, n=1024, budget_s=15.0):
                       f'fp32, {reps} repetitions'}
 
 
-def run_layer_reference(args, w, kw):
+def run_layer_reference(args, w, kw, metric='nsa_layer_fwd_bwd_tokens_per_s', layers=1):
     if int(os.environ.get('RANK', '0')) != 0:
         return
     base = layer_cpu_sample(kw, budget_s=max(5.0, min(60.0, 3.0 * args.steps)))
+    if layers > 1:
+        base['value'] /= layers
+        base['sample'] = f'one of the {layers} attention layers (value = its tokens/s / {layers}): ' + base['sample']
     print(json.dumps({
-        'impl': 'reference', 'metric': 'nsa_layer_fwd_bwd_tokens_per_s', 'value': base['value'], 'unit': 'tokens/s',
+        'impl': 'reference', 'metric': metric, 'value': base['value'], 'unit': 'tokens/s',
         'n_gpus': args.gpus, 'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': 1e3 * 1024 / base['value'],
         'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
         'config': {'workload': args.workload, **w}, 'cpu_baseline': base,
@@ -841,6 +860,131 @@ def run_prefill_reference(args, w):
         'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
         'config': {'workload': args.workload, **w}, 'cpu_baseline': base,
         'e2e': {'value': base['value'], 'unit': 'tokens/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0}}))
+
+
+def build_lm(w, dev):
+    """A small byte-level language model around the layer, with the sizes of upstream's training example: token
+    embedding, `depth` pre-norm residual blocks of [SparseAttention, RMSNorm -> Linear x4 -> GELU -> Linear], final
+    RMSNorm, logits.  It is a harness for the layer, not part of the library."""
+    import native_sparse_attention_pytorch_b200 as nsa
+    from torch import nn
+    kw = {k: w[k] for k in ('dim', 'dim_head', 'heads', 'kv_heads', 'sliding_window_size', 'compress_block_size',
+                            'compress_block_sliding_stride', 'selection_block_size', 'num_selected_blocks')}
+
+    class Lm(nn.Module):
+        def __init__(self):
+            super().__init__()
+            dim = w['dim']
+            self.emb = nn.Embedding(w['vocab'], dim)
+            self.blocks = nn.ModuleList([nn.ModuleList([
+                nsa.SparseAttention(causal=True, use_triton_kernel=True, **kw),
+                nn.Sequential(nn.RMSNorm(dim), nn.Linear(dim, 4 * dim), nn.GELU(), nn.Linear(4 * dim, dim))])
+                for _ in range(w['depth'])])
+            self.norm = nn.RMSNorm(dim)
+            self.to_logits = nn.Linear(dim, w['vocab'], bias=False)
+
+        def forward(self, ids):
+            ids, labels = ids[:, :-1], ids[:, 1:]
+            x = self.emb(ids)
+            for attn, ff in self.blocks:
+                x = attn(x) + x
+                x = ff(x) + x
+            logits = self.to_logits(self.norm(x))
+            return torch.nn.functional.cross_entropy(logits.flatten(0, 1).float(), labels.flatten())
+
+    torch.manual_seed(0)
+    return Lm().to(dev).bfloat16(), kw
+
+
+def run_lm(args, w):
+    """Training step (forward, backward, gradient all-reduce over the ranks) of the byte-level language model: the
+    batch is split over the ranks (strong scaling), the gradients are summed with one NCCL all-reduce per step."""
+    if args.impl == 'reference':
+        kw = {k: w[k] for k in ('dim', 'dim_head', 'heads', 'kv_heads', 'sliding_window_size', 'compress_block_size',
+                                'compress_block_sliding_stride', 'selection_block_size', 'num_selected_blocks')}
+        return run_layer_reference(args, w, kw, metric='nsa_lm_train_step_tokens_per_s', layers=w['depth'])
+    dist, rank, world, local, dev = _dist_setup()
+    warmup = max(args.warmup, 3)
+    if w['batch'] % world:
+        raise SystemExit(f'batch {w["batch"]} does not split over {world} ranks')
+    per_rank = w['batch'] // world
+    model, kw = build_lm(w, dev)
+    gen = torch.Generator('cpu').manual_seed(0)
+    ids_host = torch.randint(0, w['vocab'], (w['batch'], w['seq'] + 1), generator=gen)[rank * per_rank:(rank + 1) * per_rank]
+    ids_host = ids_host.pin_memory()
+    ids = ids_host.to(dev)
+    params = [p for p in model.parameters()]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    keep = {}
+
+    def step():
+        model.zero_grad(set_to_none=True)
+        loss = model(ids)
+        loss.backward()
+        if world > 1:   # data-parallel gradient sum: one flat bucket, one all-reduce
+            grads = [p.grad for p in params if p.grad is not None]
+            flat = torch._utils._flatten_dense_tensors(grads)
+            dist.all_reduce(flat)
+            for g, f in zip(grads, torch._utils._unflatten_dense_tensors(flat, grads)):
+                g.copy_(f)
+        keep['loss'] = loss
+
+    total_ms, clocks = _timed_steps(step, args.steps, warmup, flush, dist, world, rank, local)
+    h_loss = torch.empty(1, dtype=torch.float32).pin_memory()
+    def e2e_step():
+        ids.copy_(ids_host, non_blocking=True)
+        step()
+        h_loss.copy_(keep['loss'].detach().float().view(1), non_blocking=True)
+    e2e_step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_steps = max(3, min(args.steps, 10))
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    ms = total_ms / args.steps
+    tokens = w['batch'] * w['seq']
+    n, st = w['seq'], w['compress_block_sliding_stride']
+    g = w['heads'] // w['kv_heads']
+    units = w['batch'] * w['kv_heads']
+    # selected blocks: every query past its first blocks sees min(nsel, own block index) of them
+    i = torch.arange(n)
+    visible = torch.clamp(i // w['selection_block_size'], max=w['num_selected_blocks']).sum().item() * units
+    flops = hot_path_flops(n, w['dim_head'], g, units, st, n // st, 1, w['selection_block_size'],
+                           w['sliding_window_size'], visible)
+    f_step = 3.5 * sum(flops.values()) * w['depth']
+    burst, sustained, src = peaks()
+    n_params = sum(p.numel() for p in params)
+    line = {
+        'metric': 'nsa_lm_train_step_tokens_per_s', 'value': tokens / (ms / 1e3), 'unit': 'tokens/s', 'n_gpus': world,
+        'steps': args.steps, 'warmup': warmup, 'ms_per_step': ms, 'higher_is_better': True, 'scaling': 'strong',
+        'vs_baseline': None, 'dtype': 'bf16', 'data': 'synthetic',
+        'config': {'workload': args.workload, **w, 'l2': 'flushed between timed steps', 'parameters': n_params,
+                   'parallelism': f'data parallel, {per_rank} sequences per rank, one NCCL all-reduce of '
+                                  f'{n_params * 2 / 1e6:.0f} MB of bf16 gradients per step'},
+        'roofline': {'bound': 'tensor', 'kernel': 'whole training step; FLOPs of the three attention branches only',
+                     'achieved': f_step / world / (ms / 1e3) / 1e12, 'peak': burst, 'unit': 'TFLOP/s',
+                     'frac': f_step / world / (ms / 1e3) / 1e12 / burst, 'peak_source': src,
+                     'peak_sustained': sustained, 'flops_per_step': f_step, 'traffic': None},
+        'e2e': {'value': tokens / (t.item() / e2e_steps / 1e3), 'unit': 'tokens/s',
+                'h2d_bytes_per_step': ids_host.numel() * 8 * world, 'd2h_bytes_per_step': 4, 'steps': e2e_steps},
+        'gpu_launches': (3 * 13 + 2 + 3) * w['depth'] * args.steps, 'clocks': clocks,
+        'loss': float(keep['loss']),
+    }
+    if not args.no_cpu_baseline and world == 1:
+        base = layer_cpu_sample(kw)
+        base['value'] /= w['depth']
+        base['sample'] = f'one of the {w["depth"]} attention layers (value = its tokens/s / {w["depth"]}; feed-forward not timed): ' + base['sample']
+        line['cpu_baseline'] = base
+    print(json.dumps(line))
 
 
 def launches_per_step(kernels, w):

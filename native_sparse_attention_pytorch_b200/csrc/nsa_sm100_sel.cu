@@ -1227,7 +1227,7 @@ constexpr int kLoaderThreads = 128;
 struct Bars {
   uint64_t q_full[kStages], q_free[kStages];
   uint64_t s_full[2], p_full[2], mma2_done[2], dq_free[2];
-  uint64_t kv_full[2], kv_free[2], acc_full, acc_free;
+  uint64_t kv_full[2], kv_free[2], acc_full[2], acc_free;
   uint64_t drain;
 };
 }  // namespace ws
@@ -1263,7 +1263,8 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
       mbar_init(smem_u32(&bars.kv_full[i]), 1);
       mbar_init(smem_u32(&bars.kv_free[i]), 1);
     }
-    mbar_init(smem_u32(&bars.acc_full), 1);
+    mbar_init(smem_u32(&bars.acc_full[0]), 1);
+    mbar_init(smem_u32(&bars.acc_full[1]), 1);
     mbar_init(smem_u32(&bars.acc_free), kRows);
     mbar_init(smem_u32(&bars.drain), 1);
     fence_mbar_init();
@@ -1433,11 +1434,16 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
 #endif
       }
     };
+    uint32_t flushes = 0;   // items this group has flushed
     auto flush_item = [&](const int4 item, const int t) {
       const int list = item.x, j = list % P.nfb, bh = list / P.nfb, h = bh % P.Hkv, b = bh / P.Hkv;
       {
-        // flush dK/dV of this item: accumulator rows 16w..16w+15 live in lanes 0..15 of warp w of the group
-        mbar_wait_warp(smem_u32(&bars.acc_full), (uint32_t)t & 1, &abort_flag);
+        // flush dK/dV of this item: accumulator rows 16w..16w+15 live in lanes 0..15 of warp w of the group.
+        // "Accumulator complete" has one barrier per flushing group, counted by that group: with one barrier for both,
+        // a group that reached its wait before the other group's item was complete saw the phase before that one
+        // (same parity) as its own and flushed early.
+        mbar_wait_warp(smem_u32(&bars.acc_full[wg]), flushes & 1, &abort_flag);
+        ++flushes;
         tc_fence_after_sync();
         __syncwarp();
         const int key = j * kBlock + (warp & 3) * 16 + lane;
@@ -1532,7 +1538,7 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
       if (lane == 0) TR(2, pn, 3)
       if (last) {
         mma_commit_elect(smem_u32(&bars.kv_free[kb]));
-        mma_commit_elect(smem_u32(&bars.acc_full));
+        mma_commit_elect(smem_u32(&bars.acc_full[grp]));   // the group of the item's last chunk flushes
       }
     };
     for (int it = blockIdx.x; it < nitems; it += gridDim.x, ++t) {

@@ -276,3 +276,27 @@ def test_full_benchmark_size_properties():
     rhs = (dk.float() * kg.float()).sum(dim=(2, 3))
     scale_ref = (dq.float() * qg.float()).view(b, hkv, -1).abs().sum(dim=-1)
     assert ((lhs - rhs).abs() <= 2e-3 * scale_ref).all(), (lhs, rhs)
+
+
+def test_many_single_chunk_items_keep_the_accumulator_handover_in_order():
+    """A layer with fresh weights at the language-model shape: nearly every key block is selected by its own queries
+    only, so the backward walks thousands of one-chunk items and hands its dK/dV accumulator over at every chunk.
+    (This is the shape on which a flush once started one item early.)  Every run must end with a clean status and
+    agree with the generic kernels."""
+    from native_sparse_attention_pytorch_b200 import SparseAttention
+    kw = dict(dim=512, dim_head=64, heads=8, kv_heads=4, causal=True, sliding_window_size=512, compress_block_size=32,
+              compress_block_sliding_stride=16, selection_block_size=64, num_selected_blocks=16)
+    torch.manual_seed(0)
+    fast = SparseAttention(**kw, use_triton_kernel=True, kernel_impl='sm100').to(DEV).bfloat16()
+    slow = SparseAttention(**kw, use_triton_kernel=True, kernel_impl='simt').to(DEV).bfloat16()
+    slow.load_state_dict(fast.state_dict())
+    x = recipe.randn((4, 8192, 512), 3).bfloat16().to(DEV)
+    up = recipe.randn((4, 8192, 512), 4).bfloat16().to(DEV)
+    xs = x.clone().requires_grad_()
+    slow(xs).backward(up)
+    for _ in range(4):
+        xf = x.clone().requires_grad_()
+        out = fast(xf)
+        out.backward(up)
+        ops.check_device_status()
+        assert_close_bf16(xf.grad, xs.grad, 'd input', rel_to_max=5e-3, roundings=2)
