@@ -288,7 +288,6 @@ def main():
         flush.fill_(i & 0xff)             # evict L2 between timed iterations (outside the events)
         step(q, k, v, idx, mask, do, events[i])
     torch.cuda.synchronize()
-    clocks = sampler.stop() if rank == 0 else None
     nsa.ops.check_device_status()     # a kernel that gave up on a bounded wait makes the whole measurement void
     fwd_ms = [e[0].elapsed_time(e[1]) for e in events]
     bwd_ms = [e[1].elapsed_time(e[2]) for e in events]
@@ -333,6 +332,7 @@ def main():
     e1.record()
     torch.cuda.synchronize()
     e2e_ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None     # sampled over both timed regions (device-resident and end to end)
 
     t = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=dev)
     if world > 1:

@@ -113,6 +113,73 @@ __global__ void __launch_bounds__(128) combine_bwd_kernel(const CombineParams P)
   }
 }
 
+// The same with 16-byte accesses: TPR threads share a (batch, head, position) row, 32 / TPR rows per warp.
+template <typename T, int TPR>
+__global__ void __launch_bounds__(256) combine_bwd_vec_kernel(const CombineParams P) {
+  constexpr int V = 16 / (int)sizeof(T);
+  const int64_t tasks = (int64_t)P.batch * P.q_heads * P.seq;
+  const int64_t task = ((int64_t)blockIdx.x * 256 + threadIdx.x) / TPR;
+  const int part = threadIdx.x % TPR;
+  const bool live = task < tasks;
+  float dg[3] = {0.f, 0.f, 0.f};
+  if (live) {
+    const int n = (int)(task % P.seq);
+    const int h = (int)((task / P.seq) % P.q_heads);
+    const int b = (int)(task / ((int64_t)P.seq * P.q_heads));
+    const T* g = (const T*)P.gates + b * P.g_sb + h * P.g_sh + (int64_t)n * P.g_sn;
+    const int c = part * V;
+    const uint4 draw = *reinterpret_cast<const uint4*>((const T*)P.dout + (((int64_t)b * P.seq + n) * P.q_heads + h) * P.d + c);
+    const T* dy = reinterpret_cast<const T*>(&draw);
+#pragma unroll
+    for (int s = 0; s < 3; ++s) {
+      const float gs = Elem<T>::to_float(g[s]);
+      const uint4 oraw = *reinterpret_cast<const uint4*>((const T*)P.o[s] + b * P.o_sb[s] + h * P.o_sh[s] +
+                                                        (int64_t)n * P.o_sn[s] + c);
+      const T* ov = reinterpret_cast<const T*>(&oraw);
+      uint4 packed;
+      T* pv = reinterpret_cast<T*>(&packed);
+#pragma unroll
+      for (int x = 0; x < V; ++x) {
+        const float d = Elem<T>::to_float(dy[x]);
+        dg[s] = fmaf(d, Elem<T>::to_float(ov[x]), dg[s]);
+        pv[x] = Elem<T>::from_float(gs * d);
+      }
+      *reinterpret_cast<uint4*>((T*)P.d_o[s] + task * P.d + c) = packed;
+    }
+  }
+#pragma unroll
+  for (int s = 0; s < 3; ++s) {
+#pragma unroll
+    for (int o = TPR / 2; o > 0; o >>= 1) dg[s] += __shfl_xor_sync(kFullMask, dg[s], o);
+    if (live && part == 0) P.d_gates[task * 3 + s] = dg[s];
+  }
+}
+
+template <typename T>
+static bool launch_combine_bwd_vec(const CombineParams& P, cudaStream_t stream) {
+  constexpr int V = 16 / (int)sizeof(T);
+  if (P.d % V) return false;
+  const uintptr_t ptrs[5] = {(uintptr_t)P.dout, (uintptr_t)P.o[0], (uintptr_t)P.o[1], (uintptr_t)P.o[2], (uintptr_t)P.d_o[0]};
+  for (uintptr_t p : ptrs)
+    if (p & 15u) return false;
+  if (((uintptr_t)P.d_o[1] & 15u) || ((uintptr_t)P.d_o[2] & 15u)) return false;
+  for (int s = 0; s < 3; ++s)
+    if (P.o_sb[s] % V || P.o_sh[s] % V || P.o_sn[s] % V) return false;
+  const int tpr = P.d / V;
+  const int64_t threads = (int64_t)P.batch * P.q_heads * P.seq * tpr;
+  const int64_t blocks = (threads + 255) / 256;
+  if (blocks > 0x7fffffffLL) return false;
+  const unsigned grid = (unsigned)blocks;
+  switch (tpr) {
+    case 2: combine_bwd_vec_kernel<T, 2><<<grid, 256, 0, stream>>>(P); return true;
+    case 4: combine_bwd_vec_kernel<T, 4><<<grid, 256, 0, stream>>>(P); return true;
+    case 8: combine_bwd_vec_kernel<T, 8><<<grid, 256, 0, stream>>>(P); return true;
+    case 16: combine_bwd_vec_kernel<T, 16><<<grid, 256, 0, stream>>>(P); return true;
+    case 32: combine_bwd_vec_kernel<T, 32><<<grid, 256, 0, stream>>>(P); return true;
+    default: return false;
+  }
+}
+
 int launch_combine(const CombineParams& P, int dtype, bool backward, cudaStream_t stream) {
   const int64_t rows = (int64_t)P.batch * P.q_heads * P.seq;
   if (rows == 0) return NSA_OK;
@@ -122,6 +189,8 @@ int launch_combine(const CombineParams& P, int dtype, bool backward, cudaStream_
     const unsigned grid = (unsigned)(blocks < 148 * 32 ? blocks : 148 * 32);
     if (dtype == NSA_F32) combine_fwd_kernel<float><<<grid, 256, 0, stream>>>(P);
     else combine_fwd_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(P);
+  } else if (dtype == NSA_F32 ? launch_combine_bwd_vec<float>(P, stream) : launch_combine_bwd_vec<__nv_bfloat16>(P, stream)) {
+    // 16-byte accesses served it
   } else {
     const int64_t blocks = (rows + 3) / 4;
     if (blocks > 0x7fffffffLL) return fail(NSA_ERR_SHAPE, "too many rows for one launch");
