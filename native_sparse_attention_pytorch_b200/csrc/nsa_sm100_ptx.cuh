@@ -266,6 +266,21 @@ __device__ __forceinline__ void tmem_st_bf16_row64(uint32_t taddr, const float (
         "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+// Half a row: 32 probabilities as 16 columns of bf16 pairs.
+__device__ __forceinline__ void tmem_st_bf16_row32(uint32_t taddr, const float (&x)[32]) {
+  uint32_t r[16];
+#pragma unroll
+  for (int c = 0; c < 16; ++c) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(x[2 * c], x[2 * c + 1]);
+    r[c] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
 // D[tmem] (+)= A[tmem] * B[smem], A as written by tmem_st_bf16_row64; called by a converged warp, one lane issues.
 __device__ __forceinline__ void mma_bf16_tmem_a_elect(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
                                                       bool accumulate) {

@@ -626,6 +626,8 @@ __global__ void __launch_bounds__(256) sel_merge_kernel(const SelParams P) {
 // CTA here owns a tile of 128/G consecutive queries (128 rows with the G heads of the group), walks the key blocks
 // the tile can see and keeps the running maximum and sum of every row in registers and the output accumulator in
 // tensor memory, as a flash-attention forward does.  No index, no partial results, no merge.
+//   * Two threads share a row (32 of a block's 64 columns each; they exchange their maxima through shared memory),
+//     so a CTA has eight warps to hide latencies with.
 //   * S of block t+2 is issued as soon as P of block t has been handed to the PV MMA, so the tensor cores work on
 //     PV(t) and S(t+2) while the threads do the softmax of block t+1 (two S buffers in tensor memory, two K and two V
 //     buffers in shared memory, filled by TMA).
@@ -634,12 +636,13 @@ __global__ void __launch_bounds__(256) sel_merge_kernel(const SelParams P) {
 //     range, and the sum is fp32).
 //   * MODE compressed with IMP also writes the head-averaged logits of the visible columns (the importance).
 template <int D, int MODE, int GI>   // GI: 0 = no importance output, else the number of heads per KV head (importance written)
-__global__ void __launch_bounds__(kRows, 2)
+__global__ void __launch_bounds__(2 * kRows, 2)
 dense_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const SelParams P) {
   constexpr int NC = D / 64;
   constexpr uint32_t kTileQ = NC * 16384, kTileKV = NC * 8192;
   constexpr uint32_t kStageStride = D * 2 + 16;
   constexpr uint32_t kCols = 256;
+  constexpr int kThreads = 2 * kRows;   // two threads per row: each owns 32 of the 64 columns of a key block
   // The dynamic segment is declared 1024-byte aligned (the swizzled tiles need it) and holds exactly the tiles: with
   // dim_head 128 two CTAs then fill an SM's shared memory to the byte.
   extern __shared__ __align__(1024) uint8_t dense_smem[];
@@ -648,16 +651,19 @@ dense_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
   __shared__ __align__(8) uint64_t bars[8];
 
   const uint32_t base = smem_u32(dense_smem);
-  const uint32_t sQ = base, sP = sQ + kTileQ, sK0 = sP + 16384, sV0 = sK0 + 2 * kTileKV;
-  // the Q and P tiles become the staging area of the output rows at the end, followed by the rows' destinations
+  const uint32_t sQ = base, sX = sQ + kTileQ, sK0 = sX + 16384, sV0 = sK0 + 2 * kTileKV;
+  // sX (16 KB): the two threads of a row exchange their partial maxima (and, at the end, sums) through it.  The Q tile
+  // and sX become the staging area of the output rows at the end, followed by the rows' destinations.
   const uint32_t sStage = sQ;
   int* const row_dst = reinterpret_cast<int*>(dense_smem + kRows * kStageStride);
+  float* const xchg = reinterpret_cast<float*>(dense_smem + kTileQ);   // [2 halves][kRows]
   // barriers: K buffers full (2), V buffers full (2), S buffers complete (2), PV complete, drain
   const uint32_t bar0 = smem_u32(&bars[0]), bar_pv = bar0 + 48;
   auto bar_k = [&](int t) { return bar0 + (uint32_t)(t & 1) * 8; };
   auto bar_v = [&](int t) { return bar0 + 16 + (uint32_t)(t & 1) * 8; };
   auto bar_s = [&](int t) { return bar0 + 32 + (uint32_t)(t & 1) * 8; };
   const int tid = threadIdx.x, warp = tid >> 5;
+  const int half = tid >> 7, row = tid & (kRows - 1);
 
   if (tid == 0) {
     abort_flag = 0;
@@ -676,7 +682,7 @@ dense_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tm = tmem_slot;
-  const uint32_t tm_lane = tm + ((uint32_t)(warp * 32) << 16);
+  const uint32_t tm_lane = tm + ((uint32_t)((warp & 3) * 32) << 16);   // warps w and w + 4 share a lane quarter
   const uint32_t tO = 128;
   constexpr uint32_t idS = instr_desc_bf16(128, 64, false, false);
   constexpr uint32_t idO = instr_desc_bf16(128, D, false, true);
@@ -688,7 +694,7 @@ dense_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
   const int64_t tile = (int64_t)gridDim.x - 1 - blockIdx.x;
   const int qt = (int)(tile % tiles_per_head), bh = (int)(tile / tiles_per_head), h = bh % P.Hkv, b = bh / P.Hkv;
   const int i0 = qt * QT, i_last = min(i0 + QT - 1, P.N - 1);
-  const int q_local = tid >> g_shift, g = tid - (q_local << g_shift);
+  const int q_local = row >> g_shift, g = row - (q_local << g_shift);
   const int i = i0 + q_local;
   const bool valid = i < P.N;
   const int64_t hq = (int64_t)h * G + g;
@@ -704,15 +710,15 @@ dense_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
 
   // Q rows of the tile (zero rows past the end of the sequence) and the first K/V blocks
   {
-    constexpr int CH = D / 8, RPP = kRows / CH;
+    constexpr int CH = D / 8, RPP = kThreads / CH;
     const int sub = tid % CH, r0 = tid / CH;
     const __nv_bfloat16* qb = P.q + b * P.q_sb;
 #pragma unroll
-    for (int it = 0; it < CH; ++it) {
-      const int row = r0 + it * RPP;
-      const int qi = i0 + (row >> g_shift), gg = row & ((1 << g_shift) - 1);
+    for (int it = 0; it < kRows / RPP; ++it) {
+      const int rr = r0 + it * RPP;
+      const int qi = i0 + (rr >> g_shift), gg = rr & ((1 << g_shift) - 1);
       const bool ok = qi < P.N;
-      cp_async16(sQ + (sub / 8) * (kRows * 128) + sw128_offset(row, sub % 8),
+      cp_async16(sQ + (sub / 8) * (kRows * 128) + sw128_offset(rr, sub % 8),
                  qb + (int64_t)((h << g_shift) + gg) * P.q_sh + (int64_t)(ok ? qi : 0) * P.q_sn + sub * 8, ok ? 16u : 0u);
     }
     cp_async_commit();
@@ -753,7 +759,7 @@ dense_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     if (nb > 1) issue_s(1);
   }
 
-  float m_ref = -INFINITY, l = 0.f;
+  float m_ref = -INFINITY, l = 0.f;   // l: this thread's half of the row sum
   for (int t = 0; t < nb; ++t) {
     const int j = jb + t, sb = t & 1;
     __syncwarp();
@@ -761,19 +767,10 @@ dense_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     tc_fence_after_sync();
     if (tid == 0 && t + 2 < nb) load_k(t + 2);   // S(t) is complete: its K buffer is free
     __syncwarp();
-    float s[64];
-    {
-      float tt[32];
-      tmem_ld32(tm_lane + sb * 64, tt);
-      tmem_ld_wait();
-#pragma unroll
-      for (int x = 0; x < 32; ++x) s[x] = tt[x];
-      tmem_ld32(tm_lane + sb * 64 + 32, tt);
-      tmem_ld_wait();
-#pragma unroll
-      for (int x = 0; x < 32; ++x) s[32 + x] = tt[x];
-    }
-    // visible columns of this block for this row
+    float s[32];
+    tmem_ld32(tm_lane + sb * 64 + half * 32, s);
+    tmem_ld_wait();
+    // visible columns of this block for this row, relative to this thread's half
     int lo = 0, lim;
     if (MODE == kModeCmp) {
       lim = min(kBlock - 1, P.rule.num_mem + i / P.rule.stride - 1 - j * kBlock);
@@ -782,23 +779,25 @@ dense_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
       lo = max(0, i - P.rule.window - j * kBlock);
     }
     if (!valid) lim = -1;
+    lim -= half * 32;
+    lo -= half * 32;
     if constexpr (IMP) {
       // the scaled logit of every visible block column, averaged over the G heads of the query (G neighbouring
       // lanes), as the tensor of that dtype would hold it upstream: product, scaled logit and mean each rounded to
       // bf16.  The G lanes reduce-scatter: every step a lane hands half of its columns to its partner and keeps the
-      // other half, so that it ends with 64/G fully summed columns, which it stores.
-      float v[64];
+      // other half, so that it ends with 32/G fully summed columns, which it stores.
+      float v[32];
 #pragma unroll
-      for (int x = 0; x < 64; ++x) v[x] = round_bf16(round_bf16(s[x]) * P.scale);
+      for (int x = 0; x < 32; ++x) v[x] = round_bf16(round_bf16(s[x]) * P.scale);
       int first = 0;
 #pragma unroll
       for (int step = 0; step < 4; ++step) {
         constexpr int kG = IMP ? GI : 1;
-        const int width = 32 >> step;
+        const int width = 16 >> step;
         if ((1 << step) < kG) {
           const bool upper = (g >> step) & 1;
 #pragma unroll
-          for (int x = 0; x < 32; ++x) {
+          for (int x = 0; x < 16; ++x) {
             if (x < width) {
               const float give = upper ? v[x] : v[x + width];
               const float keep = upper ? v[x + width] : v[x];
@@ -808,10 +807,10 @@ dense_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
           first += upper ? width : 0;
         }
       }
-      constexpr int owned = kBlock / (IMP ? (GI > 16 ? 16 : GI) : 1);
+      constexpr int owned = 32 / (IMP ? (GI > 16 ? 16 : GI) : 1);
       float* imp_row = P.importance + (((int64_t)b * P.Hkv + h) * P.N + (valid ? i : 0)) * P.ncb;
       constexpr float inv_g = 1.f / (float)(IMP ? GI : 1);
-      const int col0 = j * kBlock + first - P.rule.num_mem;
+      const int col0 = j * kBlock + half * 32 + first - P.rule.num_mem;
 #pragma unroll
       for (int x = 0; x < owned; ++x) {
         const int col = col0 + x;
@@ -819,15 +818,19 @@ dense_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
       }
     }
     // most blocks are fully visible to every row of the warp: they take the loops without per-column tests
-    const bool all_full = __all_sync(kFullMask, lim == kBlock - 1 && lo == 0);
+    const bool all_full = __all_sync(kFullMask, lim >= 31 && lo <= 0);
     float m = -INFINITY;
     if (all_full) {
 #pragma unroll
-      for (int x = 0; x < 64; ++x) m = fmaxf(m, s[x]);
+      for (int x = 0; x < 32; ++x) m = fmaxf(m, s[x]);
     } else {
 #pragma unroll
-      for (int x = 0; x < 64; ++x) m = ((MODE == kModeCmp || x >= lo) && x <= lim) ? fmaxf(m, s[x]) : m;
+      for (int x = 0; x < 32; ++x) m = ((MODE == kModeCmp || x >= lo) && x <= lim) ? fmaxf(m, s[x]) : m;
     }
+    // the row maximum over both halves
+    xchg[half * kRows + row] = m;
+    __syncthreads();
+    m = fmaxf(m, xchg[(half ^ 1) * kRows + row]);
     const float m_blk2 = m * P.scale_log2;   // -inf when the row sees nothing of this block
     bool need = false;
     float alpha = 1.f;
@@ -840,43 +843,45 @@ dense_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
       need = true;
     }
     if (t > 0 && __any_sync(kFullMask, need)) {
-      // some row of this warp outgrew its reference maximum: scale the accumulator rows (PV(t-1) must be complete)
+      // some row of this warp outgrew its reference maximum: scale the accumulator rows (PV(t-1) must be complete);
+      // each half scales its half of the output columns
       mbar_wait_warp(bar_pv, (uint32_t)(t - 1) & 1, &abort_flag);
       tc_fence_after_sync();
 #pragma unroll 1
-      for (int c2 = 0; c2 < D / 16; ++c2) {
+      for (int c2 = 0; c2 < D / 32; ++c2) {
         float o[16];
-        tmem_ld16(tm_lane + tO + c2 * 16, o);
+        tmem_ld16(tm_lane + tO + half * (D / 2) + c2 * 16, o);
         tmem_ld_wait();
 #pragma unroll
         for (int x = 0; x < 16; ++x) o[x] *= alpha;
-        tmem_st16(tm_lane + tO + c2 * 16, o);
+        tmem_st16(tm_lane + tO + half * (D / 2) + c2 * 16, o);
       }
       tmem_st_wait();
     }
     if (all_full) {
 #pragma unroll
-      for (int x = 0; x < 64; ++x) {
+      for (int x = 0; x < 32; ++x) {
         const float p = ex2(s[x] * P.scale_log2 - m_ref);
         s[x] = p;
         l += p;
       }
     } else {
 #pragma unroll
-      for (int x = 0; x < 64; ++x) {
+      for (int x = 0; x < 32; ++x) {
         const float p = ((MODE == kModeCmp || x >= lo) && x <= lim) ? ex2(s[x] * P.scale_log2 - m_ref) : 0.f;
         s[x] = p;
         l += p;
       }
     }
-    if (t > 0) {   // PV(t-1) is complete: the P tile and V buffer (t-1) & 1 are free
+    if (t > 0) {   // PV(t-1) is complete: V buffer (t-1) & 1 is free
       mbar_wait_warp(bar_pv, (uint32_t)(t - 1) & 1, &abort_flag);
       tc_fence_after_sync();
     }
     if (tid == 0 && t + 1 < nb) load_v(t + 1);
-    // P through tensor memory, over the first half of this row's S columns of buffer sb; S(t+2), which is issued
-    // after PV(t) by the same lane, overwrites them only after PV(t) has read them
-    tmem_st_bf16_row64(tm_lane + sb * 64, s);
+    // P through tensor memory, over the first 32 columns of S buffer sb (both threads of the row have read their S
+    // columns: the exchange of the maxima lies in between); S(t+2), which is issued after PV(t) by the same lane,
+    // overwrites them only after PV(t) has read them
+    tmem_st_bf16_row32(tm_lane + sb * 64 + half * 16, s);
     tmem_st_wait();
     tc_fence_before_sync();
     __syncthreads();
@@ -899,12 +904,17 @@ dense_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     mbar_wait_warp(bar_pv, (uint32_t)(nb - 1) & 1, &abort_flag);
     tc_fence_after_sync();
   }
+  __syncthreads();                       // nobody reads the maxima any more: the exchange area takes the sums
+  xchg[half * kRows + row] = l;
+  __syncthreads();
+  l += xchg[(half ^ 1) * kRows + row];
+  __syncthreads();                       // the sums are read: the staging area (which covers them) may be written
   const float inv = l > 0.f ? 1.f / l : 0.f;
   const int64_t row_global = ((int64_t)b * P.Hq + hq) * P.N + (valid ? i : 0);
 #pragma unroll
-  for (int c2 = 0; c2 < D / 32; ++c2) {
+  for (int c2 = 0; c2 < D / 64; ++c2) {
     float tt[32];
-    tmem_ld32(tm_lane + tO + c2 * 32, tt);
+    tmem_ld32(tm_lane + tO + half * (D / 2) + c2 * 32, tt);
     tmem_ld_wait();
 #pragma unroll
     for (int x = 0; x < 4; ++x) {
@@ -913,13 +923,15 @@ dense_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
       v.y = pack_bf16(tt[x * 8 + 2] * inv, tt[x * 8 + 3] * inv);
       v.z = pack_bf16(tt[x * 8 + 4] * inv, tt[x * 8 + 5] * inv);
       v.w = pack_bf16(tt[x * 8 + 6] * inv, tt[x * 8 + 7] * inv);
-      sts_v4(sStage + tid * kStageStride + c2 * 64 + x * 16, v);
+      sts_v4(sStage + row * kStageStride + half * D + c2 * 64 + x * 16, v);
     }
   }
-  row_dst[tid] = valid && nb > 0 ? (int)row_global : -1;
+  if (half == 0) row_dst[row] = valid && nb > 0 ? (int)row_global : -1;
   __syncthreads();
-  store_rows_coalesced<D * 2>(sStage, kStageStride, row_dst, reinterpret_cast<uint8_t*>(P.out), tid);
-  if (valid) P.lse[row_global] = l > 0.f ? (m_ref + log2f(l)) * kLn2 : -INFINITY;
+  if (half == 0) {
+    store_rows_coalesced<D * 2>(sStage, kStageStride, row_dst, reinterpret_cast<uint8_t*>(P.out), row);
+    if (valid) P.lse[row_global] = l > 0.f ? (m_ref + log2f(l)) * kLn2 : -INFINITY;
+  }
 
   // nothing of this CTA may still be running on the tensor cores when tensor memory is freed
   if (warp == 0) {
@@ -1939,7 +1951,7 @@ static int run_fwd(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaStrea
       CUDA_TRY(cudaFuncSetAttribute(dense_fwd_kernel<D, MODE, GI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
       CUDA_TRY(cudaFuncSetAttribute(dense_fwd_kernel<D, MODE, GI>, cudaFuncAttributePreferredSharedMemoryCarveout,    \
                                     cudaSharedmemCarveoutMaxShared));                                                 \
-      dense_fwd_kernel<D, MODE, GI><<<(unsigned)tiles, kRows, smem, st>>>(tmK, tmV, P);                               \
+      dense_fwd_kernel<D, MODE, GI><<<(unsigned)tiles, 2 * kRows, smem, st>>>(tmK, tmV, P);                               \
     } while (0)
     if (a.mode == kModeSwa) NSA_DENSE_LAUNCH(kModeSwa, 0);
     else if (P.importance == nullptr) NSA_DENSE_LAUNCH(kModeCmp, 0);
