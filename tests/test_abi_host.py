@@ -78,3 +78,36 @@ def test_state_dict_names_match_upstream():
         'k_compress.3.weight', 'k_intrablock_positions', 'norm.weight', 'to_qkv.weight',
         'to_strategy_combine.0.bias', 'to_strategy_combine.0.weight', 'v_compress.1.bias', 'v_compress.1.weight',
         'v_compress.3.bias', 'v_compress.3.weight', 'v_intrablock_positions']
+
+
+def test_rotary_and_gather_entry_points_validate_their_arguments():
+    lib = L.load()
+    assert lib.nsa_rotary(None, None) == -1
+    r = L.RotaryArgs(batch=1, heads=2, seq=8, dim_head=60, dtype=L.NSA_BF16, inverse=0)
+    assert lib.nsa_rotary(C.byref(r), None) == -2            # dim_head not a multiple of 16 bytes
+    r.dim_head = 64
+    assert lib.nsa_rotary(C.byref(r), None) == -1            # pointers are NULL
+    r.dtype = 9
+    assert lib.nsa_rotary(C.byref(r), None) == -3
+    r.dtype, r.seq = L.NSA_F32, 0
+    assert lib.nsa_rotary(C.byref(r), None) == 0             # nothing to do
+
+    assert lib.nsa_combine_fwd_gather(None, None) == -1
+    fwd = L.CombineFwdArgs(batch=1, q_heads=2, seq=4, dim_head=64, dtype=L.NSA_BF16)
+    g = L.CombineGatherArgs(fwd=fwd, num_outs=0, total_features=256, feature_offset=0)
+    assert lib.nsa_combine_fwd_gather(C.byref(g), None) == -1    # branch outputs are NULL: reported first
+    assert L.MAX_GATHER == 8
+
+
+def test_decode_and_diff_topk_are_part_of_the_module_interface():
+    import inspect
+    sig = inspect.signature(SparseAttention.forward)
+    assert list(sig.parameters)[:7] == ['self', 'inp', 'cache', 'disable_triton_kernel', 'sliding_window_flex_mask',
+                                        'fine_selection_flex_mask', 'return_cache']
+    assert hasattr(SparseAttention, 'forward_inference')
+    attn = SparseAttention(dim=64, dim_head=16, heads=4, sliding_window_size=2, compress_block_size=4,
+                           compress_block_sliding_stride=2, selection_block_size=4, num_selected_blocks=2,
+                           causal=True, use_diff_topk=True, use_triton_kernel=True)
+    assert attn.use_diff_topk
+    with pytest.raises(RuntimeError):                         # still no CPU path, also with a cache
+        attn(torch.randn(1, 1, 64), cache=((torch.zeros(1, 4, 0, 16),) * 2, ((torch.zeros(1, 4, 0, 16),) * 2,) * 2))
