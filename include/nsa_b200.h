@@ -334,10 +334,33 @@ typedef struct {
 
 int nsa_rotary(const nsa_rotary_args* args, void* stream);
 
+/* Input of the compress networks (NSA:589-614): the windows of `block` rows taken every `stride` rows of the un-rotated
+ * keys or values -- window w holds rows (w+1)*stride - block .. (w+1)*stride - 1, zero before the sequence start, what
+ * upstream gets from pad + unfold (NSA:270-275) -- plus the intra-block position embedding (NSA:600-601):
+ *   out[b,h,w,j,:] = x[b,h,(w+1)*stride - block + j,:] + pos[h,j,:].
+ * The backward writes dx (zero for rows no window holds) and dpos = sum over batch and windows of dout. */
+typedef struct {
+  nsa_tensor x;                   /* [B, H, N, d] view, last axis contiguous, rows 16-byte aligned      */
+  const void* pos;                /* [H, block, d] contiguous, same dtype                               */
+  void* out;                      /* [B, H, ncb, block, d] contiguous, same dtype, written              */
+  int32_t batch, heads, seq, dim_head, block, stride, ncb, dtype;
+} nsa_windows_fwd_args;
+
+int nsa_windows_fwd(const nsa_windows_fwd_args* args, void* stream);
+
+typedef struct {
+  nsa_windows_fwd_args fwd;       /* sizes as in the forward; x, pos and out are not read               */
+  const void* dout;               /* [B, H, ncb, block, d] contiguous                                   */
+  void* dx;                       /* [B, H, N, d] contiguous, same dtype, written                       */
+  float* dpos;                    /* [H, block, d] contiguous fp32, written                             */
+} nsa_windows_bwd_args;
+
+int nsa_windows_bwd(const nsa_windows_bwd_args* args, void* stream);
+
 /* Library information.  nsa_struct_size(i) is sizeof() of the i-th argument
  * struct in declaration order (0 nsa_tensor, 1 sel_fwd, 2 sel_bwd, 3 cmp_fwd,
  * 4 cmp_bwd, 5 select, 6 swa_fwd, 7 swa_bwd, 8 combine_fwd, 9 combine_bwd, 10 combine_gather,
- * 11 rotary), so
+ * 11 rotary, 12 windows_fwd, 13 windows_bwd), so
  * a foreign-function binding can verify its own layout; -1 for other i. */
 const char* nsa_last_error(void);
 int nsa_abi_version(void);

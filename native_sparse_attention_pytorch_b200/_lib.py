@@ -84,12 +84,21 @@ class RotaryArgs(C.Structure):
                 ('seq', i32), ('dim_head', i32), ('dtype', i32), ('inverse', i32)]
 
 
+class WindowsFwdArgs(C.Structure):
+    _fields_ = [('x', Tensor4), ('pos', vp), ('out', vp), ('batch', i32), ('heads', i32), ('seq', i32),
+                ('dim_head', i32), ('block', i32), ('stride', i32), ('ncb', i32), ('dtype', i32)]
+
+
+class WindowsBwdArgs(C.Structure):
+    _fields_ = [('fwd', WindowsFwdArgs), ('dout', vp), ('dx', vp), ('dpos', vp)]
+
+
 _STRUCTS = [Tensor4, SelFwdArgs, SelBwdArgs, CmpFwdArgs, CmpBwdArgs, SelectArgs, SwaFwdArgs, SwaBwdArgs,
-            CombineFwdArgs, CombineBwdArgs, CombineGatherArgs, RotaryArgs]
+            CombineFwdArgs, CombineBwdArgs, CombineGatherArgs, RotaryArgs, WindowsFwdArgs, WindowsBwdArgs]
 
 ENTRY_POINTS = ['nsa_sel_fwd', 'nsa_sel_bwd', 'nsa_sel_workspace_bytes', 'nsa_sel_fwd_static',
                 'nsa_sel_static_scratch_bytes', 'nsa_cmp_workspace_bytes', 'nsa_swa_workspace_bytes', 'nsa_cmp_fwd', 'nsa_cmp_bwd', 'nsa_select',
-                'nsa_swa_fwd', 'nsa_swa_bwd', 'nsa_combine_fwd', 'nsa_combine_bwd', 'nsa_combine_fwd_gather', 'nsa_rotary', 'nsa_last_error',
+                'nsa_swa_fwd', 'nsa_swa_bwd', 'nsa_combine_fwd', 'nsa_combine_bwd', 'nsa_combine_fwd_gather', 'nsa_rotary', 'nsa_windows_fwd', 'nsa_windows_bwd', 'nsa_last_error',
                 'nsa_abi_version', 'nsa_struct_size']
 
 _lib = None

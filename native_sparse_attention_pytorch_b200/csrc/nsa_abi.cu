@@ -111,6 +111,8 @@ int nsa_struct_size(int which) {
     case 9: return (int)sizeof(nsa_combine_bwd_args);
     case 10: return (int)sizeof(nsa_combine_gather_args);
     case 11: return (int)sizeof(nsa_rotary_args);
+    case 12: return (int)sizeof(nsa_windows_fwd_args);
+    case 13: return (int)sizeof(nsa_windows_bwd_args);
     default: return -1;
   }
 }
@@ -412,6 +414,46 @@ int nsa_rotary(const nsa_rotary_args* a, void* stream) {
   P.x_sb = a->x.stride_b; P.x_sh = a->x.stride_h; P.x_sn = a->x.stride_n;
   P.batch = a->batch; P.heads = a->heads; P.seq = a->seq; P.d = a->dim_head; P.inverse = a->inverse;
   return launch_rotary(P, a->dtype, (cudaStream_t)stream);
+}
+
+static int fill_windows(WindowParams& P, const nsa_windows_fwd_args& a) {
+  if (a.dtype != NSA_F32 && a.dtype != NSA_BF16) return fail(NSA_ERR_DTYPE, "dtype must be NSA_F32 or NSA_BF16");
+  const int V = a.dtype == NSA_F32 ? 4 : 8;
+  if (a.batch < 0 || a.heads < 0 || a.seq < 0 || a.ncb < 0 || a.dim_head <= 0 || a.dim_head % V || a.dim_head > 256 ||
+      a.block <= 0 || a.stride <= 0 || a.block < a.stride)
+    return fail(NSA_ERR_SHAPE, "sizes: negative, dim_head not a multiple of 16 bytes (or above 256), or block < stride");
+  if ((int64_t)a.ncb * a.stride > a.seq) return fail(NSA_ERR_SHAPE, "ncb windows do not fit the sequence");
+  memset(&P, 0, sizeof(P));
+  P.batch = a.batch; P.heads = a.heads; P.seq = a.seq; P.d = a.dim_head; P.block = a.block; P.stride = a.stride;
+  P.ncb = a.ncb;
+  return NSA_OK;
+}
+
+int nsa_windows_fwd(const nsa_windows_fwd_args* a, void* stream) {
+  if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
+  WindowParams P;
+  NSA_TRY(fill_windows(P, *a));
+  if ((int64_t)a->batch * a->heads * a->ncb == 0) return NSA_OK;
+  const int V = a->dtype == NSA_F32 ? 4 : 8;
+  if (!a->x.ptr || !a->pos || !a->out) return fail(NSA_ERR_NULL, "tensor: NULL pointer");
+  if ((reinterpret_cast<uintptr_t>(a->x.ptr) & 15u) || (reinterpret_cast<uintptr_t>(a->pos) & 15u) ||
+      (reinterpret_cast<uintptr_t>(a->out) & 15u) || a->x.stride_b % V || a->x.stride_h % V || a->x.stride_n % V)
+    return fail(NSA_ERR_ALIGN, "x, pos and out must keep 16-byte pieces aligned");
+  P.x = a->x.ptr; P.x_sb = a->x.stride_b; P.x_sh = a->x.stride_h; P.x_sn = a->x.stride_n;
+  P.pos = a->pos; P.out = a->out;
+  return launch_windows(P, a->dtype, false, (cudaStream_t)stream);
+}
+
+int nsa_windows_bwd(const nsa_windows_bwd_args* a, void* stream) {
+  if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
+  WindowParams P;
+  NSA_TRY(fill_windows(P, a->fwd));
+  if (!a->dout || !a->dx || !a->dpos) return fail(NSA_ERR_NULL, "gradient buffer: NULL pointer");
+  if ((reinterpret_cast<uintptr_t>(a->dout) & 15u) || (reinterpret_cast<uintptr_t>(a->dx) & 15u))
+    return fail(NSA_ERR_ALIGN, "dout and dx must be 16-byte aligned");
+  if (256 % a->fwd.dim_head) return fail(NSA_ERR_SHAPE, "dim_head must divide 256 for the position gradient");
+  P.dout = a->dout; P.dx = a->dx; P.dpos = a->dpos;
+  return launch_windows(P, a->fwd.dtype, true, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -62,6 +62,14 @@ struct GatherTargets {
   int64_t total_features, feature_offset;
 };
 
+struct WindowParams {
+  const void *x, *pos, *dout;
+  void *out, *dx;
+  float* dpos;
+  int64_t x_sb, x_sh, x_sn;
+  int batch, heads, seq, d, block, stride, ncb;
+};
+
 struct RotaryParams {
   const void* x;
   void* out;
@@ -76,6 +84,7 @@ int simt_attend(const AttnParams& P, int branch, int dtype, bool backward, cudaS
 int launch_select(const SelectParams& P, cudaStream_t stream);
 int launch_combine(const CombineParams& P, int dtype, bool backward, cudaStream_t stream);
 int launch_rotary(const RotaryParams& P, int dtype, cudaStream_t stream);
+int launch_windows(const WindowParams& P, int dtype, bool backward, cudaStream_t stream);
 int launch_combine_gather(const CombineParams& P, const GatherTargets& Gt, int dtype, cudaStream_t stream);
 
 // Tensor-core family for the selected-block branch.  Each returns

@@ -1,0 +1,112 @@
+// Input of the compress networks: overlapping windows of the (un-rotated) keys or values plus the learned
+// intra-block positions, and the backward of that step.  Upstream pads, unfolds, permutes and adds with four tensor
+// operations and lets autograd invert them (an index-add and two reductions); here each direction is one pass.
+//   out[b,h,w,j,:] = x[b,h,(w+1)*stride - block + j,:] (zero before the sequence start) + pos[h,j,:]
+
+#include "nsa_common.cuh"
+#include "nsa_kernels.h"
+
+namespace nsa {
+
+template <typename T>
+__global__ void __launch_bounds__(256) windows_fwd_kernel(const WindowParams P) {
+  constexpr int V = 16 / (int)sizeof(T);
+  const int vpr = P.d / V;
+  const int64_t total = (int64_t)P.batch * P.heads * P.ncb * P.block * vpr;
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(e % vpr) * V;
+    const int j = (int)((e / vpr) % P.block);
+    const int w = (int)((e / ((int64_t)vpr * P.block)) % P.ncb);
+    const int h = (int)((e / ((int64_t)vpr * P.block * P.ncb)) % P.heads);
+    const int b = (int)(e / ((int64_t)vpr * P.block * P.ncb * P.heads));
+    const int tok = (w + 1) * P.stride - P.block + j;
+    uint4 xraw = make_uint4(0u, 0u, 0u, 0u);
+    if (tok >= 0) xraw = *reinterpret_cast<const uint4*>((const T*)P.x + b * P.x_sb + h * P.x_sh + (int64_t)tok * P.x_sn + c);
+    const uint4 praw = *reinterpret_cast<const uint4*>((const T*)P.pos + ((int64_t)h * P.block + j) * P.d + c);
+    const T* xv = reinterpret_cast<const T*>(&xraw);
+    const T* pv = reinterpret_cast<const T*>(&praw);
+    uint4 packed;
+    T* ov = reinterpret_cast<T*>(&packed);
+#pragma unroll
+    for (int x = 0; x < V; ++x) ov[x] = Elem<T>::from_float(Elem<T>::to_float(xv[x]) + Elem<T>::to_float(pv[x]));
+    *reinterpret_cast<uint4*>((T*)P.out + e * V) = packed;
+  }
+}
+
+// dx[b,h,tok,:] = sum of dout over the windows that hold tok (at most ceil(block / stride) of them)
+template <typename T>
+__global__ void __launch_bounds__(256) windows_bwd_x_kernel(const WindowParams P) {
+  constexpr int V = 16 / (int)sizeof(T);
+  const int vpr = P.d / V;
+  const int64_t total = (int64_t)P.batch * P.heads * P.seq * vpr;
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(e % vpr) * V;
+    const int tok = (int)((e / vpr) % P.seq);
+    const int64_t bh = e / ((int64_t)vpr * P.seq);
+    float acc[V];
+#pragma unroll
+    for (int x = 0; x < V; ++x) acc[x] = 0.f;
+    const int w_lo = tok / P.stride, w_hi = min(P.ncb, (tok + P.block) / P.stride);   // windows w_lo .. w_hi - 1
+    for (int w = w_lo; w < w_hi; ++w) {
+      const int j = tok - (w + 1) * P.stride + P.block;
+      const uint4 raw = *reinterpret_cast<const uint4*>((const T*)P.dout + ((bh * P.ncb + w) * P.block + j) * P.d + c);
+      const T* dv = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int x = 0; x < V; ++x) acc[x] += Elem<T>::to_float(dv[x]);
+    }
+    uint4 packed;
+    T* ov = reinterpret_cast<T*>(&packed);
+#pragma unroll
+    for (int x = 0; x < V; ++x) ov[x] = Elem<T>::from_float(acc[x]);
+    *reinterpret_cast<uint4*>((T*)P.dx + e * V) = packed;
+  }
+}
+
+// dpos[h,j,c] = sum over (batch, window) of dout[b,h,w,j,c]; one block per (h, j), threads = d columns x 256/d parts
+template <typename T>
+__global__ void __launch_bounds__(256) windows_bwd_pos_kernel(const WindowParams P) {
+  __shared__ float part_sum[256];
+  const int h = blockIdx.x / P.block, j = blockIdx.x % P.block;
+  const int parts = 256 / P.d, c = threadIdx.x % P.d, part = threadIdx.x / P.d;
+  float acc = 0.f;
+  if (part < parts) {
+    const int64_t pairs = (int64_t)P.batch * P.ncb;
+    for (int64_t k = part; k < pairs; k += parts) {
+      const int b = (int)(k / P.ncb), w = (int)(k % P.ncb);
+      acc += Elem<T>::to_float(((const T*)P.dout)[((((int64_t)b * P.heads + h) * P.ncb + w) * P.block + j) * P.d + c]);
+    }
+  }
+  part_sum[threadIdx.x] = acc;
+  __syncthreads();
+  if (part == 0) {
+    for (int k = 1; k < parts; ++k) acc += part_sum[k * P.d + c];
+    P.dpos[((int64_t)h * P.block + j) * P.d + c] = acc;
+  }
+}
+
+int launch_windows(const WindowParams& P, int dtype, bool backward, cudaStream_t stream) {
+  const int V = dtype == NSA_F32 ? 4 : 8;
+  const int64_t total = backward ? (int64_t)P.batch * P.heads * P.seq * (P.d / V)
+                                 : (int64_t)P.batch * P.heads * P.ncb * P.block * (P.d / V);
+  if (total > 0) {
+    const int64_t blocks = (total + 255) / 256;
+    const unsigned grid = (unsigned)(blocks < 148 * 16 ? blocks : 148 * 16);
+    if (!backward) {
+      if (dtype == NSA_F32) windows_fwd_kernel<float><<<grid, 256, 0, stream>>>(P);
+      else windows_fwd_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(P);
+    } else {
+      if (dtype == NSA_F32) windows_bwd_x_kernel<float><<<grid, 256, 0, stream>>>(P);
+      else windows_bwd_x_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(P);
+    }
+  }
+  if (backward && P.heads > 0 && P.block > 0) {
+    const unsigned grid = (unsigned)(P.heads * P.block);
+    if (dtype == NSA_F32) windows_bwd_pos_kernel<float><<<grid, 256, 0, stream>>>(P);
+    else windows_bwd_pos_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(P);
+  }
+  const cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return fail((int)err, cudaGetErrorString(err));
+  return NSA_OK;
+}
+
+}  // namespace nsa

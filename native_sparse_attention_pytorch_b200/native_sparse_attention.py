@@ -228,7 +228,10 @@ class SparseAttention(Module):
         q, k, v = map(self._split_heads, (q, k, v))
 
         # compressed keys / values: plug-in networks on un-rotated k, v (NSA:589-614)
-        if ncb > 0:
+        if ncb > 0 and ops.compress_windows_supported(k):
+            kw = ops.compress_windows(k, self.k_intrablock_positions, self.compress_block_size, st, ncb)
+            vw = ops.compress_windows(v, self.v_intrablock_positions, self.compress_block_size, st, ncb)
+        elif ncb > 0:
             kw = self.split_compress_window(k[..., : ncb * st, :]) + self.k_intrablock_positions[None, :, None]
             vw = self.split_compress_window(v[..., : ncb * st, :]) + self.v_intrablock_positions[None, :, None]
         else:

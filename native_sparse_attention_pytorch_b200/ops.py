@@ -436,3 +436,53 @@ def gated_combine_gather(o_cmp, o_sel, o_swa, gates, out_ptrs, total_features, f
                                total_features=total_features, feature_offset=feature_offset)
     with torch.cuda.device(o_cmp.device):
         L.check(lib.nsa_combine_fwd_gather(C.byref(args), L.stream_of(o_cmp)))
+
+
+# --------------------------------------------------------------------------
+# input of the compress networks: windows + intra-block positions (NSA:589-614)
+# --------------------------------------------------------------------------
+
+class CompressWindows(Function):
+    """out[b,h,w,j,:] = x[b,h,(w+1)*stride - block + j,:] (zero before the start) + pos[h,j,:], w < ncb."""
+
+    @staticmethod
+    def forward(ctx, x, pos, block, stride, ncb):
+        L.require_cuda(x, pos)
+        lib = L.load()
+        if not _vec_ok(x):
+            x = x.contiguous()
+        pos = pos.contiguous()
+        b, h, n, d = x.shape
+        out = torch.empty(b, h, ncb, block, d, dtype=x.dtype, device=x.device)
+        args = L.WindowsFwdArgs(x=L.t4(x), pos=L.ptr(pos), out=L.ptr(out), batch=b, heads=h, seq=n, dim_head=d,
+                                block=block, stride=stride, ncb=ncb, dtype=L.dtype_code(x))
+        with torch.cuda.device(x.device):
+            L.check(lib.nsa_windows_fwd(C.byref(args), L.stream_of(x)))
+        ctx.cfg = (b, h, n, d, block, stride, ncb, x.dtype, pos.dtype)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        b, h, n, d, block, stride, ncb, xdtype, pdtype = ctx.cfg
+        lib = L.load()
+        dout = dout.contiguous()
+        dx = torch.empty(b, h, n, d, dtype=xdtype, device=dout.device)
+        dpos = torch.empty(h, block, d, dtype=torch.float32, device=dout.device)
+        fwd = L.WindowsFwdArgs(x=L.Tensor4(), pos=None, out=None, batch=b, heads=h, seq=n, dim_head=d, block=block,
+                               stride=stride, ncb=ncb, dtype=L.dtype_code(dout))
+        args = L.WindowsBwdArgs(fwd=fwd, dout=L.ptr(dout), dx=L.ptr(dx), dpos=L.ptr(dpos))
+        with torch.cuda.device(dout.device):
+            L.check(lib.nsa_windows_bwd(C.byref(args), L.stream_of(dout)))
+        return dx, dpos.to(pdtype), None, None, None
+
+
+def compress_windows(x, pos, block, stride, ncb):
+    """Windows of `block` rows every `stride` rows of x [B,H,N,d] plus the intra-block positions pos [H,block,d]:
+    the input of the compress networks, [B,H,ncb,block,d]."""
+    return CompressWindows.apply(x, pos, block, stride, ncb)
+
+
+def compress_windows_supported(x):
+    v = 16 // x.element_size()
+    d = x.shape[-1]
+    return x.is_cuda and x.dtype in (torch.float32, torch.bfloat16) and d % v == 0 and d <= 256 and 256 % d == 0

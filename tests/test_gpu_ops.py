@@ -344,3 +344,27 @@ def test_selection_at_full_size_equals_the_oracle_steps(shape):
     ulp = 2e-7 * probs.amax(dim=-1, keepdim=True)
     assert (picked >= top[..., -1:] - ulp).all()        # none of them is below the (k+1)-th largest
     assert (picked[..., :-1] >= picked[..., 1:] - ulp).all()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize('block,stride', [(8, 4), (5, 2), (4, 4), (32, 16)])
+def test_compress_windows_match_pad_unfold_add(dtype, block, stride):
+    from native_sparse_attention_pytorch_b200 import ops
+    b, h, n, d = 2, 3, 77, 32
+    ncb = n // stride
+    base = recipe.randn((b, n, h * d), 1).to(dtype)                   # heads as a strided view
+    pos = recipe.randn((h, block, d), 2).to(dtype)
+    up = recipe.randn((b, h, ncb, block, d), 3).to(dtype)
+    xr = base.float().view(b, n, h, d).transpose(1, 2).requires_grad_()
+    pr = pos.float().requires_grad_()
+    ref = O.compress_windows(xr[..., : ncb * stride, :], block, stride) + pr[None, :, None]
+    gx, gp = torch.autograd.grad((ref * up.float()).sum(), (xr, pr))
+    xg = base.to(DEV).view(b, n, h, d).transpose(1, 2).requires_grad_()
+    pg = pos.to(DEV).requires_grad_()
+    out = ops.compress_windows(xg, pg, block, stride, ncb)
+    dx, dp = torch.autograd.grad((out * up.to(DEV)).sum(), (xg, pg))
+    close = closeness(dtype)
+    close(out, ref, 'windows')
+    close(dx, gx, 'd x')
+    assert_close_bf16(dp, gp, 'd positions', rel_to_max=5e-3) if dtype == torch.bfloat16 else close(dp, gp, 'd positions')
