@@ -62,25 +62,26 @@ __global__ void __launch_bounds__(256) windows_bwd_x_kernel(const WindowParams P
   }
 }
 
-// dpos[h,j,c] = sum over (batch, window) of dout[b,h,w,j,c]; one block per (h, j), threads = d columns x 256/d parts
+// dpos[h,j,c] = sum over (batch, window) of dout[b,h,w,j,c]; blockIdx.x = (h, j), blockIdx.y = a slice of the
+// (batch, window) pairs; threads = d columns x 256/d parts; slices add their sums into the zeroed dpos
 template <typename T>
 __global__ void __launch_bounds__(256) windows_bwd_pos_kernel(const WindowParams P) {
   __shared__ float part_sum[256];
   const int h = blockIdx.x / P.block, j = blockIdx.x % P.block;
   const int parts = 256 / P.d, c = threadIdx.x % P.d, part = threadIdx.x / P.d;
+  const int64_t pairs = (int64_t)P.batch * P.ncb;
+  const int64_t per = (pairs + gridDim.y - 1) / gridDim.y;
+  const int64_t k0 = blockIdx.y * per, k1 = k0 + per < pairs ? k0 + per : pairs;
   float acc = 0.f;
-  if (part < parts) {
-    const int64_t pairs = (int64_t)P.batch * P.ncb;
-    for (int64_t k = part; k < pairs; k += parts) {
-      const int b = (int)(k / P.ncb), w = (int)(k % P.ncb);
-      acc += Elem<T>::to_float(((const T*)P.dout)[((((int64_t)b * P.heads + h) * P.ncb + w) * P.block + j) * P.d + c]);
-    }
+  for (int64_t k = k0 + part; k < k1; k += parts) {
+    const int b = (int)(k / P.ncb), w = (int)(k % P.ncb);
+    acc += Elem<T>::to_float(((const T*)P.dout)[((((int64_t)b * P.heads + h) * P.ncb + w) * P.block + j) * P.d + c]);
   }
   part_sum[threadIdx.x] = acc;
   __syncthreads();
   if (part == 0) {
     for (int k = 1; k < parts; ++k) acc += part_sum[k * P.d + c];
-    P.dpos[((int64_t)h * P.block + j) * P.d + c] = acc;
+    atomicAdd(&P.dpos[((int64_t)h * P.block + j) * P.d + c], acc);
   }
 }
 
@@ -100,7 +101,12 @@ int launch_windows(const WindowParams& P, int dtype, bool backward, cudaStream_t
     }
   }
   if (backward && P.heads > 0 && P.block > 0) {
-    const unsigned grid = (unsigned)(P.heads * P.block);
+    const cudaError_t zerr = cudaMemsetAsync(P.dpos, 0, (size_t)P.heads * P.block * P.d * sizeof(float), stream);
+    if (zerr != cudaSuccess) return fail((int)zerr, cudaGetErrorString(zerr));
+    const int64_t pairs = (int64_t)P.batch * P.ncb;
+    int slices = (int)((pairs + 63) / 64);
+    slices = slices < 1 ? 1 : (slices > 32 ? 32 : slices);
+    const dim3 grid((unsigned)(P.heads * P.block), (unsigned)slices);
     if (dtype == NSA_F32) windows_bwd_pos_kernel<float><<<grid, 256, 0, stream>>>(P);
     else windows_bwd_pos_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(P);
   }
