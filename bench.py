@@ -865,8 +865,9 @@ def run_prefill_reference(args, w):
 def build_lm(w, dev):
     """A small byte-level language model around the layer, with the sizes of upstream's training example: token
     embedding, `depth` pre-norm residual blocks of [SparseAttention, RMSNorm -> Linear x4 -> GELU -> Linear], final
-    RMSNorm, logits.  It is a harness for the layer, not part of the library."""
+    RMSNorm (the library's, as inside the layer), logits.  It is a harness for the layer, not part of the library."""
     import native_sparse_attention_pytorch_b200 as nsa
+    from native_sparse_attention_pytorch_b200.norm import RMSNorm
     from torch import nn
     kw = {k: w[k] for k in ('dim', 'dim_head', 'heads', 'kv_heads', 'sliding_window_size', 'compress_block_size',
                             'compress_block_sliding_stride', 'selection_block_size', 'num_selected_blocks')}
@@ -878,9 +879,9 @@ def build_lm(w, dev):
             self.emb = nn.Embedding(w['vocab'], dim)
             self.blocks = nn.ModuleList([nn.ModuleList([
                 nsa.SparseAttention(causal=True, use_triton_kernel=True, **kw),
-                nn.Sequential(nn.RMSNorm(dim), nn.Linear(dim, 4 * dim), nn.GELU(), nn.Linear(4 * dim, dim))])
+                nn.Sequential(RMSNorm(dim), nn.Linear(dim, 4 * dim), nn.GELU(), nn.Linear(4 * dim, dim))])
                 for _ in range(w['depth'])])
-            self.norm = nn.RMSNorm(dim)
+            self.norm = RMSNorm(dim)
             self.to_logits = nn.Linear(dim, w['vocab'], bias=False)
 
         def forward(self, ids):

@@ -357,10 +357,37 @@ typedef struct {
 
 int nsa_windows_bwd(const nsa_windows_bwd_args* args, void* stream);
 
+/* RMS normalisation of the layer input, the first step of the layer's forward (NSA:579 and NSA:369 `inp = self.norm(inp)`, an
+ * nn.RMSNorm built at NSA:230; the same module normalises the feed-forward input and the final tokens of the
+ * language model, transformer.py:134, 210):  y = x * rsqrt(mean(x^2, last axis) + eps) * weight, fp32 arithmetic, one rounding.
+ * The forward also writes the reciprocal root per row, which the backward reads:
+ *   dx = rstd * (dy*weight - xhat * mean(dy*weight*xhat)),  dweight = sum over rows of dy * xhat,  xhat = x * rstd.
+ * dim must be a multiple of 16 bytes and at most 256 sixteen-byte pieces (2048 bf16 / 1024 fp32 elements). */
+typedef struct {
+  const void* x;                  /* [rows, dim], rows x_stride elements apart, 16-byte aligned rows     */
+  const void* weight;             /* [dim] in the dtype of x, or fp32 when weight_f32 != 0              */
+  void* y;                        /* [rows, dim] contiguous, dtype of x, written                          */
+  float* rstd;                    /* [rows] fp32, written                                                 */
+  int64_t rows, x_stride;
+  int32_t dim, dtype, weight_f32, reserved;
+  float eps, reserved2;
+} nsa_rmsnorm_fwd_args;
+
+int nsa_rmsnorm_fwd(const nsa_rmsnorm_fwd_args* args, void* stream);
+
+typedef struct {
+  nsa_rmsnorm_fwd_args fwd;       /* x, weight, rstd and the sizes as in the forward; y is not read        */
+  const void* dy;                 /* [rows, dim] contiguous, dtype of x                                   */
+  void* dx;                       /* [rows, dim] contiguous, dtype of x, written                          */
+  float* dweight;                 /* [dim] fp32, written                                                  */
+} nsa_rmsnorm_bwd_args;
+
+int nsa_rmsnorm_bwd(const nsa_rmsnorm_bwd_args* args, void* stream);
+
 /* Library information.  nsa_struct_size(i) is sizeof() of the i-th argument
  * struct in declaration order (0 nsa_tensor, 1 sel_fwd, 2 sel_bwd, 3 cmp_fwd,
  * 4 cmp_bwd, 5 select, 6 swa_fwd, 7 swa_bwd, 8 combine_fwd, 9 combine_bwd, 10 combine_gather,
- * 11 rotary, 12 windows_fwd, 13 windows_bwd), so
+ * 11 rotary, 12 windows_fwd, 13 windows_bwd, 14 rmsnorm_fwd, 15 rmsnorm_bwd), so
  * a foreign-function binding can verify its own layout; -1 for other i. */
 const char* nsa_last_error(void);
 int nsa_abi_version(void);

@@ -93,12 +93,22 @@ class WindowsBwdArgs(C.Structure):
     _fields_ = [('fwd', WindowsFwdArgs), ('dout', vp), ('dx', vp), ('dpos', vp)]
 
 
+class RmsNormFwdArgs(C.Structure):
+    _fields_ = [('x', vp), ('weight', vp), ('y', vp), ('rstd', vp), ('rows', i64), ('x_stride', i64), ('dim', i32),
+                ('dtype', i32), ('weight_f32', i32), ('reserved', i32), ('eps', C.c_float), ('reserved2', C.c_float)]
+
+
+class RmsNormBwdArgs(C.Structure):
+    _fields_ = [('fwd', RmsNormFwdArgs), ('dy', vp), ('dx', vp), ('dweight', vp)]
+
+
 _STRUCTS = [Tensor4, SelFwdArgs, SelBwdArgs, CmpFwdArgs, CmpBwdArgs, SelectArgs, SwaFwdArgs, SwaBwdArgs,
-            CombineFwdArgs, CombineBwdArgs, CombineGatherArgs, RotaryArgs, WindowsFwdArgs, WindowsBwdArgs]
+            CombineFwdArgs, CombineBwdArgs, CombineGatherArgs, RotaryArgs, WindowsFwdArgs, WindowsBwdArgs,
+            RmsNormFwdArgs, RmsNormBwdArgs]
 
 ENTRY_POINTS = ['nsa_sel_fwd', 'nsa_sel_bwd', 'nsa_sel_workspace_bytes', 'nsa_sel_fwd_static',
                 'nsa_sel_static_scratch_bytes', 'nsa_cmp_workspace_bytes', 'nsa_swa_workspace_bytes', 'nsa_cmp_fwd', 'nsa_cmp_bwd', 'nsa_select',
-                'nsa_swa_fwd', 'nsa_swa_bwd', 'nsa_combine_fwd', 'nsa_combine_bwd', 'nsa_combine_fwd_gather', 'nsa_rotary', 'nsa_windows_fwd', 'nsa_windows_bwd', 'nsa_last_error',
+                'nsa_swa_fwd', 'nsa_swa_bwd', 'nsa_combine_fwd', 'nsa_combine_bwd', 'nsa_combine_fwd_gather', 'nsa_rotary', 'nsa_windows_fwd', 'nsa_windows_bwd', 'nsa_rmsnorm_fwd', 'nsa_rmsnorm_bwd', 'nsa_last_error',
                 'nsa_abi_version', 'nsa_struct_size']
 
 _lib = None

@@ -113,6 +113,8 @@ int nsa_struct_size(int which) {
     case 11: return (int)sizeof(nsa_rotary_args);
     case 12: return (int)sizeof(nsa_windows_fwd_args);
     case 13: return (int)sizeof(nsa_windows_bwd_args);
+    case 14: return (int)sizeof(nsa_rmsnorm_fwd_args);
+    case 15: return (int)sizeof(nsa_rmsnorm_bwd_args);
     default: return -1;
   }
 }
@@ -451,9 +453,49 @@ int nsa_windows_bwd(const nsa_windows_bwd_args* a, void* stream) {
   if (!a->dout || !a->dx || !a->dpos) return fail(NSA_ERR_NULL, "gradient buffer: NULL pointer");
   if ((reinterpret_cast<uintptr_t>(a->dout) & 15u) || (reinterpret_cast<uintptr_t>(a->dx) & 15u))
     return fail(NSA_ERR_ALIGN, "dout and dx must be 16-byte aligned");
-  if (256 % a->fwd.dim_head) return fail(NSA_ERR_SHAPE, "dim_head must divide 256 for the position gradient");
   P.dout = a->dout; P.dx = a->dx; P.dpos = a->dpos;
   return launch_windows(P, a->fwd.dtype, true, (cudaStream_t)stream);
+}
+
+static int fill_norm(NormParams& P, const nsa_rmsnorm_fwd_args& a) {
+  if (a.dtype != NSA_F32 && a.dtype != NSA_BF16) return fail(NSA_ERR_DTYPE, "dtype must be NSA_F32 or NSA_BF16");
+  const int V = a.dtype == NSA_F32 ? 4 : 8;
+  if (a.rows < 0 || a.dim <= 0 || a.dim % V || a.dim / V > 256 || a.x_stride < a.dim)
+    return fail(NSA_ERR_SHAPE, "rows negative, dim not a multiple of 16 bytes or above 256 such pieces, or rows overlap");
+  if (a.x_stride % V) return fail(NSA_ERR_ALIGN, "rows of x must start on 16-byte boundaries");
+  memset(&P, 0, sizeof(P));
+  P.rows = a.rows; P.x_stride = a.x_stride; P.dim = a.dim; P.weight_f32 = a.weight_f32 != 0; P.eps = a.eps;
+  if (a.rows == 0) return NSA_OK;
+  if (!a.x || !a.weight || !a.rstd) return fail(NSA_ERR_NULL, "tensor: NULL pointer");
+  if ((reinterpret_cast<uintptr_t>(a.x) & 15u) || (reinterpret_cast<uintptr_t>(a.weight) & 15u))
+    return fail(NSA_ERR_ALIGN, "x and weight must be 16-byte aligned");
+  P.x = a.x; P.weight = a.weight; P.rstd = a.rstd;
+  return NSA_OK;
+}
+
+int nsa_rmsnorm_fwd(const nsa_rmsnorm_fwd_args* a, void* stream) {
+  if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
+  NormParams P;
+  NSA_TRY(fill_norm(P, *a));
+  if (a->rows == 0) return NSA_OK;
+  if (!a->y) return fail(NSA_ERR_NULL, "y: NULL pointer");
+  if (reinterpret_cast<uintptr_t>(a->y) & 15u) return fail(NSA_ERR_ALIGN, "y must be 16-byte aligned");
+  P.y = a->y;
+  return launch_rmsnorm(P, a->dtype, false, (cudaStream_t)stream);
+}
+
+int nsa_rmsnorm_bwd(const nsa_rmsnorm_bwd_args* a, void* stream) {
+  if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
+  NormParams P;
+  NSA_TRY(fill_norm(P, a->fwd));
+  if (!a->dweight) return fail(NSA_ERR_NULL, "dweight: NULL pointer");
+  if (a->fwd.rows > 0) {
+    if (!a->dy || !a->dx) return fail(NSA_ERR_NULL, "gradient buffer: NULL pointer");
+    if ((reinterpret_cast<uintptr_t>(a->dy) & 15u) || (reinterpret_cast<uintptr_t>(a->dx) & 15u))
+      return fail(NSA_ERR_ALIGN, "dy and dx must be 16-byte aligned");
+  }
+  P.dy = a->dy; P.dx = a->dx; P.dweight = a->dweight;
+  return launch_rmsnorm(P, a->fwd.dtype, true, (cudaStream_t)stream);
 }
 
 }  // extern "C"

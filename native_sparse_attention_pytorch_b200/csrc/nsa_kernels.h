@@ -78,6 +78,19 @@ struct RotaryParams {
   int batch, heads, seq, d, inverse;
 };
 
+struct NormParams {
+  const void* x;      // [rows, dim] rows x_stride elements apart
+  const void* weight; // [dim] in the dtype of x, or fp32 when weight_f32
+  void* y;            // [rows, dim] contiguous (forward)
+  float* rstd;        // [rows]: written by the forward, read by the backward
+  const void* dy;     // [rows, dim] contiguous (backward)
+  void* dx;           // [rows, dim] contiguous (backward)
+  float* dweight;     // [dim] fp32 (backward)
+  int64_t rows, x_stride;
+  int dim, weight_f32;
+  float eps;
+};
+
 int fail(int code, const char* msg);
 
 int simt_attend(const AttnParams& P, int branch, int dtype, bool backward, cudaStream_t stream);
@@ -85,6 +98,7 @@ int launch_select(const SelectParams& P, cudaStream_t stream);
 int launch_combine(const CombineParams& P, int dtype, bool backward, cudaStream_t stream);
 int launch_rotary(const RotaryParams& P, int dtype, cudaStream_t stream);
 int launch_windows(const WindowParams& P, int dtype, bool backward, cudaStream_t stream);
+int launch_rmsnorm(const NormParams& P, int dtype, bool backward, cudaStream_t stream);
 int launch_combine_gather(const CombineParams& P, const GatherTargets& Gt, int dtype, cudaStream_t stream);
 
 // Tensor-core family for the selected-block branch.  Each returns

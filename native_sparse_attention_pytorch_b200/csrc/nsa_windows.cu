@@ -62,27 +62,33 @@ __global__ void __launch_bounds__(256) windows_bwd_x_kernel(const WindowParams P
   }
 }
 
-// dpos[h,j,c] = sum over (batch, window) of dout[b,h,w,j,c]; blockIdx.x = (h, j), blockIdx.y = a slice of the
-// (batch, window) pairs; threads = d columns x 256/d parts; slices add their sums into the zeroed dpos
+// dpos[h,j,c] = sum over (batch, window) of dout[b,h,w,j,c].  A window is block * d contiguous elements: thread t of
+// blockIdx.x = (h, group of 128 sixteen-byte slots) owns one slot of the window, blockIdx.y a slice of the
+// (batch, window) pairs; every slice adds its sums into the zeroed dpos.
 template <typename T>
-__global__ void __launch_bounds__(256) windows_bwd_pos_kernel(const WindowParams P) {
-  __shared__ float part_sum[256];
-  const int h = blockIdx.x / P.block, j = blockIdx.x % P.block;
-  const int parts = 256 / P.d, c = threadIdx.x % P.d, part = threadIdx.x / P.d;
+__global__ void __launch_bounds__(128) windows_bwd_pos_kernel(const WindowParams P, int slot_groups) {
+  constexpr int V = 16 / (int)sizeof(T);
+  const int slots = P.block * P.d / V;
+  const int h = blockIdx.x / slot_groups, slot = (blockIdx.x % slot_groups) * 128 + threadIdx.x;
+  if (slot >= slots) return;
   const int64_t pairs = (int64_t)P.batch * P.ncb;
   const int64_t per = (pairs + gridDim.y - 1) / gridDim.y;
   const int64_t k0 = blockIdx.y * per, k1 = k0 + per < pairs ? k0 + per : pairs;
-  float acc = 0.f;
-  for (int64_t k = k0 + part; k < k1; k += parts) {
-    const int b = (int)(k / P.ncb), w = (int)(k % P.ncb);
-    acc += Elem<T>::to_float(((const T*)P.dout)[((((int64_t)b * P.heads + h) * P.ncb + w) * P.block + j) * P.d + c]);
+  float acc[V];
+#pragma unroll
+  for (int x = 0; x < V; ++x) acc[x] = 0.f;
+#pragma unroll 4
+  for (int64_t k = k0; k < k1; ++k) {
+    const int64_t b = k / P.ncb, w = k % P.ncb;
+    const uint4 raw = *reinterpret_cast<const uint4*>((const T*)P.dout + ((b * P.heads + h) * P.ncb + w) * ((int64_t)slots * V) +
+                                                      (int64_t)slot * V);
+    const T* dv = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int x = 0; x < V; ++x) acc[x] += Elem<T>::to_float(dv[x]);
   }
-  part_sum[threadIdx.x] = acc;
-  __syncthreads();
-  if (part == 0) {
-    for (int k = 1; k < parts; ++k) acc += part_sum[k * P.d + c];
-    atomicAdd(&P.dpos[((int64_t)h * P.block + j) * P.d + c], acc);
-  }
+  float* dst = P.dpos + (int64_t)h * slots * V + (int64_t)slot * V;
+#pragma unroll
+  for (int x = 0; x < V; ++x) atomicAdd(dst + x, acc[x]);
 }
 
 int launch_windows(const WindowParams& P, int dtype, bool backward, cudaStream_t stream) {
@@ -104,11 +110,14 @@ int launch_windows(const WindowParams& P, int dtype, bool backward, cudaStream_t
     const cudaError_t zerr = cudaMemsetAsync(P.dpos, 0, (size_t)P.heads * P.block * P.d * sizeof(float), stream);
     if (zerr != cudaSuccess) return fail((int)zerr, cudaGetErrorString(zerr));
     const int64_t pairs = (int64_t)P.batch * P.ncb;
-    int slices = (int)((pairs + 63) / 64);
-    slices = slices < 1 ? 1 : (slices > 32 ? 32 : slices);
-    const dim3 grid((unsigned)(P.heads * P.block), (unsigned)slices);
-    if (dtype == NSA_F32) windows_bwd_pos_kernel<float><<<grid, 256, 0, stream>>>(P);
-    else windows_bwd_pos_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(P);
+    const int slot_groups = (P.block * P.d / V + 127) / 128;
+    const int64_t ctas = (int64_t)P.heads * slot_groups;
+    int64_t slices = (148 * 8 + ctas - 1) / ctas;            // about eight CTAs per SM in total
+    slices = slices > pairs ? pairs : slices;
+    slices = slices < 1 ? 1 : (slices > 65535 ? 65535 : slices);
+    const dim3 grid((unsigned)ctas, (unsigned)slices);
+    if (dtype == NSA_F32) windows_bwd_pos_kernel<float><<<grid, 128, 0, stream>>>(P, slot_groups);
+    else windows_bwd_pos_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(P, slot_groups);
   }
   const cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return fail((int)err, cudaGetErrorString(err));

@@ -16,6 +16,7 @@ from torch import nn
 from torch.nn import Module
 
 from . import ops
+from .norm import RMSNorm
 from .rotary import RotaryEmbedding
 
 
@@ -64,7 +65,7 @@ class SparseAttention(Module):
         self.causal = causal
         self.kernel_impl = kernel_impl
 
-        self.norm = nn.RMSNorm(dim) if norm else nn.Identity()
+        self.norm = RMSNorm(dim) if norm else nn.Identity()
         self.rotary_emb = RotaryEmbedding(dim_head)
         self.qkv_split = (dim_head * heads, dim_head * kv_heads, dim_head * kv_heads)
         self.to_qkv = nn.Linear(dim, sum(self.qkv_split), bias=False)

@@ -18,7 +18,9 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(HERE, 'standins'))
 sys.path.insert(0, HERE)
-upstream = sys.argv[1] if len(sys.argv) > 1 else '/root/reference'
+if len(sys.argv) < 2:
+    sys.exit('usage: make_golden.py /path/to/upstream/checkout')
+upstream = sys.argv[1]
 sys.path.insert(0, upstream)
 
 import recipe  # noqa: E402

@@ -99,6 +99,33 @@ def test_rotary_and_gather_entry_points_validate_their_arguments():
     assert L.MAX_GATHER == 8
 
 
+def test_norm_entry_points_validate_their_arguments():
+    lib = L.load()
+    assert lib.nsa_rmsnorm_fwd(None, None) == -1 and lib.nsa_rmsnorm_bwd(None, None) == -1
+    a = L.RmsNormFwdArgs(rows=4, x_stride=60, dim=60, dtype=L.NSA_BF16, eps=1e-6)
+    assert lib.nsa_rmsnorm_fwd(C.byref(a), None) == -2        # dim not a multiple of 16 bytes
+    a.dim, a.x_stride = 4096, 4096
+    assert lib.nsa_rmsnorm_fwd(C.byref(a), None) == -2        # more pieces than a warp keeps in registers
+    a.dim, a.x_stride = 512, 256
+    assert lib.nsa_rmsnorm_fwd(C.byref(a), None) == -2        # overlapping rows
+    a.x_stride = 512
+    assert lib.nsa_rmsnorm_fwd(C.byref(a), None) == -1        # pointers are NULL
+    a.dtype = 7
+    assert lib.nsa_rmsnorm_fwd(C.byref(a), None) == -3
+    a.dtype, a.rows = L.NSA_F32, 0
+    assert lib.nsa_rmsnorm_fwd(C.byref(a), None) == 0         # nothing to do
+    b = L.RmsNormBwdArgs(fwd=a)
+    assert lib.nsa_rmsnorm_bwd(C.byref(b), None) == -1        # the weight gradient is written even for no rows
+
+
+def test_norm_module_is_state_dict_compatible_and_runs_on_cpu():
+    from native_sparse_attention_pytorch_b200.norm import RMSNorm, rms_norm
+    m, ref = RMSNorm(24), torch.nn.RMSNorm(24)
+    assert list(m.state_dict()) == list(ref.state_dict()) and m.eps is None
+    x = torch.randn(3, 5, 24)
+    assert torch.equal(m(x), ref(x)) and torch.equal(rms_norm(x, m.weight), ref(x))
+
+
 def test_decode_and_diff_topk_are_part_of_the_module_interface():
     import inspect
     sig = inspect.signature(SparseAttention.forward)

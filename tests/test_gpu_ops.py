@@ -317,6 +317,42 @@ def test_rotary_kernel_matches_oracle(dtype):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize('shape', [(3, 37, 64), (2, 1000, 512), (1, 5, 1000), (4, 9, 2048 // 2), (0, 4, 64)])
+def test_rms_norm_kernel_matches_the_formula(dtype, shape):
+    """y = x * rsqrt(mean(x^2) + eps) * weight in fp32 on the CPU (the formula of torch.nn.RMSNorm; its default eps is
+    the machine epsilon of fp32 for bf16 inputs too), forward and backward, also through a strided view and an fp32 weight."""
+    from native_sparse_attention_pytorch_b200.norm import RMSNorm, rms_norm, rms_norm_supported
+    b, n, dim = shape
+    x = recipe.randn((b, n, 2 * dim), 11).to(dtype)[..., :dim]        # rows 2*dim apart
+    wt = (1.0 + 0.3 * recipe.randn((dim,), 12)).to(dtype)
+    up = recipe.randn((b, n, dim), 13).to(dtype)
+    eps = torch.finfo(torch.float32).eps
+    xr, wr = x.float().requires_grad_(), wt.float().requires_grad_()
+    ref = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + eps) * wr
+    rdx, rdw = torch.autograd.grad((ref * up.float()).sum(), (xr, wr))
+    for weight_dtype in sorted({dtype, torch.float32}, key=str):
+        mod = RMSNorm(dim).to(DEV).to(weight_dtype)
+        with torch.no_grad():
+            mod.weight.copy_(wt)
+        xg = x.to(DEV).requires_grad_()
+        assert rms_norm_supported(xg, mod.weight)
+        out = mod(xg)
+        assert out.dtype == dtype and out.shape == x.shape
+        gdx, gdw = torch.autograd.grad((out * up.to(DEV)).sum(), (xg, mod.weight))
+        assert gdw.dtype == weight_dtype
+        if dtype == torch.float32:
+            assert_close_f32(out, ref, 'y')
+            assert_close_f32(gdx, rdx, 'dx')
+            assert_close_f32(gdw, rdw, 'dweight')
+        else:
+            assert_close_bf16(out, ref, 'y')
+            assert_close_bf16(gdx, rdx, 'dx')
+            assert_close_bf16(gdw, rdw, 'dweight')
+        assert torch.equal(rms_norm(x.to(DEV), mod.weight.detach()), out.detach())
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize('shape', [(2, 4, 16384, 16, 64, 16), (1, 1, 65536, 16, 64, 16)])
 def test_selection_at_full_size_equals_the_oracle_steps(shape):
     """The selection kernel at the row lengths of the full-layer and the long-context configuration (256 and 1024
