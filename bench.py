@@ -596,9 +596,7 @@ def run_layer(args, w):
                 'steps': e2e_steps},
         'gpu_launches': None, 'clocks': clocks,
     }
-    # kernels of this library per step: three branches forward and backward (13 + 13 + 13 with the tensor-core
-    # family), selection, combine forward and backward
-    line['gpu_launches'] = (3 * 13 + 3) * args.steps
+    line['gpu_launches'] = LAYER_LAUNCHES * args.steps
     if not args.no_cpu_baseline and world == 1:
         line['cpu_baseline'] = layer_cpu_sample(kw)
     print(json.dumps(line))
@@ -977,7 +975,8 @@ def run_lm(args, w):
                      'peak_sustained': sustained, 'flops_per_step': f_step, 'traffic': None},
         'e2e': {'value': tokens / (t.item() / e2e_steps / 1e3), 'unit': 'tokens/s',
                 'h2d_bytes_per_step': ids_host.numel() * 8 * world, 'd2h_bytes_per_step': 4, 'steps': e2e_steps},
-        'gpu_launches': (3 * 13 + 2 + 3) * w['depth'] * args.steps, 'clocks': clocks,
+        # per block the layer plus the feed-forward's norm (forward, backward); the final norm
+        'gpu_launches': ((LAYER_LAUNCHES + 2) * w['depth'] + 2) * args.steps, 'clocks': clocks,
         'loss': float(keep['loss']),
     }
     if not args.no_cpu_baseline and world == 1:
@@ -988,13 +987,21 @@ def run_lm(args, w):
     print(json.dumps(line))
 
 
+# Kernels of this library launched by one forward+backward of the layer at a shape the tensor-core family serves.
+# Forward 16: norm, window split of k and v (2), compressed (importance prefill + dense kernel: 2), selection, rotary of
+# q and k (2), selected (index pre-pass 4 + main + merge: 6), sliding (dense kernel), combine.  Backward 25: combine,
+# sliding (pre-pass 4 + delta + main + dQ merge: 7), selected (delta + main + dQ merge on the forward's index: 3),
+# inverse rotary (2), compressed (7), window split (2 x 2), norm.
+LAYER_LAUNCHES = 16 + 25
+
+
 def launches_per_step(kernels, w):
     """Kernels of this library launched by one forward+backward of the operator."""
     if kernels == 'simt':
         return 2   # one forward kernel, one backward kernel (gradient buffers are cleared by memset)
     # tensor-core family: index pre-pass (4 kernels) + main + merge forward;
-    # index pre-pass + delta + main + dq merge backward
-    return 6 + 7
+    # delta + main + dq merge backward, on the index the forward built
+    return 6 + 3
 
 
 if __name__ == '__main__':

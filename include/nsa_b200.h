@@ -111,6 +111,12 @@ int nsa_sel_fwd(const nsa_sel_fwd_args* args, void* stream);
  * TRI:1900-1902).  slot_grads, if not NULL, receives for every slot the
  * gradient of a multiplier of 1 on that slot's logits (TRI:1061-1080), fp32
  * [B, sel_heads, N, nsel].
+ * The tensor-core kernels walk an index of which queries attend which key
+ * block, built from idx and mask at the start of each call into the first
+ * nsa_sel_index_bytes(args) bytes of the work buffer.  A caller that kept a
+ * copy of those bytes from the forward call over the same idx, mask and
+ * sizes may pass it as `index` (read only, 16-byte aligned, index_bytes ==
+ * nsa_sel_index_bytes): the backward then skips rebuilding it.  NULL = build.
  * ---------------------------------------------------------------------- */
 typedef struct {
   nsa_sel_fwd_args fwd;  /* same tensors as the forward call; out and lse are read */
@@ -119,9 +125,15 @@ typedef struct {
   float* dk;             /* [B, kv_heads, N, d] contiguous fp32, written      */
   float* dv;             /* [B, kv_heads, N, d] contiguous fp32, written      */
   float* slot_grads;     /* optional                                          */
+  const void* index;     /* optional: the forward's index, see above          */
+  int64_t index_bytes;
 } nsa_sel_bwd_args;
 
 int nsa_sel_bwd(const nsa_sel_bwd_args* args, void* stream);
+
+/* Bytes at the start of the forward's work buffer that hold the index the
+ * backward can reuse; 0 when the generic kernels serve the problem. */
+int64_t nsa_sel_index_bytes(const nsa_sel_fwd_args* args);
 
 /* Bytes of work buffer the selected-block kernels need for this problem
  * (backward != 0: for nsa_sel_bwd).  0 when the SIMT family serves it.

@@ -32,7 +32,8 @@ class SelFwdArgs(C.Structure):
 
 
 class SelBwdArgs(C.Structure):
-    _fields_ = [('fwd', SelFwdArgs), ('dout', Tensor4), ('dq', vp), ('dk', vp), ('dv', vp), ('slot_grads', vp)]
+    _fields_ = [('fwd', SelFwdArgs), ('dout', Tensor4), ('dq', vp), ('dk', vp), ('dv', vp), ('slot_grads', vp),
+                ('index', vp), ('index_bytes', i64)]
 
 
 class CmpFwdArgs(C.Structure):
@@ -106,7 +107,7 @@ _STRUCTS = [Tensor4, SelFwdArgs, SelBwdArgs, CmpFwdArgs, CmpBwdArgs, SelectArgs,
             CombineFwdArgs, CombineBwdArgs, CombineGatherArgs, RotaryArgs, WindowsFwdArgs, WindowsBwdArgs,
             RmsNormFwdArgs, RmsNormBwdArgs]
 
-ENTRY_POINTS = ['nsa_sel_fwd', 'nsa_sel_bwd', 'nsa_sel_workspace_bytes', 'nsa_sel_fwd_static',
+ENTRY_POINTS = ['nsa_sel_fwd', 'nsa_sel_bwd', 'nsa_sel_workspace_bytes', 'nsa_sel_index_bytes', 'nsa_sel_fwd_static',
                 'nsa_sel_static_scratch_bytes', 'nsa_cmp_workspace_bytes', 'nsa_swa_workspace_bytes', 'nsa_cmp_fwd', 'nsa_cmp_bwd', 'nsa_select',
                 'nsa_swa_fwd', 'nsa_swa_bwd', 'nsa_combine_fwd', 'nsa_combine_bwd', 'nsa_combine_fwd_gather', 'nsa_rotary', 'nsa_windows_fwd', 'nsa_windows_bwd', 'nsa_rmsnorm_fwd', 'nsa_rmsnorm_bwd', 'nsa_last_error',
                 'nsa_abi_version', 'nsa_struct_size']
@@ -130,6 +131,7 @@ def load():
     lib = C.CDLL(LIB_PATH)
     lib.nsa_last_error.restype = C.c_char_p
     lib.nsa_sel_workspace_bytes.restype = i64
+    lib.nsa_sel_index_bytes.restype = i64
     lib.nsa_sel_static_scratch_bytes.restype = i64
     lib.nsa_cmp_workspace_bytes.restype = i64
     lib.nsa_swa_workspace_bytes.restype = i64

@@ -130,6 +130,15 @@ int64_t nsa_sel_workspace_bytes(const nsa_sel_fwd_args* a, int backward) {
   return need;
 }
 
+int64_t nsa_sel_index_bytes(const nsa_sel_fwd_args* a) {
+  if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
+  AttnParams P;
+  const int rc = fill_sel(P, *a);
+  if (rc != NSA_OK && rc != NSA_ERR_NULL) return rc;
+  if (a->impl == NSA_IMPL_SIMT) return 0;
+  return sm100_sel_index_bytes(*a);
+}
+
 int nsa_sel_fwd(const nsa_sel_fwd_args* a, void* stream) {
   if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
   AttnParams P;
@@ -157,14 +166,19 @@ int nsa_sel_bwd(const nsa_sel_bwd_args* a, void* stream) {
   NSA_TRY(fill_sel(P, a->fwd));
   NSA_TRY(check_tensor(a->dout, a->fwd.dtype, "dout"));
   if (!a->dq || !a->dk || !a->dv) return fail(NSA_ERR_NULL, "dq/dk/dv: NULL pointer");
+  if (a->index != nullptr && (reinterpret_cast<uintptr_t>(a->index) & 15u))
+    return fail(NSA_ERR_ALIGN, "index must be 16-byte aligned");
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t d = a->fwd.dim_head, n = a->fwd.seq, b = a->fwd.batch;
-  NSA_TRY(zero_async(a->dq, b * a->fwd.q_heads * n * d, st));
+  // dk and dv are accumulated into; dq too, unless the kernels that will run store every row of it
+  const bool dq_stored = a->fwd.impl != NSA_IMPL_SIMT && sm100_sel_bwd_overwrites_dq(a->fwd);
+  if (!dq_stored) NSA_TRY(zero_async(a->dq, b * a->fwd.q_heads * n * d, st));
   NSA_TRY(zero_async(a->dk, b * a->fwd.kv_heads * n * d, st));
   NSA_TRY(zero_async(a->dv, b * a->fwd.kv_heads * n * d, st));
   if (a->fwd.impl != NSA_IMPL_SIMT) {
     const int rc = sm100_sel_bwd(*a, st);
     if (rc != NSA_ERR_UNSUPPORTED || a->fwd.impl == NSA_IMPL_SM100) return rc;
+    if (dq_stored) NSA_TRY(zero_async(a->dq, b * a->fwd.q_heads * n * d, st));
   }
   set_dout(P, a->dout);
   P.dq = a->dq; P.dk = a->dk; P.dv = a->dv; P.slot_grads = a->slot_grads;
@@ -222,13 +236,15 @@ int nsa_cmp_bwd(const nsa_cmp_bwd_args* a, void* stream) {
   if (!a->dq || !a->dck || !a->dcv) return fail(NSA_ERR_NULL, "dq/dck/dcv: NULL pointer");
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t d = a->fwd.dim_head, rows = a->fwd.num_mem + a->fwd.ncb, b = a->fwd.batch;
-  NSA_TRY(zero_async(a->dq, b * a->fwd.q_heads * a->fwd.seq * d, st));
+  const bool dq_stored = a->fwd.impl != NSA_IMPL_SIMT && sm100_cmp_bwd_overwrites_dq(a->fwd);
+  if (!dq_stored) NSA_TRY(zero_async(a->dq, b * a->fwd.q_heads * a->fwd.seq * d, st));
   NSA_TRY(zero_async(a->dck, b * a->fwd.kv_heads * rows * d, st));
   NSA_TRY(zero_async(a->dcv, b * a->fwd.kv_heads * rows * d, st));
   if (a->fwd.impl != NSA_IMPL_SIMT) {
     const int rc = sm100_cmp_bwd(*a, st);
     if (rc != NSA_ERR_UNSUPPORTED) return rc;
     if (a->fwd.impl == NSA_IMPL_SM100) return fail(NSA_ERR_UNSUPPORTED, "compressed branch: shape outside the tensor-core family");
+    if (dq_stored) NSA_TRY(zero_async(a->dq, b * a->fwd.q_heads * a->fwd.seq * d, st));
   }
   set_dout(P, a->dout);
   P.importance = nullptr;
@@ -303,13 +319,15 @@ int nsa_swa_bwd(const nsa_swa_bwd_args* a, void* stream) {
   if (!a->dq || !a->dk || !a->dv) return fail(NSA_ERR_NULL, "dq/dk/dv: NULL pointer");
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t d = a->fwd.dim_head, n = a->fwd.seq, b = a->fwd.batch;
-  NSA_TRY(zero_async(a->dq, b * a->fwd.q_heads * n * d, st));
+  const bool dq_stored = a->fwd.impl != NSA_IMPL_SIMT && sm100_swa_bwd_overwrites_dq(a->fwd);
+  if (!dq_stored) NSA_TRY(zero_async(a->dq, b * a->fwd.q_heads * n * d, st));
   NSA_TRY(zero_async(a->dk, b * a->fwd.kv_heads * n * d, st));
   NSA_TRY(zero_async(a->dv, b * a->fwd.kv_heads * n * d, st));
   if (a->fwd.impl != NSA_IMPL_SIMT) {
     const int rc = sm100_swa_bwd(*a, st);
     if (rc != NSA_ERR_UNSUPPORTED) return rc;
     if (a->fwd.impl == NSA_IMPL_SM100) return fail(NSA_ERR_UNSUPPORTED, "sliding branch: shape outside the tensor-core family");
+    if (dq_stored) NSA_TRY(zero_async(a->dq, b * a->fwd.q_heads * n * d, st));
   }
   set_dout(P, a->dout);
   P.dq = a->dq; P.dk = a->dk; P.dv = a->dv;

@@ -105,6 +105,7 @@ int launch_combine_gather(const CombineParams& P, const GatherTargets& Gt, int d
 // NSA_ERR_UNSUPPORTED (without touching the error message state of a later
 // successful call) when the shape is outside what it serves.
 int64_t sm100_sel_workspace_bytes(const nsa_sel_fwd_args& a, bool backward);
+int64_t sm100_sel_index_bytes(const nsa_sel_fwd_args& a);
 int sm100_sel_fwd(const nsa_sel_fwd_args& a, cudaStream_t stream);
 int sm100_sel_bwd(const nsa_sel_bwd_args& a, cudaStream_t stream);
 int sm100_sel_fwd_static(const nsa_sel_fwd_args& a, cudaStream_t stream);
@@ -115,5 +116,8 @@ int64_t sm100_cmp_workspace_bytes(const nsa_cmp_fwd_args& a, bool backward);
 int sm100_cmp_fwd(const nsa_cmp_fwd_args& a, cudaStream_t stream);
 int sm100_cmp_bwd(const nsa_cmp_bwd_args& a, cudaStream_t stream);
 int64_t sm100_static_scratch_bytes();
+bool sm100_sel_bwd_overwrites_dq(const nsa_sel_fwd_args& a);
+bool sm100_swa_bwd_overwrites_dq(const nsa_swa_fwd_args& a);
+bool sm100_cmp_bwd_overwrites_dq(const nsa_cmp_fwd_args& a);
 
 }  // namespace nsa

@@ -88,6 +88,7 @@ struct SelPlan {
   // byte offsets into the work buffer
   int64_t off_status, off_num_items, off_counts, off_totals, off_list_base, off_items, off_entries;
   int64_t off_partial, off_stats, off_delta;
+  int64_t index_bytes;   // the leading part that holds the index (what the backward can take from the forward)
   int64_t total_bytes;
 };
 
@@ -99,7 +100,8 @@ struct SelParams {
   const uint8_t* mask;
   const uint32_t* entries;
   const int4* items;
-  const int* num_items;
+  const int* num_items;    // [0] items, [1] the tag the item kernel left
+  uint32_t index_tag;
   __nv_bfloat16* partial;
   float2* stats;
   float* lse;
@@ -114,6 +116,16 @@ struct SelParams {
   float* importance;
   int ncb, round_bf16;
 };
+
+// Number of items of the index, or 0 (and status 2) when the index was not built for these sizes: a caller-kept
+// index that belongs to another problem, or a buffer nobody filled, must not steer any address.
+__device__ __forceinline__ int item_count(const SelParams& P) {
+  if ((uint32_t)P.num_items[1] != P.index_tag) {
+    if (threadIdx.x == 0) atomicExch(P.status, 2);
+    return 0;
+  }
+  return P.num_items[0];
+}
 
 // ---- index pre-pass --------------------------------------------------------------
 
@@ -169,7 +181,7 @@ __global__ void __launch_bounds__(32 * kScanSeg) sel_scan_kernel(int* counts, in
 
 // list bases (padded to whole chunks) and the item table; one CTA of 1024 threads
 __global__ void __launch_bounds__(1024) sel_items_kernel(const int* totals, int* list_base, int4* items, int* num_items,
-                                                         int nlists, int QT) {
+                                                         int nlists, int QT, uint32_t tag) {
   __shared__ int s_pad[1024], s_it[1024];
   __shared__ int carry_pad, carry_it;
   if (threadIdx.x == 0) carry_pad = carry_it = 0;
@@ -203,7 +215,10 @@ __global__ void __launch_bounds__(1024) sel_items_kernel(const int* totals, int*
     if (threadIdx.x == 1023) { carry_pad += s_pad[1023]; carry_it += s_it[1023]; }
     __syncthreads();
   }
-  if (threadIdx.x == 0) *num_items = carry_it;
+  if (threadIdx.x == 0) {
+    num_items[0] = carry_it;
+    num_items[1] = (int)tag;   // marks the index as built, and for which sizes
+  }
 }
 
 // writes the entries (query | slot << 24) in a fixed order: by query block, then slot, then query
@@ -365,7 +380,7 @@ sel_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   __shared__ uint32_t tmem_slot;
   __shared__ __align__(8) uint64_t bars[3];
   __shared__ int row_dst[kRows];
-  const int nitems = *P.num_items;
+  const int nitems = item_count(P);
   if ((int)blockIdx.x >= nitems) return;
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -996,7 +1011,7 @@ sel_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   __shared__ int abort_flag;
   __shared__ uint32_t tmem_slot;
   __shared__ __align__(8) uint64_t bars[3];
-  const int nitems = *P.num_items;
+  const int nitems = item_count(P);
   if ((int)blockIdx.x >= nitems) return;
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -1252,7 +1267,7 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
   __shared__ int abort_flag;
   __shared__ uint32_t tmem_slot;
   __shared__ __align__(8) Bars bars;
-  const int nitems = *P.num_items;
+  const int nitems = item_count(P);
   if ((int)blockIdx.x >= nitems) return;
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -1758,6 +1773,8 @@ struct SelProblem {
   float* importance;
   void* workspace;
   int64_t workspace_bytes;
+  const void* index;       // backward: the index part of the forward's work buffer, or NULL to rebuild it
+  int64_t index_bytes;
   int B, Hq, Hkv, N, Nk, D;
   int nsel, diag, mode, window, stride, num_mem, ncb, round_bf16;
   float scale;
@@ -1813,6 +1830,7 @@ static SelPlan make_plan(const SelProblem& a, bool backward) {
   if (!backward && dense_forward(a)) {   // only the status word is needed
     p.off_counts = p.off_totals = p.off_list_base = p.off_items = p.off_entries = off;
     p.off_partial = p.off_stats = p.off_delta = off;
+    p.index_bytes = 0;
     p.total_bytes = off;
     return p;
   }
@@ -1821,6 +1839,7 @@ static SelPlan make_plan(const SelProblem& a, bool backward) {
   p.off_list_base = off; off = align_up(off + (int64_t)p.nlists * 4, 256);
   p.off_items = off; off = align_up(off + p.items_cap * 16, 256);
   p.off_entries = off; off = align_up(off + p.entries_cap * 4, 256);
+  p.index_bytes = off;   // status word, counts, list bases, items, entries: the same layout forward and backward
   const int64_t rows = (int64_t)a.B * a.Hq * a.N;
   p.off_partial = p.off_stats = p.off_delta = off;
   if (!backward) {
@@ -1879,6 +1898,10 @@ static BlockRule make_rule(const SelProblem& a, const SelPlan& p) {
   return R;
 }
 
+static uint32_t index_tag(const SelPlan& p) {
+  return 0x4e534149u ^ ((uint32_t)p.nlists * 0x9E3779B1u) ^ ((uint32_t)p.entries_cap * 0x85EBCA77u) ^ (uint32_t)p.QT;
+}
+
 static int build_index(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaStream_t st) {
   int* counts = reinterpret_cast<int*>(ws + p.off_counts);
   int* totals = reinterpret_cast<int*>(ws + p.off_totals);
@@ -1895,7 +1918,7 @@ static int build_index(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaS
   else if (a.mode == kModeSwa) sel_hist_kernel<kModeSwa><<<grid, kBlock, hist_smem, st>>>(R, counts);
   else sel_hist_kernel<kModeCmp><<<grid, kBlock, hist_smem, st>>>(R, counts);
   sel_scan_kernel<<<(p.nlists + 31) / 32, dim3(32, kScanSeg), 0, st>>>(counts, totals, p.nlists, p.nqb, p.nkb);
-  sel_items_kernel<<<1, 1024, 0, st>>>(totals, list_base, items, num_items, p.nlists, p.QT);
+  sel_items_kernel<<<1, 1024, 0, st>>>(totals, list_base, items, num_items, p.nlists, p.QT, index_tag(p));
   if (a.mode == kModeSel) sel_fill_kernel<kModeSel><<<grid, kBlock, hist_smem, st>>>(R, counts, list_base, entries);
   else if (a.mode == kModeSwa) sel_fill_kernel<kModeSwa><<<grid, kBlock, hist_smem, st>>>(R, counts, list_base, entries);
   else sel_fill_kernel<kModeCmp><<<grid, kBlock, hist_smem, st>>>(R, counts, list_base, entries);
@@ -1903,14 +1926,16 @@ static int build_index(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaS
   return NSA_OK;
 }
 
-static void fill_params(SelParams& P, const SelProblem& a, const SelPlan& p, uint8_t* ws) {
+static void fill_params(SelParams& P, const SelProblem& a, const SelPlan& p, uint8_t* ws, const uint8_t* ix = nullptr) {
+  if (ix == nullptr) ix = ws;   // the index lives in the work buffer unless the caller kept the forward's
   memset(&P, 0, sizeof(P));
   P.q = (const __nv_bfloat16*)a.q.ptr; P.q_sb = a.q.stride_b; P.q_sh = a.q.stride_h; P.q_sn = a.q.stride_n;
   P.out = (__nv_bfloat16*)a.out.ptr; P.o_sb = a.out.stride_b; P.o_sh = a.out.stride_h; P.o_sn = a.out.stride_n;
   P.idx = a.idx; P.mask = a.mask;
-  P.entries = reinterpret_cast<const uint32_t*>(ws + p.off_entries);
-  P.items = reinterpret_cast<const int4*>(ws + p.off_items);
-  P.num_items = reinterpret_cast<const int*>(ws + p.off_num_items);
+  P.entries = reinterpret_cast<const uint32_t*>(ix + p.off_entries);
+  P.items = reinterpret_cast<const int4*>(ix + p.off_items);
+  P.num_items = reinterpret_cast<const int*>(ix + p.off_num_items);
+  P.index_tag = index_tag(p);
   P.status = reinterpret_cast<int*>(ws + p.off_status);
   P.lse = a.lse;
   P.B = a.B; P.Hq = a.Hq; P.Hkv = a.Hkv; P.N = a.N; P.Nk = a.Nk; P.G = p.G; P.nsel = a.nsel; P.nfb = p.nkb;
@@ -1992,6 +2017,11 @@ static int run_fwd(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaStrea
   return NSA_OK;
 }
 
+static bool ws_backward_enabled() {
+  static const bool on = []() { const char* e = getenv("NSA_SEL_BWD"); return e == nullptr || strcmp(e, "v1") != 0; }();
+  return on;
+}
+
 template <int D>
 static int run_bwd(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaStream_t st) {
   CUtensorMap tmK, tmV;
@@ -1999,18 +2029,24 @@ static int run_bwd(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaStrea
   if (rc != NSA_OK) return rc;
   rc = make_kv_map(&tmV, a.v, a.B, a.Hkv, a.Nk, D);
   if (rc != NSA_OK) return rc;
-  rc = build_index(a, p, ws, st);
-  if (rc != NSA_OK) return rc;
+  const uint8_t* ix = nullptr;
+  if (a.index != nullptr) {
+    if (a.index_bytes != p.index_bytes) return fail(NSA_ERR_WORKSPACE, "index: not the size nsa_sel_index_bytes reports");
+    ix = static_cast<const uint8_t*>(a.index);
+    CUDA_TRY(cudaMemsetAsync(ws + p.off_status, 0, 256, st));
+  } else {
+    rc = build_index(a, p, ws, st);
+    if (rc != NSA_OK) return rc;
+  }
   SelParams P;
-  fill_params(P, a, p, ws);
+  fill_params(P, a, p, ws, ix);
   P.dout = (const __nv_bfloat16*)a.dout.ptr; P.do_sb = a.dout.stride_b; P.do_sh = a.dout.stride_h; P.do_sn = a.dout.stride_n;
   float* delta = reinterpret_cast<float*>(ws + p.off_delta);
   P.delta = delta;
   P.dq = a.dq; P.dk = a.dk; P.dv = a.dv; P.slot_grads = a.slot_grads;
   const int64_t threads = (int64_t)a.B * a.Hq * a.N * (D / 8);
   sel_delta_kernel<D><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(P, delta);
-  static const bool use_ws = []() { const char* e = getenv("NSA_SEL_BWD"); return e == nullptr || strcmp(e, "v1") != 0; }();
-  if (D == 64 && use_ws) {
+  if (D == 64 && ws_backward_enabled()) {
     const int smem = 1024 + ws::kStages * 32768 + 2 * ws::kPBytes + 2 * 16384 + ws::kStages * ws::kMetaBytes +
                      8 * ws::kDqStage;
     CUDA_TRY(cudaFuncSetAttribute(sel_bwd_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -2096,6 +2132,11 @@ int64_t sm100_sel_workspace_bytes(const nsa_sel_fwd_args& a, bool backward) {
   if (!sel_problem(x, a)) return NSA_ERR_UNSUPPORTED;
   return make_plan(x, backward).total_bytes;
 }
+int64_t sm100_sel_index_bytes(const nsa_sel_fwd_args& a) {
+  SelProblem x;
+  if (!sel_problem(x, a)) return 0;
+  return make_plan(x, false).index_bytes;
+}
 int sm100_sel_fwd(const nsa_sel_fwd_args& a, cudaStream_t st) {
   SelProblem x;
   if (!sel_problem(x, a)) return NSA_ERR_UNSUPPORTED;
@@ -2105,7 +2146,22 @@ int sm100_sel_bwd(const nsa_sel_bwd_args& b, cudaStream_t st) {
   SelProblem x;
   if (!sel_problem(x, b.fwd)) return NSA_ERR_UNSUPPORTED;
   x.dout = b.dout; x.dq = b.dq; x.dk = b.dk; x.dv = b.dv; x.slot_grads = b.slot_grads;
+  x.index = b.index; x.index_bytes = b.index_bytes;
   return problem_bwd(x, st);
+}
+
+// True when the backward of this problem stores every row of dq (partials + ordered merge) instead of adding into it.
+bool sm100_sel_bwd_overwrites_dq(const nsa_sel_fwd_args& a) {
+  SelProblem x;
+  return sel_problem(x, a) && x.D == 64 && ws_backward_enabled();
+}
+bool sm100_swa_bwd_overwrites_dq(const nsa_swa_fwd_args& a) {
+  SelProblem x;
+  return swa_problem(x, a) && x.D == 64 && ws_backward_enabled();
+}
+bool sm100_cmp_bwd_overwrites_dq(const nsa_cmp_fwd_args& a) {
+  SelProblem x;
+  return cmp_problem(x, a) && x.D == 64 && ws_backward_enabled();
 }
 
 int64_t sm100_swa_workspace_bytes(const nsa_swa_fwd_args& a, bool backward) {

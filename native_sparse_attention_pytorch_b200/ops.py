@@ -54,11 +54,19 @@ def _keep_status(ws):
 
 
 def check_device_status():
-    """Synchronise and raise if any tensor-core kernel launched since the last call gave up on a wait."""
+    """Synchronise and raise if any tensor-core kernel launched since the last call gave up on a wait (status 1) or
+    was handed an index that was not built for its problem (status 2)."""
     words, _status_words[:] = list(_status_words), []
     for w in words:
-        if w.view(torch.int32).item() != 0:
+        code = w.view(torch.int32).item()
+        if code == 2:
+            raise L.NsaError('a tensor-core kernel was given an index that was not built for its problem; '
+                             'its results are invalid')
+        if code != 0:
             raise L.NsaError('a tensor-core kernel gave up on a bounded wait; its results are invalid')
+
+
+REUSE_INDEX = True     # the selected-block backward takes the index the forward built instead of rebuilding it
 
 
 class SelectedAttention(Function):
@@ -80,6 +88,10 @@ class SelectedAttention(Function):
             args = _sel_args(q, k, v, out, idx, mask, lse, block, diag, impl, scale)
             ws = _with_workspace(args, False, q.device)
             L.check(lib.nsa_sel_fwd(C.byref(args), L.stream_of(q)))
+            # the index of which queries attend which key block: a few MB the backward need not rebuild
+            keep = REUSE_INDEX and ws is not None and any(ctx.needs_input_grad[:3])
+            index_bytes = int(lib.nsa_sel_index_bytes(C.byref(args))) if keep else 0
+        ctx.index = ws[:index_bytes].clone() if index_bytes > 0 else None
         _keep_status(ws)
         del ws
         ctx.save_for_backward(q, k, v, idx, mask, out, lse)
@@ -101,8 +113,10 @@ class SelectedAttention(Function):
         with torch.cuda.device(q.device):
             fwd = _sel_args(q, k, v, out, idx, mask, lse, block, diag, impl, scale)
             ws = _with_workspace(fwd, True, q.device)
+            index = ctx.index
             args = L.SelBwdArgs(fwd=fwd, dout=L.t4(dout), dq=L.ptr(dq), dk=L.ptr(dk), dv=L.ptr(dv),
-                                slot_grads=L.ptr(slot))
+                                slot_grads=L.ptr(slot), index=L.ptr(index),
+                                index_bytes=0 if index is None else index.numel())
             L.check(lib.nsa_sel_bwd(C.byref(args), L.stream_of(q)))
         _keep_status(ws)
         del ws

@@ -300,3 +300,33 @@ def test_many_single_chunk_items_keep_the_accumulator_handover_in_order():
         out.backward(up)
         ops.check_device_status()
         assert_close_bf16(xf.grad, xs.grad, 'd input', rel_to_max=5e-3, roundings=2)
+
+
+@pytest.mark.parametrize('case', [(2, 8, 2, 300, 64, 3), (1, 16, 1, 260, 128, 2), (1, 8, 1, 2000, 64, 6)])
+def test_backward_with_the_forwards_index_equals_a_rebuilt_one(case, monkeypatch):
+    # the backward normally takes the index (which queries attend which key block) the forward built; rebuilding it
+    # from the same idx and mask must give the same gradients (dq exactly: its merge is ordered; dk, dv are sums of
+    # fp32 atomics whose order may differ from launch to launch)
+    b, hq, hkv, n, d, nsel = case
+    q, k, v, idx, mask, up = make_case(b, hq, hkv, n, d, nsel, seed=21)
+    assert ops.REUSE_INDEX
+    kept = run_gpu(q, k, v, idx, mask, up, 'sm100', scale_grad=True)
+    monkeypatch.setattr(ops, 'REUSE_INDEX', False)
+    rebuilt = run_gpu(q, k, v, idx, mask, up, 'sm100', scale_grad=True)
+    assert torch.equal(kept[0], rebuilt[0]) and torch.equal(kept[2], rebuilt[2])
+    for a, r, what in zip(kept[3:], rebuilt[3:], ('dk', 'dv', 'dscale')):
+        assert (a.float() - r.float()).abs().max().item() <= 1e-5 * max(1.0, r.float().abs().max().item()) + \
+            2.0 ** -8 * r.float().abs().max().item() * (a.dtype == torch.bfloat16), what
+
+
+def test_backward_refuses_an_index_that_was_not_built_for_it():
+    # a kept index whose tag does not match (here: cleared) makes the kernels do nothing and report status 2;
+    # no address is ever derived from it
+    q, k, v, idx, mask, up = make_case(1, 8, 2, 300, 64, 3, seed=5)
+    qg, kg, vg = (t.to(DEV).requires_grad_() for t in (q, k, v))
+    out = nsa.native_sparse_attend(qg, kg, vg, BLOCK, idx.to(DEV), mask.to(DEV), impl='sm100')
+    assert out.grad_fn.index is not None and out.grad_fn.index.numel() > 256
+    out.grad_fn.index.zero_()
+    torch.autograd.grad((out * up.to(DEV)).sum(), (qg, kg, vg))
+    with pytest.raises(RuntimeError, match='index that was not built'):
+        ops.check_device_status()
