@@ -127,6 +127,7 @@ typedef struct {
   float* slot_grads;     /* optional                                          */
   const void* index;     /* optional: the forward's index, see above          */
   int64_t index_bytes;
+  nsa_tensor dq_out;     /* optional (ptr NULL = unused): dq in the dtype of q with these strides, see nsa_sel_bwd_stores_dq */
 } nsa_sel_bwd_args;
 
 int nsa_sel_bwd(const nsa_sel_bwd_args* args, void* stream);
@@ -134,6 +135,17 @@ int nsa_sel_bwd(const nsa_sel_bwd_args* args, void* stream);
 /* Bytes at the start of the forward's work buffer that hold the index the
  * backward can reuse; 0 when the generic kernels serve the problem. */
 int64_t nsa_sel_index_bytes(const nsa_sel_fwd_args* args);
+
+/* 1 when the backward of this problem stores every row of dq in one ordered
+ * pass (the tensor-core family at dim_head 64) instead of adding into it, 0
+ * otherwise, negative = NSA_ERR_*.  Where it is 1 the caller may set
+ * `dq_out` (rows of dim_head contiguous elements in the dtype of q, 16-byte
+ * aligned, any batch / head / row strides -- for instance the layout of q
+ * itself) and pass dq = NULL: dq is then written there, already rounded, and
+ * no fp32 dq exists.  With dq_out set on a problem that is not served this
+ * way the call returns NSA_ERR_UNSUPPORTED and writes nothing.  The same
+ * holds for nsa_cmp_bwd / nsa_swa_bwd with their *_stores_dq functions. */
+int nsa_sel_bwd_stores_dq(const nsa_sel_fwd_args* args);
 
 /* Bytes of work buffer the selected-block kernels need for this problem
  * (backward != 0: for nsa_sel_bwd).  0 when the SIMT family serves it.
@@ -219,9 +231,11 @@ typedef struct {
   float* dq;
   float* dck;
   float* dcv;
+  nsa_tensor dq_out;     /* optional, as in nsa_sel_bwd_args */
 } nsa_cmp_bwd_args;
 
 int nsa_cmp_bwd(const nsa_cmp_bwd_args* args, void* stream);
+int nsa_cmp_bwd_stores_dq(const nsa_cmp_fwd_args* args);
 
 /* ------------------------------------------------------------------------
  * Block selection: per-block mean, own-block exclusion, sink softmax, top-k.
@@ -280,9 +294,11 @@ typedef struct {
   float* dq;             /* contiguous fp32, zeroed by the call               */
   float* dk;
   float* dv;
+  nsa_tensor dq_out;     /* optional, as in nsa_sel_bwd_args */
 } nsa_swa_bwd_args;
 
 int nsa_swa_bwd(const nsa_swa_bwd_args* args, void* stream);
+int nsa_swa_bwd_stores_dq(const nsa_swa_fwd_args* args);
 
 /* ------------------------------------------------------------------------
  * Gated combine of the three branches and head merge.
@@ -338,10 +354,13 @@ int nsa_combine_fwd_gather(const nsa_combine_gather_args* args, void* stream);
  * angles of the positions the caller wants (an offset for cached keys is the caller's choice of table rows). */
 typedef struct {
   nsa_tensor x;                   /* [B, H, N, d] view, last axis contiguous, rows 16-byte aligned */
-  void* out;                      /* [B, H, N, d] contiguous, same dtype, written                  */
+  void* out;                      /* [B, H, N, d], same dtype, written; contiguous unless out_stride_* say otherwise */
   const float* cos_table;         /* [N, d/2] fp32                                                 */
   const float* sin_table;         /* [N, d/2] fp32                                                 */
   int32_t batch, heads, seq, dim_head, dtype, inverse;
+  int64_t out_stride_b, out_stride_h, out_stride_n; /* in elements, multiples of 16 bytes; all 0 = contiguous out.
+                                                     * The backward can thus write in the layout of the forward's
+                                                     * input, e.g. a [B, N, H, d] buffer seen as [B, H, N, d].       */
 } nsa_rotary_args;
 
 int nsa_rotary(const nsa_rotary_args* args, void* stream);
@@ -363,8 +382,9 @@ int nsa_windows_fwd(const nsa_windows_fwd_args* args, void* stream);
 typedef struct {
   nsa_windows_fwd_args fwd;       /* sizes as in the forward; x, pos and out are not read               */
   const void* dout;               /* [B, H, ncb, block, d] contiguous                                   */
-  void* dx;                       /* [B, H, N, d] contiguous, same dtype, written                       */
+  void* dx;                       /* [B, H, N, d], same dtype, written; contiguous unless dx_stride_* say otherwise */
   float* dpos;                    /* [H, block, d] contiguous fp32, written                             */
+  int64_t dx_stride_b, dx_stride_h, dx_stride_n; /* in elements, multiples of 16 bytes; all 0 = contiguous dx   */
 } nsa_windows_bwd_args;
 
 int nsa_windows_bwd(const nsa_windows_bwd_args* args, void* stream);

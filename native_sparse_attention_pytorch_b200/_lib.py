@@ -12,6 +12,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, 'libnsa_b200.so')
 
 NSA_F32, NSA_BF16 = 0, 1
+NSA_ERR_UNSUPPORTED = -6
 DIAG_NONE, DIAG_CAUSAL, DIAG_FULL = 0, 1, 2
 IMPL_AUTO, IMPL_SIMT, IMPL_SM100 = 0, 1, 2
 IMPL_BY_NAME = {'auto': IMPL_AUTO, 'simt': IMPL_SIMT, 'sm100': IMPL_SM100}
@@ -33,7 +34,7 @@ class SelFwdArgs(C.Structure):
 
 class SelBwdArgs(C.Structure):
     _fields_ = [('fwd', SelFwdArgs), ('dout', Tensor4), ('dq', vp), ('dk', vp), ('dv', vp), ('slot_grads', vp),
-                ('index', vp), ('index_bytes', i64)]
+                ('index', vp), ('index_bytes', i64), ('dq_out', Tensor4)]
 
 
 class CmpFwdArgs(C.Structure):
@@ -44,7 +45,7 @@ class CmpFwdArgs(C.Structure):
 
 
 class CmpBwdArgs(C.Structure):
-    _fields_ = [('fwd', CmpFwdArgs), ('dout', Tensor4), ('dq', vp), ('dck', vp), ('dcv', vp)]
+    _fields_ = [('fwd', CmpFwdArgs), ('dout', Tensor4), ('dq', vp), ('dck', vp), ('dcv', vp), ('dq_out', Tensor4)]
 
 
 class SelectArgs(C.Structure):
@@ -60,7 +61,7 @@ class SwaFwdArgs(C.Structure):
 
 
 class SwaBwdArgs(C.Structure):
-    _fields_ = [('fwd', SwaFwdArgs), ('dout', Tensor4), ('dq', vp), ('dk', vp), ('dv', vp)]
+    _fields_ = [('fwd', SwaFwdArgs), ('dout', Tensor4), ('dq', vp), ('dk', vp), ('dv', vp), ('dq_out', Tensor4)]
 
 
 class CombineFwdArgs(C.Structure):
@@ -82,7 +83,8 @@ class CombineGatherArgs(C.Structure):
 
 class RotaryArgs(C.Structure):
     _fields_ = [('x', Tensor4), ('out', vp), ('cos_table', vp), ('sin_table', vp), ('batch', i32), ('heads', i32),
-                ('seq', i32), ('dim_head', i32), ('dtype', i32), ('inverse', i32)]
+                ('seq', i32), ('dim_head', i32), ('dtype', i32), ('inverse', i32),
+                ('out_stride_b', i64), ('out_stride_h', i64), ('out_stride_n', i64)]
 
 
 class WindowsFwdArgs(C.Structure):
@@ -91,7 +93,8 @@ class WindowsFwdArgs(C.Structure):
 
 
 class WindowsBwdArgs(C.Structure):
-    _fields_ = [('fwd', WindowsFwdArgs), ('dout', vp), ('dx', vp), ('dpos', vp)]
+    _fields_ = [('fwd', WindowsFwdArgs), ('dout', vp), ('dx', vp), ('dpos', vp),
+                ('dx_stride_b', i64), ('dx_stride_h', i64), ('dx_stride_n', i64)]
 
 
 class RmsNormFwdArgs(C.Structure):
@@ -107,7 +110,8 @@ _STRUCTS = [Tensor4, SelFwdArgs, SelBwdArgs, CmpFwdArgs, CmpBwdArgs, SelectArgs,
             CombineFwdArgs, CombineBwdArgs, CombineGatherArgs, RotaryArgs, WindowsFwdArgs, WindowsBwdArgs,
             RmsNormFwdArgs, RmsNormBwdArgs]
 
-ENTRY_POINTS = ['nsa_sel_fwd', 'nsa_sel_bwd', 'nsa_sel_workspace_bytes', 'nsa_sel_index_bytes', 'nsa_sel_fwd_static',
+ENTRY_POINTS = ['nsa_sel_fwd', 'nsa_sel_bwd', 'nsa_sel_workspace_bytes', 'nsa_sel_index_bytes', 'nsa_sel_bwd_stores_dq', 'nsa_cmp_bwd_stores_dq', 'nsa_swa_bwd_stores_dq',
+                'nsa_sel_fwd_static',
                 'nsa_sel_static_scratch_bytes', 'nsa_cmp_workspace_bytes', 'nsa_swa_workspace_bytes', 'nsa_cmp_fwd', 'nsa_cmp_bwd', 'nsa_select',
                 'nsa_swa_fwd', 'nsa_swa_bwd', 'nsa_combine_fwd', 'nsa_combine_bwd', 'nsa_combine_fwd_gather', 'nsa_rotary', 'nsa_windows_fwd', 'nsa_windows_bwd', 'nsa_rmsnorm_fwd', 'nsa_rmsnorm_bwd', 'nsa_last_error',
                 'nsa_abi_version', 'nsa_struct_size']

@@ -130,6 +130,26 @@ int64_t nsa_sel_workspace_bytes(const nsa_sel_fwd_args* a, int backward) {
   return need;
 }
 
+// dq_out: rows of dim_head elements in the dtype of q; only the tensor-core family at dim_head 64 writes it
+static int check_dq_out(const nsa_tensor& t, int dtype, bool served) {
+  if (t.ptr == nullptr) return NSA_OK;
+  if (!served) return fail(NSA_ERR_UNSUPPORTED, "dq_out: this problem's backward does not store dq in one pass (see *_bwd_stores_dq)");
+  return check_tensor(t, dtype, "dq_out");
+}
+
+int nsa_sel_bwd_stores_dq(const nsa_sel_fwd_args* a) {
+  if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
+  return a->impl != NSA_IMPL_SIMT && sm100_sel_bwd_overwrites_dq(*a) ? 1 : 0;
+}
+int nsa_cmp_bwd_stores_dq(const nsa_cmp_fwd_args* a) {
+  if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
+  return a->impl != NSA_IMPL_SIMT && sm100_cmp_bwd_overwrites_dq(*a) ? 1 : 0;
+}
+int nsa_swa_bwd_stores_dq(const nsa_swa_fwd_args* a) {
+  if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
+  return a->impl != NSA_IMPL_SIMT && sm100_swa_bwd_overwrites_dq(*a) ? 1 : 0;
+}
+
 int64_t nsa_sel_index_bytes(const nsa_sel_fwd_args* a) {
   if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
   AttnParams P;
@@ -165,19 +185,21 @@ int nsa_sel_bwd(const nsa_sel_bwd_args* a, void* stream) {
   AttnParams P;
   NSA_TRY(fill_sel(P, a->fwd));
   NSA_TRY(check_tensor(a->dout, a->fwd.dtype, "dout"));
-  if (!a->dq || !a->dk || !a->dv) return fail(NSA_ERR_NULL, "dq/dk/dv: NULL pointer");
+  // dk and dv are accumulated into; dq too, unless the kernels that will run store every row of it
+  const bool dq_stored = a->fwd.impl != NSA_IMPL_SIMT && sm100_sel_bwd_overwrites_dq(a->fwd);
+  NSA_TRY(check_dq_out(a->dq_out, a->fwd.dtype, dq_stored));
+  if ((!a->dq && !a->dq_out.ptr) || !a->dk || !a->dv) return fail(NSA_ERR_NULL, "dq/dk/dv: NULL pointer");
   if (a->index != nullptr && (reinterpret_cast<uintptr_t>(a->index) & 15u))
     return fail(NSA_ERR_ALIGN, "index must be 16-byte aligned");
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t d = a->fwd.dim_head, n = a->fwd.seq, b = a->fwd.batch;
-  // dk and dv are accumulated into; dq too, unless the kernels that will run store every row of it
-  const bool dq_stored = a->fwd.impl != NSA_IMPL_SIMT && sm100_sel_bwd_overwrites_dq(a->fwd);
   if (!dq_stored) NSA_TRY(zero_async(a->dq, b * a->fwd.q_heads * n * d, st));
   NSA_TRY(zero_async(a->dk, b * a->fwd.kv_heads * n * d, st));
   NSA_TRY(zero_async(a->dv, b * a->fwd.kv_heads * n * d, st));
   if (a->fwd.impl != NSA_IMPL_SIMT) {
     const int rc = sm100_sel_bwd(*a, st);
     if (rc != NSA_ERR_UNSUPPORTED || a->fwd.impl == NSA_IMPL_SM100) return rc;
+    if (a->dq == nullptr) return fail(NSA_ERR_UNSUPPORTED, "the tensor-core kernels could not take these tensors; pass an fp32 dq");
     if (dq_stored) NSA_TRY(zero_async(a->dq, b * a->fwd.q_heads * n * d, st));
   }
   set_dout(P, a->dout);
@@ -233,10 +255,11 @@ int nsa_cmp_bwd(const nsa_cmp_bwd_args* a, void* stream) {
   AttnParams P;
   NSA_TRY(fill_cmp(P, a->fwd));
   NSA_TRY(check_tensor(a->dout, a->fwd.dtype, "dout"));
-  if (!a->dq || !a->dck || !a->dcv) return fail(NSA_ERR_NULL, "dq/dck/dcv: NULL pointer");
+  const bool dq_stored = a->fwd.impl != NSA_IMPL_SIMT && sm100_cmp_bwd_overwrites_dq(a->fwd);
+  NSA_TRY(check_dq_out(a->dq_out, a->fwd.dtype, dq_stored));
+  if ((!a->dq && !a->dq_out.ptr) || !a->dck || !a->dcv) return fail(NSA_ERR_NULL, "dq/dck/dcv: NULL pointer");
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t d = a->fwd.dim_head, rows = a->fwd.num_mem + a->fwd.ncb, b = a->fwd.batch;
-  const bool dq_stored = a->fwd.impl != NSA_IMPL_SIMT && sm100_cmp_bwd_overwrites_dq(a->fwd);
   if (!dq_stored) NSA_TRY(zero_async(a->dq, b * a->fwd.q_heads * a->fwd.seq * d, st));
   NSA_TRY(zero_async(a->dck, b * a->fwd.kv_heads * rows * d, st));
   NSA_TRY(zero_async(a->dcv, b * a->fwd.kv_heads * rows * d, st));
@@ -244,6 +267,7 @@ int nsa_cmp_bwd(const nsa_cmp_bwd_args* a, void* stream) {
     const int rc = sm100_cmp_bwd(*a, st);
     if (rc != NSA_ERR_UNSUPPORTED) return rc;
     if (a->fwd.impl == NSA_IMPL_SM100) return fail(NSA_ERR_UNSUPPORTED, "compressed branch: shape outside the tensor-core family");
+    if (a->dq == nullptr) return fail(NSA_ERR_UNSUPPORTED, "the tensor-core kernels could not take these tensors; pass an fp32 dq");
     if (dq_stored) NSA_TRY(zero_async(a->dq, b * a->fwd.q_heads * a->fwd.seq * d, st));
   }
   set_dout(P, a->dout);
@@ -316,10 +340,11 @@ int nsa_swa_bwd(const nsa_swa_bwd_args* a, void* stream) {
   AttnParams P;
   NSA_TRY(fill_swa(P, a->fwd));
   NSA_TRY(check_tensor(a->dout, a->fwd.dtype, "dout"));
-  if (!a->dq || !a->dk || !a->dv) return fail(NSA_ERR_NULL, "dq/dk/dv: NULL pointer");
+  const bool dq_stored = a->fwd.impl != NSA_IMPL_SIMT && sm100_swa_bwd_overwrites_dq(a->fwd);
+  NSA_TRY(check_dq_out(a->dq_out, a->fwd.dtype, dq_stored));
+  if ((!a->dq && !a->dq_out.ptr) || !a->dk || !a->dv) return fail(NSA_ERR_NULL, "dq/dk/dv: NULL pointer");
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t d = a->fwd.dim_head, n = a->fwd.seq, b = a->fwd.batch;
-  const bool dq_stored = a->fwd.impl != NSA_IMPL_SIMT && sm100_swa_bwd_overwrites_dq(a->fwd);
   if (!dq_stored) NSA_TRY(zero_async(a->dq, b * a->fwd.q_heads * n * d, st));
   NSA_TRY(zero_async(a->dk, b * a->fwd.kv_heads * n * d, st));
   NSA_TRY(zero_async(a->dv, b * a->fwd.kv_heads * n * d, st));
@@ -327,6 +352,7 @@ int nsa_swa_bwd(const nsa_swa_bwd_args* a, void* stream) {
     const int rc = sm100_swa_bwd(*a, st);
     if (rc != NSA_ERR_UNSUPPORTED) return rc;
     if (a->fwd.impl == NSA_IMPL_SM100) return fail(NSA_ERR_UNSUPPORTED, "sliding branch: shape outside the tensor-core family");
+    if (a->dq == nullptr) return fail(NSA_ERR_UNSUPPORTED, "the tensor-core kernels could not take these tensors; pass an fp32 dq");
     if (dq_stored) NSA_TRY(zero_async(a->dq, b * a->fwd.q_heads * n * d, st));
   }
   set_dout(P, a->dout);
@@ -433,6 +459,13 @@ int nsa_rotary(const nsa_rotary_args* a, void* stream) {
   P.x = a->x.ptr; P.out = a->out; P.cos = a->cos_table; P.sin = a->sin_table;
   P.x_sb = a->x.stride_b; P.x_sh = a->x.stride_h; P.x_sn = a->x.stride_n;
   P.batch = a->batch; P.heads = a->heads; P.seq = a->seq; P.d = a->dim_head; P.inverse = a->inverse;
+  if (a->out_stride_b == 0 && a->out_stride_h == 0 && a->out_stride_n == 0) {
+    P.o_sn = a->dim_head; P.o_sh = P.o_sn * a->seq; P.o_sb = P.o_sh * a->heads;
+  } else {
+    if (a->out_stride_b % V || a->out_stride_h % V || a->out_stride_n % V || a->out_stride_n < a->dim_head)
+      return fail(NSA_ERR_ALIGN, "out strides must keep rows apart and 16-byte aligned");
+    P.o_sb = a->out_stride_b; P.o_sh = a->out_stride_h; P.o_sn = a->out_stride_n;
+  }
   return launch_rotary(P, a->dtype, (cudaStream_t)stream);
 }
 
@@ -472,6 +505,14 @@ int nsa_windows_bwd(const nsa_windows_bwd_args* a, void* stream) {
   if ((reinterpret_cast<uintptr_t>(a->dout) & 15u) || (reinterpret_cast<uintptr_t>(a->dx) & 15u))
     return fail(NSA_ERR_ALIGN, "dout and dx must be 16-byte aligned");
   P.dout = a->dout; P.dx = a->dx; P.dpos = a->dpos;
+  if (a->dx_stride_b == 0 && a->dx_stride_h == 0 && a->dx_stride_n == 0) {
+    P.dx_sn = a->fwd.dim_head; P.dx_sh = P.dx_sn * a->fwd.seq; P.dx_sb = P.dx_sh * a->fwd.heads;
+  } else {
+    const int V = a->fwd.dtype == NSA_F32 ? 4 : 8;
+    if (a->dx_stride_b % V || a->dx_stride_h % V || a->dx_stride_n % V || a->dx_stride_n < a->fwd.dim_head)
+      return fail(NSA_ERR_ALIGN, "dx strides must keep rows apart and 16-byte aligned");
+    P.dx_sb = a->dx_stride_b; P.dx_sh = a->dx_stride_h; P.dx_sn = a->dx_stride_n;
+  }
   return launch_windows(P, a->fwd.dtype, true, (cudaStream_t)stream);
 }
 

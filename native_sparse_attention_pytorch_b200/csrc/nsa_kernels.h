@@ -67,6 +67,7 @@ struct WindowParams {
   void *out, *dx;
   float* dpos;
   int64_t x_sb, x_sh, x_sn;
+  int64_t dx_sb, dx_sh, dx_sn;   // strides of dx
   int batch, heads, seq, d, block, stride, ncb;
 };
 
@@ -75,6 +76,7 @@ struct RotaryParams {
   void* out;
   const float *cos, *sin;
   int64_t x_sb, x_sh, x_sn;
+  int64_t o_sb, o_sh, o_sn;   // strides of out
   int batch, heads, seq, d, inverse;
 };
 

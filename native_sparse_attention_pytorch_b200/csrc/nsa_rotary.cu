@@ -33,7 +33,7 @@ __global__ void __launch_bounds__(256) rotary_kernel(const RotaryParams P) {
       ov[2 * p] = Elem<T>::from_float(__fadd_rn(__fmul_rn(x0, co), __fmul_rn(-x1, si)));
       ov[2 * p + 1] = Elem<T>::from_float(__fadd_rn(__fmul_rn(x1, co), __fmul_rn(x0, si)));
     }
-    *reinterpret_cast<uint4*>((T*)P.out + (((int64_t)b * P.heads + h) * P.seq + n) * P.d + c) = packed;
+    *reinterpret_cast<uint4*>((T*)P.out + b * P.o_sb + h * P.o_sh + (int64_t)n * P.o_sn + c) = packed;
   }
 }
 

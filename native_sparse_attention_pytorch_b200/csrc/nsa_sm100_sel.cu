@@ -101,6 +101,8 @@ struct SelParams {
   const uint32_t* entries;
   const int4* items;
   const int* num_items;    // [0] items, [1] the tag the item kernel left
+  __nv_bfloat16* dq_lp;    // optional bf16 dq with its own batch / head / row strides (dq merge)
+  int64_t dq_sb, dq_sh, dq_sn;
   uint32_t index_tag;
   __nv_bfloat16* partial;
   float2* stats;
@@ -1749,8 +1751,15 @@ __global__ void __launch_bounds__(256) sel_dq_merge_kernel(const SelParams P) {
       }
     }
   }
-  float4* dst = reinterpret_cast<float4*>(P.dq + row * D + part * 8);
   // the partials hold dS K without the logit scale
+  if (P.dq_lp != nullptr) {   // the caller asked for dq in the dtype and row layout of q
+    uint4 o;
+    o.x = pack_bf16(acc[0] * P.scale, acc[1] * P.scale); o.y = pack_bf16(acc[2] * P.scale, acc[3] * P.scale);
+    o.z = pack_bf16(acc[4] * P.scale, acc[5] * P.scale); o.w = pack_bf16(acc[6] * P.scale, acc[7] * P.scale);
+    *reinterpret_cast<uint4*>(P.dq_lp + b * P.dq_sb + hq * P.dq_sh + i * P.dq_sn + part * 8) = o;
+    return;
+  }
+  float4* dst = reinterpret_cast<float4*>(P.dq + row * D + part * 8);
   dst[0] = make_float4(acc[0] * P.scale, acc[1] * P.scale, acc[2] * P.scale, acc[3] * P.scale);
   dst[1] = make_float4(acc[4] * P.scale, acc[5] * P.scale, acc[6] * P.scale, acc[7] * P.scale);
 }
@@ -1770,6 +1779,7 @@ struct SelProblem {
   const uint8_t* mask;
   float* lse;
   float *dq, *dk, *dv, *slot_grads;
+  nsa_tensor dq_out;       // backward, optional: dq in the dtype and strides the caller chose
   float* importance;
   void* workspace;
   int64_t workspace_bytes;
@@ -2044,6 +2054,9 @@ static int run_bwd(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaStrea
   float* delta = reinterpret_cast<float*>(ws + p.off_delta);
   P.delta = delta;
   P.dq = a.dq; P.dk = a.dk; P.dv = a.dv; P.slot_grads = a.slot_grads;
+  if (a.dq_out.ptr != nullptr) {
+    P.dq_lp = (__nv_bfloat16*)a.dq_out.ptr; P.dq_sb = a.dq_out.stride_b; P.dq_sh = a.dq_out.stride_h; P.dq_sn = a.dq_out.stride_n;
+  }
   const int64_t threads = (int64_t)a.B * a.Hq * a.N * (D / 8);
   sel_delta_kernel<D><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(P, delta);
   if (D == 64 && ws_backward_enabled()) {
@@ -2120,6 +2133,8 @@ static int problem_fwd(const SelProblem& x, cudaStream_t st) {
 }
 
 static int problem_bwd(const SelProblem& x, cudaStream_t st) {
+  // dq in the caller's dtype and strides: only the merge of the partials writes whole rows of dq
+  if (x.dq_out.ptr != nullptr && !(x.D == 64 && ws_backward_enabled())) return NSA_ERR_UNSUPPORTED;
   const SelPlan p = make_plan(x, true);
   uint8_t* ws = nullptr;
   const int rc = check_ws(x, p, &ws);
@@ -2146,7 +2161,7 @@ int sm100_sel_bwd(const nsa_sel_bwd_args& b, cudaStream_t st) {
   SelProblem x;
   if (!sel_problem(x, b.fwd)) return NSA_ERR_UNSUPPORTED;
   x.dout = b.dout; x.dq = b.dq; x.dk = b.dk; x.dv = b.dv; x.slot_grads = b.slot_grads;
-  x.index = b.index; x.index_bytes = b.index_bytes;
+  x.index = b.index; x.index_bytes = b.index_bytes; x.dq_out = b.dq_out;
   return problem_bwd(x, st);
 }
 
@@ -2177,7 +2192,7 @@ int sm100_swa_fwd(const nsa_swa_fwd_args& a, cudaStream_t st) {
 int sm100_swa_bwd(const nsa_swa_bwd_args& b, cudaStream_t st) {
   SelProblem x;
   if (!swa_problem(x, b.fwd)) return NSA_ERR_UNSUPPORTED;
-  x.dout = b.dout; x.dq = b.dq; x.dk = b.dk; x.dv = b.dv;
+  x.dout = b.dout; x.dq = b.dq; x.dk = b.dk; x.dv = b.dv; x.dq_out = b.dq_out;
   return problem_bwd(x, st);
 }
 
@@ -2204,7 +2219,7 @@ int sm100_cmp_bwd(const nsa_cmp_bwd_args& b, cudaStream_t st) {
   SelProblem x;
   if (!cmp_problem(x, b.fwd)) return NSA_ERR_UNSUPPORTED;
   x.importance = nullptr;
-  x.dout = b.dout; x.dq = b.dq; x.dk = b.dck; x.dv = b.dcv;
+  x.dout = b.dout; x.dq = b.dq; x.dk = b.dck; x.dv = b.dcv; x.dq_out = b.dq_out;
   return problem_bwd(x, st);
 }
 

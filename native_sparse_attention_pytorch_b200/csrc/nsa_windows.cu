@@ -43,6 +43,7 @@ __global__ void __launch_bounds__(256) windows_bwd_x_kernel(const WindowParams P
     const int c = (int)(e % vpr) * V;
     const int tok = (int)((e / vpr) % P.seq);
     const int64_t bh = e / ((int64_t)vpr * P.seq);
+    const int64_t b = bh / P.heads, h = bh % P.heads;
     float acc[V];
 #pragma unroll
     for (int x = 0; x < V; ++x) acc[x] = 0.f;
@@ -58,7 +59,7 @@ __global__ void __launch_bounds__(256) windows_bwd_x_kernel(const WindowParams P
     T* ov = reinterpret_cast<T*>(&packed);
 #pragma unroll
     for (int x = 0; x < V; ++x) ov[x] = Elem<T>::from_float(acc[x]);
-    *reinterpret_cast<uint4*>((T*)P.dx + e * V) = packed;
+    *reinterpret_cast<uint4*>((T*)P.dx + b * P.dx_sb + h * P.dx_sh + (int64_t)tok * P.dx_sn + c) = packed;
   }
 }
 

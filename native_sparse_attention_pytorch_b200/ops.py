@@ -66,6 +66,43 @@ def check_device_status():
             raise L.NsaError('a tensor-core kernel gave up on a bounded wait; its results are invalid')
 
 
+def dim_order(t):
+    """The dimensions of t from outermost to innermost in memory (the last one stays last)."""
+    return tuple(sorted(range(t.dim() - 1), key=lambda i: (-t.stride(i), i))) + (t.dim() - 1,)
+
+
+def empty_in_order(shape, order, dtype, device):
+    """Uninitialised dense tensor of `shape` whose dimensions lie in memory in `order`."""
+    buf = torch.empty([shape[i] for i in order], dtype=dtype, device=device)
+    return buf.permute([order.index(i) for i in range(len(shape))])
+
+
+def _empty_in_order_of(t):
+    """Uninitialised tensor of t's shape and dtype whose dimensions lie in memory in the order t's do: a [b, h, n, d]
+    view of a [b, n, (h d)] projection output gives a [b, n, h, d] buffer seen as [b, h, n, d], so that the gradient
+    of the view that made t is a view again instead of a copy."""
+    return empty_in_order(t.shape, dim_order(t), t.dtype, t.device)
+
+
+def _dq_buffers(lib, query, fwd, q, need_fp32=False):
+    """(fp32 dq, None), or (None, dq in q's dtype and layout) where the backward stores whole rows of dq itself."""
+    if not need_fp32 and q.dtype == torch.bfloat16 and getattr(lib, query)(C.byref(fwd)) == 1:
+        return None, _empty_in_order_of(q)
+    return torch.empty(q.shape, dtype=torch.float32, device=q.device), None
+
+
+def _call_bwd(fn, make_args, q, stream):
+    """Run a backward entry point; when the tensor-core kernels decline the tensors at run time although the direct
+    dq was offered, run it again with an fp32 dq."""
+    args, dq, dq_out = make_args(True)
+    rc = fn(C.byref(args), stream)
+    if rc == L.NSA_ERR_UNSUPPORTED and dq_out is not None:
+        args, dq, dq_out = make_args(False)
+        rc = fn(C.byref(args), stream)
+    L.check(rc)
+    return dq_out if dq_out is not None else dq.to(q.dtype)
+
+
 REUSE_INDEX = True     # the selected-block backward takes the index the forward built instead of rebuilding it
 
 
@@ -106,7 +143,6 @@ class SelectedAttention(Function):
         want_slot_grads = slot_dtype is not None
         lib = L.load()
         dout = L.rowwise(dout)
-        dq = torch.empty(q.shape, dtype=torch.float32, device=q.device)
         dk = torch.empty(k.shape, dtype=torch.float32, device=q.device)
         dv = torch.empty(v.shape, dtype=torch.float32, device=q.device)
         slot = torch.zeros(idx.shape, dtype=torch.float32, device=q.device) if want_slot_grads else None
@@ -114,13 +150,17 @@ class SelectedAttention(Function):
             fwd = _sel_args(q, k, v, out, idx, mask, lse, block, diag, impl, scale)
             ws = _with_workspace(fwd, True, q.device)
             index = ctx.index
-            args = L.SelBwdArgs(fwd=fwd, dout=L.t4(dout), dq=L.ptr(dq), dk=L.ptr(dk), dv=L.ptr(dv),
-                                slot_grads=L.ptr(slot), index=L.ptr(index),
-                                index_bytes=0 if index is None else index.numel())
-            L.check(lib.nsa_sel_bwd(C.byref(args), L.stream_of(q)))
+
+            def make_args(direct):
+                dq, dq_out = _dq_buffers(lib, 'nsa_sel_bwd_stores_dq', fwd, q, need_fp32=not direct)
+                return L.SelBwdArgs(fwd=fwd, dout=L.t4(dout), dq=L.ptr(dq), dk=L.ptr(dk), dv=L.ptr(dv),
+                                    slot_grads=L.ptr(slot), index=L.ptr(index),
+                                    index_bytes=0 if index is None else index.numel(),
+                                    dq_out=L.t4(dq_out) if dq_out is not None else L.Tensor4()), dq, dq_out
+            dq = _call_bwd(lib.nsa_sel_bwd, make_args, q, L.stream_of(q))
         _keep_status(ws)
         del ws
-        return (dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), None, None,
+        return (dq, dk.to(k.dtype), dv.to(v.dtype), None, None,
                 None if slot is None else slot.to(slot_dtype), None, None, None)
 
 
@@ -206,19 +246,28 @@ class CompressedAttention(Function):
         num_mem, stride, causal, sel_heads, impl, scale = ctx.cfg
         lib = L.load()
         dout = torch.zeros_like(out) if dout is None else L.rowwise(dout)
-        dq = torch.empty(q.shape, dtype=torch.float32, device=q.device)
         dck = torch.empty(ck.shape, dtype=torch.float32, device=q.device)
         dcv = torch.empty(cv.shape, dtype=torch.float32, device=q.device)
+        # a gradient through the importance output (differentiable top-k) is added to the fp32 dq afterwards
+        with_dimp = dimp is not None and dimp.numel() > 0 and ctx.needs_input_grad[0]
         with torch.cuda.device(q.device):
             fwd = _cmp_args(q, ck, cv, out, lse, None, sel_heads, num_mem, stride, causal, impl, scale)
             ws = _with_workspace(fwd, True, q.device, 'nsa_cmp_workspace_bytes')
-            args = L.CmpBwdArgs(fwd=fwd, dout=L.t4(dout), dq=L.ptr(dq), dck=L.ptr(dck), dcv=L.ptr(dcv))
-            L.check(lib.nsa_cmp_bwd(C.byref(args), L.stream_of(q)))
+
+            def make_args(direct):
+                dq, dq_out = _dq_buffers(lib, 'nsa_cmp_bwd_stores_dq', fwd, q, need_fp32=with_dimp or not direct)
+                return L.CmpBwdArgs(fwd=fwd, dout=L.t4(dout), dq=L.ptr(dq), dck=L.ptr(dck), dcv=L.ptr(dcv),
+                                    dq_out=L.t4(dq_out) if dq_out is not None else L.Tensor4()), dq, dq_out
+            if with_dimp:
+                args, dq32, _ = make_args(False)
+                L.check(lib.nsa_cmp_bwd(C.byref(args), L.stream_of(q)))
+                _importance_backward(dimp, q, ck, dq32, dck, num_mem, stride, causal, sel_heads, scale)
+                dq = dq32.to(q.dtype)
+            else:
+                dq = _call_bwd(lib.nsa_cmp_bwd, make_args, q, L.stream_of(q))
             _keep_status(ws)
             del ws
-        if dimp is not None and dimp.numel() > 0 and ctx.needs_input_grad[0]:
-            _importance_backward(dimp, q, ck, dq, dck, num_mem, stride, causal, sel_heads, scale)
-        return dq.to(q.dtype), dck.to(ck.dtype), dcv.to(cv.dtype), None, None, None, None, None, None
+        return dq, dck.to(ck.dtype), dcv.to(cv.dtype), None, None, None, None, None, None
 
 
 def _importance_backward(dimp, q, ck, dq, dck, num_mem, stride, causal, sel_heads, scale):
@@ -359,17 +408,20 @@ class SlidingAttention(Function):
         window, causal, impl, scale = ctx.cfg
         lib = L.load()
         dout = L.rowwise(dout)
-        dq = torch.empty(q.shape, dtype=torch.float32, device=q.device)
         dk = torch.empty(k.shape, dtype=torch.float32, device=q.device)
         dv = torch.empty(v.shape, dtype=torch.float32, device=q.device)
         with torch.cuda.device(q.device):
             fwd = _swa_args(q, k, v, out, lse, window, causal, impl, scale)
             ws = _with_workspace(fwd, True, q.device, 'nsa_swa_workspace_bytes')
-            args = L.SwaBwdArgs(fwd=fwd, dout=L.t4(dout), dq=L.ptr(dq), dk=L.ptr(dk), dv=L.ptr(dv))
-            L.check(lib.nsa_swa_bwd(C.byref(args), L.stream_of(q)))
+
+            def make_args(direct):
+                dq, dq_out = _dq_buffers(lib, 'nsa_swa_bwd_stores_dq', fwd, q, need_fp32=not direct)
+                return L.SwaBwdArgs(fwd=fwd, dout=L.t4(dout), dq=L.ptr(dq), dk=L.ptr(dk), dv=L.ptr(dv),
+                                    dq_out=L.t4(dq_out) if dq_out is not None else L.Tensor4()), dq, dq_out
+            dq = _call_bwd(lib.nsa_swa_bwd, make_args, q, L.stream_of(q))
             _keep_status(ws)
             del ws
-        return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), None, None, None
+        return dq, dk.to(k.dtype), dv.to(v.dtype), None, None, None
 
 
 def sliding_window_attend(q, k, v, window, causal, impl='auto'):
@@ -472,19 +524,20 @@ class CompressWindows(Function):
                                 block=block, stride=stride, ncb=ncb, dtype=L.dtype_code(x))
         with torch.cuda.device(x.device):
             L.check(lib.nsa_windows_fwd(C.byref(args), L.stream_of(x)))
-        ctx.cfg = (b, h, n, d, block, stride, ncb, x.dtype, pos.dtype)
+        ctx.cfg = (b, h, n, d, block, stride, ncb, x.dtype, pos.dtype, dim_order(x))
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        b, h, n, d, block, stride, ncb, xdtype, pdtype = ctx.cfg
+        b, h, n, d, block, stride, ncb, xdtype, pdtype, order = ctx.cfg
         lib = L.load()
         dout = dout.contiguous()
-        dx = torch.empty(b, h, n, d, dtype=xdtype, device=dout.device)
+        dx = empty_in_order((b, h, n, d), order, xdtype, dout.device)   # in the layout of x: see _empty_in_order_of
         dpos = torch.empty(h, block, d, dtype=torch.float32, device=dout.device)
         fwd = L.WindowsFwdArgs(x=L.Tensor4(), pos=None, out=None, batch=b, heads=h, seq=n, dim_head=d, block=block,
                                stride=stride, ncb=ncb, dtype=L.dtype_code(dout))
-        args = L.WindowsBwdArgs(fwd=fwd, dout=L.ptr(dout), dx=L.ptr(dx), dpos=L.ptr(dpos))
+        args = L.WindowsBwdArgs(fwd=fwd, dout=L.ptr(dout), dx=L.ptr(dx), dpos=L.ptr(dpos), dx_stride_b=dx.stride(0),
+                                dx_stride_h=dx.stride(1), dx_stride_n=dx.stride(2))
         with torch.cuda.device(dout.device):
             L.check(lib.nsa_windows_bwd(C.byref(args), L.stream_of(dout)))
         return dx, dpos.to(pdtype), None, None, None

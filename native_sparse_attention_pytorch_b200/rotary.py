@@ -22,25 +22,31 @@ class _Rotate(Function):
 
     @staticmethod
     def forward(ctx, x, cos, sin):
+        from .ops import dim_order
         ctx.save_for_backward(cos, sin)
+        ctx.order = dim_order(x)
         return _launch(x, cos, sin, inverse=False)
 
     @staticmethod
     def backward(ctx, grad):
+        # the gradient is written in the memory layout of the forward's input (heads as a strided view of the
+        # projection output), so that the gradient of that view is a view again instead of a copy
         cos, sin = ctx.saved_tensors
-        return _launch(grad, cos, sin, inverse=True), None, None
+        return _launch(grad, cos, sin, inverse=True, order=ctx.order), None, None
 
 
-def _launch(x, cos, sin, inverse):
+def _launch(x, cos, sin, inverse, order=None):
     from . import _lib as L
+    from .ops import empty_in_order
     lib = L.load()
     v = 16 // x.element_size()
     if x.stride(-1) != 1 or x.data_ptr() % 16 or any(s % v for s in x.stride()[:-1]):
         x = x.contiguous()
     b, h, n, d = x.shape
-    out = torch.empty(b, h, n, d, dtype=x.dtype, device=x.device)
+    out = empty_in_order((b, h, n, d), order or (0, 1, 2, 3), x.dtype, x.device)
     args = L.RotaryArgs(x=L.t4(x), out=L.ptr(out), cos_table=L.ptr(cos), sin_table=L.ptr(sin), batch=b, heads=h,
-                        seq=n, dim_head=d, dtype=L.dtype_code(x), inverse=1 if inverse else 0)
+                        seq=n, dim_head=d, dtype=L.dtype_code(x), inverse=1 if inverse else 0,
+                        out_stride_b=out.stride(0), out_stride_h=out.stride(1), out_stride_n=out.stride(2))
     with torch.cuda.device(x.device):
         L.check(lib.nsa_rotary(C.byref(args), L.stream_of(x)))
     return out

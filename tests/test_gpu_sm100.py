@@ -330,3 +330,36 @@ def test_backward_refuses_an_index_that_was_not_built_for_it():
     torch.autograd.grad((out * up.to(DEV)).sum(), (qg, kg, vg))
     with pytest.raises(RuntimeError, match='index that was not built'):
         ops.check_device_status()
+
+
+def test_gradients_come_back_in_the_layout_of_strided_inputs():
+    # q, k, v as the layer makes them: [b, h, n, d] views of a [b, n, (heads d)] projection output.  Where the backward
+    # stores whole rows of dq (tensor-core family, dim_head 64) dq is written directly in bf16 in q's layout, and the
+    # inverse rotary writes in the layout of its input: the values equal those of contiguous inputs, and turning the
+    # gradient back into [b, n, (h d)] needs no copy.
+    from native_sparse_attention_pytorch_b200.rotary import RotaryEmbedding
+    b, hq, hkv, n, d, nsel, win = 2, 8, 2, 300, 64, 3, 100
+    _, _, _, idx, mask, up = make_case(b, hq, hkv, n, d, nsel, seed=31)
+    proj = recipe.randn((b, n, (hq + 2 * hkv) * d), 32).bfloat16().to(DEV)
+    split = lambda t: tuple(x.unflatten(-1, (-1, d)).transpose(1, 2) for x in t.split((hq * d, hkv * d, hkv * d), dim=-1))
+    idx, mask, up = idx.to(DEV), mask.to(DEV), up.to(DEV)
+    rot = RotaryEmbedding(d).to(DEV)
+
+    def grads(strided):
+        q, k, v = split(proj)
+        if not strided:
+            q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        q, k, v = (t.detach().requires_grad_() if not strided else t.requires_grad_() for t in (q, k, v))
+        qr, kr = rot.rotate_queries_or_keys(q), rot.rotate_queries_or_keys(k)
+        o1 = nsa.native_sparse_attend(qr, kr, v, BLOCK, idx, mask, impl='sm100')
+        o2 = nsa.sliding_window_attend(qr, kr, v, win, True, impl='sm100')
+        return torch.autograd.grad(((o1 + o2) * up).sum(), (q, k, v, qr))
+
+    gs, gc = grads(True), grads(False)
+    ops.check_device_status()
+    for a, r, what in zip(gs, gc, ('dq', 'dk', 'dv', 'dq rotated')):
+        assert a.dtype == torch.bfloat16 and a.shape == r.shape
+        tol = 0.0 if what.startswith('dq') else 1e-5 + 2.0 ** -8      # dk, dv: fp32 atomics in any order, then one rounding
+        assert (a.float() - r.float()).abs().max().item() <= tol * max(1.0, r.float().abs().max().item()), what
+    assert gs[0].transpose(1, 2).is_contiguous() and gs[1].transpose(1, 2).is_contiguous()   # [b, n, h, d] in memory
+    assert gs[3].is_contiguous() and gc[0].is_contiguous()
