@@ -88,7 +88,8 @@ __global__ void __launch_bounds__(128) select_kernel(const SelectParams P, int w
 // The same selection with the row in registers: lane l holds columns l, l+32, ... (CPL of them), the arithmetic and its
 // order are those of select_kernel (so both pick the same blocks), but every top-k round is a scan of the lane's own
 // live entries, one warp-wide maximum over order-preserving integer keys and one warp-wide minimum over the column
-// indices of the lanes that hold that maximum; the k results are written by k lanes at the end.
+// indices of the lanes that hold that maximum; the k results are written by k lanes at the end.  With bf16-rounded
+// probabilities value and column share one word and a round is a single maximum over per-lane sorted lists.
 __device__ __forceinline__ unsigned ordered_bits(float v) {
   const unsigned u = __float_as_uint(v);
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
@@ -155,12 +156,55 @@ __global__ void __launch_bounds__(128) select_reg_kernel(const SelectParams P) {
       }
     }
   }
+  int my_idx = 0;        // lane r ends up with the r-th pick
+  float my_val = 0.f;
+  if (P.round_bf16 && !P.input_is_prob) {
+    // The probabilities were rounded to bf16, so the order-preserving key has 16 significant bits and fits one word
+    // together with the column: (key << 16) | (1023 - column) is unique per entry and its maximum is the largest
+    // value at the lowest column.  Each lane sorts its own entries once (bitonic network in registers); a round is
+    // then one warp-wide maximum over the lanes' heads, and the lane that held it shifts its list.
+    unsigned s[CPL];
+#pragma unroll
+    for (int t = 0; t < CPL; ++t)
+      s[t] = (alive >> t & 1) ? ((ordered_bits(v[t]) & 0xffff0000u) | (1023u - (unsigned)(lane + 32 * t))) : 0u;
+#pragma unroll
+    for (int k = 2; k <= CPL; k <<= 1) {
+#pragma unroll
+      for (int j = k >> 1; j > 0; j >>= 1) {
+#pragma unroll
+        for (int a = 0; a < CPL; ++a) {
+          const int b = a ^ j;
+          if (b > a) {
+            const unsigned hi = max(s[a], s[b]), lo = min(s[a], s[b]);
+            if ((a & k) == 0) { s[a] = hi; s[b] = lo; } else { s[a] = lo; s[b] = hi; }   // descending overall
+          }
+        }
+      }
+    }
+    for (int r = 0; r < P.k; ++r) {
+      const unsigned top = __reduce_max_sync(kFullMask, s[0]);
+      if (top == 0u) break;                       // fewer live entries than picks: the rest stay (0, 0.0)
+      if (lane == r) {
+        my_idx = (int)(1023u - (top & 1023u));
+        const unsigned key = (top & 0xffff0000u) | ((top & 0x80000000u) ? 0u : 0xffffu);
+        my_val = from_ordered_bits(key);
+      }
+      if (s[0] == top) {
+#pragma unroll
+        for (int t = 0; t + 1 < CPL; ++t) s[t] = s[t + 1];
+        s[CPL - 1] = 0u;
+      }
+    }
+    if (lane < P.k) {
+      P.idx[task * P.k + lane] = my_idx;
+      P.vals[task * P.k + lane] = my_val;
+    }
+    return;
+  }
   unsigned key[CPL];
 #pragma unroll
   for (int t = 0; t < CPL; ++t) key[t] = ordered_bits(v[t]);
 
-  int my_idx = 0;        // lane r ends up with the r-th pick
-  float my_val = 0.f;
   for (int r = 0; r < P.k; ++r) {
     unsigned best = 0;
     int best_t = -1;
