@@ -476,6 +476,7 @@ static int fill_windows(WindowParams& P, const nsa_windows_fwd_args& a) {
       a.block <= 0 || a.stride <= 0 || a.block < a.stride)
     return fail(NSA_ERR_SHAPE, "sizes: negative, dim_head not a multiple of 16 bytes (or above 256), or block < stride");
   if ((int64_t)a.ncb * a.stride > a.seq) return fail(NSA_ERR_SHAPE, "ncb windows do not fit the sequence");
+  if ((int64_t)a.batch * a.ncb > 0x7fffffffLL) return fail(NSA_ERR_SHAPE, "batch * ncb must stay below 2^31");
   memset(&P, 0, sizeof(P));
   P.batch = a.batch; P.heads = a.heads; P.seq = a.seq; P.d = a.dim_head; P.block = a.block; P.stride = a.stride;
   P.ncb = a.ncb;

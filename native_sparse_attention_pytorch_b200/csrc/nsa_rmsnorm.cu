@@ -74,35 +74,52 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const NormParams P) {
   }
 }
 
+// x and dy of a row stay in registers as loaded (16-byte pieces) and are decoded once for the dot product and the
+// weight gradient and once more for dx; the weight sits in shared memory: registers go to the weight-gradient
+// accumulators, and two or three blocks fit an SM.
 template <typename T, int NV>
-__global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const NormParams P) {
+__global__ void __launch_bounds__(256, NV <= 4 ? 2 : 1) rmsnorm_bwd_kernel(const NormParams P) {
   constexpr int V = Piece<T>::V;
-  __shared__ float fold[8][32 * V + 1];
+  extern __shared__ float norm_smem[];          // weight [dim], then the fold area [8][32 * V + 1]
+  float* w_s = norm_smem;
+  float (*fold)[32 * V + 1] = reinterpret_cast<float (*)[32 * V + 1]>(norm_smem + ((P.dim + 3) & ~3));
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   const int64_t warp = (int64_t)blockIdx.x * 8 + wib, warps = (int64_t)gridDim.x * 8;
   const int pieces = P.dim / V;
-  float w[NV][V], dw[NV][V];
+  for (int p = threadIdx.x; p < pieces; p += 256) {
+    float tmp[V];
+    load_weight<T>(P, p * V, tmp);
 #pragma unroll
-  for (int t = 0; t < NV; ++t) {
-#pragma unroll
-    for (int e = 0; e < V; ++e) dw[t][e] = 0.f, w[t][e] = 0.f;
-    if (lane + 32 * t < pieces) load_weight<T>(P, (lane + 32 * t) * V, w[t]);
+    for (int e = 0; e < V; ++e) w_s[p * V + e] = tmp[e];
   }
+  __syncthreads();
+  float dw[NV][V];
+#pragma unroll
+  for (int t = 0; t < NV; ++t)
+#pragma unroll
+    for (int e = 0; e < V; ++e) dw[t][e] = 0.f;
   for (int64_t row = warp; row < P.rows; row += warps) {
     const float rstd = P.rstd[row];
-    float xh[NV][V], g[NV][V];
+    uint4 xr[NV], gr[NV];
+#pragma unroll
+    for (int t = 0; t < NV; ++t) {
+      if (lane + 32 * t < pieces) {
+        xr[t] = *reinterpret_cast<const uint4*>((const T*)P.x + row * P.x_stride + (lane + 32 * t) * V);
+        gr[t] = *reinterpret_cast<const uint4*>((const T*)P.dy + row * P.dim + (lane + 32 * t) * V);
+      }
+    }
     float dot = 0.f;
 #pragma unroll
     for (int t = 0; t < NV; ++t) {
       if (lane + 32 * t < pieces) {
-        Piece<T>::load(P.x, row * P.x_stride + (lane + 32 * t) * V, xh[t]);
-        Piece<T>::load(P.dy, row * P.dim + (lane + 32 * t) * V, g[t]);
+        const T* xv = reinterpret_cast<const T*>(&xr[t]);
+        const T* gv = reinterpret_cast<const T*>(&gr[t]);
+        const float* wv = w_s + (lane + 32 * t) * V;
 #pragma unroll
         for (int e = 0; e < V; ++e) {
-          xh[t][e] *= rstd;
-          dw[t][e] += g[t][e] * xh[t][e];
-          g[t][e] *= w[t][e];
-          dot += g[t][e] * xh[t][e];
+          const float xh = Elem<T>::to_float(xv[e]) * rstd, g = Elem<T>::to_float(gv[e]);
+          dw[t][e] += g * xh;
+          dot += (g * wv[e]) * xh;
         }
       }
     }
@@ -110,9 +127,16 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const NormParams P) {
 #pragma unroll
     for (int t = 0; t < NV; ++t) {
       if (lane + 32 * t < pieces) {
+        const T* xv = reinterpret_cast<const T*>(&xr[t]);
+        const T* gv = reinterpret_cast<const T*>(&gr[t]);
+        const float* wv = w_s + (lane + 32 * t) * V;
+        float o[V];
 #pragma unroll
-        for (int e = 0; e < V; ++e) g[t][e] = rstd * (g[t][e] - xh[t][e] * c);
-        Piece<T>::store(P.dx, row * P.dim + (lane + 32 * t) * V, g[t]);
+        for (int e = 0; e < V; ++e) {
+          const float xh = Elem<T>::to_float(xv[e]) * rstd, g = Elem<T>::to_float(gv[e]);
+          o[e] = rstd * (g * wv[e] - xh * c);
+        }
+        Piece<T>::store(P.dx, row * P.dim + (lane + 32 * t) * V, o);
       }
     }
   }
@@ -137,7 +161,9 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const NormParams P) {
 
 template <typename T, int NV>
 static void launch_one(const NormParams& P, bool backward, unsigned grid, cudaStream_t stream) {
-  if (backward) rmsnorm_bwd_kernel<T, NV><<<grid, 256, 0, stream>>>(P);
+  constexpr int V = Piece<T>::V;
+  const size_t bwd_smem = (size_t)(((P.dim + 3) & ~3) + 8 * (32 * V + 1)) * sizeof(float);   // at most 16.3 KB
+  if (backward) rmsnorm_bwd_kernel<T, NV><<<grid, 256, bwd_smem, stream>>>(P);
   else rmsnorm_fwd_kernel<T, NV><<<grid, 256, 0, stream>>>(P);
 }
 
@@ -162,7 +188,7 @@ int launch_rmsnorm(const NormParams& P, int dtype, bool backward, cudaStream_t s
   }
   const int64_t blocks = (P.rows + 7) / 8;
   // the backward adds one partial per block: a few blocks per SM bound the atomics, the forward is a plain stream
-  const int64_t cap = backward ? 148 * 4 : 148 * 16;
+  const int64_t cap = backward ? 148 * 2 : 148 * 16;   // backward: the blocks one wave holds (two per SM)
   const unsigned grid = (unsigned)(blocks < cap ? blocks : cap);
   if (backward) {
     const cudaError_t zerr = cudaMemsetAsync(P.dweight, 0, (size_t)P.dim * sizeof(float), stream);

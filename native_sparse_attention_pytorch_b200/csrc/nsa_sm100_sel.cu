@@ -1768,18 +1768,25 @@ __global__ void fill_kernel(float* dst, float value, int64_t count) {
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (int64_t)gridDim.x * blockDim.x) dst[i] = value;
 }
 
-// Importance columns a causal query cannot see (column c of row i is visible iff c < i / stride): one warp per row
-// writes `value` from the first invisible column on; the attention kernel writes the visible ones.
-__global__ void __launch_bounds__(256) fill_invisible_kernel(float* dst, float value, int64_t rows, int N, int ncb, int stride) {
+// Importance columns a causal query cannot see (column c of row i is visible iff c < i / stride): `value` from the
+// first invisible column on; the attention kernel writes the visible ones.  A warp takes query i and query N-1-i of
+// a (batch, head) together, so that every warp writes about one row's worth.
+__device__ __forceinline__ void fill_row_from(float* r, int first, int ncb, float value, int lane) {
+  const int head = min(ncb, (first + 3) & ~3);          // scalar stores up to the next 16-byte boundary
+  if (first + lane < head) r[first + lane] = value;
+  const float4 v4 = make_float4(value, value, value, value);
+  for (int c = head + 4 * lane; c < ncb; c += 128) *reinterpret_cast<float4*>(r + c) = v4;
+}
+
+__global__ void __launch_bounds__(256) fill_invisible_kernel(float* dst, float value, int64_t slices, int N, int ncb, int stride) {
   const int lane = threadIdx.x & 31;
-  const int64_t warps = (int64_t)gridDim.x * 8;
-  for (int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); row < rows; row += warps) {
-    const int first = min(ncb, (int)(row % N) / stride);
-    float* r = dst + row * ncb;
-    const int head = min(ncb, (first + 3) & ~3);          // scalar stores up to the next 16-byte boundary
-    if (first + lane < head) r[first + lane] = value;
-    const float4 v4 = make_float4(value, value, value, value);
-    for (int c = head + 4 * lane; c < ncb; c += 128) *reinterpret_cast<float4*>(r + c) = v4;
+  const int half = (N + 1) / 2;
+  const int64_t warps = (int64_t)gridDim.x * 8, pairs = slices * half;
+  for (int64_t p = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); p < pairs; p += warps) {
+    const int64_t slice = p / half;
+    const int i = (int)(p % half), i2 = N - 1 - i;
+    fill_row_from(dst + (slice * N + i) * ncb, min(ncb, i / stride), ncb, value, lane);
+    if (i2 != i) fill_row_from(dst + (slice * N + i2) * ncb, min(ncb, i2 / stride), ncb, value, lane);
   }
 }
 
@@ -2228,8 +2235,9 @@ int sm100_cmp_fwd(const nsa_cmp_fwd_args& a, cudaStream_t st) {
     const int64_t count = (int64_t)x.B * x.Hkv * x.N * x.ncb;
     const int64_t rows = (int64_t)x.B * x.Hkv * x.N;
     if (x.ncb % 4 == 0 && (reinterpret_cast<uintptr_t>(x.importance) & 15u) == 0 && rows > 0) {
-      const int64_t blocks = (rows + 7) / 8;
-      fill_invisible_kernel<<<(unsigned)(blocks < 148 * 16 ? blocks : 148 * 16), 256, 0, st>>>(x.importance, fill, rows, x.N,
+      const int64_t slices = (int64_t)x.B * x.Hkv;
+      const int64_t blocks = (slices * ((x.N + 1) / 2) + 7) / 8;
+      fill_invisible_kernel<<<(unsigned)(blocks < 148 * 16 ? blocks : 148 * 16), 256, 0, st>>>(x.importance, fill, slices, x.N,
                                                                                               x.ncb, x.stride);
     } else {
       fill_kernel<<<(unsigned)((count + 1023) / 1024 < 148 * 16 ? (count + 1023) / 1024 : 148 * 16), 256, 0, st>>>(x.importance, fill, count);

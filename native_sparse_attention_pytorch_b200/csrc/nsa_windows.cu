@@ -72,17 +72,29 @@ __global__ void __launch_bounds__(128) windows_bwd_pos_kernel(const WindowParams
   const int slots = P.block * P.d / V;
   const int h = blockIdx.x / slot_groups, slot = (blockIdx.x % slot_groups) * 128 + threadIdx.x;
   if (slot >= slots) return;
-  const int64_t pairs = (int64_t)P.batch * P.ncb;
-  const int64_t per = (pairs + gridDim.y - 1) / gridDim.y;
-  const int64_t k0 = blockIdx.y * per, k1 = k0 + per < pairs ? k0 + per : pairs;
+  const int pairs = P.batch * P.ncb;                      // the entry point keeps this below 2^31
+  const int per = (pairs + (int)gridDim.y - 1) / (int)gridDim.y;
+  const int k0 = (int)blockIdx.y * per, k1 = min(k0 + per, pairs);
+  const int64_t window = (int64_t)slots * V;
+  const T* base = (const T*)P.dout + (int64_t)slot * V;
+  auto at = [&](int k) { return base + (((int64_t)(k / P.ncb) * P.heads + h) * P.ncb + k % P.ncb) * window; };
   float acc[V];
 #pragma unroll
   for (int x = 0; x < V; ++x) acc[x] = 0.f;
-#pragma unroll 4
-  for (int64_t k = k0; k < k1; ++k) {
-    const int64_t b = k / P.ncb, w = k % P.ncb;
-    const uint4 raw = *reinterpret_cast<const uint4*>((const T*)P.dout + ((b * P.heads + h) * P.ncb + w) * ((int64_t)slots * V) +
-                                                      (int64_t)slot * V);
+  int k = k0;
+  for (; k + 8 <= k1; k += 8) {                            // eight independent loads in flight per thread
+    uint4 raw[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) raw[u] = *reinterpret_cast<const uint4*>(at(k + u));
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const T* dv = reinterpret_cast<const T*>(&raw[u]);
+#pragma unroll
+      for (int x = 0; x < V; ++x) acc[x] += Elem<T>::to_float(dv[x]);
+    }
+  }
+  for (; k < k1; ++k) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(at(k));
     const T* dv = reinterpret_cast<const T*>(&raw);
 #pragma unroll
     for (int x = 0; x < V; ++x) acc[x] += Elem<T>::to_float(dv[x]);
@@ -110,10 +122,10 @@ int launch_windows(const WindowParams& P, int dtype, bool backward, cudaStream_t
   if (backward && P.heads > 0 && P.block > 0) {
     const cudaError_t zerr = cudaMemsetAsync(P.dpos, 0, (size_t)P.heads * P.block * P.d * sizeof(float), stream);
     if (zerr != cudaSuccess) return fail((int)zerr, cudaGetErrorString(zerr));
-    const int64_t pairs = (int64_t)P.batch * P.ncb;
+    const int64_t pairs = (int64_t)P.batch * P.ncb;   // below 2^31: checked by the caller of this launcher
     const int slot_groups = (P.block * P.d / V + 127) / 128;
     const int64_t ctas = (int64_t)P.heads * slot_groups;
-    int64_t slices = (148 * 8 + ctas - 1) / ctas;            // about eight CTAs per SM in total
+    int64_t slices = (148 * 3 + ctas - 1) / ctas;            // about three CTAs per SM: every slice ends in atomics
     slices = slices > pairs ? pairs : slices;
     slices = slices < 1 ? 1 : (slices > 65535 ? 65535 : slices);
     const dim3 grid((unsigned)ctas, (unsigned)slices);
