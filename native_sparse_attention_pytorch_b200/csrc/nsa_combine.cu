@@ -40,10 +40,8 @@ __global__ void __launch_bounds__(256) combine_gather_kernel(const CombineParams
   const int64_t total = (int64_t)P.batch * P.seq * P.q_heads * vpr;
   const int rot = (int)(blockIdx.x % (unsigned)Gt.num_outs);
   for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
-    const int c = (int)(e % vpr) * V;
-    const int h = (int)((e / vpr) % P.q_heads);
-    const int n = (int)((e / ((int64_t)vpr * P.q_heads)) % P.seq);
-    const int b = (int)(e / ((int64_t)vpr * P.q_heads * P.seq));
+    const Coord4 pos = split4(e, vpr, P.q_heads, P.seq);
+    const int c = pos.i0 * V, h = pos.i1, n = pos.i2, b = pos.i3;
     const T* g = (const T*)P.gates + b * P.g_sb + h * P.g_sh + (int64_t)n * P.g_sn;
     float acc[V];
 #pragma unroll
@@ -123,9 +121,8 @@ __global__ void __launch_bounds__(256) combine_bwd_vec_kernel(const CombineParam
   const bool live = task < tasks;
   float dg[3] = {0.f, 0.f, 0.f};
   if (live) {
-    const int n = (int)(task % P.seq);
-    const int h = (int)((task / P.seq) % P.q_heads);
-    const int b = (int)(task / ((int64_t)P.seq * P.q_heads));
+    const Coord4 at = split4(task, P.seq, P.q_heads, 1);
+    const int n = at.i0, h = at.i1, b = at.i3;
     const T* g = (const T*)P.gates + b * P.g_sb + h * P.g_sh + (int64_t)n * P.g_sn;
     const int c = part * V;
     const uint4 draw = *reinterpret_cast<const uint4*>((const T*)P.dout + (((int64_t)b * P.seq + n) * P.q_heads + h) * P.d + c);

@@ -63,6 +63,25 @@ __device__ __forceinline__ float round_bf16(float v) {
   return __bfloat162float(__float2bfloat16_rn(v));
 }
 
+// Split a flat index over [d3][d2][d1][d0] (d0 fastest) into its four coordinates; with 32-bit arithmetic whenever
+// the index fits (64-bit divisions cost several times more instructions, and these kernels are otherwise a few
+// loads and stores per thread).
+struct Coord4 { int i0, i1, i2, i3; };
+__device__ __forceinline__ Coord4 split4(int64_t e, int d0, int d1, int d2) {
+  Coord4 r;
+  if (e < 0x7fffffffLL) {
+    unsigned u = (unsigned)e;
+    r.i0 = (int)(u % (unsigned)d0); u /= (unsigned)d0;
+    r.i1 = (int)(u % (unsigned)d1); u /= (unsigned)d1;
+    r.i2 = (int)(u % (unsigned)d2); r.i3 = (int)(u / (unsigned)d2);
+  } else {
+    r.i0 = (int)(e % d0); e /= d0;
+    r.i1 = (int)(e % d1); e /= d1;
+    r.i2 = (int)(e % d2); r.i3 = (int)(e / d2);
+  }
+  return r;
+}
+
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(kFullMask, v, o));

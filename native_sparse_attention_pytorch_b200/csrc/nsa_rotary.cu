@@ -15,10 +15,9 @@ __global__ void __launch_bounds__(256) rotary_kernel(const RotaryParams P) {
   const int vpr = P.d / V;
   const int64_t total = (int64_t)P.batch * P.heads * P.seq * vpr;
   for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
-    const int c = (int)(e % vpr) * V;
-    const int n = (int)((e / vpr) % P.seq);
-    const int h = (int)((e / ((int64_t)vpr * P.seq)) % P.heads);
-    const int b = (int)(e / ((int64_t)vpr * P.seq * P.heads));
+    const Coord4 at = split4(e, vpr, P.seq, P.heads);
+    const int c = at.i0 * V, n = at.i1, h = at.i2;
+    const int64_t b = at.i3;
     const uint4 raw = *reinterpret_cast<const uint4*>((const T*)P.x + b * P.x_sb + h * P.x_sh + (int64_t)n * P.x_sn + c);
     const T* xv = reinterpret_cast<const T*>(&raw);
     const float* cs = P.cos + (int64_t)n * (P.d / 2) + c / 2;

@@ -14,11 +14,10 @@ __global__ void __launch_bounds__(256) windows_fwd_kernel(const WindowParams P) 
   const int vpr = P.d / V;
   const int64_t total = (int64_t)P.batch * P.heads * P.ncb * P.block * vpr;
   for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
-    const int c = (int)(e % vpr) * V;
-    const int j = (int)((e / vpr) % P.block);
-    const int w = (int)((e / ((int64_t)vpr * P.block)) % P.ncb);
-    const int h = (int)((e / ((int64_t)vpr * P.block * P.ncb)) % P.heads);
-    const int b = (int)(e / ((int64_t)vpr * P.block * P.ncb * P.heads));
+    const Coord4 at = split4(e, vpr, P.block, P.ncb);     // i3 = b * heads + h
+    const int c = at.i0 * V, j = at.i1, w = at.i2;
+    const int h = at.i3 % P.heads;
+    const int64_t b = at.i3 / P.heads;
     const int tok = (w + 1) * P.stride - P.block + j;
     uint4 xraw = make_uint4(0u, 0u, 0u, 0u);
     if (tok >= 0) xraw = *reinterpret_cast<const uint4*>((const T*)P.x + b * P.x_sb + h * P.x_sh + (int64_t)tok * P.x_sn + c);
@@ -40,10 +39,9 @@ __global__ void __launch_bounds__(256) windows_bwd_x_kernel(const WindowParams P
   const int vpr = P.d / V;
   const int64_t total = (int64_t)P.batch * P.heads * P.seq * vpr;
   for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
-    const int c = (int)(e % vpr) * V;
-    const int tok = (int)((e / vpr) % P.seq);
-    const int64_t bh = e / ((int64_t)vpr * P.seq);
-    const int64_t b = bh / P.heads, h = bh % P.heads;
+    const Coord4 at = split4(e, vpr, P.seq, P.heads);
+    const int c = at.i0 * V, tok = at.i1;
+    const int64_t h = at.i2, b = at.i3, bh = b * P.heads + h;
     float acc[V];
 #pragma unroll
     for (int x = 0; x < V; ++x) acc[x] = 0.f;
