@@ -989,10 +989,10 @@ def run_lm(args, w):
 
 # Kernels of this library launched by one forward+backward of the layer at a shape the tensor-core family serves.
 # Forward 16: norm, window split of k and v (2), compressed (importance prefill + dense kernel: 2), selection, rotary of
-# q and k (2), selected (index pre-pass 4 + main + merge: 6), sliding (dense kernel), combine.  Backward 25: combine,
-# sliding (pre-pass 4 + delta + main + dQ merge: 7), selected (delta + main + dQ merge on the forward's index: 3),
-# inverse rotary (2), compressed (7), window split (2 x 2), norm.
-LAYER_LAUNCHES = 16 + 25
+# q and k (2), selected (index pre-pass 4 + main + merge: 6), sliding (dense kernel), combine.  Backward 17: combine,
+# sliding, selected and compressed (delta + main + dQ merge each: the selected branch on the forward's index, the other
+# two on the index kept per shape since their first backward), inverse rotary (2), window split (2 x 2), norm.
+LAYER_LAUNCHES = 16 + 17
 
 
 def launches_per_step(kernels, w):

@@ -232,10 +232,19 @@ typedef struct {
   float* dck;
   float* dcv;
   nsa_tensor dq_out;     /* optional, as in nsa_sel_bwd_args */
+  const void* index;     /* optional, see nsa_cmp_index_bytes */
+  int64_t index_bytes;
 } nsa_cmp_bwd_args;
 
 int nsa_cmp_bwd(const nsa_cmp_bwd_args* args, void* stream);
 int nsa_cmp_bwd_stores_dq(const nsa_cmp_fwd_args* args);
+/* The tensor-core backward walks an index of which queries attend which block of compressed keys.  Here it depends on
+ * the sizes only (batch, heads, seq, num_mem, ncb, stride), not on any tensor: after a backward call the first
+ * nsa_cmp_index_bytes(args) bytes of its work buffer hold it, and a caller may keep a copy and pass it as `index`
+ * (16-byte aligned, index_bytes as reported) to later calls with the same sizes, which then skip building it.
+ * 0 = the generic kernels serve the problem.  A copy that does not fit the sizes is detected on the device: the
+ * kernels do nothing and set status 2 in the first word of the work buffer. */
+int64_t nsa_cmp_index_bytes(const nsa_cmp_fwd_args* args);
 
 /* ------------------------------------------------------------------------
  * Block selection: per-block mean, own-block exclusion, sink softmax, top-k.
@@ -295,10 +304,14 @@ typedef struct {
   float* dk;
   float* dv;
   nsa_tensor dq_out;     /* optional, as in nsa_sel_bwd_args */
+  const void* index;     /* optional, see nsa_swa_index_bytes */
+  int64_t index_bytes;
 } nsa_swa_bwd_args;
 
 int nsa_swa_bwd(const nsa_swa_bwd_args* args, void* stream);
 int nsa_swa_bwd_stores_dq(const nsa_swa_fwd_args* args);
+/* As nsa_cmp_index_bytes: the sliding backward's index depends on batch, heads, seq and window only. */
+int64_t nsa_swa_index_bytes(const nsa_swa_fwd_args* args);
 
 /* ------------------------------------------------------------------------
  * Gated combine of the three branches and head merge.

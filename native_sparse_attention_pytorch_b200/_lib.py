@@ -45,7 +45,8 @@ class CmpFwdArgs(C.Structure):
 
 
 class CmpBwdArgs(C.Structure):
-    _fields_ = [('fwd', CmpFwdArgs), ('dout', Tensor4), ('dq', vp), ('dck', vp), ('dcv', vp), ('dq_out', Tensor4)]
+    _fields_ = [('fwd', CmpFwdArgs), ('dout', Tensor4), ('dq', vp), ('dck', vp), ('dcv', vp), ('dq_out', Tensor4),
+                ('index', vp), ('index_bytes', i64)]
 
 
 class SelectArgs(C.Structure):
@@ -61,7 +62,8 @@ class SwaFwdArgs(C.Structure):
 
 
 class SwaBwdArgs(C.Structure):
-    _fields_ = [('fwd', SwaFwdArgs), ('dout', Tensor4), ('dq', vp), ('dk', vp), ('dv', vp), ('dq_out', Tensor4)]
+    _fields_ = [('fwd', SwaFwdArgs), ('dout', Tensor4), ('dq', vp), ('dk', vp), ('dv', vp), ('dq_out', Tensor4),
+                ('index', vp), ('index_bytes', i64)]
 
 
 class CombineFwdArgs(C.Structure):
@@ -110,7 +112,7 @@ _STRUCTS = [Tensor4, SelFwdArgs, SelBwdArgs, CmpFwdArgs, CmpBwdArgs, SelectArgs,
             CombineFwdArgs, CombineBwdArgs, CombineGatherArgs, RotaryArgs, WindowsFwdArgs, WindowsBwdArgs,
             RmsNormFwdArgs, RmsNormBwdArgs]
 
-ENTRY_POINTS = ['nsa_sel_fwd', 'nsa_sel_bwd', 'nsa_sel_workspace_bytes', 'nsa_sel_index_bytes', 'nsa_sel_bwd_stores_dq', 'nsa_cmp_bwd_stores_dq', 'nsa_swa_bwd_stores_dq',
+ENTRY_POINTS = ['nsa_sel_fwd', 'nsa_sel_bwd', 'nsa_sel_workspace_bytes', 'nsa_sel_index_bytes', 'nsa_cmp_index_bytes', 'nsa_swa_index_bytes', 'nsa_sel_bwd_stores_dq', 'nsa_cmp_bwd_stores_dq', 'nsa_swa_bwd_stores_dq',
                 'nsa_sel_fwd_static',
                 'nsa_sel_static_scratch_bytes', 'nsa_cmp_workspace_bytes', 'nsa_swa_workspace_bytes', 'nsa_cmp_fwd', 'nsa_cmp_bwd', 'nsa_select',
                 'nsa_swa_fwd', 'nsa_swa_bwd', 'nsa_combine_fwd', 'nsa_combine_bwd', 'nsa_combine_fwd_gather', 'nsa_rotary', 'nsa_windows_fwd', 'nsa_windows_bwd', 'nsa_rmsnorm_fwd', 'nsa_rmsnorm_bwd', 'nsa_last_error',
@@ -136,6 +138,8 @@ def load():
     lib.nsa_last_error.restype = C.c_char_p
     lib.nsa_sel_workspace_bytes.restype = i64
     lib.nsa_sel_index_bytes.restype = i64
+    lib.nsa_cmp_index_bytes.restype = i64
+    lib.nsa_swa_index_bytes.restype = i64
     lib.nsa_sel_static_scratch_bytes.restype = i64
     lib.nsa_cmp_workspace_bytes.restype = i64
     lib.nsa_swa_workspace_bytes.restype = i64

@@ -150,6 +150,15 @@ int nsa_swa_bwd_stores_dq(const nsa_swa_fwd_args* a) {
   return a->impl != NSA_IMPL_SIMT && sm100_swa_bwd_overwrites_dq(*a) ? 1 : 0;
 }
 
+int64_t nsa_cmp_index_bytes(const nsa_cmp_fwd_args* a) {
+  if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
+  return a->impl == NSA_IMPL_SIMT ? 0 : sm100_cmp_index_bytes(*a);
+}
+int64_t nsa_swa_index_bytes(const nsa_swa_fwd_args* a) {
+  if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
+  return a->impl == NSA_IMPL_SIMT ? 0 : sm100_swa_index_bytes(*a);
+}
+
 int64_t nsa_sel_index_bytes(const nsa_sel_fwd_args* a) {
   if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
   AttnParams P;
@@ -258,6 +267,8 @@ int nsa_cmp_bwd(const nsa_cmp_bwd_args* a, void* stream) {
   const bool dq_stored = a->fwd.impl != NSA_IMPL_SIMT && sm100_cmp_bwd_overwrites_dq(a->fwd);
   NSA_TRY(check_dq_out(a->dq_out, a->fwd.dtype, dq_stored));
   if ((!a->dq && !a->dq_out.ptr) || !a->dck || !a->dcv) return fail(NSA_ERR_NULL, "dq/dck/dcv: NULL pointer");
+  if (a->index != nullptr && (reinterpret_cast<uintptr_t>(a->index) & 15u))
+    return fail(NSA_ERR_ALIGN, "index must be 16-byte aligned");
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t d = a->fwd.dim_head, rows = a->fwd.num_mem + a->fwd.ncb, b = a->fwd.batch;
   if (!dq_stored) NSA_TRY(zero_async(a->dq, b * a->fwd.q_heads * a->fwd.seq * d, st));
@@ -343,6 +354,8 @@ int nsa_swa_bwd(const nsa_swa_bwd_args* a, void* stream) {
   const bool dq_stored = a->fwd.impl != NSA_IMPL_SIMT && sm100_swa_bwd_overwrites_dq(a->fwd);
   NSA_TRY(check_dq_out(a->dq_out, a->fwd.dtype, dq_stored));
   if ((!a->dq && !a->dq_out.ptr) || !a->dk || !a->dv) return fail(NSA_ERR_NULL, "dq/dk/dv: NULL pointer");
+  if (a->index != nullptr && (reinterpret_cast<uintptr_t>(a->index) & 15u))
+    return fail(NSA_ERR_ALIGN, "index must be 16-byte aligned");
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t d = a->fwd.dim_head, n = a->fwd.seq, b = a->fwd.batch;
   if (!dq_stored) NSA_TRY(zero_async(a->dq, b * a->fwd.q_heads * n * d, st));

@@ -108,6 +108,8 @@ int launch_combine_gather(const CombineParams& P, const GatherTargets& Gt, int d
 // successful call) when the shape is outside what it serves.
 int64_t sm100_sel_workspace_bytes(const nsa_sel_fwd_args& a, bool backward);
 int64_t sm100_sel_index_bytes(const nsa_sel_fwd_args& a);
+int64_t sm100_swa_index_bytes(const nsa_swa_fwd_args& a);
+int64_t sm100_cmp_index_bytes(const nsa_cmp_fwd_args& a);
 int sm100_sel_fwd(const nsa_sel_fwd_args& a, cudaStream_t stream);
 int sm100_sel_bwd(const nsa_sel_bwd_args& a, cudaStream_t stream);
 int sm100_sel_fwd_static(const nsa_sel_fwd_args& a, cudaStream_t stream);

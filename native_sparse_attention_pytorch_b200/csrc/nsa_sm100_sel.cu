@@ -2201,6 +2201,19 @@ bool sm100_cmp_bwd_overwrites_dq(const nsa_cmp_fwd_args& a) {
   return cmp_problem(x, a) && x.D == 64 && ws_backward_enabled();
 }
 
+// The index of the sliding and the compressed backward depends on the sizes only: a caller may keep it across calls.
+int64_t sm100_swa_index_bytes(const nsa_swa_fwd_args& a) {
+  SelProblem x;
+  if (!swa_problem(x, a)) return 0;
+  return make_plan(x, true).index_bytes;
+}
+int64_t sm100_cmp_index_bytes(const nsa_cmp_fwd_args& a) {
+  SelProblem x;
+  if (!cmp_problem(x, a)) return 0;
+  x.importance = nullptr;
+  return make_plan(x, true).index_bytes;
+}
+
 int64_t sm100_swa_workspace_bytes(const nsa_swa_fwd_args& a, bool backward) {
   SelProblem x;
   if (!swa_problem(x, a)) return NSA_ERR_UNSUPPORTED;
@@ -2215,6 +2228,7 @@ int sm100_swa_bwd(const nsa_swa_bwd_args& b, cudaStream_t st) {
   SelProblem x;
   if (!swa_problem(x, b.fwd)) return NSA_ERR_UNSUPPORTED;
   x.dout = b.dout; x.dq = b.dq; x.dk = b.dk; x.dv = b.dv; x.dq_out = b.dq_out;
+  x.index = b.index; x.index_bytes = b.index_bytes;
   return problem_bwd(x, st);
 }
 
@@ -2250,6 +2264,7 @@ int sm100_cmp_bwd(const nsa_cmp_bwd_args& b, cudaStream_t st) {
   if (!cmp_problem(x, b.fwd)) return NSA_ERR_UNSUPPORTED;
   x.importance = nullptr;
   x.dout = b.dout; x.dq = b.dq; x.dk = b.dck; x.dv = b.dcv; x.dq_out = b.dq_out;
+  x.index = b.index; x.index_bytes = b.index_bytes;
   return problem_bwd(x, st);
 }
 

@@ -103,6 +103,23 @@ def _call_bwd(fn, make_args, q, stream):
     return dq_out if dq_out is not None else dq.to(q.dtype)
 
 
+# The index the sliding and the compressed backward walk depends on the sizes only: built once per shape and device
+# (by the first backward call, inside its work buffer), then handed to later calls.  A few MB per entry.
+_shape_index = {}
+_SHAPE_INDEX_ENTRIES = 8
+
+
+def _cached_index(key):
+    return _shape_index.get(key) if REUSE_INDEX else None
+
+
+def _keep_index(key, ws, nbytes):
+    if REUSE_INDEX and ws is not None and nbytes > 0 and key not in _shape_index:
+        while len(_shape_index) >= _SHAPE_INDEX_ENTRIES:
+            _shape_index.pop(next(iter(_shape_index)))
+        _shape_index[key] = ws[:nbytes].clone()
+
+
 REUSE_INDEX = True     # the selected-block backward takes the index the forward built instead of rebuilding it
 
 
@@ -253,11 +270,14 @@ class CompressedAttention(Function):
         with torch.cuda.device(q.device):
             fwd = _cmp_args(q, ck, cv, out, lse, None, sel_heads, num_mem, stride, causal, impl, scale)
             ws = _with_workspace(fwd, True, q.device, 'nsa_cmp_workspace_bytes')
+            key = ('cmp', q.device.index, tuple(q.shape), tuple(ck.shape), num_mem, stride, bool(causal), impl)
+            index = _cached_index(key)
 
             def make_args(direct):
                 dq, dq_out = _dq_buffers(lib, 'nsa_cmp_bwd_stores_dq', fwd, q, need_fp32=with_dimp or not direct)
                 return L.CmpBwdArgs(fwd=fwd, dout=L.t4(dout), dq=L.ptr(dq), dck=L.ptr(dck), dcv=L.ptr(dcv),
-                                    dq_out=L.t4(dq_out) if dq_out is not None else L.Tensor4()), dq, dq_out
+                                    dq_out=L.t4(dq_out) if dq_out is not None else L.Tensor4(), index=L.ptr(index),
+                                    index_bytes=0 if index is None else index.numel()), dq, dq_out
             if with_dimp:
                 args, dq32, _ = make_args(False)
                 L.check(lib.nsa_cmp_bwd(C.byref(args), L.stream_of(q)))
@@ -265,6 +285,8 @@ class CompressedAttention(Function):
                 dq = dq32.to(q.dtype)
             else:
                 dq = _call_bwd(lib.nsa_cmp_bwd, make_args, q, L.stream_of(q))
+            if index is None:
+                _keep_index(key, ws, int(lib.nsa_cmp_index_bytes(C.byref(fwd))))
             _keep_status(ws)
             del ws
         return dq, dck.to(ck.dtype), dcv.to(cv.dtype), None, None, None, None, None, None
@@ -413,12 +435,17 @@ class SlidingAttention(Function):
         with torch.cuda.device(q.device):
             fwd = _swa_args(q, k, v, out, lse, window, causal, impl, scale)
             ws = _with_workspace(fwd, True, q.device, 'nsa_swa_workspace_bytes')
+            key = ('swa', q.device.index, tuple(q.shape), tuple(k.shape), window, bool(causal), impl)
+            index = _cached_index(key)
 
             def make_args(direct):
                 dq, dq_out = _dq_buffers(lib, 'nsa_swa_bwd_stores_dq', fwd, q, need_fp32=not direct)
                 return L.SwaBwdArgs(fwd=fwd, dout=L.t4(dout), dq=L.ptr(dq), dk=L.ptr(dk), dv=L.ptr(dv),
-                                    dq_out=L.t4(dq_out) if dq_out is not None else L.Tensor4()), dq, dq_out
+                                    dq_out=L.t4(dq_out) if dq_out is not None else L.Tensor4(), index=L.ptr(index),
+                                    index_bytes=0 if index is None else index.numel()), dq, dq_out
             dq = _call_bwd(lib.nsa_swa_bwd, make_args, q, L.stream_of(q))
+            if index is None:
+                _keep_index(key, ws, int(lib.nsa_swa_index_bytes(C.byref(fwd))))
             _keep_status(ws)
             del ws
         return dq, dk.to(k.dtype), dv.to(v.dtype), None, None, None

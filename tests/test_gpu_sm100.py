@@ -363,3 +363,26 @@ def test_gradients_come_back_in_the_layout_of_strided_inputs():
         assert (a.float() - r.float()).abs().max().item() <= tol * max(1.0, r.float().abs().max().item()), what
     assert gs[0].transpose(1, 2).is_contiguous() and gs[1].transpose(1, 2).is_contiguous()   # [b, n, h, d] in memory
     assert gs[3].is_contiguous() and gc[0].is_contiguous()
+
+
+def test_sliding_and_compressed_backward_reuse_a_per_shape_index():
+    # their index depends on the sizes only: the first backward of a shape builds it, later ones take the kept copy
+    b, hq, hkv, n, d, win, st, m = 1, 8, 2, 700, 64, 130, 4, 1
+    ops._shape_index.clear()
+    q, k, v, up = (recipe.randn((b, h, n, d), s).bfloat16().to(DEV) for h, s in ((hq, 1), (hkv, 2), (hkv, 3), (hq, 4)))
+    ck, cv = (recipe.randn((b, hkv, m + n // st, d), s).bfloat16().to(DEV) for s in (5, 6))
+
+    def grads():
+        qs, ks, vs, cks, cvs = (t.clone().requires_grad_() for t in (q, k, v, ck, cv))
+        o1 = nsa.sliding_window_attend(qs, ks, vs, win, True, impl='sm100')
+        o2, _ = nsa.compressed_attend(qs, cks, cvs, m, st, True, impl='sm100')
+        return torch.autograd.grad(((o1 + o2) * up).sum(), (qs, ks, vs, cks, cvs))
+
+    first = grads()
+    assert len(ops._shape_index) == 2
+    second = grads()
+    ops.check_device_status()
+    assert len(ops._shape_index) == 2
+    assert torch.equal(first[0], second[0])                         # dq: ordered merge
+    for a, r in zip(first[1:], second[1:]):                         # fp32 atomics in any order, then one rounding
+        assert (a.float() - r.float()).abs().max().item() <= (1e-5 + 2.0 ** -8) * max(1.0, r.float().abs().max().item())
