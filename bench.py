@@ -860,39 +860,48 @@ def run_prefill_reference(args, w):
         'e2e': {'value': base['value'], 'unit': 'tokens/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0}}))
 
 
-def build_lm(w, dev):
-    """A small byte-level language model around the layer, with the sizes of upstream's training example: token
-    embedding, `depth` pre-norm residual blocks of [SparseAttention, RMSNorm -> Linear x4 -> GELU -> Linear], final
-    RMSNorm (the library's, as inside the layer), logits.  It is a harness for the layer, not part of the library."""
-    import native_sparse_attention_pytorch_b200 as nsa
-    from native_sparse_attention_pytorch_b200.norm import RMSNorm
+def build_lm(w, dev, dtype=torch.bfloat16, attn_cls=None, norm_cls=None):
+    """The language model of upstream's training example around the layer (transformer.py:142-330): token embedding,
+    `depth` pre-norm residual blocks of [SparseAttention, RMSNorm -> Linear x4 -> GELU -> Linear], final RMSNorm,
+    logits; next-token cross-entropy on ids[:, 1:].  Module names are upstream's (token_emb, layers, norm,
+    to_logits), so a state_dict moves across.  It is a harness around the layer, not part of the library; the tests
+    check it against stored results of upstream's model.  `attn_cls` / `norm_cls` default to the library's layer and
+    RMS norm (the CPU tests pass the oracle's layer and torch's norm)."""
     from torch import nn
     kw = {k: w[k] for k in ('dim', 'dim_head', 'heads', 'kv_heads', 'sliding_window_size', 'compress_block_size',
                             'compress_block_sliding_stride', 'selection_block_size', 'num_selected_blocks')}
+    if attn_cls is None:
+        import native_sparse_attention_pytorch_b200 as nsa
+        from native_sparse_attention_pytorch_b200.norm import RMSNorm
+        attn_cls = lambda **k: nsa.SparseAttention(use_triton_kernel=True, **k)
+        norm_cls = RMSNorm
+    norm_cls = norm_cls or nn.RMSNorm
 
     class Lm(nn.Module):
         def __init__(self):
             super().__init__()
             dim = w['dim']
-            self.emb = nn.Embedding(w['vocab'], dim)
-            self.blocks = nn.ModuleList([nn.ModuleList([
-                nsa.SparseAttention(causal=True, use_triton_kernel=True, **kw),
-                nn.Sequential(RMSNorm(dim), nn.Linear(dim, 4 * dim), nn.GELU(), nn.Linear(4 * dim, dim))])
+            self.token_emb = nn.Embedding(w['vocab'], dim)
+            self.layers = nn.ModuleList([nn.ModuleList([
+                attn_cls(causal=True, **kw),
+                nn.Sequential(norm_cls(dim), nn.Linear(dim, 4 * dim), nn.GELU(), nn.Linear(4 * dim, dim))])
                 for _ in range(w['depth'])])
-            self.norm = RMSNorm(dim)
+            self.norm = norm_cls(dim)
             self.to_logits = nn.Linear(dim, w['vocab'], bias=False)
+
+        def logits(self, ids):
+            x = self.token_emb(ids)
+            for attn, ff in self.layers:
+                x = attn(x) + x
+                x = ff(x) + x
+            return self.to_logits(self.norm(x))
 
         def forward(self, ids):
             ids, labels = ids[:, :-1], ids[:, 1:]
-            x = self.emb(ids)
-            for attn, ff in self.blocks:
-                x = attn(x) + x
-                x = ff(x) + x
-            logits = self.to_logits(self.norm(x))
-            return torch.nn.functional.cross_entropy(logits.flatten(0, 1).float(), labels.flatten())
+            return torch.nn.functional.cross_entropy(self.logits(ids).flatten(0, 1).float(), labels.flatten())
 
     torch.manual_seed(0)
-    return Lm().to(dev).bfloat16(), kw
+    return Lm().to(dev).to(dtype), kw
 
 
 def run_lm(args, w):

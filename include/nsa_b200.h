@@ -181,6 +181,16 @@ int64_t nsa_sel_workspace_bytes(const nsa_sel_fwd_args* args, int backward);
 int nsa_sel_fwd_static(const nsa_sel_fwd_args* args, void* stream);
 int64_t nsa_sel_static_scratch_bytes(void);
 
+/* The device status of the last nsa_sel_fwd_static call on the current
+ * device: 0 = its kernels ran to the end, 1 = one of them gave up on a bounded
+ * wait (the outputs are invalid), 2 = internal index mismatch.  The word
+ * lives at the start of the built-in area; this copies it to `out` -- host
+ * memory (pinned, for a copy that does not block the host) or device memory --
+ * in the order of `stream`, so issue it on the stream of the forward call
+ * and read `out` once that stream has reached it.  Allocates nothing.  (No
+ * counterpart in upstream, which checks nothing on the device.) */
+int nsa_sel_static_status(int* out, void* stream);
+
 /* ------------------------------------------------------------------------
  * Compressed-KV attention with the importance reduction fused in.
  * Replaces NSA:621-639 + attend NSA:153-184 and the first half of the
@@ -434,6 +444,23 @@ int nsa_rmsnorm_bwd(const nsa_rmsnorm_bwd_args* args, void* stream);
  * 4 cmp_bwd, 5 select, 6 swa_fwd, 7 swa_bwd, 8 combine_fwd, 9 combine_bwd, 10 combine_gather,
  * 11 rotary, 12 windows_fwd, 13 windows_bwd, 14 rmsnorm_fwd, 15 rmsnorm_bwd), so
  * a foreign-function binding can verify its own layout; -1 for other i. */
+/* ------------------------------------------------------------------------
+ * Housekeeping (no counterparts in upstream).
+ * ---------------------------------------------------------------------- */
+
+/* Kernels this library has launched in this process so far, all entry points
+ * and threads together.  A benchmark reads it before and after its timed
+ * region. */
+int64_t nsa_launch_count(void);
+
+/* Self-test of the bounded waits every tensor-core kernel uses: launches one
+ * block that allocates tensor memory and waits, for at most `limit_cycles` SM
+ * clock cycles, on a barrier nobody arrives on; it must give up, free its
+ * tensor memory and leave 1 in *status_device (device memory, cleared first),
+ * the way a kernel that lost a hand-over would.  Returns at once; nothing
+ * traps or spins without a bound. */
+int nsa_selftest_bounded_wait(int* status_device, int64_t limit_cycles, void* stream);
+
 const char* nsa_last_error(void);
 int nsa_abi_version(void);
 int nsa_struct_size(int which);

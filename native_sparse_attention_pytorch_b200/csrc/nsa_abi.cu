@@ -3,6 +3,8 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <atomic>
+
 #include "nsa_common.cuh"
 #include "nsa_kernels.h"
 
@@ -14,6 +16,9 @@ int fail(int code, const char* msg) {
   snprintf(g_error, sizeof(g_error), "%s", msg ? msg : "");
   return code;
 }
+
+static std::atomic<long long> g_launches{0};
+void count_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -188,6 +193,14 @@ int nsa_sel_fwd_static(const nsa_sel_fwd_args* a, void* stream) {
 }
 
 int64_t nsa_sel_static_scratch_bytes(void) { return sm100_static_scratch_bytes(); }
+
+int nsa_sel_static_status(int* out, void* stream) { return sm100_sel_static_status(out, (cudaStream_t)stream); }
+
+int64_t nsa_launch_count(void) { return (int64_t)g_launches.load(std::memory_order_relaxed); }
+
+int nsa_selftest_bounded_wait(int* status_device, int64_t limit_cycles, void* stream) {
+  return sm100_wait_selftest(status_device, limit_cycles, (cudaStream_t)stream);
+}
 
 int nsa_sel_bwd(const nsa_sel_bwd_args* a, void* stream) {
   if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");

@@ -76,6 +76,7 @@ int launch_combine_gather(const CombineParams& P, const GatherTargets& Gt, int d
   const unsigned grid = (unsigned)(blocks < 148 * 16 ? blocks : 148 * 16);
   if (dtype == NSA_F32) combine_gather_kernel<float><<<grid, 256, 0, stream>>>(P, Gt);
   else combine_gather_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(P, Gt);
+  count_launches(1);
   const cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return fail((int)err, cudaGetErrorString(err));
   return NSA_OK;
@@ -194,6 +195,7 @@ int launch_combine(const CombineParams& P, int dtype, bool backward, cudaStream_
     if (dtype == NSA_F32) combine_bwd_kernel<float><<<(unsigned)blocks, 128, 0, stream>>>(P);
     else combine_bwd_kernel<__nv_bfloat16><<<(unsigned)blocks, 128, 0, stream>>>(P);
   }
+  count_launches(1);   // every path above launched exactly one kernel
   const cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return fail((int)err, cudaGetErrorString(err));
   return NSA_OK;

@@ -95,6 +95,10 @@ struct NormParams {
 
 int fail(int code, const char* msg);
 
+// Every host function that launches kernels of this library reports how many it launched; nsa_launch_count() returns
+// the running total (a benchmark reads it before and after its timed region).
+void count_launches(int n);
+
 int simt_attend(const AttnParams& P, int branch, int dtype, bool backward, cudaStream_t stream);
 int launch_select(const SelectParams& P, cudaStream_t stream);
 int launch_combine(const CombineParams& P, int dtype, bool backward, cudaStream_t stream);
@@ -120,6 +124,8 @@ int64_t sm100_cmp_workspace_bytes(const nsa_cmp_fwd_args& a, bool backward);
 int sm100_cmp_fwd(const nsa_cmp_fwd_args& a, cudaStream_t stream);
 int sm100_cmp_bwd(const nsa_cmp_bwd_args& a, cudaStream_t stream);
 int64_t sm100_static_scratch_bytes();
+int sm100_sel_static_status(int* out, cudaStream_t stream);
+int sm100_wait_selftest(int* status_device, int64_t limit_cycles, cudaStream_t stream);
 bool sm100_sel_bwd_overwrites_dq(const nsa_sel_fwd_args& a);
 bool sm100_swa_bwd_overwrites_dq(const nsa_swa_fwd_args& a);
 bool sm100_cmp_bwd_overwrites_dq(const nsa_cmp_fwd_args& a);

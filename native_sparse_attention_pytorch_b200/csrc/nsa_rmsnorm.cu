@@ -165,6 +165,7 @@ static void launch_one(const NormParams& P, bool backward, unsigned grid, cudaSt
   const size_t bwd_smem = (size_t)(((P.dim + 3) & ~3) + 8 * (32 * V + 1)) * sizeof(float);   // at most 16.3 KB
   if (backward) rmsnorm_bwd_kernel<T, NV><<<grid, 256, bwd_smem, stream>>>(P);
   else rmsnorm_fwd_kernel<T, NV><<<grid, 256, 0, stream>>>(P);
+  count_launches(1);
 }
 
 template <typename T>

@@ -44,6 +44,7 @@ int launch_rotary(const RotaryParams& P, int dtype, cudaStream_t stream) {
   const unsigned grid = (unsigned)(blocks < 148 * 16 ? blocks : 148 * 16);
   if (dtype == NSA_F32) rotary_kernel<float><<<grid, 256, 0, stream>>>(P);
   else rotary_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(P);
+  count_launches(1);
   const cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return fail((int)err, cudaGetErrorString(err));
   return NSA_OK;

@@ -245,6 +245,7 @@ int launch_select(const SelectParams& P, cudaStream_t stream) {
       else if (P.cols <= 256) select_reg_kernel<8><<<grid, 128, 0, stream>>>(P);
       else if (P.cols <= 512) select_reg_kernel<16><<<grid, 128, 0, stream>>>(P);
       else select_reg_kernel<32><<<grid, 128, 0, stream>>>(P);
+      count_launches(1);
       const cudaError_t err = cudaGetLastError();
       if (err != cudaSuccess) return fail((int)err, cudaGetErrorString(err));
       return NSA_OK;
@@ -262,6 +263,7 @@ int launch_select(const SelectParams& P, cudaStream_t stream) {
   const int64_t blocks = (tasks + warps - 1) / warps;
   if (blocks > 0x7fffffffLL) return fail(NSA_ERR_SHAPE, "too many query rows for one launch");
   select_kernel<<<(unsigned)blocks, 128, smem, stream>>>(P, warps);
+  count_launches(1);
   err = cudaGetLastError();
   if (err != cudaSuccess) return fail((int)err, cudaGetErrorString(err));
   return NSA_OK;

@@ -411,6 +411,7 @@ static int launch_one(const AttnParams& P, bool backward, cudaStream_t stream) {
     if (err != cudaSuccess) return fail((int)err, cudaGetErrorString(err));
     kern<<<(unsigned)blocks, kWarpsPerBlock * 32, smem, stream>>>(P);
   }
+  count_launches(1);
   err = cudaGetLastError();
   if (err != cudaSuccess) return fail((int)err, cudaGetErrorString(err));
   return NSA_OK;

@@ -43,14 +43,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // second: when the limit passes (or another thread of the block already gave
 // up) it raises *abort_flag (shared memory) and returns false, so the kernel
 // can run to its end, free its tensor memory and report through a status word.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+constexpr long long kWaitLimitCycles = 2000000000LL;
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                  long long limit = kWaitLimitCycles) {
   if (*abort_flag) return false;
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (clock64() - t0 > 2000000000LL) {
+    if (clock64() - t0 > limit) {
       *abort_flag = 1;
       return false;
     }
@@ -59,8 +61,9 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
 
 // The same for a whole warp: one lane polls, the others sleep at the warp barrier and then observe the completed
 // phase themselves (one probe), so that 32 lanes do not poll side by side.
-__device__ __forceinline__ void mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if ((threadIdx.x & 31) == 0) mbar_wait_bounded(bar, parity, abort_flag);
+__device__ __forceinline__ void mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                               long long limit = kWaitLimitCycles) {
+  if ((threadIdx.x & 31) == 0) mbar_wait_bounded(bar, parity, abort_flag, limit);
   __syncwarp();
   while (!mbar_try_wait(bar, parity)) {
     if (*abort_flag) break;

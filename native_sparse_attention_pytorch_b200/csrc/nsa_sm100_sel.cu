@@ -989,21 +989,6 @@ __global__ void __launch_bounds__(256) sel_delta_kernel(const SelParams P, float
   if (row < nrows && part == 0) delta[row] = acc;
 }
 
-#ifdef NSA_PHASE_TIMING
-#define WT(i, expr) { const long long t0_ = clock64(); expr; wt_[i] += clock64() - t0_; }
-#define WT_DECL long long wt_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long wt_start = clock64();
-#define WT_REPORT(name, cond, nchunks) if (cond) printf("%s total %lld per-chunk: w0 %lld w1 %lld w2 %lld w3 %lld w4 %lld w5 %lld w6 %lld\n", name, (clock64() - wt_start) / max(1, nchunks), wt_[0] / max(1, nchunks), wt_[1] / max(1, nchunks), wt_[2] / max(1, nchunks), wt_[3] / max(1, nchunks), wt_[4] / max(1, nchunks), wt_[5] / max(1, nchunks), wt_[6] / max(1, nchunks));
-#define PT_DECL long long pt_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long pt_last = clock64(); int pt_chunks = 0;
-#define PT_MARK(i) { const long long now_ = clock64(); pt_[i] += now_ - pt_last; pt_last = now_; }
-#define PT_REPORT(name) if (threadIdx.x == 0 && blockIdx.x == 0) printf("%s chunks %d: gather %lld mma1 %lld softmax %lld mma2 %lld out %lld flush %lld item %lld (cycles per chunk)\n", name, pt_chunks, pt_[0]/pt_chunks, pt_[1]/pt_chunks, pt_[2]/pt_chunks, pt_[3]/pt_chunks, pt_[4]/pt_chunks, pt_[5]/pt_chunks, pt_[6]/pt_chunks);
-#else
-#define WT(i, expr) expr;
-#define WT_DECL
-#define WT_REPORT(name, cond, nchunks)
-#define PT_DECL
-#define PT_MARK(i)
-#define PT_REPORT(name)
-#endif
 
 template <int D>
 __global__ void __launch_bounds__(kRows, D == 64 ? 2 : 1)
@@ -1055,7 +1040,6 @@ sel_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   constexpr uint32_t idDQ = instr_desc_bf16(128, D, false, true);     // dQ = dS K    : B MN-major
   constexpr uint32_t idKV = instr_desc_bf16(64, D, true, true);       // dK, dV       : A and B MN-major
 
-  PT_DECL
   for (int it = blockIdx.x; it < nitems; it += gridDim.x) {
     const int4 item = P.items[it];
     const int list = item.x, j = list % P.nfb, bh = list / P.nfb, h = bh % P.Hkv, b = bh / P.Hkv;
@@ -1080,7 +1064,6 @@ sel_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       fence_proxy_async_smem();
       bulk_wait_read();   // the previous chunk's dQ rows have left the staging area (= the P and dS tiles)
       __syncthreads();
-      PT_MARK(0)
       if (tid == 0) {
         if (c == 0) mbar_wait_bounded(bar_kv, ph_kv, &abort_flag);
         tc_fence_after_sync();
@@ -1098,7 +1081,6 @@ sel_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       __syncwarp();
       mbar_wait_bounded(bar_1, ph_1, &abort_flag);
       ph_1 ^= 1;
-      PT_MARK(1)
       tc_fence_after_sync();
       __syncwarp();
       float p[64], ds[64];
@@ -1141,7 +1123,6 @@ sel_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       fence_proxy_async_smem();
       tc_fence_before_sync();
       __syncthreads();
-      PT_MARK(2)
       if (tid == 0) {
         tc_fence_after_sync();
         // dV += P^T dO, dK += dS^T Q over the 128 rows of the chunk (8 steps of 16 rows) and dQ_chunk = dS K over
@@ -1160,7 +1141,6 @@ sel_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       __syncwarp();
       mbar_wait_bounded(bar_2, ph_2, &abort_flag);
       ph_2 ^= 1;
-      PT_MARK(3)
       tc_fence_after_sync();
       __syncwarp();
 #pragma unroll
@@ -1177,10 +1157,6 @@ sel_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       if (r.valid) bulk_reduce_add_f32(P.dq + row_global * D, sStage + tid * kStageStride, D * 4);
       bulk_commit();
       tc_fence_before_sync();
-      PT_MARK(4)
-#ifdef NSA_PHASE_TIMING
-      ++pt_chunks;
-#endif
     }
     // flush dK, dV of this item: accumulator rows 16w..16w+15 live in lanes 0..15 of warp w
     {
@@ -1208,9 +1184,7 @@ sel_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     }
     ph_kv ^= 1;
     __syncthreads();
-    PT_MARK(5)
   }
-  PT_REPORT("bwd")
 
   bulk_wait_read();
   tc_fence_before_sync();
@@ -1238,12 +1212,6 @@ sel_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 // columns of its own so that a group can go on to the S/dP of its next chunk and read dQ of the previous one out
 // afterwards, while the tensor cores are busy with the other group's chunk.
 // Every hand-over is an mbarrier; every wait is bounded.
-#ifdef NSA_PHASE_TIMING
-__device__ long long g_trace[4][64][8];
-#define TR(role, n, k) if (blockIdx.x == 0 && (n) < 64) g_trace[role][n][k] = clock64();
-#else
-#define TR(role, n, k) ;
-#endif
 namespace ws {
 constexpr int kStages = 3;
 constexpr uint32_t kMetaBytes = 3 * kRows * 4;   // per stage: entry, lse, delta of every row of the chunk
@@ -1316,7 +1284,6 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     const int wg = warp >> 2, r_tid = tid & 127;
     const uint32_t tm_lane = tm + ((uint32_t)((warp & 3) * 32) << 16);
     const int q_local = r_tid >> g_shift, g = r_tid - (q_local << g_shift);
-    WT_DECL
     const uint32_t tS = wg * 192, tDP = tS + 64, tDQ = tS + 128;
     const uint32_t sP = sP0 + wg * kPBytes, sDS = sP + 16384;
     // dQ row of the group's previous chunk, still to be read out of tensor memory: index of its (row, slot) partial
@@ -1329,7 +1296,7 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     // 128-byte row would make every store instruction touch 32 lines; the warp stages half rows in shared memory
     // instead and stores them eight rows per instruction.
     auto dq_out = [&]() {
-      WT(1, mbar_wait_warp(smem_u32(&bars.mma2_done[wg]), prev_use & 1, &abort_flag))
+      mbar_wait_warp(smem_u32(&bars.mma2_done[wg]), prev_use & 1, &abort_flag);
       tc_fence_after_sync();
       __syncwarp();
       uint8_t* const pbase = reinterpret_cast<uint8_t*>(P.partial);
@@ -1367,9 +1334,7 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         const int list = item.x, j = list % P.nfb, bh = list / P.nfb, h = bh % P.Hkv, b = bh / P.Hkv;
         const uint32_t use = (uint32_t)(n >> 1);   // how many chunks this group has had before
         const uint32_t sMeta = sMeta0 + (n % kStages) * kMetaBytes + r_tid * 4;
-        if (r_tid == 0) TR(wg, n, 0)
-        WT(0, mbar_wait_warp(smem_u32(&bars.s_full[wg]), use & 1, &abort_flag))
-        if (r_tid == 0) TR(wg, n, 1)
+        mbar_wait_warp(smem_u32(&bars.s_full[wg]), use & 1, &abort_flag);
         tc_fence_after_sync();
         const uint32_t e = lds_u32(sMeta);
         const float lse2 = __uint_as_float(lds_u32(sMeta + kRows * 4)) * kLog2e;
@@ -1377,9 +1342,6 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         const RowInfo r = decode_row(e, j, P.rule);
         const int64_t hq = (int64_t)h * G + g;
         const int64_t row_global = ((int64_t)b * P.Hq + hq) * P.N + r.i;
-#ifdef NSA_PHASE_TIMING
-        const long long tc0_ = clock64();
-#endif
         float slot_part = 0.f;
         const bool want_slot = P.slot_grads != nullptr;
         // rows that see the whole block need no per-column test; only own-block (causal) and padding rows do
@@ -1442,25 +1404,16 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         fence_proxy_async_smem();
         tc_fence_before_sync();
         mbar_arrive(smem_u32(&bars.p_full[wg]));
-        if (r_tid == 0) TR(wg, n, 2)
         if (P.slot_grads != nullptr) {
           for (int o = G / 2; o > 0; o >>= 1) slot_part += __shfl_xor_sync(kFullMask, slot_part, o);
           if (r.valid && g == 0 && r.slot < P.nsel)
             P.slot_grads[(((int64_t)b * P.Hkv + h) * P.N + r.i) * P.nsel + r.slot] = slot_part * P.scale;
         }
-#ifdef NSA_PHASE_TIMING
-        wt_[2] += clock64() - tc0_;
-        const long long tc1_ = clock64();
-#endif
         // while the tensor cores work on this chunk's P and dS, read out dQ of the previous chunk of the group
         if (have_prev) dq_out();
-        if (r_tid == 0) TR(wg, n, 4)
         prev_dst = r.valid ? (int)(row_global * P.ns + r.slot) : -1;
         prev_use = use;
         have_prev = true;
-#ifdef NSA_PHASE_TIMING
-        wt_[3] += clock64() - tc1_;
-#endif
       }
     };
     uint32_t flushes = 0;   // items this group has flushed
@@ -1503,20 +1456,16 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     };
     // dK/dV of an item are flushed by the group that had the item's last chunk, as soon as the tensor cores are done
     // with it: the next item's dV/dK MMAs wait for the accumulator
-    int n = 0, t = 0, own_chunks = 0;
+    int n = 0, t = 0;
     for (int it = blockIdx.x; it < nitems; it += gridDim.x, ++t) {
       const int4 item = P.items[it];
       for (int c = 0; c < item.z; ++c, ++n) {
         if ((n & 1) != wg) continue;
-        if (r_tid == 0) TR(wg, n, 6)
-        WT(5, process_chunk(item, n))
-        if (r_tid == 0) TR(wg, n, 5)
-        ++own_chunks;
-        if (c == item.z - 1) WT(4, flush_item(item, t))
+        process_chunk(item, n);
+        if (c == item.z - 1) flush_item(item, t);
       }
     }
     if (have_prev) dq_out();
-    WT_REPORT("softmax: w0 s_full, w1 mma2_done, w2 math, w3 dq out, w4 flush, w5 whole chunk, w6 group barrier;", blockIdx.x == 0 && r_tid == 0, own_chunks)
   } else if (warp == 8) {
     // ------------------------------------------------------------------ MMA issuer: the whole warp runs the loop
     // (so that its state lives in uniform registers), one elected lane issues
@@ -1525,7 +1474,6 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     constexpr uint32_t idDQ = instr_desc_bf16(128, D, false, true);
     constexpr uint32_t idKV = instr_desc_bf16(64, D, true, true);
     int n = 0, t = 0;
-    WT_DECL
     // state of the chunk whose second set of MMAs is still to be issued
     bool pending = false;
     int p_n = 0, p_t = 0, p_c = 0;
@@ -1535,10 +1483,9 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
       const uint32_t sQ = sQ0 + stage * 32768, sDO = sQ + 16384;
       const uint32_t sP = sP0 + grp * kPBytes, sDS = sP + 16384;
       const uint32_t sK = sKV0 + kb * 16384;
-      WT(3, mbar_wait_bounded(smem_u32(&bars.p_full[grp]), (uint32_t)(pn >> 1) & 1, &abort_flag))
-      if (lane == 0) TR(2, pn, 2)
+      mbar_wait_bounded(smem_u32(&bars.p_full[grp]), (uint32_t)(pn >> 1) & 1, &abort_flag);
       // the accumulators are single: the first chunk of an item waits until the previous item has been flushed
-      if (pc == 0 && pt >= 1) WT(4, mbar_wait_bounded(smem_u32(&bars.acc_free), (uint32_t)(pt - 1) & 1, &abort_flag))
+      if (pc == 0 && pt >= 1) mbar_wait_bounded(smem_u32(&bars.acc_free), (uint32_t)(pt - 1) & 1, &abort_flag);
       __syncwarp();
       tc_fence_after_sync();
       const uint32_t tDK = 384, tDV = 448, tDQ = grp * 192 + 128;
@@ -1555,7 +1502,7 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
       for (int k = 0; k < 8; ++k)
         mma_bf16_elect(tm + tDK, desc_advance(dDSt, k * 2048), desc_advance(dQt, k * 2048), idKV, pc > 0 || k > 0);
       if (pn >= 2) {
-        WT(1, mbar_wait_bounded(smem_u32(&bars.dq_free[grp]), (uint32_t)((pn >> 1) - 1) & 1, &abort_flag))
+        mbar_wait_bounded(smem_u32(&bars.dq_free[grp]), (uint32_t)((pn >> 1) - 1) & 1, &abort_flag);
         __syncwarp();
         tc_fence_after_sync();
       }
@@ -1564,7 +1511,6 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         mma_bf16_elect(tm + tDQ, desc_advance(dDSt, k * 32), desc_advance(dKt, k * 2048), idDQ, k > 0);
       mma_commit_elect(smem_u32(&bars.mma2_done[grp]));
       mma_commit_elect(smem_u32(&bars.q_free[stage]));
-      if (lane == 0) TR(2, pn, 3)
       if (last) {
         mma_commit_elect(smem_u32(&bars.kv_free[kb]));
         mma_commit_elect(smem_u32(&bars.acc_full[grp]));   // the group of the item's last chunk flushes
@@ -1577,10 +1523,8 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         const int grp = n & 1, stage = n % kStages;
         const uint32_t sQ = sQ0 + stage * 32768, sDO = sQ + 16384;
         const uint32_t sK = sKV0 + kb * 16384, sV = sK + 8192;
-        if (lane == 0) TR(2, n, 0)
-        WT(0, mbar_wait_bounded(smem_u32(&bars.q_full[stage]), (uint32_t)(n / kStages) & 1, &abort_flag))
-        if (lane == 0) TR(2, n, 4)
-        if (c == 0) WT(2, mbar_wait_bounded(smem_u32(&bars.kv_full[kb]), (uint32_t)(t >> 1) & 1, &abort_flag))
+        mbar_wait_bounded(smem_u32(&bars.q_full[stage]), (uint32_t)(n / kStages) & 1, &abort_flag);
+        if (c == 0) mbar_wait_bounded(smem_u32(&bars.kv_full[kb]), (uint32_t)(t >> 1) & 1, &abort_flag);
         __syncwarp();
         tc_fence_after_sync();
         {
@@ -1595,7 +1539,6 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
             mma_bf16_elect(tm + tDP, desc_advance(dDOt, k * 32), desc_advance(dVt, k * 32), idS, k > 0);
           }
           mma_commit_elect(smem_u32(&bars.s_full[grp]));
-          if (lane == 0) TR(2, n, 1)
         }
         if (pending) issue_mma2(p_n, p_t, p_c, p_last);
         pending = true;
@@ -1606,7 +1549,6 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     // nothing of this block may still be running on the tensor cores when tensor memory is freed
     mma_commit_elect(smem_u32(&bars.drain));
     mbar_wait_drain(smem_u32(&bars.drain), 0);
-    WT_REPORT("mma: w0 q_full, w1 t_free, w2 kv_full, w3 p_full, w4 acc_free;", blockIdx.x == 0 && lane == 0, n)
     }
   } else if (warp == 13) {
     // ------------------------------------------------------------------ K/V tiles
@@ -1634,7 +1576,6 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     const int lt = tid - 9 * 32;           // 0..127
     const int sub = lt & 7, r0 = lt >> 3;  // 16-byte piece of a row, first row (rows r0 + 16*k)
     int n = 0, t = 0;
-    WT_DECL
     for (int it = blockIdx.x; it < nitems; it += gridDim.x, ++t) {
       const int4 item = P.items[it];
       const int list = item.x, bh = list / P.nfb, h = bh % P.Hkv, b = bh / P.Hkv;
@@ -1642,23 +1583,14 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
       const __nv_bfloat16* dob = P.dout + b * P.do_sb;
       for (int c = 0; c < item.z; ++c, ++n) {
         const int stage = n % kStages;
-        if (n >= kStages) WT(0, mbar_wait_warp(smem_u32(&bars.q_free[stage]), (uint32_t)(n / kStages - 1) & 1, &abort_flag))
-        if (lt == 0) TR(3, n, 0)
+        if (n >= kStages) mbar_wait_warp(smem_u32(&bars.q_free[stage]), (uint32_t)(n / kStages - 1) & 1, &abort_flag);
         const uint32_t sQ = sQ0 + stage * 32768, sDO = sQ + 16384;
         const uint32_t* chunk_entries = P.entries + item.w + c * QT;
         // read the entries first: the copies below are compiler barriers, a load placed between them would be
         // waited for eight times per chunk
         uint32_t ev[8];
-#ifdef NSA_PHASE_TIMING
-        const long long tl0_ = clock64();
-#endif
 #pragma unroll
         for (int k = 0; k < 8; ++k) ev[k] = __ldg(chunk_entries + ((r0 + k * 16) >> g_shift));
-#ifdef NSA_PHASE_TIMING
-        if (ev[0] == 0x12345678u) ++t;   // keeps the loads before the timestamp
-        const long long tl1_ = clock64();
-        wt_[2] += tl1_ - tl0_;
-#endif
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const int row = r0 + k * 16;
@@ -1684,33 +1616,16 @@ sel_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         }
         // the stage announces itself when this thread's copies have landed; the thread moves on at once
         cp_async_arrive_noinc(smem_u32(&bars.q_full[stage]));
-        if (lt == 0) TR(3, n, 1)
-#ifdef NSA_PHASE_TIMING
-        wt_[3] += clock64() - tl1_;
-#endif
       }
     }
     cp_async_commit();
     cp_async_wait<0>();
-    WT_REPORT("loader: w0 q_free, w1 cp.async wait, w2 entries, w3 cp.async issue, w4 fence;", blockIdx.x == 0 && lt == 0, n)
   }
 
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tm, 512);
   if (tid == 0 && abort_flag) atomicExch(P.status, 1);
-#ifdef NSA_PHASE_TIMING
-  if (tid == 0 && blockIdx.x == 0) {
-    const long long z = g_trace[3][0][0];
-    for (int n = 8; n < 28; ++n) {
-      const int w = n & 1;
-      printf("TRACE n %2d wg%d: call %6lld enter %6lld s_full %6lld p_arrive %6lld mma2_done %6lld end %6lld ret %6lld | mma: wait_q %6lld got_q %6lld mma1 %6lld got_p %6lld mma2 %6lld\n", n, w,
-             g_trace[w][n][6] - z, g_trace[w][n][0] - z, g_trace[w][n][1] - z, g_trace[w][n][2] - z, g_trace[w][n][3] - z,
-             g_trace[w][n][4] - z, g_trace[w][n][5] - z, g_trace[2][n][0] - z, g_trace[2][n][4] - z, g_trace[2][n][1] - z,
-             g_trace[2][n][2] - z, g_trace[2][n][3] - z);
-    }
-  }
-#endif
 }
 
 
@@ -1837,12 +1752,12 @@ static bool supported(const SelProblem& a) {
   return true;
 }
 
-// The forward of the compressed and the sliding-window branch runs query-tile stationary (dense_fwd_kernel) when the
-// output is a plain contiguous tensor; NSA_DENSE_FWD=0 keeps the key-block-stationary form for comparison.
-static bool dense_forward(const SelProblem& a) {
-  static const bool enabled = []() { const char* e = getenv("NSA_DENSE_FWD"); return e == nullptr || strcmp(e, "0") != 0; }();
-  if (!enabled || a.mode == kModeSel) return false;
-  if (a.mode == kModeCmp && a.num_mem < 1) return false;   // a query must see at least one key
+// The forward of the compressed and the sliding-window branch runs query-tile stationary (dense_fwd_kernel).  It
+// stores whole rows of a plain contiguous output; other layouts of `out` (and a compressed branch without a memory
+// slot, where a query may see no key) are left to the generic kernels.
+static bool dense_forward(const SelProblem& a) { return a.mode != kModeSel; }
+static bool dense_forward_serves(const SelProblem& a) {
+  if (a.mode == kModeCmp && a.num_mem < 1) return false;
   return a.out.stride_n == a.D && a.out.stride_h == (int64_t)a.N * a.D && a.out.stride_b == (int64_t)a.Hq * a.N * a.D;
 }
 
@@ -1930,8 +1845,14 @@ static BlockRule make_rule(const SelProblem& a, const SelPlan& p) {
   return R;
 }
 
-static uint32_t index_tag(const SelPlan& p) {
-  return 0x4e534149u ^ ((uint32_t)p.nlists * 0x9E3779B1u) ^ ((uint32_t)p.entries_cap * 0x85EBCA77u) ^ (uint32_t)p.QT;
+// A hash of everything the index depends on besides idx/mask themselves: sizes, head grouping, branch and its rule.
+static uint32_t index_tag(const SelProblem& a, const SelPlan& p) {
+  const uint32_t f[] = {(uint32_t)a.B, (uint32_t)a.Hkv, (uint32_t)p.G, (uint32_t)a.N, (uint32_t)a.Nk, (uint32_t)p.ns,
+                        (uint32_t)a.mode, (uint32_t)a.diag, (uint32_t)a.window, (uint32_t)a.stride, (uint32_t)a.num_mem,
+                        (uint32_t)a.nsel, (uint32_t)p.QT, (uint32_t)p.entries_cap};
+  uint32_t h = 0x4e534149u;
+  for (uint32_t v : f) h = (h ^ v) * 0x01000193u + 0x9E3779B1u;
+  return h == 0 ? 1u : h;   // 0 is what a cleared buffer holds
 }
 
 static int build_index(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaStream_t st) {
@@ -1950,11 +1871,12 @@ static int build_index(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaS
   else if (a.mode == kModeSwa) sel_hist_kernel<kModeSwa><<<grid, kBlock, hist_smem, st>>>(R, counts);
   else sel_hist_kernel<kModeCmp><<<grid, kBlock, hist_smem, st>>>(R, counts);
   sel_scan_kernel<<<(p.nlists + 31) / 32, dim3(32, kScanSeg), 0, st>>>(counts, totals, p.nlists, p.nqb, p.nkb);
-  sel_items_kernel<<<1, 1024, 0, st>>>(totals, list_base, items, num_items, p.nlists, p.QT, index_tag(p));
+  sel_items_kernel<<<1, 1024, 0, st>>>(totals, list_base, items, num_items, p.nlists, p.QT, index_tag(a, p));
   if (a.mode == kModeSel) sel_fill_kernel<kModeSel><<<grid, kBlock, hist_smem, st>>>(R, counts, list_base, entries);
   else if (a.mode == kModeSwa) sel_fill_kernel<kModeSwa><<<grid, kBlock, hist_smem, st>>>(R, counts, list_base, entries);
   else sel_fill_kernel<kModeCmp><<<grid, kBlock, hist_smem, st>>>(R, counts, list_base, entries);
   CUDA_TRY(cudaGetLastError());
+  count_launches(4);   // histogram, scan, items, fill
   return NSA_OK;
 }
 
@@ -1967,7 +1889,7 @@ static void fill_params(SelParams& P, const SelProblem& a, const SelPlan& p, uin
   P.entries = reinterpret_cast<const uint32_t*>(ix + p.off_entries);
   P.items = reinterpret_cast<const int4*>(ix + p.off_items);
   P.num_items = reinterpret_cast<const int*>(ix + p.off_num_items);
-  P.index_tag = index_tag(p);
+  P.index_tag = index_tag(a, p);
   P.status = reinterpret_cast<int*>(ws + p.off_status);
   P.lse = a.lse;
   P.B = a.B; P.Hq = a.Hq; P.Hkv = a.Hkv; P.N = a.N; P.Nk = a.Nk; P.G = p.G; P.nsel = a.nsel; P.nfb = p.nkb;
@@ -2019,6 +1941,7 @@ static int run_fwd(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaStrea
     else NSA_DENSE_LAUNCH(kModeCmp, 16);
 #undef NSA_DENSE_LAUNCH
     CUDA_TRY(cudaGetLastError());
+    count_launches(1);
     return NSA_OK;
   }
   rc = build_index(a, p, ws, st);
@@ -2032,26 +1955,14 @@ static int run_fwd(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaStrea
   constexpr int NC = D / 64;
   const int smem = 1024 + NC * (16384 + 8192 + 8192) + kRows * (D * 2 + 16);
   const int per_sm = D == 64 ? 4 : 2;
-  if (P.importance != nullptr) {
-    CUDA_TRY(cudaFuncSetAttribute(sel_fwd_kernel<D, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    sel_fwd_kernel<D, true, false><<<num_sms() * per_sm, kRows, smem, st>>>(tmK, tmV, P);
-  } else if (a.mode == kModeSwa) {
-    CUDA_TRY(cudaFuncSetAttribute(sel_fwd_kernel<D, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    sel_fwd_kernel<D, false, true><<<num_sms() * per_sm, kRows, smem, st>>>(tmK, tmV, P);
-  } else {
-    CUDA_TRY(cudaFuncSetAttribute(sel_fwd_kernel<D, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    sel_fwd_kernel<D, false, false><<<num_sms() * per_sm, kRows, smem, st>>>(tmK, tmV, P);
-  }
+  CUDA_TRY(cudaFuncSetAttribute(sel_fwd_kernel<D, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  sel_fwd_kernel<D, false, false><<<num_sms() * per_sm, kRows, smem, st>>>(tmK, tmV, P);
   const int64_t threads = (int64_t)a.B * a.Hq * a.N * (D / 8);
   const unsigned mblocks = (unsigned)((threads + 255) / 256);
   sel_merge_kernel<D><<<mblocks, 256, 0, st>>>(P);
   CUDA_TRY(cudaGetLastError());
+  count_launches(2);   // forward kernel, merge
   return NSA_OK;
-}
-
-static bool ws_backward_enabled() {
-  static const bool on = []() { const char* e = getenv("NSA_SEL_BWD"); return e == nullptr || strcmp(e, "v1") != 0; }();
-  return on;
 }
 
 template <int D>
@@ -2081,7 +1992,7 @@ static int run_bwd(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaStrea
   }
   const int64_t threads = (int64_t)a.B * a.Hq * a.N * (D / 8);
   sel_delta_kernel<D><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(P, delta);
-  if (D == 64 && ws_backward_enabled()) {
+  if (D == 64) {
     const int smem = 1024 + ws::kStages * 32768 + 2 * ws::kPBytes + 2 * 16384 + ws::kStages * ws::kMetaBytes +
                      8 * ws::kDqStage;
     CUDA_TRY(cudaFuncSetAttribute(sel_bwd_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -2092,6 +2003,7 @@ static int run_bwd(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaStrea
     else if (a.mode == kModeSwa) sel_dq_merge_kernel<64, kModeSwa><<<mblocks, 256, 0, st>>>(P);
     else sel_dq_merge_kernel<64, kModeCmp><<<mblocks, 256, 0, st>>>(P);
     CUDA_TRY(cudaGetLastError());
+    count_launches(3);   // delta, backward kernel, dQ merge
     return NSA_OK;
   }
   constexpr int NC = D / 64;
@@ -2100,6 +2012,7 @@ static int run_bwd(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaStrea
   CUDA_TRY(cudaFuncSetAttribute(sel_bwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   sel_bwd_kernel<D><<<num_sms() * per_sm, kRows, smem, st>>>(tmK, tmV, P);
   CUDA_TRY(cudaGetLastError());
+  count_launches(2);   // delta, backward kernel
   return NSA_OK;
 }
 
@@ -2156,7 +2069,7 @@ static int problem_fwd(const SelProblem& x, cudaStream_t st) {
 
 static int problem_bwd(const SelProblem& x, cudaStream_t st) {
   // dq in the caller's dtype and strides: only the merge of the partials writes whole rows of dq
-  if (x.dq_out.ptr != nullptr && !(x.D == 64 && ws_backward_enabled())) return NSA_ERR_UNSUPPORTED;
+  if (x.dq_out.ptr != nullptr && !(x.D == 64)) return NSA_ERR_UNSUPPORTED;
   const SelPlan p = make_plan(x, true);
   uint8_t* ws = nullptr;
   const int rc = check_ws(x, p, &ws);
@@ -2190,15 +2103,15 @@ int sm100_sel_bwd(const nsa_sel_bwd_args& b, cudaStream_t st) {
 // True when the backward of this problem stores every row of dq (partials + ordered merge) instead of adding into it.
 bool sm100_sel_bwd_overwrites_dq(const nsa_sel_fwd_args& a) {
   SelProblem x;
-  return sel_problem(x, a) && x.D == 64 && ws_backward_enabled();
+  return sel_problem(x, a) && x.D == 64;
 }
 bool sm100_swa_bwd_overwrites_dq(const nsa_swa_fwd_args& a) {
   SelProblem x;
-  return swa_problem(x, a) && x.D == 64 && ws_backward_enabled();
+  return swa_problem(x, a) && x.D == 64;
 }
 bool sm100_cmp_bwd_overwrites_dq(const nsa_cmp_fwd_args& a) {
   SelProblem x;
-  return cmp_problem(x, a) && x.D == 64 && ws_backward_enabled();
+  return cmp_problem(x, a) && x.D == 64;
 }
 
 // The index of the sliding and the compressed backward depends on the sizes only: a caller may keep it across calls.
@@ -2221,7 +2134,7 @@ int64_t sm100_swa_workspace_bytes(const nsa_swa_fwd_args& a, bool backward) {
 }
 int sm100_swa_fwd(const nsa_swa_fwd_args& a, cudaStream_t st) {
   SelProblem x;
-  if (!swa_problem(x, a)) return NSA_ERR_UNSUPPORTED;
+  if (!swa_problem(x, a) || !dense_forward_serves(x)) return NSA_ERR_UNSUPPORTED;
   return problem_fwd(x, st);
 }
 int sm100_swa_bwd(const nsa_swa_bwd_args& b, cudaStream_t st) {
@@ -2239,7 +2152,7 @@ int64_t sm100_cmp_workspace_bytes(const nsa_cmp_fwd_args& a, bool backward) {
 }
 int sm100_cmp_fwd(const nsa_cmp_fwd_args& a, cudaStream_t st) {
   SelProblem x;
-  if (!cmp_problem(x, a)) return NSA_ERR_UNSUPPORTED;
+  if (!cmp_problem(x, a) || !dense_forward_serves(x)) return NSA_ERR_UNSUPPORTED;
   if (x.importance != nullptr) {
     // columns a query cannot see carry the head mean of the sentinel; the kernel overwrites the visible ones
     float fill = 0.f;
@@ -2256,6 +2169,7 @@ int sm100_cmp_fwd(const nsa_cmp_fwd_args& a, cudaStream_t st) {
     } else {
       fill_kernel<<<(unsigned)((count + 1023) / 1024 < 148 * 16 ? (count + 1023) / 1024 : 148 * 16), 256, 0, st>>>(x.importance, fill, count);
     }
+    count_launches(1);
   }
   return problem_fwd(x, st);
 }
@@ -2278,6 +2192,7 @@ int sm100_cmp_bwd(const nsa_cmp_bwd_args& b, cudaStream_t st) {
 constexpr int64_t kStaticScratchBytes = 32ll << 20;
 static __device__ __align__(256) unsigned char g_sel_scratch[kStaticScratchBytes];
 
+// Filled on first use per device without a lock: every thread that races here stores the same address.
 constexpr int kMaxDevices = 64;
 static unsigned char* g_scratch_ptr[kMaxDevices] = {nullptr};
 
@@ -2314,5 +2229,58 @@ int sm100_sel_fwd_static(const nsa_sel_fwd_args& a, cudaStream_t st) {
 }
 
 int64_t sm100_static_scratch_bytes() { return kStaticScratchBytes; }
+
+// The status word the kernels of the last nsa_sel_fwd_static call on this device left in the built-in area (its
+// first four bytes): copied to `out`, host or device memory, in stream order.  Nothing is allocated.
+int sm100_sel_static_status(int* out, cudaStream_t st) {
+  if (out == nullptr) return fail(NSA_ERR_NULL, "nsa_sel_static_status: NULL output pointer");
+  unsigned char* ws = nullptr;
+  const int rc = static_scratch(&ws);
+  if (rc != NSA_OK) return rc;
+  CUDA_TRY(cudaMemcpyAsync(out, ws, sizeof(int), cudaMemcpyDefault, st));
+  return NSA_OK;
+}
+
+// ---- self-test of the bounded waits ----------------------------------------------------------------
+//
+// One block that does what every tensor-core kernel here does around a wait -- allocates tensor memory, waits on an
+// mbarrier with a limit, and on giving up raises its abort flag, frees the tensor memory and reports status 1 -- except
+// that nobody ever arrives on its barrier and the limit is `limit_cycles` (about a millisecond in the test) instead of
+// a second.  It returns by itself; nothing traps, faults or spins without a bound.
+__global__ void __launch_bounds__(128) wait_selftest_kernel(int* status, long long limit_cycles) {
+  __shared__ int abort_flag;
+  __shared__ uint32_t tmem_slot;
+  __shared__ __align__(8) uint64_t bar;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (tid == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (warp == 0) {
+    tmem_alloc(smem_u32(&tmem_slot), 32);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tm = tmem_slot;
+  mbar_wait_warp(smem_u32(&bar), 0, &abort_flag, limit_cycles);   // nobody arrives: every warp runs into the limit
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tm, 32);
+  if (tid == 0 && abort_flag) atomicExch(status, 1);
+}
+
+int sm100_wait_selftest(int* status_device, int64_t limit_cycles, cudaStream_t st) {
+  if (status_device == nullptr) return fail(NSA_ERR_NULL, "nsa_selftest_bounded_wait: NULL status pointer");
+  if (limit_cycles < 1 || limit_cycles > kWaitLimitCycles) return fail(NSA_ERR_SHAPE, "nsa_selftest_bounded_wait: limit out of range");
+  CUDA_TRY(cudaMemsetAsync(status_device, 0, sizeof(int), st));
+  wait_selftest_kernel<<<1, 128, 0, st>>>(status_device, (long long)limit_cycles);
+  CUDA_TRY(cudaGetLastError());
+  count_launches(1);
+  return NSA_OK;
+}
 
 }  // namespace nsa

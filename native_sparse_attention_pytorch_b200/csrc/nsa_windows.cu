@@ -116,6 +116,7 @@ int launch_windows(const WindowParams& P, int dtype, bool backward, cudaStream_t
       if (dtype == NSA_F32) windows_bwd_x_kernel<float><<<grid, 256, 0, stream>>>(P);
       else windows_bwd_x_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(P);
     }
+    count_launches(1);
   }
   if (backward && P.heads > 0 && P.block > 0) {
     const cudaError_t zerr = cudaMemsetAsync(P.dpos, 0, (size_t)P.heads * P.block * P.d * sizeof(float), stream);
@@ -129,6 +130,7 @@ int launch_windows(const WindowParams& P, int dtype, bool backward, cudaStream_t
     const dim3 grid((unsigned)ctas, (unsigned)slices);
     if (dtype == NSA_F32) windows_bwd_pos_kernel<float><<<grid, 128, 0, stream>>>(P, slot_groups);
     else windows_bwd_pos_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(P, slot_groups);
+    count_launches(1);
   }
   const cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return fail((int)err, cudaGetErrorString(err));

@@ -204,7 +204,15 @@ class SparseAttention(Module):
         fine_selection_flex_mask=None,
         return_cache=False,
         return_intermediates=False,
+        forced_selection=None,
     ):
+        """Upstream's signature (NSA:549-557) plus two keyword arguments of this package: ``return_intermediates``
+        also returns the tensors at the boundaries of the hot path, and ``forced_selection`` = (block indices,
+        mask), both [B, Hs, N, k], replaces the layer's own block selection (used to compare two precisions of the
+        layer on identical blocks).  A tensor-core kernel of an earlier call that gave up on a bounded wait is
+        reported here, one call late and without synchronising (`ops.poll_device_status`)."""
+        if inp.is_cuda:
+            ops.poll_device_status(inp.device)
         if cache is not None:
             if not inp.is_cuda:
                 raise RuntimeError('SparseAttention (B200 kernels) needs CUDA tensors; there is no CPU path here')
@@ -267,6 +275,8 @@ class SparseAttention(Module):
             vals, idx = ops.select_blocks(importance if self.use_diff_topk else importance.detach(), sel, st,
                                           num_selected, dtype=q.dtype)
             fmask = vals > 1e-10
+            if forced_selection is not None:
+                idx, fmask = forced_selection
             # differentiable top-k (NSA:715): the slots are scaled by 1 in the forward, the gradient of that scale
             # reaches the selected probabilities and through them the compressed logits
             slot_scale = vals + (1. - vals).detach() if self.use_diff_topk else None

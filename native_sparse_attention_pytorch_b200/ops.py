@@ -3,6 +3,7 @@ branch plus the block selection and the gated combine.  Tensors stay owned by
 PyTorch's allocator; the library only sees device pointers, sizes and the
 current CUDA stream."""
 import ctypes as C
+import threading
 
 import torch
 from torch.autograd import Function
@@ -30,7 +31,14 @@ def _sel_args(q, k, v, out, idx, mask, lse, block, diag, impl, scale):
                         workspace=None, workspace_bytes=0)
 
 
-_status_words = []
+# Device status of the tensor-core kernels.  Every such kernel reports through the first word of its work buffer:
+# 0 = fine, 1 = a bounded wait ran out (results invalid), 2 = it was handed an index built for another problem.  The
+# words are folded, in stream order, into one int32 per device (bitwise or), so nothing is lost however many kernels
+# run between two checks.  The autograd engine calls the backward functions from its own thread: one lock guards the
+# tables below.
+_state_lock = threading.Lock()
+_status_acc = {}      # device index -> int32[1] device tensor
+_status_polls = {}    # device index -> (pinned int32[1], event) of the copy issued by the last poll
 
 
 def _with_workspace(args, backward, device, sizer='nsa_sel_workspace_bytes'):
@@ -46,24 +54,66 @@ def _with_workspace(args, backward, device, sizer='nsa_sel_workspace_bytes'):
 
 
 def _keep_status(ws):
-    """The tensor-core kernels report a bounded wait that ran out through the first word of their work
-    buffer; keep a 4-byte device copy so it can be read later without holding the buffer."""
-    if ws is not None:
-        _status_words.append(ws[:4].clone())
-        del _status_words[:-64]
+    """Fold the status word of a work buffer into the device's accumulator (one tiny stream-ordered kernel)."""
+    if ws is None:
+        return
+    key = ws.device.index
+    with _state_lock:
+        acc = _status_acc.get(key)
+        if acc is None:
+            acc = _status_acc[key] = torch.zeros(1, dtype=torch.int32, device=ws.device)
+    acc.bitwise_or_(ws[:4].view(torch.int32))
+
+
+def _raise_for(code):
+    if code & 2:
+        raise L.NsaError('a tensor-core kernel was given an index that was not built for its problem; '
+                         'its results are invalid')
+    if code != 0:
+        raise L.NsaError('a tensor-core kernel gave up on a bounded wait; its results are invalid')
 
 
 def check_device_status():
-    """Synchronise and raise if any tensor-core kernel launched since the last call gave up on a wait (status 1) or
+    """Synchronise and raise if any tensor-core kernel launched since the last check gave up on a wait (status 1) or
     was handed an index that was not built for its problem (status 2)."""
-    words, _status_words[:] = list(_status_words), []
-    for w in words:
-        code = w.view(torch.int32).item()
-        if code == 2:
-            raise L.NsaError('a tensor-core kernel was given an index that was not built for its problem; '
-                             'its results are invalid')
+    with _state_lock:
+        accs = list(_status_acc.values())
+        _status_polls.clear()
+    code = 0
+    for acc in accs:
+        code |= int(acc.item())
+        acc.zero_()
+    _raise_for(code)
+
+
+def poll_device_status(device):
+    """The same check without a synchronisation, one call late: looks at the status copy the previous poll started
+    (if it has landed) and starts the next one.  `SparseAttention.forward` calls this, so a training loop learns of
+    an invalid step at its next forward without any host wait on the hot path."""
+    key = torch.device(device).index
+    if key is None:
+        key = torch.cuda.current_device()
+    with _state_lock:
+        acc = _status_acc.get(key)
+        pending = _status_polls.get(key)
+    if acc is None:
+        return
+    if pending is not None:
+        host, event = pending
+        if not event.query():
+            return                      # the previous copy is still in flight: look again at the next call
+        code = int(host.item())
         if code != 0:
-            raise L.NsaError('a tensor-core kernel gave up on a bounded wait; its results are invalid')
+            acc.zero_()
+            with _state_lock:
+                _status_polls.pop(key, None)
+            _raise_for(code)
+    host = pending[0] if pending is not None else torch.zeros(1, dtype=torch.int32).pin_memory()
+    host.copy_(acc, non_blocking=True)
+    event = torch.cuda.Event()
+    event.record(torch.cuda.current_stream(acc.device))
+    with _state_lock:
+        _status_polls[key] = (host, event)
 
 
 def dim_order(t):
@@ -110,11 +160,18 @@ _SHAPE_INDEX_ENTRIES = 8
 
 
 def _cached_index(key):
-    return _shape_index.get(key) if REUSE_INDEX else None
+    if not REUSE_INDEX:
+        return None
+    with _state_lock:
+        return _shape_index.get(key)
 
 
 def _keep_index(key, ws, nbytes):
-    if REUSE_INDEX and ws is not None and nbytes > 0 and key not in _shape_index:
+    if not (REUSE_INDEX and ws is not None and nbytes > 0):
+        return
+    with _state_lock:
+        if key in _shape_index:
+            return
         while len(_shape_index) >= _SHAPE_INDEX_ENTRIES:
             _shape_index.pop(next(iter(_shape_index)))
         _shape_index[key] = ws[:nbytes].clone()

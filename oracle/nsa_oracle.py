@@ -72,17 +72,23 @@ def compress_windows(t: torch.Tensor, cbs: int, st: int) -> torch.Tensor:
 # branch 1: attention over the compressed keys, returning its logits
 # --------------------------------------------------------------------------
 
-def compressed_attend(q, ck, cv, mem_k, mem_v, st: int, causal: bool):
+def compressed_attend(q, ck, cv, mem_k, mem_v, st: int, causal: bool, rows=None):
     """NSA:621-639 with ``attend`` NSA:153-184.
 
     q [B,Hq,N,d] (not rotated); ck, cv [B,Hkv,ncb,d]; mem_k, mem_v [Hkv,M,d].
     Returns (out [B,Hq,N,d], csim [B,Hq,N,M+ncb]).  Compressed key w is visible
     to a causal query i iff (w+1)*st-1 < i; memory slots are always visible.
     Invisible logits are *replaced* by (-finfo.max)//10, a finite sentinel.
+    ``rows`` (1-D int64) restricts the computation to those query positions
+    (used to check samples of large cases); N in the results is then len(rows).
     """
-    b, hq, n, d = q.shape
+    b, hq, _, d = q.shape
     hkv, m = mem_k.shape[0], mem_k.shape[1]
     g = hq // hkv
+    pos = torch.arange(q.shape[2], device=q.device) if rows is None else rows
+    if rows is not None:
+        q = q[:, :, rows]
+    n = pos.numel()
     keys = torch.cat((mem_k.expand(b, -1, -1, -1), ck), dim=-2)
     vals = torch.cat((mem_v.expand(b, -1, -1, -1), cv), dim=-2)
     qg = q.reshape(b, hkv, g, n, d)
@@ -90,7 +96,7 @@ def compressed_attend(q, ck, cv, mem_k, mem_v, st: int, causal: bool):
     if causal:
         last_token = (torch.arange(ck.shape[-2], device=q.device) + 1) * st - 1
         last_token = F.pad(last_token, (m, 0), value=-1)
-        visible = last_token[None, :] < torch.arange(n, device=q.device)[:, None]
+        visible = last_token[None, :] < pos[:, None]
         sim = sim.masked_fill(~visible, neg_max(sim) // 10)
     attn = sim.softmax(dim=-1)
     out = torch.einsum('bhgij,bhjd->bhgid', attn, vals)
@@ -101,7 +107,7 @@ def compressed_attend(q, ck, cv, mem_k, mem_v, st: int, causal: bool):
 # selection: importance reduction and top-k
 # --------------------------------------------------------------------------
 
-def importance_scores(csim, num_mem: int, hkv: int, st: int, sel: int, share_heads: bool = True):
+def importance_scores(csim, num_mem: int, hkv: int, st: int, sel: int, share_heads: bool = True, rows=None):
     """NSA:652-695.  csim [B,Hq,N,M+ncb] -> probabilities [B,Hsel,N,cols].
 
     Steps, each rounded to the tensor dtype as upstream does: drop the memory
@@ -109,6 +115,7 @@ def importance_scores(csim, num_mem: int, hkv: int, st: int, sel: int, share_hea
     truncate to a multiple of cpf = sel//st columns, mean over each cpf
     consecutive columns and overwrite the query's own block column with
     -finfo.max; prepend a sink column of -1000; softmax; drop the sink.
+    ``rows`` gives the query positions when csim holds a subset of the queries.
     """
     imp = csim[..., num_mem:]
     b, hq, n, _ = imp.shape
@@ -120,7 +127,7 @@ def importance_scores(csim, num_mem: int, hkv: int, st: int, sel: int, share_hea
         imp = imp[..., : cols * cpf]
         if imp.numel() > 0:
             imp = imp.reshape(*imp.shape[:-1], cols, cpf).mean(dim=-1)
-            own = torch.arange(n, device=imp.device) // sel
+            own = (torch.arange(n, device=imp.device) if rows is None else rows) // sel
             diag = own[:, None] == torch.arange(cols, device=imp.device)[None, :]
             imp = imp.masked_fill(diag, neg_max(csim))
     imp = F.pad(imp, (1, 0), value=-1e3)
@@ -223,14 +230,19 @@ def block_diagonal_attend(fq, fk, fv, sel: int, causal: bool):
 # branch 3: sliding window, and the gated combine
 # --------------------------------------------------------------------------
 
-def sliding_attend(q, k, v, window: int, causal: bool):
+def sliding_attend(q, k, v, window: int, causal: bool, rows=None):
     """NSA:841-850.  Causal: keys j with 0 <= i-j <= window (window+1 keys,
-    cf. NSA:524-530); non-causal: |i-j| <= window (NSA:46-56)."""
-    b, hq, n, d = q.shape
+    cf. NSA:524-530); non-causal: |i-j| <= window (NSA:46-56).  ``rows``
+    restricts the computation to those query positions."""
+    b, hq, _, d = q.shape
     hkv = k.shape[1]
     g = hq // hkv
-    pos = torch.arange(n, device=q.device)
-    dist = pos[:, None] - pos[None, :]
+    kpos = torch.arange(k.shape[2], device=q.device)
+    pos = kpos if rows is None else rows
+    if rows is not None:
+        q = q[:, :, rows]
+    n = pos.numel()
+    dist = pos[:, None] - kpos[None, :]
     visible = (dist <= window) & (dist >= (0 if causal else -window))
     sim = torch.einsum('bhgid,bhjd->bhgij', q.reshape(b, hkv, g, n, d), k) * (d ** -0.5)
     sim = sim.masked_fill(~visible, neg_max(sim))
@@ -287,7 +299,9 @@ class OracleSparseAttention(nn.Module):
         self.to_strategy_combine = nn.Sequential(gate, nn.Sigmoid())
         self.combine_heads = nn.Linear(dim_head * heads, dim, bias=False)
 
-    def forward(self, inp, return_intermediates: bool = False):
+    def forward(self, inp, return_intermediates: bool = False, forced_selection=None):
+        """``forced_selection`` = (idx, fmask) replaces the layer's own block selection (the tests use it to compare
+        two precisions of the layer on identical blocks)."""
         b, n, _ = inp.shape
         h, hkv, d = self.heads, self.kv_heads, self.dim_head
         x = self.norm(inp)
@@ -315,6 +329,8 @@ class OracleSparseAttention(nn.Module):
         if num_selected > 0:
             vals, idx = select_blocks(probs, num_selected)
             fmask = vals > 1e-10
+            if forced_selection is not None:
+                idx, fmask = forced_selection
             gates_topk = (vals + (1. - vals).detach()) if self.use_diff_topk else None
             o_sel = selected_attend(qr, kr, v, self.sel, idx, fmask, self.causal, gates=gates_topk)
         else:

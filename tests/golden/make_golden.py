@@ -1,7 +1,8 @@
 """Generate the golden vectors under tests/golden/ from the UNMODIFIED upstream
 library.  Run in a container that has the upstream checkout:
 
-    python tests/golden/make_golden.py /path/to/upstream/checkout
+    python tests/golden/make_golden.py /path/to/upstream/checkout        (all cases)
+    python tests/golden/make_golden.py /path/to/upstream/checkout lm     (the language-model case only)
 
 The three third-party packages upstream imports but this image lacks are
 replaced by the stand-ins in tests/golden/standins/.  Upstream code is imported,
@@ -151,9 +152,40 @@ def run_op_case(name):
     print('op', name, 'out', tuple(out.shape), 'abs mean', out.abs().mean().item())
 
 
+def run_lm_case():
+    """Upstream's Transformer (pure-PyTorch SparseAttention path) on seeded token ids: loss, logits of the loss's
+    inputs, and two norms of every parameter gradient."""
+    import native_sparse_attention_pytorch.transformer as tf_mod
+    c = recipe.LM_CASE
+    torch.manual_seed(0)
+    model = tf_mod.Transformer(
+        num_tokens=c['vocab'], dim=c['dim'], depth=c['depth'], heads=c['heads'], kv_heads=c['kv_heads'],
+        dim_head=c['dim_head'], use_sparse_attn=True, causal=True, use_triton_fine_selection=False,
+        sparse_attn_kwargs=dict(sliding_window_size=c['sliding_window_size'], compress_block_size=c['compress_block_size'],
+                                compress_block_sliding_stride=c['compress_block_sliding_stride'],
+                                selection_block_size=c['selection_block_size'],
+                                num_selected_blocks=c['num_selected_blocks']))
+    recipe.lm_fill_weights(model, seed=9)
+    ids = recipe.lm_ids()
+    loss = model(ids, return_loss=True)
+    loss.backward()
+    with torch.no_grad():
+        logits = model(ids[:, :-1])
+    res = dict(loss=np.array([loss.item()]), logits=np_(logits))
+    for pname, p in model.named_parameters():
+        if p.grad is not None:
+            res['pgrad.' + pname] = np.array([p.grad.abs().sum().item(), p.grad.pow(2).sum().item()])
+    np.savez_compressed(os.path.join(HERE, 'lm_toy.npz'), **res)
+    print('lm loss', loss.item(), 'params with grad', sum(1 for k in res if k.startswith('pgrad.')))
+
+
 if __name__ == '__main__':
     torch.set_num_threads(8)
+    if len(sys.argv) > 2 and sys.argv[2] == 'lm':
+        run_lm_case()
+        sys.exit(0)
     for n in recipe.LAYER_CASES:
         run_layer_case(n)
     for n in recipe.OP_CASES:
         run_op_case(n)
+    run_lm_case()

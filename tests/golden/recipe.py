@@ -98,3 +98,34 @@ def op_inputs(case, seed=23):
     idx = randint(0, c['idx_high'], (b, hkv, n, c['nsel']), seed + 3)
     mask = randint(0, 2, (b, hkv, n, c['nsel']), seed + 4).bool()
     return q, k, v, idx, mask
+
+
+# ---- language-model case: upstream's Transformer around the layer (transformer.py:142-330), toy size ----
+LM_CASE = dict(vocab=256, dim=64, depth=2, heads=4, kv_heads=2, dim_head=16, batch=2, seq=64,
+               sliding_window_size=8, compress_block_size=8, compress_block_sliding_stride=4, selection_block_size=8,
+               num_selected_blocks=2)
+
+
+def lm_ids(seed=17):
+    c = LM_CASE
+    return randint(0, c['vocab'], (c['batch'], c['seq'] + 1), seed)
+
+
+def lm_fill_weights(module, seed):
+    """Overwrite every parameter of a Transformer-shaped module (token embedding, blocks of [SparseAttention,
+    feed-forward], final norm, logits), visiting parameters in sorted-name order; the rule for a parameter depends on
+    the end of its name and its rank only, so upstream's model and a harness with the same names get the same values."""
+    with torch.no_grad():
+        for i, (name, p) in enumerate(sorted(module.named_parameters())):
+            s = seed * 1000 + i
+            leaf = name.split('.')[-1]
+            if leaf in ('compress_mem_kv', 'k_intrablock_positions', 'v_intrablock_positions'):
+                p.copy_(randn(p.shape, s, 0.5))
+            elif p.dim() == 1 and leaf == 'weight':          # RMS norm gains
+                p.copy_(1.0 + randn(p.shape, s, 0.1))
+            elif leaf == 'bias':
+                p.copy_(randn(p.shape, s, 0.5 if 'to_strategy_combine' in name else 0.1))
+            elif name.startswith('token_emb'):
+                p.copy_(randn(p.shape, s, 1.0))
+            else:                                            # linear weights [out, in]
+                p.copy_(randn(p.shape, s, p.shape[-1] ** -0.5))

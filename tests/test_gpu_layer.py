@@ -5,7 +5,7 @@ import torch
 
 import recipe
 from oracle import nsa_oracle as O
-from util import assert_close_bf16, assert_close_f32, load_golden, same_selection
+from util import agreeing_queries, assert_close_bf16, assert_close_f32, load_golden, observe, same_selection
 
 from native_sparse_attention_pytorch_b200 import SparseAttention
 
@@ -70,8 +70,21 @@ def test_layer_bf16_boundary_tensors(name):
     assert_close_bf16(mid['o_cmp'], rmid['o_cmp'], 'compressed branch')
     assert_close_bf16(mid['o_swa'], rmid['o_swa'], 'sliding branch')
     if rmid['idx'] is None:
+        assert mid['idx'] is None
         assert_close_bf16(mid['o_sel'], rmid['o_sel'], 'selected branch')
         assert_close_bf16(out, rout, 'out', tol=4e-2)
+        return
+    # the selection first: identical masks, and the share of queries with identical block sets
+    assert torch.equal(mid['fmask'].sum(-1).cpu(), rmid['fmask'].sum(-1)), 'number of visible blocks per query'
+    same = agreeing_queries(mid['idx'], mid['fmask'], rmid['idx'], rmid['fmask'])          # [B, Hkv, N]
+    observe('selection agreement', share=same.float().mean().item())
+    assert same.float().mean().item() > 0.5
+    # then the selected branch and the output on the queries whose selection agrees
+    heads, kv_heads = c['kw']['heads'], c['kw'].get('kv_heads') or c['kw']['heads']
+    per_head = same.repeat_interleave(heads // kv_heads, dim=1)                          # [B, Hq, N]
+    assert_close_bf16(mid['o_sel'].cpu()[per_head], rmid['o_sel'][per_head], 'selected branch')
+    whole = same.all(dim=1)                                                              # every head group of the token
+    assert_close_bf16(out.cpu()[whole], rout[whole], 'out', tol=4e-2)
 
 
 @pytest.mark.parametrize('seq_len', (2, 8, 16))
@@ -117,3 +130,27 @@ def test_decoding_with_grouped_heads_and_memory_slots():
             one, cache = attn(tokens[:, i:i + 1], cache=cache, return_cache=True)
             steps.append(one)
     assert (parallel - torch.cat(steps, dim=1))[:, 4:].abs().max().item() <= 2e-5
+
+
+def test_language_model_harness_matches_upstream_transformer_on_gpu():
+    """The language-model training step the benchmark times (bench.build_lm around the library's layer), in fp32 at a
+    toy size, against the stored loss, logits and gradient norms of upstream's Transformer (transformer.py:254-330)
+    with the same seeded weights and token ids."""
+    import bench
+    gold = load_golden('lm_toy')
+    model, _ = bench.build_lm(recipe.LM_CASE, DEV, dtype=torch.float32)
+    recipe.lm_fill_weights(model, seed=9)
+    ids = recipe.lm_ids().to(DEV)
+    loss = model(ids)
+    loss.backward()
+    observe('loss', ours=loss.item(), upstream=gold['loss'].item())
+    assert abs(loss.item() - gold['loss'].item()) <= 1e-4 * abs(gold['loss'].item())
+    with torch.no_grad():
+        assert_close_f32(model.logits(ids[:, :-1]), gold['logits'], 'logits')
+    for pname, p in model.named_parameters():
+        g = gold.get('pgrad.' + pname)
+        if g is None:
+            assert p.grad is None or p.grad.abs().sum().item() == 0, pname
+            continue
+        got = torch.tensor([p.grad.abs().sum().item(), p.grad.pow(2).sum().item()], dtype=torch.float64)
+        assert torch.allclose(got, g, rtol=1e-3, atol=1e-6), (pname, got, g)

@@ -6,7 +6,7 @@ import torch
 
 import recipe
 from oracle import nsa_oracle as O
-from util import SUM_REL, assert_close_bf16
+from util import SUM_REL, agreeing_queries, assert_close_bf16, observe
 
 import native_sparse_attention_pytorch_b200 as nsa
 from native_sparse_attention_pytorch_b200 import ops
@@ -46,6 +46,7 @@ CASES = [
     (1, 8, 1, 515, 64, 4),
     (1, 2, 2, 200, 64, 2),
     (1, 16, 1, 260, 128, 2),
+    (1, 8, 1, 330, 128, 3),        # 8 heads per KV head at dim_head 128: the long-context grouping
     (2, 4, 2, 129, 128, 3),
     (1, 4, 2, 64, 64, 1),
     (1, 2, 1, 1, 64, 1),
@@ -245,6 +246,15 @@ def test_sm100_layer_bf16_uses_tensor_core_branches():
     ops.check_device_status()
     assert_close_bf16(mid['o_cmp'], rmid['o_cmp'], 'compressed branch')
     assert_close_bf16(mid['o_swa'], rmid['o_swa'], 'sliding branch')
+    # the selection, then the selected branch and the output on the queries whose selection agrees
+    assert torch.equal(mid['fmask'].sum(-1).cpu(), rmid['fmask'].sum(-1)), 'number of visible blocks per query'
+    same = agreeing_queries(mid['idx'], mid['fmask'], rmid['idx'], rmid['fmask'])          # [B, Hkv, N]
+    observe('selection agreement', share=same.float().mean().item())
+    assert same.float().mean().item() > 0.5
+    per_head = same.repeat_interleave(kw['heads'] // kw['kv_heads'], dim=1)
+    assert_close_bf16(mid['o_sel'].cpu()[per_head], rmid['o_sel'][per_head], 'selected branch')
+    whole = same.all(dim=1)
+    assert_close_bf16(out.cpu()[whole], rout[whole], 'out', tol=4e-2)
 
 
 def test_full_benchmark_size_properties():
@@ -265,9 +275,12 @@ def test_full_benchmark_size_properties():
     g = w['q_heads'] // w['kv_heads']
     rows = torch.tensor([0, 1, 63, 64, 65, 127, 128, 1000, 4095, 4096, 8000, 8190, 8191])
     hs = slice(2 * g, 3 * g)
-    ref = O.selected_attend(q[1:2, hs].float(), k[1:2, 2:3].float(), v[1:2, 2:3].float(), w['block'], idx[1:2, 2:3],
+    qs = q[1:2, hs].float().requires_grad_()
+    ref = O.selected_attend(qs, k[1:2, 2:3].float(), v[1:2, 2:3].float(), w['block'], idx[1:2, 2:3],
                             mask[1:2, 2:3], True, rows=rows)
     assert_close_bf16(out[1:2, hs][:, :, rows.to(DEV)], ref, 'sampled output rows')
+    (ref * do[1:2, hs][:, :, rows].float()).sum().backward()      # a query's dq depends on its own row only
+    assert_close_bf16(dq[1:2, hs][:, :, rows.to(DEV)], qs.grad[:, :, rows], 'dq of the sampled rows')
     b, hkv, n, d = k.shape
     do_sum = do.float().view(b, hkv, g, n, d).sum(dim=(2, 3)).to(DEV)            # [B, Hkv, d]
     dv_sum = dv.float().sum(dim=2)
@@ -386,3 +399,44 @@ def test_sliding_and_compressed_backward_reuse_a_per_shape_index():
     assert torch.equal(first[0], second[0])                         # dq: ordered merge
     for a, r in zip(first[1:], second[1:]):                         # fp32 atomics in any order, then one rounding
         assert (a.float() - r.float()).abs().max().item() <= (1e-5 + 2.0 ** -8) * max(1.0, r.float().abs().max().item())
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_the_context_stays_usable():
+    """The library's self-test block waits, with a limit of about a millisecond, on a barrier nobody arrives on: it
+    must return by itself, free its tensor memory and report status 1 -- the path every tensor-core kernel takes when
+    a hand-over is lost.  Afterwards the same context runs a tensor-core kernel normally."""
+    import ctypes as C
+    from native_sparse_attention_pytorch_b200 import _lib as L
+    lib = L.load()
+    status = torch.full((1,), -1, dtype=torch.int32, device=DEV)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    L.check(lib.nsa_selftest_bounded_wait(status.data_ptr(), 2_000_000, stream))
+    torch.cuda.synchronize()
+    assert status.item() == 1
+    assert lib.nsa_selftest_bounded_wait(status.data_ptr(), 0, stream) == -2          # the limit must be positive
+    # the status travels through the module's accumulator like a real kernel's would, and surfaces at the next poll
+    ws = torch.zeros(256, dtype=torch.uint8, device=DEV)
+    ws[:4].view(torch.int32).copy_(status)
+    ops.check_device_status()                               # clean so far
+    ops._keep_status(ws)
+    with pytest.raises(RuntimeError, match='bounded wait'):
+        ops.check_device_status()
+    ops._keep_status(ws)
+    ops.poll_device_status(DEV)                             # starts the copy
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match='bounded wait'):
+        ops.poll_device_status(DEV)                         # sees it, one call late, without synchronising
+    ops.check_device_status()                               # and the accumulator is clean again
+    q, k, v, idx, mask, up = make_case(1, 8, 2, 300, 64, 3, seed=3)
+    run_gpu(q, k, v, idx, mask, up, 'sm100')                # tensor memory is free again: a real kernel runs
+
+
+def test_launch_counter_counts_the_kernels_of_a_step():
+    import ctypes as C
+    from native_sparse_attention_pytorch_b200 import _lib as L
+    lib = L.load()
+    q, k, v, idx, mask, up = make_case(1, 8, 2, 300, 64, 3, seed=3)
+    before = lib.nsa_launch_count()
+    run_gpu(q, k, v, idx, mask, up, 'sm100')
+    # forward: index pre-pass (4) + forward + merge; backward on the forward's index: delta + backward + dQ merge
+    assert lib.nsa_launch_count() - before == 9

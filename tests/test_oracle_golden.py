@@ -87,3 +87,29 @@ def test_rows_subset_is_consistent():
     rows = torch.tensor([0, 5, 16, 31, 106])
     part = O.selected_attend(q, k, v, 16, idx, mask, causal=True, rows=rows)
     close(part, full[:, :, rows], 1e-6)
+
+
+def test_language_model_harness_matches_upstream_transformer():
+    """The benchmark's language-model harness (bench.build_lm), built around the oracle's layer, against the stored
+    results of upstream's Transformer on the same seeded weights and token ids: loss, logits, gradient norms."""
+    import bench
+    gold = load('lm_toy')
+    model, _ = bench.build_lm(recipe.LM_CASE, 'cpu', dtype=torch.float32,
+                              attn_cls=lambda **kw: O.OracleSparseAttention(**kw))
+    recipe.lm_fill_weights(model, seed=9)
+    ids = recipe.lm_ids()
+    loss = model(ids)
+    loss.backward()
+    assert abs(loss.item() - gold['loss'].item()) <= 1e-5 * abs(gold['loss'].item())
+    with torch.no_grad():
+        close(model.logits(ids[:, :-1]), gold['logits'], 2e-5)
+    seen = 0
+    for pname, p in model.named_parameters():
+        g = gold.get('pgrad.' + pname)
+        if g is None:
+            assert p.grad is None or p.grad.abs().sum().item() == 0, pname
+            continue
+        got = torch.tensor([p.grad.abs().sum().item(), p.grad.pow(2).sum().item()], dtype=torch.float64)
+        assert torch.allclose(got, g, rtol=1e-3, atol=1e-7), (pname, got, g)
+        seen += 1
+    assert seen == sum(1 for k in gold if k.startswith('pgrad.'))

@@ -10,6 +10,7 @@ import pytest
 import torch
 
 import recipe
+from oracle import nsa_oracle as O
 from util import assert_close_bf16
 
 from native_sparse_attention_pytorch_b200 import _lib as L
@@ -51,16 +52,28 @@ def run_both(lib, seed, **kw):
     assert 0 < need <= lib.nsa_sel_static_scratch_bytes()
     ws = torch.empty(need, dtype=torch.uint8, device=DEV)
     L.check(lib.nsa_sel_fwd(C.byref(args_for(q, k, v, idx, mask, ref_out, ref_lse, ws)), stream))
-    L.check(lib.nsa_sel_fwd_static(C.byref(args_for(q, k, v, idx, mask, new_out, new_lse)), stream))
+    status = torch.full((1,), -1, dtype=torch.int32).pin_memory()
     torch.cuda.synchronize()
+    free_before, held_before = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
+    L.check(lib.nsa_sel_fwd_static(C.byref(args_for(q, k, v, idx, mask, new_out, new_lse)), stream))
+    L.check(lib.nsa_sel_static_status(status.data_ptr(), stream))
+    torch.cuda.synchronize()
+    # the call took no device memory: neither from the driver nor from PyTorch's pool
+    assert torch.cuda.mem_get_info()[0] >= free_before and torch.cuda.memory_allocated() == held_before
+    assert status.item() == 0, 'a kernel of the static forward gave up on a wait'
     assert_close_bf16(new_out, ref_out, 'out', roundings=2)
     assert_close_bf16(new_lse, ref_lse, 'lse')
+    return q, k, v, idx, mask, new_out
 
 
 def test_static_scratch_forward_matches_the_regular_entry_point_twice_in_a_row():
     lib = L.load()
-    run_both(lib, seed=41)
+    run_both(lib, seed=41)                                 # the first call on the device also looks the area up
     run_both(lib, seed=97, n=333, hq=4, hkv=1, nsel=2)     # a different, smaller problem over the same area
+    # dim_head 128, and the result against the CPU oracle as well
+    q, k, v, idx, mask, out = run_both(lib, seed=7, n=400, hq=8, hkv=1, d=128, nsel=3)
+    ref = O.selected_attend(q.float().cpu(), k.float().cpu(), v.float().cpu(), BLOCK, idx.cpu(), mask.bool().cpu(), True)
+    assert_close_bf16(out, ref, 'out vs oracle')
 
 
 def test_static_scratch_forward_rejects_what_does_not_fit():

@@ -17,6 +17,21 @@ BF16_ABS = 2e-2     # bf16: |a-b| <= BF16_ABS + 2^-8 |b| elementwise; the second
 SUM_REL = {'dk': 2e-3, 'dv': 2e-3, 'dscale': 5e-3}
 
 
+# Every comparison leaves the error it observed here; conftest.py writes the table to the file named by the
+# environment variable NSA_PARITY_REPORT at the end of the session (and pytest -rA shows nothing of it otherwise).
+OBSERVED = {}
+
+
+def _current_test():
+    return os.environ.get('PYTEST_CURRENT_TEST', '?').split(' ')[0]
+
+
+def observe(what, **numbers):
+    """Record named numbers (errors, agreement rates) of the running test."""
+    OBSERVED.setdefault(_current_test(), {}).setdefault(what or 'value', {}).update(
+        {k: (float(v) if v is not None else None) for k, v in numbers.items()})
+
+
 def load_golden(name):
     z = np.load(os.path.join(GOLDEN, name + '.npz'))
     return {k: torch.from_numpy(z[k]) for k in z.files}
@@ -29,6 +44,7 @@ def assert_close_f32(got, ref, what='', tol=F32_REL):
         return
     err = (got - ref).abs().max().item()
     bound = tol * max(1.0, ref.abs().max().item())
+    observe(what, max_abs_err=err, bound=bound, max_abs_ref=ref.abs().max().item())
     assert err <= bound, f'{what}: max abs err {err:.3e} > {bound:.3e}'
 
 
@@ -40,7 +56,30 @@ def assert_close_bf16(got, ref, what='', tol=BF16_ABS, roundings=1, rel_to_max=0
     # `roundings`: how many of the two tensors were themselves rounded to bf16 (each adds half a spacing)
     # `rel_to_max`: extra allowance as a fraction of max |ref|, for sums whose size grows with the problem
     excess = ((got - ref).abs() - roundings * ref.abs() * 2.0 ** -8).max().item() - rel_to_max * ref.abs().max().item()
+    observe(what, max_abs_err=(got - ref).abs().max().item(), beyond_spacing=excess, tol=tol,
+            max_abs_ref=ref.abs().max().item(), rel_to_max=rel_to_max)
     assert excess <= tol, f'{what}: max abs err beyond bf16 spacing {excess:.3e} > {tol:.1e}'
+
+
+def selection_agreement(idx_a, mask_a, idx_b, mask_b):
+    """Fraction of queries (rows of the last axis) whose masks and sets of visible block indices are identical."""
+    ia, ib, ma, mb = idx_a.cpu(), idx_b.cpu(), mask_a.cpu().bool(), mask_b.cpu().bool()
+    if ia.numel() == 0:
+        return 1.0
+    big = int(max(ia.max().item(), ib.max().item())) + 1
+    a = torch.where(ma, ia, torch.full_like(ia, big)).sort(dim=-1).values
+    b = torch.where(mb, ib, torch.full_like(ib, big)).sort(dim=-1).values
+    same = (a == b).all(dim=-1) & (ma.sum(dim=-1) == mb.sum(dim=-1))
+    return same.float().mean().item()
+
+
+def agreeing_queries(idx_a, mask_a, idx_b, mask_b):
+    """[..., N] bool: the two selections name the same set of visible blocks for the query."""
+    ia, ib, ma, mb = idx_a.cpu(), idx_b.cpu(), mask_a.cpu().bool(), mask_b.cpu().bool()
+    big = int(max(ia.max().item(), ib.max().item())) + 1
+    a = torch.where(ma, ia, torch.full_like(ia, big)).sort(dim=-1).values
+    b = torch.where(mb, ib, torch.full_like(ib, big)).sort(dim=-1).values
+    return (a == b).all(dim=-1)
 
 
 def same_selection(idx_a, mask_a, idx_b, mask_b):
@@ -53,3 +92,19 @@ def same_selection(idx_a, mask_a, idx_b, mask_b):
     a = torch.where(mask_a.cpu(), idx_a.cpu(), torch.full_like(idx_a.cpu(), big)).sort(dim=-1).values
     b = torch.where(mask_b.cpu(), idx_b.cpu(), torch.full_like(idx_b.cpu(), big)).sort(dim=-1).values
     return torch.equal(a, b)
+
+
+class Checks:
+    """Runs several comparisons to the end and fails once, with every message, so that one run shows all errors."""
+
+    def __init__(self):
+        self.failures = []
+
+    def __call__(self, fn, *args, **kw):
+        try:
+            fn(*args, **kw)
+        except AssertionError as e:
+            self.failures.append(str(e))
+
+    def done(self):
+        assert not self.failures, '; '.join(self.failures)
