@@ -373,8 +373,35 @@ __device__ __forceinline__ void store_rows_coalesced(uint32_t stage, uint32_t st
 
 // ---- forward -------------------------------------------------------------------------
 
-template <int D, bool IMP, bool LO>   // IMP: also write the compressed branch's importance; LO: rows may have a first visible column > 0
-__global__ void __launch_bounds__(kRows, D == 64 ? 4 : 2)
+// Forward of the selected-block branch.  A CTA of 256 threads walks gather -> S -> softmax -> P V -> store chunk by
+// chunk; several CTAs share an SM (4 at dim_head 64) and fill each other's waits.  Two threads share a row (32 of the
+// block's 64 columns each; they exchange maximum and sum through shared memory), which halves the serial work per
+// thread and, above all, doubles the number of warps that issue the gather: a warp gets only about 1.3 bytes per
+// clock of scattered 128-byte rows out of the L2 however many copies it has in flight (measured: 5.5 B/clk per SM
+// with 4 warps copying, 17 with 16, 26 with 32), and the gather of the Q rows is what bounds this kernel.
+template <int D>
+__device__ __forceinline__ void gather_tile_async2(uint32_t tile, const __nv_bfloat16* base, int64_t stride_h,
+                                                   int64_t stride_n, const uint32_t* entries, int g_shift, int h,
+                                                   int tid) {
+  constexpr int CH = D / 8;               // 16-byte pieces per row
+  constexpr int RPP = 2 * kRows / CH;     // rows covered by one pass of the 256 threads
+  const int sub = tid % CH, r0 = tid / CH;
+  uint32_t ev[kRows / RPP];
+#pragma unroll
+  for (int it = 0; it < kRows / RPP; ++it) ev[it] = __ldg(entries + ((r0 + it * RPP) >> g_shift));
+#pragma unroll
+  for (int it = 0; it < kRows / RPP; ++it) {
+    const int row = r0 + it * RPP;
+    const int g = row & ((1 << g_shift) - 1);
+    const bool valid = ev[it] != kInvalidEntry;
+    const int64_t i = valid ? (int64_t)(ev[it] & 0xffffffu) : 0;
+    cp_async16(tile + (sub / 8) * (kRows * 128) + sw128_offset(row, sub % 8),
+               base + (int64_t)((h << g_shift) + g) * stride_h + i * stride_n + sub * 8, valid ? 16u : 0u);
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(2 * kRows, D == 64 ? 4 : 2)
 sel_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const SelParams P) {
   constexpr int NC = D / 64;
   extern __shared__ uint8_t smem_raw[];
@@ -382,16 +409,16 @@ sel_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   __shared__ uint32_t tmem_slot;
   __shared__ __align__(8) uint64_t bars[3];
   __shared__ int row_dst[kRows];
+  __shared__ float xmax[2][kRows], xsum[2][kRows];
   const int nitems = item_count(P);
   if ((int)blockIdx.x >= nitems) return;
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t sQ = base, sK = sQ + NC * 16384, sV = sK + NC * 8192, sP = sV + NC * 8192;
-  // the P tile doubles as the staging area of the partial-output rows (one padded row per thread)
-  constexpr uint32_t kStageStride = D * 2 + 16;
-  const uint32_t sStage = sP;
+  const uint32_t sQ = base, sK = sQ + NC * 16384, sV = sK + NC * 8192, sStage = sV + NC * 8192;
+  constexpr uint32_t kStageStride = D * 2 + 16;   // one padded partial-output row per row of the chunk
   const uint32_t bar_kv = smem_u32(&bars[0]), bar_s = smem_u32(&bars[1]), bar_o = smem_u32(&bars[2]);
   const int tid = threadIdx.x, warp = tid >> 5;
+  const int half = tid >> 7, row = tid & (kRows - 1);   // this thread: columns 32*half .. 32*half+31 of row `row`
   constexpr uint32_t kCols = D == 64 ? 128 : 256;
 
   if (tid == 0) {
@@ -412,11 +439,11 @@ sel_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tm = tmem_slot;
-  const uint32_t tm_lane = tm + ((uint32_t)(warp * 32) << 16);
+  const uint32_t tm_lane = tm + ((uint32_t)((warp & 3) * 32) << 16);   // warps w and w + 4 share a lane quarter
   const uint32_t tS = 0, tO = 64;
 
   const int G = P.G, QT = kRows / G, g_shift = 31 - __clz(G);
-  const int q_local = tid / G, g = tid - q_local * G;
+  const int q_local = row >> g_shift, g = row - (q_local << g_shift);
   uint32_t ph_kv = 0, ph_s = 0, ph_o = 0;
   constexpr uint32_t idS = instr_desc_bf16(128, 64, false, false);
   constexpr uint32_t idO = instr_desc_bf16(128, D, false, true);
@@ -436,9 +463,7 @@ sel_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     for (int c = 0; c < item.z; ++c) {
       const uint32_t* chunk_entries = P.entries + item.w + c * QT;
       const uint32_t e = chunk_entries[q_local];
-      const RowInfo r = decode_row(e, j, P.rule);
-      const int64_t hq = (int64_t)h * G + g;
-      if (!prefetched) gather_tile_async<D>(sQ, P.q + b * P.q_sb, P.q_sh, P.q_sn, chunk_entries, g_shift, h, tid);
+      if (!prefetched) gather_tile_async2<D>(sQ, P.q + b * P.q_sb, P.q_sh, P.q_sn, chunk_entries, g_shift, h, tid);
       cp_async_commit();
       cp_async_wait<0>();
       fence_proxy_async_smem();
@@ -465,71 +490,45 @@ sel_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       // softmax, second MMA and output run
       prefetched = c + 1 < item.z;
       if (prefetched)
-        gather_tile_async<D>(sQ, P.q + b * P.q_sb, P.q_sh, P.q_sn, chunk_entries + QT, g_shift, h, tid);
+        gather_tile_async2<D>(sQ, P.q + b * P.q_sb, P.q_sh, P.q_sn, chunk_entries + QT, g_shift, h, tid);
       __syncwarp();
-      float s[64];
-      {
-        float t[32];
-        tmem_ld32(tm_lane + tS, t);
-        tmem_ld_wait();
+      const RowInfo r = decode_row(e, j, P.rule);
+      const int lim = r.lim - half * 32;   // last visible column of this thread's half (negative: none)
+      float s[32];
+      tmem_ld32(tm_lane + tS + half * 32, s);
+      tmem_ld_wait();
+      const bool all_full = __all_sync(kFullMask, lim >= 31);
+      float mm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (all_full) {
 #pragma unroll
-        for (int x = 0; x < 32; ++x) s[x] = t[x];
-        tmem_ld32(tm_lane + tS + 32, t);
-        tmem_ld_wait();
+        for (int x = 0; x < 32; ++x) mm[x & 3] = fmaxf(mm[x & 3], s[x]);
+      } else {
 #pragma unroll
-        for (int x = 0; x < 32; ++x) s[32 + x] = t[x];
+        for (int x = 0; x < 32; ++x) mm[x & 3] = x <= lim ? fmaxf(mm[x & 3], s[x]) : mm[x & 3];
       }
-      if constexpr (IMP) {
-        // Compressed branch: the scaled logit of every visible block column, averaged over the G heads of the query
-        // (G neighbouring lanes), as the tensor of that dtype would hold it upstream: product, scaled logit and mean
-        // each rounded to bf16.  The G lanes reduce-scatter: every step a lane hands half of its columns to its
-        // partner and keeps the other half, so that it ends with 64/G fully summed columns, which it stores.
-        float v[64];
-#pragma unroll
-        for (int x = 0; x < 64; ++x) v[x] = round_bf16(round_bf16(s[x]) * P.scale);
-        int first = 0;   // first block column this lane ends up owning
-#pragma unroll
-        for (int step = 0; step < 4; ++step) {
-          const int width = 32 >> step;          // columns kept after this step
-          if ((1 << step) < G) {
-            const bool upper = (g >> step) & 1;  // this lane keeps the upper half
-#pragma unroll
-            for (int x = 0; x < 32; ++x) {
-              if (x < width) {
-                const float give = upper ? v[x] : v[x + width];
-                const float keep = upper ? v[x + width] : v[x];
-                v[x] = keep + __shfl_xor_sync(kFullMask, give, 1 << step);
-              }
-            }
-            first += upper ? width : 0;
-          }
-        }
-        const int owned = kBlock / G;
-        float* imp_row = P.importance + (((int64_t)b * P.Hkv + h) * P.N + r.i) * P.ncb;
-        const float inv_g = 1.f / (float)G;
-#pragma unroll
-        for (int x = 0; x < 64; ++x) {
-          if (x < owned) {
-            const int col_in_block = first + x;
-            const int col = j * kBlock + col_in_block - P.rule.num_mem;
-            if (r.valid && col_in_block <= r.lim && col >= 0 && col < P.ncb) imp_row[col] = round_bf16(v[x] * inv_g);
-          }
-        }
-      }
-      float m = -INFINITY;
-#pragma unroll
-      for (int x = 0; x < 64; ++x) m = ((!LO || x >= r.lo) && x <= r.lim) ? fmaxf(m, s[x]) : m;
+      float m = fmaxf(fmaxf(mm[0], mm[1]), fmaxf(mm[2], mm[3]));
+      xmax[half][row] = m;
+      __syncthreads();
+      m = fmaxf(m, xmax[half ^ 1][row]);
       const float m2 = r.valid ? m * P.scale_log2 : 0.f;
-      float l = 0.f;
+      float ll[4] = {0.f, 0.f, 0.f, 0.f};
+      if (all_full) {
 #pragma unroll
-      for (int x = 0; x < 64; ++x) {
-        const float p = ((!LO || x >= r.lo) && x <= r.lim) ? ex2(s[x] * P.scale_log2 - m2) : 0.f;
-        s[x] = p;
-        l += p;   // the fp32 sum: the log-sum-exp stays exact although P is rounded to bf16 for the MMA
+        for (int x = 0; x < 32; ++x) {
+          s[x] = ex2(fmaf(s[x], P.scale_log2, -m2));
+          ll[x & 3] += s[x];   // the fp32 sum: the log-sum-exp stays exact although P is rounded to bf16 for the MMA
+        }
+      } else {
+#pragma unroll
+        for (int x = 0; x < 32; ++x) {
+          s[x] = x <= lim ? ex2(fmaf(s[x], P.scale_log2, -m2)) : 0.f;
+          ll[x & 3] += s[x];
+        }
       }
-      // P goes to the tensor cores through tensor memory, over the first half of this row's S columns (which the
-      // thread has read): no shared-memory tile, no proxy fence
-      tmem_st_bf16_row64(tm_lane + tS, s);
+      xsum[half][row] = (ll[0] + ll[1]) + (ll[2] + ll[3]);
+      // P goes to the tensor cores through tensor memory, over the first half of this row's S columns (both threads
+      // of the row have read their S columns: the exchange of the maxima lies in between)
+      tmem_st_bf16_row32(tm_lane + tS + half * 16, s);
       tmem_st_wait();
       tc_fence_before_sync();
       __syncthreads();
@@ -540,18 +539,20 @@ sel_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
           mma_bf16_tmem_a_elect(tm + tO, tm + tS + k * 8, smem_desc_sw128(sV + k * 2048, 8192), idO, k > 0);
         mma_commit_elect(bar_o);
       }
+      const float l = xsum[0][row] + xsum[1][row];
+      const int64_t hq = (int64_t)h * G + g;
+      const int64_t row_global = ((int64_t)b * P.Hq + hq) * P.N + r.i;
+      const int64_t pslot = r.valid ? row_global * P.ns + r.slot : 0;
       __syncwarp();
       mbar_wait_warp(bar_o, ph_o, &abort_flag);
       ph_o ^= 1;
       tc_fence_after_sync();
       __syncwarp();
-      const int64_t row_global = ((int64_t)b * P.Hq + hq) * P.N + r.i;
-      const int64_t pslot = r.valid ? row_global * P.ns + r.slot : 0;
       // the partial row stays unnormalised (sum of p * v, at most 64 max|v|): the merge divides once per row
 #pragma unroll
-      for (int c2 = 0; c2 < D / 32; ++c2) {
+      for (int c2 = 0; c2 < D / 64; ++c2) {
         float t[32];
-        tmem_ld32(tm_lane + tO + c2 * 32, t);
+        tmem_ld32(tm_lane + tO + half * (D / 2) + c2 * 32, t);
         tmem_ld_wait();
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
@@ -560,14 +561,25 @@ sel_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
           v.y = pack_bf16(t[x * 8 + 2], t[x * 8 + 3]);
           v.z = pack_bf16(t[x * 8 + 4], t[x * 8 + 5]);
           v.w = pack_bf16(t[x * 8 + 6], t[x * 8 + 7]);
-          sts_v4(sStage + tid * kStageStride + c2 * 64 + x * 16, v);
+          sts_v4(sStage + row * kStageStride + half * D + c2 * 64 + x * 16, v);
         }
       }
-      row_dst[tid] = r.valid ? (int)pslot : -1;
-      __syncthreads();
-      store_rows_coalesced<D * 2>(sStage, kStageStride, row_dst, reinterpret_cast<uint8_t*>(P.partial), tid);
-      if (r.valid) P.stats[pslot] = make_float2(m2, l);
+      if (half == 0) row_dst[row] = r.valid ? (int)pslot : -1;
       tc_fence_before_sync();
+      __syncthreads();
+      {   // whole 128-byte lines per store instruction: D/8 neighbouring threads share a row
+        constexpr int TPR = D / 8, RPP = 2 * kRows / TPR;
+        const int sub = tid % TPR, r0 = tid / TPR;
+        uint8_t* const pbase = reinterpret_cast<uint8_t*>(P.partial);
+#pragma unroll
+        for (int k = 0; k < kRows / RPP; ++k) {
+          const int rr = r0 + k * RPP;
+          const int dst = row_dst[rr];
+          const uint4 v = lds_v4(sStage + rr * kStageStride + sub * 16);
+          if (dst >= 0) *reinterpret_cast<uint4*>(pbase + (int64_t)dst * (D * 2) + sub * 16) = v;
+        }
+      }
+      if (half == 0 && r.valid) P.stats[pslot] = make_float2(m2, l);
     }
     ph_kv ^= 1;
     __syncthreads();   // every thread is done with this item's tiles before the next TMA overwrites them
@@ -1955,8 +1967,8 @@ static int run_fwd(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaStrea
   constexpr int NC = D / 64;
   const int smem = 1024 + NC * (16384 + 8192 + 8192) + kRows * (D * 2 + 16);
   const int per_sm = D == 64 ? 4 : 2;
-  CUDA_TRY(cudaFuncSetAttribute(sel_fwd_kernel<D, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  sel_fwd_kernel<D, false, false><<<num_sms() * per_sm, kRows, smem, st>>>(tmK, tmV, P);
+  CUDA_TRY(cudaFuncSetAttribute(sel_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  sel_fwd_kernel<D><<<num_sms() * per_sm, 2 * kRows, smem, st>>>(tmK, tmV, P);
   const int64_t threads = (int64_t)a.B * a.Hq * a.N * (D / 8);
   const unsigned mblocks = (unsigned)((threads + 255) / 256);
   sel_merge_kernel<D><<<mblocks, 256, 0, st>>>(P);

@@ -16,7 +16,8 @@ import torch
 
 import recipe
 from oracle import nsa_oracle as O
-from util import SUM_REL, Checks, assert_close_bf16, observe, selection_agreement
+from util import (SUM_REL, Checks, assert_bf16_no_worse_than_reference, assert_close_bf16, observe,
+                  selection_agreement)
 
 import native_sparse_attention_pytorch_b200 as nsa
 from native_sparse_attention_pytorch_b200 import SparseAttention, ops
@@ -169,16 +170,21 @@ def test_layer_bf16_with_the_oracles_selection_forced():
     ops.check_device_status()
     x16 = x.clone().requires_grad_()
     out16, mid16 = ref16(x16, return_intermediates=True, forced_selection=forced)
+    for key in boundary:
+        mid16[key].retain_grad()
     (out16 * up).sum().backward()
 
+    # The kernels see bf16 q, k, v, gates where the fp32 oracle sees unrounded ones, so every tensor is held to the
+    # bf16 contract against the fp32 oracle or, failing that, to the error of the oracle's own bf16 run (same weights,
+    # same blocks).
     check = Checks()
     for key in ('o_cmp', 'o_swa', 'o_sel', 'merged'):
-        check(assert_close_bf16, mid[key], rmid[key], key)
-    check(assert_close_bf16, out, rout, 'out')
+        check(assert_bf16_no_worse_than_reference, mid[key], rmid[key], mid16[key], key)
+    check(assert_bf16_no_worse_than_reference, out, rout, out16, 'out')
     for key in boundary:
-        check(assert_close_bf16, mid[key].grad, rmid[key].grad, 'd ' + key,
+        check(assert_bf16_no_worse_than_reference, mid[key].grad, rmid[key].grad, mid16[key].grad, 'd ' + key,
               rel_to_max=SUM_REL['dk'] if key in ('k', 'v', 'ck', 'cv') else 0.0)
-    check(assert_close_bf16, xg.grad, xr.grad, 'd inp')
+    check(assert_bf16_no_worse_than_reference, xg.grad, xr.grad, x16.grad, 'd inp')
     ours, theirs = dict(attn.named_parameters()), dict(ref16.named_parameters())
 
     def param_grad(name, truth):
@@ -253,9 +259,14 @@ def test_full_layer_shape_sampled_rows():
     for dtype, label in ((torch.float32, 'fp32'), (torch.bfloat16, 'bf16')):
         c = csim if dtype == torch.float32 else O.compressed_attend(q.bfloat16(), ck.bfloat16(), cv.bfloat16(), mem[0].bfloat16(),
                                                                     mem[1].bfloat16(), st, True, rows=rows)[1]
-        rv, ri = O.select_blocks(O.importance_scores(c, 1, 1, st, blk, True, rows=rows), 16)
+        probs = O.importance_scores(c, 1, 1, st, blk, True, rows=rows)
+        rv, ri = O.select_blocks(probs, 16)
+        # identical block sets, and -- probabilities tie often with fresh weights -- picks that are a top-16 of the
+        # oracle's probabilities (the same multiset of values) whichever of the tied blocks were taken
+        mine = probs.gather(-1, idx).float().sort(dim=-1).values
         observe('selection agreement on the sampled rows, oracle in ' + label,
-                share=selection_agreement(idx, fmask, ri, rv > 1e-10))
+                share=selection_agreement(idx, fmask, ri, rv > 1e-10),
+                share_valid_top16=(mine == rv.float().sort(dim=-1).values).all(dim=-1).float().mean().item())
         assert torch.equal(fmask.sum(-1), (rv > 1e-10).sum(-1)), 'number of visible blocks per query'
     o_sel = _selected_rows(qr, kr, v, blk, idx, fmask, rows)
     assert_close_bf16(got('o_sel'), o_sel, 'selected branch')

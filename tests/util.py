@@ -73,6 +73,25 @@ def selection_agreement(idx_a, mask_a, idx_b, mask_b):
     return same.float().mean().item()
 
 
+def assert_bf16_no_worse_than_reference(got, truth, ref16, what='', tol=BF16_ABS, factor=1.5, rel_to_max=0.0):
+    """The bf16 contract against the fp32 truth, or -- for tensors whose inputs were themselves rounded on the way
+    (a whole layer: the branches see bf16 q, k, v where the fp32 run sees unrounded ones) -- an error against the
+    truth of at most `factor` times the error of the reference's own bf16 run (`ref16`, same weights, same selected
+    blocks) plus one bf16 spacing.  Both errors are recorded."""
+    got, truth, ref16 = (t.detach().float().cpu() for t in (got, truth, ref16))
+    assert got.shape == truth.shape == ref16.shape, (what, got.shape, truth.shape, ref16.shape)
+    if truth.numel() == 0:
+        return
+    top = truth.abs().max().item()
+    e_ours = (got - truth).abs().max().item()
+    e_ref = (ref16 - truth).abs().max().item()
+    beyond = ((got - truth).abs() - truth.abs() * 2.0 ** -8).max().item() - rel_to_max * top
+    observe(what, max_abs_err=e_ours, reference_bf16_max_abs_err=e_ref, beyond_spacing=beyond, tol=tol, max_abs_ref=top)
+    assert beyond <= tol or e_ours <= factor * e_ref + 2.0 ** -8 * top, \
+        f'{what}: max abs err {e_ours:.3e} (beyond bf16 spacing {beyond:.3e} > {tol:.1e}) and above {factor} x the ' \
+        f'reference bf16 run\'s own error {e_ref:.3e}'
+
+
 def agreeing_queries(idx_a, mask_a, idx_b, mask_b):
     """[..., N] bool: the two selections name the same set of visible blocks for the query."""
     ia, ib, ma, mb = idx_a.cpu(), idx_b.cpu(), mask_a.cpu().bool(), mask_b.cpu().bool()
