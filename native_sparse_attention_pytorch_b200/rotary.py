@@ -11,9 +11,19 @@ from torch import nn
 from torch.autograd import Function
 
 
-def _tables(inv_freq, n, offset, device):
+_INV_FREQ = {}
+
+
+def _tables(dim, theta, n, offset, device):
+    """cos / sin of the angles [n, dim/2], always in fp32: the inverse frequencies are rebuilt here instead of being
+    kept as a module buffer, which `module.bfloat16()` would round to 8 bits and so turn positions past a few hundred
+    into wrong angles."""
+    key = (dim, theta, str(device))
+    inv_freq = _INV_FREQ.get(key)
+    if inv_freq is None:   # computed on the host (as upstream's package does at construction), kept per device
+        inv_freq = _INV_FREQ[key] = (theta ** (-torch.arange(0, dim, 2).float() / dim)).to(device)
     pos = torch.arange(n, device=device, dtype=torch.float32) + offset
-    ang = pos[:, None] * inv_freq.to(device)[None, :]
+    ang = pos[:, None] * inv_freq[None, :]
     return ang.cos().contiguous(), ang.sin().contiguous()
 
 
@@ -55,11 +65,11 @@ def _launch(x, cos, sin, inverse, order=None):
 class RotaryEmbedding(nn.Module):
     def __init__(self, dim, theta=10000.0):
         super().__init__()
-        self.register_buffer('inv_freq', theta ** (-torch.arange(0, dim, 2).float() / dim), persistent=False)
+        self.dim, self.theta = dim, theta
 
     def rotate_queries_or_keys(self, t, offset=0):
         n = t.shape[-2]
-        cos, sin = _tables(self.inv_freq, n, offset, t.device)
+        cos, sin = _tables(self.dim, self.theta, n, offset, t.device)
         if t.is_cuda and t.dim() == 4 and t.dtype in (torch.float32, torch.bfloat16) and \
                 t.shape[-1] % (16 // t.element_size()) == 0:
             return _Rotate.apply(t, cos, sin)
