@@ -13,8 +13,14 @@ operator shards over batch and KV-head groups with no exchange), so scaling is
 weak and the only collective is the timing reduction.
 
 The printed JSON line also carries:
-  roofline     achieved tensor throughput of the dominant kernel (the backward)
-               from the algorithmic FLOP count of the selected keys
+  roofline     achieved tensor throughput of the whole step (forward+backward)
+               from the algorithmic FLOP count of the selected keys; `kernels`
+               below it lists every kernel of the step with its own time
+               (CUPTI, a separate untimed pass), work and fraction
+  workloads    the full-layer step and the long-context prefill (sharded over
+               the ranks by KV-head group, output gathered: strong scaling)
+               measured by the same file in child processes, so that one
+               record holds all three
   e2e          the same metric through the public operator with pinned HOST
                buffers, host<->device copies inside the timed region
   cpu_baseline the CPU oracle (a port of upstream's PyTorch formulation) timed
@@ -72,13 +78,13 @@ PREFILL_WORKLOADS = {
 }
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the main backward kernel, from an ncu capture of this
-# command (profiles/tcgen05_selected_attention_b4_n8192_h32kv4_d64.md, profiles/simt_selected_attention_...md).
-NCU_TRAFFIC = {
-    (DEFAULT_WORKLOAD, 'auto'): 703.7e6 + 2202.2e6,
-    (DEFAULT_WORKLOAD, 'sm100'): 703.7e6 + 2202.2e6,
-    (DEFAULT_WORKLOAD, 'simt'): 531.8e6 + 300.4e6,
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, from single-launch ncu captures of this command
+# (`ncu --set full -k regex:<kernel> -c 1 python bench.py --steps 2 --warmup 3 --no-cpu-baseline`) at this build.
+NCU_DRAM_BYTES = {
+    'sel_fwd_kernel': 899.0e6 + 2427.3e6,
 }
+# the other workloads whose numbers ride on the default line: (name, timed steps)
+EXTRA_WORKLOADS = (('layer_fwd_bwd_b2_n16384_dim1024_h16kv4_d64', 5), ('prefill_b1_n65536_h64kv8_d128', 3))
 
 
 def make_inputs(w, seed, dtype=torch.bfloat16):
@@ -218,6 +224,69 @@ def run_reference(args, w, name):
     }))
 
 
+def emit(line):
+    """Rank 0 prints the line of a workload; every rank leaves its process group."""
+    import torch.distributed as dist
+    if line is not None:
+        print(json.dumps(line))
+    if dist.is_available() and dist.is_initialized():
+        dist.destroy_process_group()
+
+
+def launch_count():
+    from native_sparse_attention_pytorch_b200 import _lib
+    return int(_lib.load().nsa_launch_count())
+
+
+def kernel_breakdown(step_fn, steps=2):
+    """Per-kernel device time of `steps` untimed steps, from CUPTI through torch.profiler: {name: (launches per step,
+    mean microseconds per launch)}; None when the profiler is not available."""
+    try:
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(steps):
+                step_fn()
+            torch.cuda.synchronize()
+        rows = {}
+        for ev in prof.key_averages():
+            us = getattr(ev, 'device_time_total', None)
+            if us is None:
+                us = getattr(ev, 'cuda_time_total', 0.0)
+            if us and ev.count:
+                rows[ev.key] = (ev.count / steps, us / ev.count)
+        return rows
+    except Exception as exc:      # the breakdown is an explanation, never a reason to lose the measurement
+        sys.stderr.write(f'kernel breakdown unavailable: {exc}\n')
+        return None
+
+
+def child_workload(name, steps, world, index):
+    """Runs `bench.py --workload name` as a child process of this rank (all ranks do, on a rendezvous port of their own)
+    and returns rank 0's line in short form.  A child that fails or overruns costs its entry, not the parent's line."""
+    env = os.environ.copy()
+    if world > 1:
+        env['MASTER_PORT'] = str(int(env.get('MASTER_PORT', '29500')) + 1 + index)
+    cmd = [sys.executable, os.path.abspath(__file__), '--gpus', str(world), '--steps', str(steps), '--warmup', '3',
+           '--workload', name, '--no-cpu-baseline']
+    try:
+        out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    except subprocess.TimeoutExpired:
+        return {'error': 'child run exceeded 600 s'}
+    if int(os.environ.get('RANK', '0')) != 0:
+        return None
+    lines = [ln for ln in out.stdout.splitlines() if ln.startswith('{')]
+    if out.returncode != 0 or not lines:
+        return {'error': f'child run failed (rc {out.returncode}): ' + out.stderr.strip().splitlines()[-1][:200]
+                if out.stderr.strip() else f'child run failed (rc {out.returncode})'}
+    full = json.loads(lines[-1])
+    keep = ('metric', 'value', 'unit', 'n_gpus', 'steps', 'ms_per_step', 'scaling', 'gpu_launches')
+    short = {k: full.get(k) for k in keep}
+    short['config'] = {k: v for k, v in full.get('config', {}).items() if k in ('workload', 'sharding', 'parallelism', 'per_rank')}
+    short['roofline'] = {k: v for k, v in full.get('roofline', {}).items() if k in ('achieved', 'peak', 'unit', 'frac', 'kernel')}
+    short['e2e'] = full.get('e2e')
+    return short
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
@@ -231,13 +300,14 @@ def main():
     ap.add_argument('--gather', default='fused', choices=['fused', 'nccl'],
                     help='prefill workloads, N > 1: combine kernel stores into every rank (fused) or NCCL all-gather')
     ap.add_argument('--rows', action='store_true', help='also time the other kernels of the hot path (N=1 only)')
+    ap.add_argument('--no-workloads', action='store_true', help='default workload: skip the layer and prefill child runs')
     args = ap.parse_args()
     if args.workload in LAYER_WORKLOADS:
-        return run_layer(args, LAYER_WORKLOADS[args.workload])
+        return emit(run_layer(args, LAYER_WORKLOADS[args.workload]))
     if args.workload in PREFILL_WORKLOADS:
-        return run_prefill(args, PREFILL_WORKLOADS[args.workload])
+        return emit(run_prefill(args, PREFILL_WORKLOADS[args.workload]))
     if args.workload in LM_WORKLOADS:
-        return run_lm(args, LM_WORKLOADS[args.workload])
+        return emit(run_lm(args, LM_WORKLOADS[args.workload]))
     w = WORKLOADS[args.workload]
     if args.impl == 'reference':
         return run_reference(args, w, args.workload)
@@ -284,10 +354,12 @@ def main():
     if rank == 0:
         sampler.start()
     events = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    launches_before = launch_count()
     for i in range(args.steps):
         flush.fill_(i & 0xff)             # evict L2 between timed iterations (outside the events)
         step(q, k, v, idx, mask, do, events[i])
     torch.cuda.synchronize()
+    launches = launch_count() - launches_before
     nsa.ops.check_device_status()     # a kernel that gave up on a bounded wait makes the whole measurement void
     fwd_ms = [e[0].elapsed_time(e[1]) for e in events]
     bwd_ms = [e[1].elapsed_time(e[2]) for e in events]
@@ -333,53 +405,107 @@ def main():
     torch.cuda.synchronize()
     e2e_ms = e0.elapsed_time(e1)
     clocks = sampler.stop() if rank == 0 else None     # sampled over both timed regions (device-resident and end to end)
+    breakdown = kernel_breakdown(lambda: step(q, k, v, idx, mask, do)) if rank == 0 else None
 
     t = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     total_ms, e2e_ms = t.tolist()
     tokens_per_step = w['batch'] * w['seq'] * world
-    if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
 
-    ms_per_step = total_ms / args.steps
-    value = tokens_per_step / (ms_per_step / 1e3)
-    burst, sustained, src = peaks()
-    bwd_avg_ms = sum(bwd_ms) / len(bwd_ms)
-    fwd_avg_ms = sum(fwd_ms) / len(fwd_ms)
-    achieved = f_bwd / (bwd_avg_ms / 1e3) / 1e12
-    h2d = sum(t.numel() * t.element_size() for t in pinned)
-    d2h = sum(t.numel() * t.element_size() for t in h_out)
-    line = {
-        'metric': 'nsa_selected_attention_fwd_bwd_tokens_per_s', 'value': value, 'unit': 'tokens/s',
-        'n_gpus': world, 'steps': args.steps, 'warmup': warmup, 'ms_per_step': ms_per_step,
-        'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'bf16', 'data': 'synthetic',
-        'config': {'workload': args.workload, **w, 'kernels': args.kernels, 'l2': 'flushed between timed steps',
-                   'per_rank': 'each rank runs the full shape on its own seeded batch'},
-        'fwd_ms': fwd_avg_ms, 'bwd_ms': bwd_avg_ms,
-        'tensor_frac_fwd_bwd': (f_fwd + f_bwd) / (ms_per_step / 1e3) / 1e12 / burst,
-        'roofline': {'bound': 'tensor', 'kernel': 'selected-block backward', 'achieved': achieved, 'peak': burst,
-                     'unit': 'TFLOP/s', 'frac': achieved / burst, 'peak_source': src, 'peak_sustained': sustained,
-                     'flops_per_launch': f_bwd, 'traffic': NCU_TRAFFIC.get((args.workload, args.kernels))},
-        'e2e': {'value': tokens_per_step / (e2e_ms / e2e_steps / 1e3), 'unit': 'tokens/s',
-                'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h, 'steps': e2e_steps},
-        'gpu_launches': None,
-        'clocks': clocks,
-    }
-    from native_sparse_attention_pytorch_b200 import _lib
-    line['gpu_launches'] = launches_per_step(args.kernels, w) * args.steps
-    if args.rows and world == 1:
-        del q, k, v, idx, mask, do
-        line['rows'] = measure_rows(dev, flush)
-    if not args.no_cpu_baseline and world == 1:
-        val, sample = time_cpu_port(w, host)
-        line['cpu_baseline'] = {'value': val, 'unit': 'tokens/s', 'cores': os.cpu_count(), 'kind': 'port',
-                                'sample': sample}
-    print(json.dumps(line))
+    line = None
+    if rank == 0:
+        ms_per_step = total_ms / args.steps
+        value = tokens_per_step / (ms_per_step / 1e3)
+        burst, sustained, src = peaks()
+        bwd_avg_ms = sum(bwd_ms) / len(bwd_ms)
+        fwd_avg_ms = sum(fwd_ms) / len(fwd_ms)
+        achieved = (f_fwd + f_bwd) / (ms_per_step / 1e3) / 1e12
+        h2d = sum(t_.numel() * t_.element_size() for t_ in pinned)
+        d2h = sum(t_.numel() * t_.element_size() for t_ in h_out)
+        line = {
+            'metric': 'nsa_selected_attention_fwd_bwd_tokens_per_s', 'value': value, 'unit': 'tokens/s',
+            'n_gpus': world, 'steps': args.steps, 'warmup': warmup, 'ms_per_step': ms_per_step,
+            'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'bf16', 'data': 'synthetic',
+            'config': {'workload': args.workload, **w, 'kernels': args.kernels, 'l2': 'flushed between timed steps',
+                       'per_rank': 'each rank runs the full shape on its own seeded batch'},
+            'fwd_ms': fwd_avg_ms, 'bwd_ms': bwd_avg_ms,
+            'roofline': {'bound': 'tensor', 'kernel': 'selected-block attention, forward + backward (whole step)',
+                         'achieved': achieved, 'peak': burst, 'unit': 'TFLOP/s', 'frac': achieved / burst,
+                         'peak_source': src, 'peak_sustained': sustained, 'frac_of_sustained': achieved / sustained,
+                         'flops_per_step': f_fwd + f_bwd, 'flops_fwd': f_fwd, 'flops_bwd': f_bwd,
+                         'frac_fwd': f_fwd / (fwd_avg_ms / 1e3) / 1e12 / burst,
+                         'frac_bwd': f_bwd / (bwd_avg_ms / 1e3) / 1e12 / burst,
+                         'traffic': None, 'kernels': kernel_rows(breakdown, w, host[4], f_fwd, f_bwd, burst)},
+            'e2e': {'value': tokens_per_step / (e2e_ms / e2e_steps / 1e3), 'unit': 'tokens/s',
+                    'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h, 'steps': e2e_steps},
+            'gpu_launches': launches,
+            'clocks': clocks,
+        }
+        top = max(line['roofline']['kernels'] or [{'dram_bytes': None, 'ms': 0}], key=lambda r: r['ms'])
+        line['roofline']['traffic'] = top.get('dram_bytes')
+        if args.rows and world == 1:
+            del q, k, v, idx, mask, do
+            line['rows'] = measure_rows(dev, flush)
+        if not args.no_cpu_baseline and world == 1:
+            val, sample = time_cpu_port(w, host)
+            line['cpu_baseline'] = {'value': val, 'unit': 'tokens/s', 'cores': os.cpu_count(), 'kind': 'port',
+                                    'sample': sample}
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
+    if not args.no_workloads and args.workload == DEFAULT_WORKLOAD:
+        # the other baseline configurations in child processes of every rank; this process gives its memory back first
+        del pinned, h_out, dev_in, flush, events
+        q = k = v = idx = mask = do = None
+        torch.cuda.empty_cache()
+        extra = {}
+        for index, (name, steps) in enumerate(EXTRA_WORKLOADS):
+            extra[name] = child_workload(name, steps, world, index)
+        if line is not None:
+            line['workloads'] = extra
+    if line is not None:
+        print(json.dumps(line))
+
+
+def kernel_rows(breakdown, w, mask, f_fwd, f_bwd, tensor_peak):
+    """The kernels of one step with their own device time: algorithmic work, achieved rate and fraction of the peak
+    that bounds them (tensor cores for the two attention kernels, HBM for the rest)."""
+    if not breakdown:
+        return None
+    hbm = hbm_peak()
+    b, n, hq, hkv, d = w['batch'], w['seq'], w['q_heads'], w['kv_heads'], w['dim_head']
+    slots = int(mask.sum().item()) * (hq // hkv) + b * hq * n          # (row, slot) pairs incl. the own block
+    part = slots * (d * 2)                                            # bf16 partial rows
+    rows_bytes = b * hq * n * d * 2
+    work = {   # kernel name prefix -> (bound, algorithmic FLOPs or bytes per launch)
+        'sel_fwd_kernel': ('tensor', f_fwd), 'sel_bwd_ws_kernel': ('tensor', f_bwd), 'sel_bwd_kernel': ('tensor', f_bwd),
+        'sel_merge_kernel': ('hbm', part + slots * 8 + rows_bytes), 'sel_dq_merge_kernel': ('hbm', part + rows_bytes),
+        'sel_delta_kernel': ('hbm', 2 * rows_bytes + b * hq * n * 4),
+        'attend_fwd_kernel': ('tensor', f_fwd), 'attend_bwd_kernel': ('tensor', f_bwd),
+    }
+    out = []
+    for name, (per_step, us) in sorted(breakdown.items(), key=lambda kv: -kv[1][0] * kv[1][1]):
+        short = name.split('(')[0].split('::')[-1].replace('void ', '')
+        row = {'name': short[:60], 'launches_per_step': per_step, 'ms': us / 1e3, 'share_of_step': None}
+        key = next((k_ for k_ in work if short.startswith(k_)), None)
+        if key is not None:
+            bound, amount = work[key]
+            rate = amount / (us / 1e6)
+            row.update(bound=bound, work=amount, achieved=rate / (1e12 if bound == 'tensor' else 1e9),
+                       unit='TFLOP/s' if bound == 'tensor' else 'GB/s',
+                       frac=rate / ((tensor_peak * 1e12) if bound == 'tensor' else (hbm * 1e9)),
+                       dram_bytes=NCU_DRAM_BYTES.get(key))
+        out.append(row)
+    total = sum(r['ms'] * r['launches_per_step'] for r in out)
+    for r in out:
+        r['share_of_step'] = r['ms'] * r['launches_per_step'] / total if total else None
+    return out[:16]
+
+
+def hbm_peak():
+    path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    return json.load(open(path))['hbm_gbs'] if os.path.exists(path) else 6650.0
 
 
 def measure_rows(dev, flush, iters=5):
@@ -483,7 +609,7 @@ def _dist_setup():
 
 def _timed_steps(step, steps, warmup, flush, dist, world, rank, local):
     """`warmup` untimed steps, then `steps` steps timed one by one with CUDA events (L2 flushed outside the events);
-    returns (total ms as the max over ranks, clocks of rank 0)."""
+    returns (total ms as the max over ranks, clocks of rank 0, kernels of this library launched in the timed region)."""
     for _ in range(warmup):
         step()
     torch.cuda.synchronize()
@@ -494,6 +620,7 @@ def _timed_steps(step, steps, warmup, flush, dist, world, rank, local):
     if rank == 0:
         sampler.start()
     evs = []
+    launches_before = launch_count()
     for i in range(steps):
         flush.fill_(i & 0xff)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -502,13 +629,14 @@ def _timed_steps(step, steps, warmup, flush, dist, world, rank, local):
         e1.record()
         evs.append((e0, e1))
     torch.cuda.synchronize()
+    launches = launch_count() - launches_before
     clocks = sampler.stop() if rank == 0 else None
     from native_sparse_attention_pytorch_b200 import ops
     ops.check_device_status()     # a kernel that gave up on a bounded wait makes the whole measurement void
     t = torch.tensor([sum(a.elapsed_time(b) for a, b in evs)], dtype=torch.float64, device=flush.device)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return t.item(), clocks
+    return t.item(), clocks, launches
 
 
 def hot_path_flops(n, d, g, units, stride, ncb, num_mem, block, window, visible_slots):
@@ -527,7 +655,8 @@ def run_layer(args, w):
     import native_sparse_attention_pytorch_b200 as nsa
     kw = {k: v for k, v in w.items() if k not in ('batch', 'seq')}
     if args.impl == 'reference':
-        return run_layer_reference(args, w, kw)
+        run_layer_reference(args, w, kw)
+        return None
     dist, rank, world, local, dev = _dist_setup()
     warmup = max(args.warmup, 3)
     torch.manual_seed(0)
@@ -552,7 +681,7 @@ def run_layer(args, w):
     flops = hot_path_flops(n, d, w['heads'] // hkv, w['batch'] * hkv, st, n // st, 1, w['selection_block_size'],
                            w['sliding_window_size'], mid['fmask'].sum().item())
     del mid
-    total_ms, clocks = _timed_steps(step, args.steps, warmup, flush, dist, world, rank, local)
+    total_ms, clocks, launches = _timed_steps(step, args.steps, warmup, flush, dist, world, rank, local)
 
     # end to end: the input arrives from pinned host memory, the output and the input gradient go back
     h_out, h_dx = torch.empty_like(x_host).pin_memory(), torch.empty_like(x_host).pin_memory()
@@ -574,9 +703,8 @@ def run_layer(args, w):
     t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dist.destroy_process_group()
     if rank != 0:
-        return
+        return None
     ms = total_ms / args.steps
     tokens = w['batch'] * w['seq'] * world
     burst, sustained, src = peaks()
@@ -596,10 +724,10 @@ def run_layer(args, w):
                 'steps': e2e_steps},
         'gpu_launches': None, 'clocks': clocks,
     }
-    line['gpu_launches'] = LAYER_LAUNCHES * args.steps
+    line['gpu_launches'] = launches
     if not args.no_cpu_baseline and world == 1:
         line['cpu_baseline'] = layer_cpu_sample(kw)
-    print(json.dumps(line))
+    return line
 
 
 def layer_cpu_sample(kw, n=1024, budget_s=15.0):
@@ -679,7 +807,8 @@ def run_prefill(args, w):
     (the baseline's fifth configuration).  Total work is fixed: strong scaling."""
     from native_sparse_attention_pytorch_b200 import sharding
     if args.impl == 'reference':
-        return run_prefill_reference(args, w)
+        run_prefill_reference(args, w)
+        return None
     dist, rank, world, local, dev = _dist_setup()
     warmup = max(args.warmup, 3)
     h0, h1 = sharding.kv_head_range(w['kv_heads'], world, rank)
@@ -695,7 +824,7 @@ def run_prefill(args, w):
         keep['out'] = sharding.sharded_attend_core(t['q'], t['qr'], t['kr'], t['v'], t['ck'], t['cv'], t['gates'],
                                                    peer_output=peer, **cfg)
 
-    total_ms, clocks = _timed_steps(step, args.steps, warmup, flush, dist, world, rank, local)
+    total_ms, clocks, launches = _timed_steps(step, args.steps, warmup, flush, dist, world, rank, local)
 
     # end to end: this rank's inputs arrive from pinned host memory every step, rank 0 reads the gathered output back
     host = {k: v.cpu().pin_memory() for k, v in t.items()}
@@ -733,9 +862,8 @@ def run_prefill(args, w):
     if world > 1:
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
         dist.all_reduce(tv)
-        dist.destroy_process_group()
     if rank != 0:
-        return
+        return None
     ms = total_ms / args.steps
     n = w['seq']
     tokens = w['batch'] * n
@@ -759,13 +887,13 @@ def run_prefill(args, w):
         'e2e': {'value': tokens / (te.item() / e2e_steps / 1e3), 'unit': 'tokens/s',
                 'h2d_bytes_per_step': in_bytes * world, 'd2h_bytes_per_step': keep['out'].numel() * 2,
                 'steps': e2e_steps},
-        'gpu_launches': (3 * 6 + 2) * (h1 - h0) * args.steps, 'clocks': clocks,
+        'gpu_launches': launches, 'clocks': clocks,
     }
     if args.rows and world == 1:
         line['rows'] = prefill_rows(w, t, flush)
     if not args.no_cpu_baseline and world == 1:
         line['cpu_baseline'] = prefill_cpu_sample(w)
-    print(json.dumps(line))
+    return line
 
 
 def prefill_rows(w, t, flush, iters=5):
@@ -910,7 +1038,8 @@ def run_lm(args, w):
     if args.impl == 'reference':
         kw = {k: w[k] for k in ('dim', 'dim_head', 'heads', 'kv_heads', 'sliding_window_size', 'compress_block_size',
                                 'compress_block_sliding_stride', 'selection_block_size', 'num_selected_blocks')}
-        return run_layer_reference(args, w, kw, metric='nsa_lm_train_step_tokens_per_s', layers=w['depth'])
+        run_layer_reference(args, w, kw, metric='nsa_lm_train_step_tokens_per_s', layers=w['depth'])
+        return None
     dist, rank, world, local, dev = _dist_setup()
     warmup = max(args.warmup, 3)
     if w['batch'] % world:
@@ -937,7 +1066,7 @@ def run_lm(args, w):
                 g.copy_(f)
         keep['loss'] = loss
 
-    total_ms, clocks = _timed_steps(step, args.steps, warmup, flush, dist, world, rank, local)
+    total_ms, clocks, launches = _timed_steps(step, args.steps, warmup, flush, dist, world, rank, local)
     h_loss = torch.empty(1, dtype=torch.float32).pin_memory()
     def e2e_step():
         ids.copy_(ids_host, non_blocking=True)
@@ -955,9 +1084,8 @@ def run_lm(args, w):
     t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dist.destroy_process_group()
     if rank != 0:
-        return
+        return None
     ms = total_ms / args.steps
     tokens = w['batch'] * w['seq']
     n, st = w['seq'], w['compress_block_sliding_stride']
@@ -984,8 +1112,7 @@ def run_lm(args, w):
                      'peak_sustained': sustained, 'flops_per_step': f_step, 'traffic': None},
         'e2e': {'value': tokens / (t.item() / e2e_steps / 1e3), 'unit': 'tokens/s',
                 'h2d_bytes_per_step': ids_host.numel() * 8 * world, 'd2h_bytes_per_step': 4, 'steps': e2e_steps},
-        # per block the layer plus the feed-forward's norm (forward, backward); the final norm
-        'gpu_launches': ((LAYER_LAUNCHES + 2) * w['depth'] + 2) * args.steps, 'clocks': clocks,
+        'gpu_launches': launches, 'clocks': clocks,
         'loss': float(keep['loss']),
     }
     if not args.no_cpu_baseline and world == 1:
@@ -993,24 +1120,7 @@ def run_lm(args, w):
         base['value'] /= w['depth']
         base['sample'] = f'one of the {w["depth"]} attention layers (value = its tokens/s / {w["depth"]}; feed-forward not timed): ' + base['sample']
         line['cpu_baseline'] = base
-    print(json.dumps(line))
-
-
-# Kernels of this library launched by one forward+backward of the layer at a shape the tensor-core family serves.
-# Forward 16: norm, window split of k and v (2), compressed (importance prefill + dense kernel: 2), selection, rotary of
-# q and k (2), selected (index pre-pass 4 + main + merge: 6), sliding (dense kernel), combine.  Backward 17: combine,
-# sliding, selected and compressed (delta + main + dQ merge each: the selected branch on the forward's index, the other
-# two on the index kept per shape since their first backward), inverse rotary (2), window split (2 x 2), norm.
-LAYER_LAUNCHES = 16 + 17
-
-
-def launches_per_step(kernels, w):
-    """Kernels of this library launched by one forward+backward of the operator."""
-    if kernels == 'simt':
-        return 2   # one forward kernel, one backward kernel (gradient buffers are cleared by memset)
-    # tensor-core family: index pre-pass (4 kernels) + main + merge forward;
-    # delta + main + dq merge backward, on the index the forward built
-    return 6 + 3
+    return line
 
 
 if __name__ == '__main__':
