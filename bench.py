@@ -85,6 +85,7 @@ NCU_DRAM_BYTES = {
 }
 # the other workloads whose numbers ride on the default line: (name, timed steps)
 EXTRA_WORKLOADS = (('layer_fwd_bwd_b2_n16384_dim1024_h16kv4_d64', 5), ('prefill_b1_n65536_h64kv8_d128', 3))
+CHILD_TIMEOUT_S = 240
 
 
 def make_inputs(w, seed, dtype=torch.bfloat16):
@@ -263,15 +264,17 @@ def kernel_breakdown(step_fn, steps=2):
 def child_workload(name, steps, world, index):
     """Runs `bench.py --workload name` as a child process of this rank (all ranks do, on a rendezvous port of their own)
     and returns rank 0's line in short form.  A child that fails or overruns costs its entry, not the parent's line."""
-    env = os.environ.copy()
+    # torchrun's own variables must not reach the child: with TORCHELASTIC_USE_AGENT_STORE set a rank 0 would look
+    # for the launcher's rendezvous store on the new port instead of opening one, and every child would wait for it
+    env = {k: v for k, v in os.environ.items() if not k.startswith('TORCHELASTIC_')}
     if world > 1:
         env['MASTER_PORT'] = str(int(env.get('MASTER_PORT', '29500')) + 1 + index)
     cmd = [sys.executable, os.path.abspath(__file__), '--gpus', str(world), '--steps', str(steps), '--warmup', '3',
            '--workload', name, '--no-cpu-baseline']
     try:
-        out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+        out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=CHILD_TIMEOUT_S)
     except subprocess.TimeoutExpired:
-        return {'error': 'child run exceeded 600 s'}
+        return {'error': f'child run exceeded {CHILD_TIMEOUT_S} s'} if int(os.environ.get('RANK', '0')) == 0 else None
     if int(os.environ.get('RANK', '0')) != 0:
         return None
     lines = [ln for ln in out.stdout.splitlines() if ln.startswith('{')]
