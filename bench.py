@@ -284,7 +284,7 @@ def child_workload(name, steps, world, index):
     full = json.loads(lines[-1])
     keep = ('metric', 'value', 'unit', 'n_gpus', 'steps', 'ms_per_step', 'scaling', 'gpu_launches')
     short = {k: full.get(k) for k in keep}
-    short['config'] = {k: v for k, v in full.get('config', {}).items() if k in ('workload', 'sharding', 'parallelism', 'per_rank')}
+    short['config'] = {k: v for k, v in full.get('config', {}).items() if k in ('workload', 'sharding', 'parallelism', 'per_rank', 'gather_check')}
     short['roofline'] = {k: v for k, v in full.get('roofline', {}).items() if k in ('achieved', 'peak', 'unit', 'frac', 'kernel')}
     short['e2e'] = full.get('e2e')
     return short
@@ -300,8 +300,10 @@ def main():
                     choices=list(WORKLOADS) + list(LAYER_WORKLOADS) + list(PREFILL_WORKLOADS) + list(LM_WORKLOADS))
     ap.add_argument('--kernels', default='auto', choices=['auto', 'simt', 'sm100'])
     ap.add_argument('--no-cpu-baseline', action='store_true')
-    ap.add_argument('--gather', default='fused', choices=['fused', 'nccl'],
-                    help='prefill workloads, N > 1: combine kernel stores into every rank (fused) or NCCL all-gather')
+    ap.add_argument('--gather', default='multimem', choices=['multimem', 'fused', 'nccl'],
+                    help='prefill workloads, N > 1: the combine kernel stores its heads into every rank, through the '
+                         'NVLink multicast address with multimem.st (multimem; falls back to fused where the symmetric '
+                         'memory has no multicast) or with one peer store per rank (fused); or an NCCL all-gather')
     ap.add_argument('--rows', action='store_true', help='also time the other kernels of the hot path (N=1 only)')
     ap.add_argument('--no-workloads', action='store_true', help='default workload: skip the layer and prefill child runs')
     args = ap.parse_args()
@@ -820,13 +822,26 @@ def run_prefill(args, w):
                causal=True, impl=args.kernels, local=True)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     keep = {}
-    fused = world > 1 and args.gather == 'fused'
-    peer = sharding.PeerOutput(w['batch'], w['seq'], w['q_heads'] * w['dim_head'], torch.bfloat16, dev) if fused else None
+    fused = world > 1 and args.gather in ('fused', 'multimem')
+    peer = sharding.PeerOutput(w['batch'], w['seq'], w['q_heads'] * w['dim_head'], torch.bfloat16, dev,
+                               multicast=args.gather == 'multimem') if fused else None
+    multimem = peer is not None and peer.multicast_ptr is not None
 
     def step():
         keep['out'] = sharding.sharded_attend_core(t['q'], t['qr'], t['kr'], t['v'], t['ck'], t['cv'], t['gates'],
                                                    peer_output=peer, **cfg)
 
+    gather_check = None
+    if multimem:   # once, untimed: the multicast stores give every rank the bytes the per-peer stores give
+        step()
+        via_multicast = keep['out'].clone()
+        mc, peer.multicast_ptr = peer.multicast_ptr, None
+        step()
+        same = torch.tensor([int(torch.equal(via_multicast, keep['out']))], device=dev)
+        peer.multicast_ptr = mc
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        gather_check = 'identical to per-peer stores on every rank' if same.item() == 1 else 'DIFFERS from per-peer stores'
+        del via_multicast
     total_ms, clocks, launches = _timed_steps(step, args.steps, warmup, flush, dist, world, rank, local)
 
     # end to end: this rank's inputs arrive from pinned host memory every step, rank 0 reads the gathered output back
@@ -881,7 +896,10 @@ def run_prefill(args, w):
         'vs_baseline': None, 'dtype': 'bf16', 'data': 'synthetic',
         'config': {'workload': args.workload, **w, 'kernels': args.kernels, 'l2': 'flushed between timed steps',
                    'sharding': f'{w["kv_heads"] // world} KV-head group(s) per rank, output gathered by '
-                               + ('the combine kernel storing into every rank' if fused else 'NCCL all-gather')},
+                               + ('the combine kernel storing once through the NVLink multicast address (multimem.st)'
+                                  if multimem else 'the combine kernel storing into every rank' if fused
+                                  else 'NCCL all-gather'),
+                   'gather_check': gather_check},
         'roofline': {'bound': 'tensor', 'kernel': 'whole forward step of all branches (per GPU)',
                      'achieved': f_step / world / (ms / 1e3) / 1e12, 'peak': burst, 'unit': 'TFLOP/s',
                      'frac': f_step / world / (ms / 1e3) / 1e12 / burst, 'peak_source': src,

@@ -355,6 +355,9 @@ int nsa_combine_bwd(const nsa_combine_bwd_args* args, void* stream);
  * peers' (their device memory mapped into this process, e.g. CUDA IPC or symmetric memory), so no local copy of the
  * merged rows and no separate collective are needed.  Upstream runs on one GPU and has no counterpart of the gather;
  * the partition (KV-head groups per GPU, output all-gathered) is the one this library is specified with.
+ * With `multicast` set, outs[0] is instead the multicast address of a buffer that every rank has bound to one NVLink
+ * multicast object (symmetric memory): each piece is stored once with multimem.st and the switch writes all ranks'
+ * copies, the caller's own included, so a rank sends its heads once instead of once per peer.
  * The caller orders the call against the other ranks (a barrier before the buffers are reused, one after the call
  * before they are read).  Pointers, strides and dim_head must keep 16-byte pieces aligned. */
 #define NSA_MAX_GATHER 8
@@ -362,7 +365,7 @@ typedef struct {
   nsa_combine_fwd_args fwd;       /* fwd.out is not used                      */
   void* outs[NSA_MAX_GATHER];     /* destinations, own buffer included        */
   int32_t num_outs;               /* 1 .. NSA_MAX_GATHER                      */
-  int32_t reserved;
+  int32_t multicast;              /* 1: outs[0] is a multicast address (num_outs == 1) */
   int64_t total_features;         /* features per position in the destinations */
   int64_t feature_offset;         /* first feature of this rank's heads       */
 } nsa_combine_gather_args;

@@ -79,7 +79,7 @@ MAX_GATHER = 8
 
 
 class CombineGatherArgs(C.Structure):
-    _fields_ = [('fwd', CombineFwdArgs), ('outs', vp * MAX_GATHER), ('num_outs', i32), ('reserved', i32),
+    _fields_ = [('fwd', CombineFwdArgs), ('outs', vp * MAX_GATHER), ('num_outs', i32), ('multicast', i32),
                 ('total_features', i64), ('feature_offset', i64)]
 
 

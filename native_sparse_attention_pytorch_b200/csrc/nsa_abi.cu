@@ -453,7 +453,10 @@ int nsa_combine_fwd_gather(const nsa_combine_gather_args* a, void* stream) {
     if (reinterpret_cast<uintptr_t>(a->outs[r]) & 15u) return fail(NSA_ERR_ALIGN, "outs must be 16-byte aligned");
     Gt.outs[r] = a->outs[r];
   }
+  if (a->multicast != 0 && a->num_outs != 1)
+    return fail(NSA_ERR_SHAPE, "a multicast destination is the only destination (num_outs == 1)");
   Gt.num_outs = a->num_outs;
+  Gt.multicast = a->multicast != 0;
   Gt.total_features = a->total_features;
   Gt.feature_offset = a->feature_offset;
   return launch_combine_gather(P, Gt, f.dtype, (cudaStream_t)stream);

@@ -33,7 +33,9 @@ __global__ void __launch_bounds__(256) combine_fwd_kernel(const CombineParams P)
 // With more than one destination this is the combine fused with the all-gather of the head-sharded layout: the
 // merged rows never exist as a local tensor, each 16-byte piece goes straight to every rank.  Blocks start their
 // round over the destinations at different ranks so that the links are used side by side.
-template <typename T>
+// With MC the one destination is the multicast address of a symmetric buffer: a single `multimem.st` per piece and the
+// NVSwitch writes every rank's copy, this rank's included, so the rank sends its heads once instead of once per peer.
+template <typename T, bool MC>
 __global__ void __launch_bounds__(256) combine_gather_kernel(const CombineParams P, const GatherTargets Gt) {
   constexpr int V = 16 / (int)sizeof(T);
   const int vpr = P.d / V;
@@ -60,12 +62,20 @@ __global__ void __launch_bounds__(256) combine_gather_kernel(const CombineParams
 #pragma unroll
     for (int x = 0; x < V; ++x) pv[x] = Elem<T>::from_float(acc[x]);
     const int64_t at = ((int64_t)b * P.seq + n) * Gt.total_features + Gt.feature_offset + (int64_t)h * P.d + c;
-    for (int r = 0; r < Gt.num_outs; ++r) {
-      int k = r + rot;
-      if (k >= Gt.num_outs) k -= Gt.num_outs;
-      *reinterpret_cast<uint4*>((T*)Gt.outs[k] + at) = packed;
+    if (MC) {
+      asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"((T*)Gt.outs[0] + at),
+                   "f"(__uint_as_float(packed.x)), "f"(__uint_as_float(packed.y)), "f"(__uint_as_float(packed.z)),
+                   "f"(__uint_as_float(packed.w))
+                   : "memory");
+    } else {
+      for (int r = 0; r < Gt.num_outs; ++r) {
+        int k = r + rot;
+        if (k >= Gt.num_outs) k -= Gt.num_outs;
+        *reinterpret_cast<uint4*>((T*)Gt.outs[k] + at) = packed;
+      }
     }
   }
+  if (MC) __threadfence_system();   // the stores have left for the switch before the kernel counts as finished
 }
 
 int launch_combine_gather(const CombineParams& P, const GatherTargets& Gt, int dtype, cudaStream_t stream) {
@@ -74,8 +84,13 @@ int launch_combine_gather(const CombineParams& P, const GatherTargets& Gt, int d
   if (total == 0) return NSA_OK;
   const int64_t blocks = (total + 255) / 256;
   const unsigned grid = (unsigned)(blocks < 148 * 16 ? blocks : 148 * 16);
-  if (dtype == NSA_F32) combine_gather_kernel<float><<<grid, 256, 0, stream>>>(P, Gt);
-  else combine_gather_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(P, Gt);
+  if (Gt.multicast) {
+    if (dtype == NSA_F32) combine_gather_kernel<float, true><<<grid, 256, 0, stream>>>(P, Gt);
+    else combine_gather_kernel<__nv_bfloat16, true><<<grid, 256, 0, stream>>>(P, Gt);
+  } else {
+    if (dtype == NSA_F32) combine_gather_kernel<float, false><<<grid, 256, 0, stream>>>(P, Gt);
+    else combine_gather_kernel<__nv_bfloat16, false><<<grid, 256, 0, stream>>>(P, Gt);
+  }
   count_launches(1);
   const cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return fail((int)err, cudaGetErrorString(err));

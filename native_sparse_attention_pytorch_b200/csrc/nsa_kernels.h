@@ -58,7 +58,7 @@ struct CombineParams {
 constexpr int kMaxGather = NSA_MAX_GATHER;
 struct GatherTargets {
   void* outs[kMaxGather];
-  int num_outs;
+  int num_outs, multicast;
   int64_t total_features, feature_offset;
 };
 

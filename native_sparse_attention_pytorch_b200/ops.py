@@ -567,10 +567,12 @@ def _vec_ok(t):
     return t.stride(-1) == 1 and t.data_ptr() % 16 == 0 and all(s % v == 0 for s in t.stride()[:-1])
 
 
-def gated_combine_gather(o_cmp, o_sel, o_swa, gates, out_ptrs, total_features, feature_offset):
+def gated_combine_gather(o_cmp, o_sel, o_swa, gates, out_ptrs, total_features, feature_offset, multicast=False):
     """Forward-only gated combine of this rank's heads, written at `feature_offset` into every [B, N, total_features]
     buffer whose device address is listed in `out_ptrs` (own buffer and the peers' mappings): the combine fused with
-    the all-gather of the head-sharded layout.  The caller synchronises the ranks around the call."""
+    the all-gather of the head-sharded layout.  With `multicast`, `out_ptrs` is the one multicast address of the
+    symmetric buffer and every piece is stored once (multimem.st), the switch writing all ranks' copies.  The caller
+    synchronises the ranks around the call."""
     L.require_cuda(o_cmp, o_sel, o_swa, gates)
     lib = L.load()
     o_cmp, o_sel, o_swa = (t if _vec_ok(t) else t.contiguous() for t in (o_cmp, o_sel, o_swa))
@@ -582,7 +584,7 @@ def gated_combine_gather(o_cmp, o_sel, o_swa, gates, out_ptrs, total_features, f
     fwd = L.CombineFwdArgs(o_cmp=L.t4(o_cmp), o_sel=L.t4(o_sel), o_swa=L.t4(o_swa), gates=L.t4(gates), out=None,
                            batch=b, q_heads=h, seq=n, dim_head=d, dtype=L.dtype_code(o_cmp))
     outs = (C.c_void_p * L.MAX_GATHER)(*[int(p) for p in out_ptrs])
-    args = L.CombineGatherArgs(fwd=fwd, outs=outs, num_outs=len(out_ptrs), reserved=0,
+    args = L.CombineGatherArgs(fwd=fwd, outs=outs, num_outs=len(out_ptrs), multicast=int(bool(multicast)),
                                total_features=total_features, feature_offset=feature_offset)
     with torch.cuda.device(o_cmp.device):
         L.check(lib.nsa_combine_fwd_gather(C.byref(args), L.stream_of(o_cmp)))

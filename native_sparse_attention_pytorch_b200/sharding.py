@@ -126,15 +126,21 @@ class PeerOutput:
     and without a local copy of the merged rows.  `begin()` / `end()` order one step against the other ranks: nobody
     stores into a buffer that a peer may still be reading, nobody reads before every peer's stores have landed."""
 
-    def __init__(self, batch, seq, features, dtype, device, group=None):
+    def __init__(self, batch, seq, features, dtype, device, group=None, multicast=False):
         import torch.distributed._symmetric_memory as symm
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
         self.buffer = symm.empty(batch, seq, features, dtype=dtype, device=device)
         self.handle = symm.rendezvous(self.buffer, self.group)
-        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        # the handle's addresses are those of the allocation; the tensor may start inside it
+        inside = self.buffer.data_ptr() - int(self.handle.buffer_ptrs[self.rank])
+        self.ptrs = [int(p) + inside for p in self.handle.buffer_ptrs]
         self.features = features
+        # `multicast`: store through the buffer's NVLink multicast address (one multimem.st per piece, the switch
+        # writes every rank's copy) where the symmetric memory has one; plain peer stores otherwise
+        mc = int(getattr(self.handle, 'multicast_ptr', 0) or 0) if multicast else 0
+        self.multicast_ptr = mc + inside if mc != 0 else None
 
     def begin(self):
         self.handle.barrier(channel=0)
@@ -166,7 +172,11 @@ def sharded_attend_core(q, qr, kr, v, ck, cv, gates, *, group=None, heads_per_pa
 
             def combine_into_peers(o_cmp, o_sel, o_swa, gts, offset=first + (a - h0) * g * d):
                 from . import ops
-                ops.gated_combine_gather(o_cmp, o_sel, o_swa, gts, peer_output.ptrs, peer_output.features, offset)
+                if peer_output.multicast_ptr is not None:
+                    ops.gated_combine_gather(o_cmp, o_sel, o_swa, gts, [peer_output.multicast_ptr], peer_output.features,
+                                             offset, multicast=True)
+                else:
+                    ops.gated_combine_gather(o_cmp, o_sel, o_swa, gts, peer_output.ptrs, peer_output.features, offset)
 
             attend_core(q[:, qs], qr[:, qs], kr[:, hs], v[:, hs], ck[:, hs], cv[:, hs], gates[:, qs],
                         combine=combine_into_peers, **cfg)
