@@ -442,11 +442,49 @@ typedef struct {
 
 int nsa_rmsnorm_bwd(const nsa_rmsnorm_bwd_args* args, void* stream);
 
-/* Library information.  nsa_struct_size(i) is sizeof() of the i-th argument
- * struct in declaration order (0 nsa_tensor, 1 sel_fwd, 2 sel_bwd, 3 cmp_fwd,
- * 4 cmp_bwd, 5 select, 6 swa_fwd, 7 swa_bwd, 8 combine_fwd, 9 combine_bwd, 10 combine_gather,
- * 11 rotary, 12 windows_fwd, 13 windows_bwd, 14 rmsnorm_fwd, 15 rmsnorm_bwd), so
- * a foreign-function binding can verify its own layout; -1 for other i. */
+/* ------------------------------------------------------------------------
+ * One decoding step of the hot path in a single launch.  Replaces the
+ * attention part of upstream's forward_inference (NSA:387-547): for the
+ * newest token at position T-1,
+ *   - compressed attention over the ncb blocks compressed so far, with the
+ *     num_mem memory slots in front (none of it when ncb == 0, as upstream),
+ *     un-rotated queries;
+ *   - block selection from the compressed logits: mean over the heads of a KV
+ *     head and over the block/stride compressed blocks of a selection block,
+ *     softmax with the -1000 sink, top-nsel, slots with probability <= 1e-10
+ *     dropped (no own-block exclusion: upstream's decode path has none);
+ *   - attention of the rotated queries over the selected blocks plus keys
+ *     (T-1)/block*block .. T-1 of the own block;
+ *   - sliding window over keys max(0, T-1-window) .. T-1;
+ *   - out[b, (h d)] = sum_s gates[b,h,s] * branch_s.
+ * One selection per KV head (query_heads_share_selected_kv).  q, qr, gates,
+ * mem_k, mem_v and out are contiguous; keys, vals, ck, cv take strides in
+ * elements (rows 16-byte aligned).  fp32 arithmetic; dtype as elsewhere.
+ * Limits: q_heads / kv_heads <= 16, dim_head <= 128, nsel <= 32, and
+ * ncb + ncb / (block / stride) block logits must fit one CTA's shared memory
+ * (NSA_ERR_UNSUPPORTED beyond, about 20000 compressed blocks).
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  const void* q;          /* [B, q_heads, d] un-rotated queries of the token  */
+  const void* qr;         /* [B, q_heads, d] rotated queries                   */
+  nsa_tensor keys;        /* [B, kv_heads, T, d] rotated keys, token included  */
+  nsa_tensor vals;        /* [B, kv_heads, T, d]                               */
+  nsa_tensor ck;          /* [B, kv_heads, ncb, d] (ptr may be NULL if ncb==0) */
+  nsa_tensor cv;
+  const void* mem_k;      /* [kv_heads, num_mem, d]                            */
+  const void* mem_v;
+  const void* gates;      /* [B, q_heads, 3]: compressed, selected, sliding    */
+  void* out;              /* [B, q_heads * d]                                  */
+  int32_t batch, q_heads, kv_heads, dim_head;
+  int32_t cache_len;      /* T                                                 */
+  int32_t ncb, num_mem, stride, block, nsel, window;
+  int32_t dtype;
+  float scale;
+  int32_t reserved;
+} nsa_decode_args;
+
+int nsa_decode_step(const nsa_decode_args* args, void* stream);
+
 /* ------------------------------------------------------------------------
  * Housekeeping (no counterparts in upstream).
  * ---------------------------------------------------------------------- */
@@ -464,6 +502,11 @@ int64_t nsa_launch_count(void);
  * traps or spins without a bound. */
 int nsa_selftest_bounded_wait(int* status_device, int64_t limit_cycles, void* stream);
 
+/* Library information.  nsa_struct_size(i) is sizeof() of the i-th argument
+ * struct in declaration order (0 nsa_tensor, 1 sel_fwd, 2 sel_bwd, 3 cmp_fwd,
+ * 4 cmp_bwd, 5 select, 6 swa_fwd, 7 swa_bwd, 8 combine_fwd, 9 combine_bwd, 10 combine_gather,
+ * 11 rotary, 12 windows_fwd, 13 windows_bwd, 14 rmsnorm_fwd, 15 rmsnorm_bwd, 16 decode), so
+ * a foreign-function binding can verify its own layout; -1 for other i. */
 const char* nsa_last_error(void);
 int nsa_abi_version(void);
 int nsa_struct_size(int which);

@@ -108,12 +108,20 @@ class RmsNormBwdArgs(C.Structure):
     _fields_ = [('fwd', RmsNormFwdArgs), ('dy', vp), ('dx', vp), ('dweight', vp)]
 
 
+class DecodeArgs(C.Structure):
+    _fields_ = [('q', vp), ('qr', vp), ('keys', Tensor4), ('vals', Tensor4), ('ck', Tensor4), ('cv', Tensor4),
+                ('mem_k', vp), ('mem_v', vp), ('gates', vp), ('out', vp), ('batch', i32), ('q_heads', i32),
+                ('kv_heads', i32), ('dim_head', i32), ('cache_len', i32), ('ncb', i32), ('num_mem', i32),
+                ('stride', i32), ('block', i32), ('nsel', i32), ('window', i32), ('dtype', i32), ('scale', f32),
+                ('reserved', i32)]
+
+
 _STRUCTS = [Tensor4, SelFwdArgs, SelBwdArgs, CmpFwdArgs, CmpBwdArgs, SelectArgs, SwaFwdArgs, SwaBwdArgs,
             CombineFwdArgs, CombineBwdArgs, CombineGatherArgs, RotaryArgs, WindowsFwdArgs, WindowsBwdArgs,
-            RmsNormFwdArgs, RmsNormBwdArgs]
+            RmsNormFwdArgs, RmsNormBwdArgs, DecodeArgs]
 
 ENTRY_POINTS = ['nsa_sel_fwd', 'nsa_sel_bwd', 'nsa_sel_workspace_bytes', 'nsa_sel_index_bytes', 'nsa_cmp_index_bytes', 'nsa_swa_index_bytes', 'nsa_sel_bwd_stores_dq', 'nsa_cmp_bwd_stores_dq', 'nsa_swa_bwd_stores_dq',
-                'nsa_sel_fwd_static', 'nsa_sel_static_status', 'nsa_launch_count', 'nsa_selftest_bounded_wait',
+                'nsa_sel_fwd_static', 'nsa_sel_static_status', 'nsa_launch_count', 'nsa_selftest_bounded_wait', 'nsa_decode_step',
                 'nsa_sel_static_scratch_bytes', 'nsa_cmp_workspace_bytes', 'nsa_swa_workspace_bytes', 'nsa_cmp_fwd', 'nsa_cmp_bwd', 'nsa_select',
                 'nsa_swa_fwd', 'nsa_swa_bwd', 'nsa_combine_fwd', 'nsa_combine_bwd', 'nsa_combine_fwd_gather', 'nsa_rotary', 'nsa_windows_fwd', 'nsa_windows_bwd', 'nsa_rmsnorm_fwd', 'nsa_rmsnorm_bwd', 'nsa_last_error',
                 'nsa_abi_version', 'nsa_struct_size']

@@ -10,7 +10,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, 'csrc')
 LIB = os.path.join(HERE, 'libnsa_b200.so')
-SOURCES = ['nsa_abi.cu', 'nsa_simt_attend.cu', 'nsa_select.cu', 'nsa_combine.cu', 'nsa_rotary.cu', 'nsa_windows.cu', 'nsa_rmsnorm.cu', 'nsa_sm100_sel.cu']
+SOURCES = ['nsa_abi.cu', 'nsa_simt_attend.cu', 'nsa_select.cu', 'nsa_combine.cu', 'nsa_rotary.cu', 'nsa_windows.cu', 'nsa_rmsnorm.cu', 'nsa_decode.cu', 'nsa_sm100_sel.cu']
 
 
 def _newest_source_mtime():

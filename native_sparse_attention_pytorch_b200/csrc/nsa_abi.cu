@@ -120,6 +120,7 @@ int nsa_struct_size(int which) {
     case 13: return (int)sizeof(nsa_windows_bwd_args);
     case 14: return (int)sizeof(nsa_rmsnorm_fwd_args);
     case 15: return (int)sizeof(nsa_rmsnorm_bwd_args);
+    case 16: return (int)sizeof(nsa_decode_args);
     default: return -1;
   }
 }
@@ -195,6 +196,38 @@ int nsa_sel_fwd_static(const nsa_sel_fwd_args* a, void* stream) {
 int64_t nsa_sel_static_scratch_bytes(void) { return sm100_static_scratch_bytes(); }
 
 int nsa_sel_static_status(int* out, void* stream) { return sm100_sel_static_status(out, (cudaStream_t)stream); }
+
+int nsa_decode_step(const nsa_decode_args* a, void* stream) {
+  if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
+  NSA_TRY(check_common(a->dtype, a->batch, a->q_heads, a->kv_heads, a->cache_len, a->dim_head));
+  if (a->cache_len < 1) return fail(NSA_ERR_SHAPE, "decode step: the caches hold at least the new token");
+  if (a->stride < 1 || a->block < a->stride || a->block % a->stride || a->nsel < 0 || a->nsel > 32 || a->window < 0 ||
+      a->ncb < 0 || a->num_mem < 1)
+    return fail(NSA_ERR_SHAPE, "decode step: stride / block / nsel (<= 32) / window / ncb / num_mem out of range");
+  if ((int64_t)a->ncb * a->stride > a->cache_len)
+    return fail(NSA_ERR_SHAPE, "decode step: more compressed blocks than the cache length allows");
+  if (!a->q || !a->qr || !a->gates || !a->out || !a->mem_k || !a->mem_v) return fail(NSA_ERR_NULL, "decode step: NULL pointer");
+  NSA_TRY(check_tensor(a->keys, a->dtype, "keys"));
+  NSA_TRY(check_tensor(a->vals, a->dtype, "vals"));
+  if (a->ncb > 0) {
+    NSA_TRY(check_tensor(a->ck, a->dtype, "ck"));
+    NSA_TRY(check_tensor(a->cv, a->dtype, "cv"));
+  }
+  const void* small[] = {a->q, a->qr, a->mem_k, a->mem_v, a->out};
+  for (const void* p : small)
+    if (!aligned16(p)) return fail(NSA_ERR_ALIGN, "decode step: q, qr, mem_k, mem_v, out must be 16-byte aligned");
+  DecodeParams P;
+  memset(&P, 0, sizeof(P));
+  P.q = a->q; P.qr = a->qr; P.gates = a->gates; P.out = a->out; P.mem_k = a->mem_k; P.mem_v = a->mem_v;
+  P.keys = a->keys.ptr; P.k_sb = a->keys.stride_b; P.k_sh = a->keys.stride_h; P.k_sn = a->keys.stride_n;
+  P.vals = a->vals.ptr; P.v_sb = a->vals.stride_b; P.v_sh = a->vals.stride_h; P.v_sn = a->vals.stride_n;
+  P.ck = a->ck.ptr; P.ck_sb = a->ck.stride_b; P.ck_sh = a->ck.stride_h; P.ck_sn = a->ck.stride_n;
+  P.cv = a->cv.ptr; P.cv_sb = a->cv.stride_b; P.cv_sh = a->cv.stride_h; P.cv_sn = a->cv.stride_n;
+  P.batch = a->batch; P.q_heads = a->q_heads; P.kv_heads = a->kv_heads; P.d = a->dim_head; P.T = a->cache_len;
+  P.ncb = a->ncb; P.num_mem = a->num_mem; P.stride = a->stride; P.block = a->block; P.nsel = a->nsel;
+  P.window = a->window; P.scale = a->scale;
+  return launch_decode(P, a->dtype, (cudaStream_t)stream);
+}
 
 int64_t nsa_launch_count(void) { return (int64_t)g_launches.load(std::memory_order_relaxed); }
 

@@ -93,6 +93,20 @@ struct NormParams {
   float eps;
 };
 
+// One decoding step (see nsa_decode.cu): the newest token's queries against the caches.
+struct DecodeParams {
+  const void *q, *qr;            // [B, Hq, d] contiguous: un-rotated / rotated queries of the token
+  const void *keys, *vals;       // [B, Hkv, T, d]: rotated keys and values, the token included
+  int64_t k_sb, k_sh, k_sn, v_sb, v_sh, v_sn;
+  const void *ck, *cv;           // [B, Hkv, ncb, d]: compressed blocks, without memory slots
+  int64_t ck_sb, ck_sh, ck_sn, cv_sb, cv_sh, cv_sn;
+  const void *mem_k, *mem_v;     // [Hkv, num_mem, d] contiguous
+  const void* gates;             // [B, Hq, 3] contiguous
+  void* out;                     // [B, Hq * d]
+  int batch, q_heads, kv_heads, d, T, ncb, num_mem, stride, block, nsel, window;
+  float scale;
+};
+
 int fail(int code, const char* msg);
 
 // Every host function that launches kernels of this library reports how many it launched; nsa_launch_count() returns
@@ -106,6 +120,7 @@ int launch_rotary(const RotaryParams& P, int dtype, cudaStream_t stream);
 int launch_windows(const WindowParams& P, int dtype, bool backward, cudaStream_t stream);
 int launch_rmsnorm(const NormParams& P, int dtype, bool backward, cudaStream_t stream);
 int launch_combine_gather(const CombineParams& P, const GatherTargets& Gt, int dtype, cudaStream_t stream);
+int launch_decode(const DecodeParams& P, int dtype, cudaStream_t stream);
 
 // Tensor-core family for the selected-block branch.  Each returns
 // NSA_ERR_UNSUPPORTED (without touching the error message state of a later

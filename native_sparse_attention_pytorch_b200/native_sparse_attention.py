@@ -119,16 +119,18 @@ class SparseAttention(Module):
     def forward_inference(self, inp, cache, return_cache=True):
         """One decoding step (upstream NSA:338-547): `inp` is the newest token [B, 1, dim], `cache` what the previous
         call returned: ((rotated keys, values), ((compressed keys, compressed values), (keys, values of the window
-        that is being filled for the next compressed block, un-rotated))).  A single query row is a handful of small
-        matrix products, so this step is written with tensor operations and launches none of the attention kernels;
-        the rotary kernel places the token at its position."""
+        that is being filled for the next compressed block, un-rotated))).  The attention part -- compressed branch,
+        block selection, selected blocks plus the own block, sliding window, gated combine -- is one kernel launch
+        (`ops.decode_step`, all (batch, KV head) units in its grid); the projections, the rotary kernel and the
+        compress network of a window that has just filled up stay tensor operations.  It keeps upstream's behaviour,
+        including that the memory slots are attended only once a compressed block exists."""
         assert self.causal, 'inference only relevant for autoregressive'
         if not self.query_heads_share_selected_kv:
             raise NotImplementedError('decoding with per-query-head selection is not built (upstream gathers K/V with '
                                       'indices of the wrong head count in that case)')
         (past_k, past_v), ((ck, cv), (run_k, run_v)) = cache
         b = inp.shape[0]
-        h, hkv, d, g, scale = self.heads, self.kv_heads, self.dim_head, self.num_grouped_queries, self.scale
+        h, d = self.heads, self.dim_head
         st, cbs, sel = self.compress_block_sliding_stride, self.compress_block_size, self.selection_block_size
         pos = past_k.shape[-2]                       # position of the new token
         x = self.norm(inp)
@@ -137,60 +139,21 @@ class SparseAttention(Module):
         qr = self.rotary_emb.rotate_queries_or_keys(q, offset=pos)
         keys = torch.cat((past_k, self.rotary_emb.rotate_queries_or_keys(k, offset=pos)), dim=-2)
         vals = torch.cat((past_v, v), dim=-2)
-        qg, qrg = q.view(b, hkv, g, 1, d), qr.view(b, hkv, g, 1, d)
 
-        def attend(query, kk, vv, visible=None):   # query [B,Hkv,G,1,d]; kk, vv [B,Hkv,J,d]
-            sim = torch.einsum('bhgid,bhjd->bhgij', query, kk) * scale
-            if visible is not None:
-                sim = sim.masked_fill(~visible[:, :, None, None, :], -torch.finfo(sim.dtype).max)
-            return torch.einsum('bhgij,bhjd->bhgid', sim.softmax(dim=-1), vv), sim
+        gates = self.to_strategy_combine(x).view(b, h, 3)
+        merged = ops.decode_step(q.view(b, h, d), qr.view(b, h, d), keys, vals, ck, cv, self.compress_mem_kv[0],
+                                 self.compress_mem_kv[1], gates, stride=st, block=sel,
+                                 num_selected=self.num_selected_blocks, window=self.sliding_window_size)
 
-        # 1. compressed branch over the blocks completed so far (memory slots in front once there is a block)
-        m = self.num_mem_compress_kv
-        if ck.shape[-2] > 0:
-            ckm = torch.cat((self.compress_mem_kv[0].expand(b, -1, -1, -1), ck), dim=-2)
-            cvm = torch.cat((self.compress_mem_kv[1].expand(b, -1, -1, -1), cv), dim=-2)
-            o_cmp, csim = attend(qg, ckm, cvm)
-            imp = csim[..., m:]
-        else:
-            o_cmp, imp = qg.new_zeros(b, hkv, g, 1, d), qg.new_zeros(b, hkv, g, 1, 0)
-        # the window that was being filled is complete: compress it and keep its overlap with the next one
+        # the window that was being filled is complete: compress it and keep its overlap with the next one (the step
+        # above attended the blocks that existed before this token, as upstream's does)
         if run_k.shape[-2] % cbs == 0:
             ck = torch.cat((ck, self.k_compress((run_k + self.k_intrablock_positions)[:, :, None])), dim=-2)
             cv = torch.cat((cv, self.v_compress((run_v + self.v_intrablock_positions)[:, :, None])), dim=-2)
             keep = cbs - st
             run_k, run_v = run_k[..., run_k.shape[-2] - keep:, :], run_v[..., run_v.shape[-2] - keep:, :]
 
-        # 2. selected blocks (picked from the compressed logits) plus the part of the own block up to the token
-        cpf = sel // st
-        if st != sel:
-            cols = imp.shape[-1] // cpf
-            imp = imp[..., : cols * cpf].reshape(b, hkv, g, 1, cols, cpf).mean(dim=-1)
-        num_selected = min(self.num_selected_blocks, imp.shape[-1])
-        own = pos % sel + 1
-        fk, fv, visible = keys[..., -own:, :], vals[..., -own:, :], None
-        if num_selected > 0:
-            prob = F.pad(imp.mean(dim=2), (1, 0), value=-1e3).softmax(dim=-1)[..., 1:]       # [B,Hkv,1,cols]
-            score, idx = prob.topk(num_selected, dim=-1)
-            nfb = -(-(pos + 1) // sel)
-            pad = nfb * sel - keys.shape[-2]
-            kb = F.pad(keys, (0, 0, 0, pad)).view(b, hkv, nfb, sel, d)
-            vb = F.pad(vals, (0, 0, 0, pad)).view(b, hkv, nfb, sel, d)
-            take = idx.view(b, hkv, num_selected, 1, 1).expand(-1, -1, -1, sel, d)
-            fk = torch.cat((kb.gather(2, take).flatten(2, 3), fk), dim=-2)
-            fv = torch.cat((vb.gather(2, take).flatten(2, 3), fv), dim=-2)
-            visible = F.pad((score > 1e-10).view(b, hkv, num_selected, 1).expand(-1, -1, -1, sel).flatten(2),
-                            (0, own), value=True)
-        o_sel, _ = attend(qrg, fk, fv, visible)
-
-        # 3. sliding window: the last window + 1 keys
-        w = self.sliding_window_size + 1
-        o_swa, _ = attend(qrg, keys[..., -w:, :], vals[..., -w:, :])
-
-        gates = self.to_strategy_combine(x).view(b, 1, h, 3).transpose(1, 2)                  # [B,H,1,3]
-        branches = torch.stack([t.reshape(b, h, 1, d) for t in (o_cmp, o_sel, o_swa)], dim=-1)   # [B,H,1,d,3]
-        merged = (branches * gates[..., None, :]).sum(dim=-1).transpose(1, 2).reshape(b, 1, h * d)
-        out = self.combine_heads(merged)
+        out = self.combine_heads(merged.view(b, 1, h * d))
         if not return_cache:
             return out
         return out, ((keys, vals), ((ck, cv), (run_k, run_v)))

@@ -591,6 +591,38 @@ def gated_combine_gather(o_cmp, o_sel, o_swa, gates, out_ptrs, total_features, f
 
 
 # --------------------------------------------------------------------------
+# one decoding step (replaces the attention part of upstream's forward_inference, NSA:387-547)
+# --------------------------------------------------------------------------
+
+@torch.no_grad()
+def decode_step(q, qr, keys, vals, ck, cv, mem_k, mem_v, gates, *, stride, block, num_selected, window):
+    """The newest token against the caches, one kernel launch.  q, qr [B, Hq, d]: un-rotated / rotated queries of
+    the token; keys, vals [B, Hkv, T, d]: rotated keys and values with the token appended; ck, cv [B, Hkv, ncb, d]:
+    the blocks compressed so far (without memory slots, ncb may be 0); mem_k, mem_v [Hkv, M, d]; gates [B, Hq, 3]
+    (compressed, selected, sliding).  Returns the merged row [B, Hq * d].  See nsa_decode_step in include/nsa_b200.h."""
+    L.require_cuda(q, qr, keys, vals, ck, cv, mem_k, mem_v, gates)
+    lib = L.load()
+    dt = q.dtype
+    q, qr, gates = q.contiguous(), qr.to(dt).contiguous(), gates.to(dt).contiguous()
+    mem_k, mem_v = mem_k.to(dt).contiguous(), mem_v.to(dt).contiguous()
+    keys, vals = L.rowwise(keys.to(dt)), L.rowwise(vals.to(dt))
+    b, hq, d = q.shape
+    ncb = ck.shape[2]
+    if ncb > 0:
+        ck, cv = L.rowwise(ck.to(dt)), L.rowwise(cv.to(dt))
+    out = torch.empty(b, hq * d, dtype=dt, device=q.device)
+    args = L.DecodeArgs(q=L.ptr(q), qr=L.ptr(qr), keys=L.t4(keys), vals=L.t4(vals),
+                        ck=L.t4(ck) if ncb > 0 else L.Tensor4(), cv=L.t4(cv) if ncb > 0 else L.Tensor4(),
+                        mem_k=L.ptr(mem_k), mem_v=L.ptr(mem_v), gates=L.ptr(gates), out=L.ptr(out), batch=b,
+                        q_heads=hq, kv_heads=keys.shape[1], dim_head=d, cache_len=keys.shape[2], ncb=ncb,
+                        num_mem=mem_k.shape[1], stride=stride, block=block, nsel=num_selected, window=window,
+                        dtype=L.dtype_code(q), scale=d ** -0.5, reserved=0)
+    with torch.cuda.device(q.device):
+        L.check(lib.nsa_decode_step(C.byref(args), L.stream_of(q)))
+    return out
+
+
+# --------------------------------------------------------------------------
 # input of the compress networks: windows + intra-block positions (NSA:589-614)
 # --------------------------------------------------------------------------
 

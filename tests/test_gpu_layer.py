@@ -154,3 +154,60 @@ def test_language_model_harness_matches_upstream_transformer_on_gpu():
             continue
         got = torch.tensor([p.grad.abs().sum().item(), p.grad.pow(2).sum().item()], dtype=torch.float64)
         assert torch.allclose(got, g, rtol=1e-3, atol=1e-6), (pname, got, g)
+
+
+@pytest.mark.parametrize('case', [(2, 8, 2, 64, 1500, 16, 64, 8, 200, torch.float32), (1, 16, 2, 128, 3000, 16, 64, 16, 512, torch.bfloat16),
+                                  (1, 4, 4, 64, 70, 4, 4, 3, 9, torch.float32)])
+def test_decode_step_kernel_matches_the_restated_step(case):
+    """The decode kernel (one launch per token) on caches far longer than upstream's own grid reaches, against the same
+    step restated with tensor operations on the host: compressed attention over all compressed blocks with the memory
+    slots in front, selection without own-block exclusion, selected blocks plus the own block's past, window + 1 keys,
+    gates."""
+    import torch.nn.functional as F
+    from native_sparse_attention_pytorch_b200 import _lib as L, ops
+    b, hq, hkv, d, t, st, sel, nsel, win, dtype = case
+    g, ncb, m = hq // hkv, (t - 1) // st, 2
+    pos = t - 1
+    rnd = lambda shape, seed: recipe.randn(shape, seed).to(dtype)
+    q, qr = rnd((b, hq, d), 1), rnd((b, hq, d), 2)
+    keys, vals = rnd((b, hkv, t, d), 3), rnd((b, hkv, t, d), 4)
+    ck, cv = rnd((b, hkv, ncb, d), 5), rnd((b, hkv, ncb, d), 6)
+    mem = rnd((2, hkv, m, d), 7)
+    gates = torch.sigmoid(recipe.randn((b, hq, 3), 8)).to(dtype)
+    before = L.load().nsa_launch_count()
+    got = ops.decode_step(*(x.to(DEV) for x in (q, qr, keys, vals, ck, cv, mem[0], mem[1], gates)), stride=st, block=sel,
+                          num_selected=nsel, window=win)
+    assert L.load().nsa_launch_count() - before == 1
+
+    f = lambda x: x.float()
+    scale = d ** -0.5
+    qg, qrg = f(q).view(b, hkv, g, d), f(qr).view(b, hkv, g, d)
+
+    def attend(query, kk, vv):            # query [b,hkv,g,d]; kk, vv [b,hkv,J,d]
+        sim = torch.einsum('bhgd,bhjd->bhgj', query, kk) * scale
+        return torch.einsum('bhgj,bhjd->bhgd', sim.softmax(dim=-1), vv), sim
+
+    ckm = torch.cat((f(mem[0]).expand(b, -1, -1, -1), f(ck)), dim=2)
+    cvm = torch.cat((f(mem[1]).expand(b, -1, -1, -1), f(cv)), dim=2)
+    o_cmp, csim = attend(qg, ckm, cvm)
+    imp = csim[..., m:]
+    cpf = sel // st
+    if st != sel:
+        cols = ncb // cpf
+        imp = imp[..., : cols * cpf].reshape(b, hkv, g, cols, cpf).mean(dim=-1)
+    prob = F.pad(imp.mean(dim=2), (1, 0), value=-1e3).softmax(dim=-1)[..., 1:]
+    score, idx = prob.topk(min(nsel, prob.shape[-1]), dim=-1)
+    own0 = pos // sel * sel
+    o_sel = torch.empty(b, hkv, g, d)
+    for bi in range(b):
+        for h in range(hkv):
+            rows = [torch.arange(j * sel, (j + 1) * sel) for j, sc in zip(idx[bi, h].tolist(), score[bi, h].tolist()) if sc > 1e-10]
+            rows.append(torch.arange(own0, pos + 1))
+            rows = torch.cat(rows)
+            o, _ = attend(qrg[bi:bi + 1, h:h + 1], f(keys)[bi:bi + 1, h:h + 1, rows], f(vals)[bi:bi + 1, h:h + 1, rows])
+            o_sel[bi, h] = o[0, 0]
+    lo = max(0, pos - win)
+    o_swa, _ = attend(qrg, f(keys)[:, :, lo:], f(vals)[:, :, lo:])
+    gt = f(gates).view(b, hkv, g, 3)
+    ref = (gt[..., 0:1] * o_cmp + gt[..., 1:2] * o_sel + gt[..., 2:3] * o_swa).reshape(b, hq * d)
+    (assert_close_f32 if dtype == torch.float32 else assert_close_bf16)(got, ref, 'merged row')
