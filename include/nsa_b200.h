@@ -128,6 +128,8 @@ typedef struct {
   const void* index;     /* optional: the forward's index, see above          */
   int64_t index_bytes;
   nsa_tensor dq_out;     /* optional (ptr NULL = unused): dq in the dtype of q with these strides, see nsa_sel_bwd_stores_dq */
+  const float* delta;    /* optional [B, q_heads, N] fp32: sum over d of out * dout for every row, for a caller that
+                            has it already (the gated combine's backward forms it: gate * d gate); NULL = computed */
 } nsa_sel_bwd_args;
 
 int nsa_sel_bwd(const nsa_sel_bwd_args* args, void* stream);
@@ -244,6 +246,7 @@ typedef struct {
   nsa_tensor dq_out;     /* optional, as in nsa_sel_bwd_args */
   const void* index;     /* optional, see nsa_cmp_index_bytes */
   int64_t index_bytes;
+  const float* delta;    /* optional, as in nsa_sel_bwd_args */
 } nsa_cmp_bwd_args;
 
 int nsa_cmp_bwd(const nsa_cmp_bwd_args* args, void* stream);
@@ -316,6 +319,7 @@ typedef struct {
   nsa_tensor dq_out;     /* optional, as in nsa_sel_bwd_args */
   const void* index;     /* optional, see nsa_swa_index_bytes */
   int64_t index_bytes;
+  const float* delta;    /* optional, as in nsa_sel_bwd_args */
 } nsa_swa_bwd_args;
 
 int nsa_swa_bwd(const nsa_swa_bwd_args* args, void* stream);

@@ -34,7 +34,7 @@ class SelFwdArgs(C.Structure):
 
 class SelBwdArgs(C.Structure):
     _fields_ = [('fwd', SelFwdArgs), ('dout', Tensor4), ('dq', vp), ('dk', vp), ('dv', vp), ('slot_grads', vp),
-                ('index', vp), ('index_bytes', i64), ('dq_out', Tensor4)]
+                ('index', vp), ('index_bytes', i64), ('dq_out', Tensor4), ('delta', vp)]
 
 
 class CmpFwdArgs(C.Structure):
@@ -46,7 +46,7 @@ class CmpFwdArgs(C.Structure):
 
 class CmpBwdArgs(C.Structure):
     _fields_ = [('fwd', CmpFwdArgs), ('dout', Tensor4), ('dq', vp), ('dck', vp), ('dcv', vp), ('dq_out', Tensor4),
-                ('index', vp), ('index_bytes', i64)]
+                ('index', vp), ('index_bytes', i64), ('delta', vp)]
 
 
 class SelectArgs(C.Structure):
@@ -63,7 +63,7 @@ class SwaFwdArgs(C.Structure):
 
 class SwaBwdArgs(C.Structure):
     _fields_ = [('fwd', SwaFwdArgs), ('dout', Tensor4), ('dq', vp), ('dk', vp), ('dv', vp), ('dq_out', Tensor4),
-                ('index', vp), ('index_bytes', i64)]
+                ('index', vp), ('index_bytes', i64), ('delta', vp)]
 
 
 class CombineFwdArgs(C.Structure):

@@ -1734,6 +1734,7 @@ struct SelProblem {
   int64_t workspace_bytes;
   const void* index;       // backward: the index part of the forward's work buffer, or NULL to rebuild it
   int64_t index_bytes;
+  const float* delta;      // backward, optional: sum_d out * dout per row from the caller
   int B, Hq, Hkv, N, Nk, D;
   int nsel, diag, mode, window, stride, num_mem, ncb, round_bf16;
   float scale;
@@ -1997,13 +1998,14 @@ static int run_bwd(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaStrea
   fill_params(P, a, p, ws, ix);
   P.dout = (const __nv_bfloat16*)a.dout.ptr; P.do_sb = a.dout.stride_b; P.do_sh = a.dout.stride_h; P.do_sn = a.dout.stride_n;
   float* delta = reinterpret_cast<float*>(ws + p.off_delta);
-  P.delta = delta;
+  P.delta = a.delta != nullptr ? a.delta : delta;
   P.dq = a.dq; P.dk = a.dk; P.dv = a.dv; P.slot_grads = a.slot_grads;
   if (a.dq_out.ptr != nullptr) {
     P.dq_lp = (__nv_bfloat16*)a.dq_out.ptr; P.dq_sb = a.dq_out.stride_b; P.dq_sh = a.dq_out.stride_h; P.dq_sn = a.dq_out.stride_n;
   }
   const int64_t threads = (int64_t)a.B * a.Hq * a.N * (D / 8);
-  sel_delta_kernel<D><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(P, delta);
+  const int own_delta = a.delta == nullptr ? 1 : 0;   // the caller may hand the row sums over
+  if (own_delta) sel_delta_kernel<D><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(P, delta);
   if (D == 64) {
     const int smem = 1024 + ws::kStages * 32768 + 2 * ws::kPBytes + 2 * 16384 + ws::kStages * ws::kMetaBytes +
                      8 * ws::kDqStage;
@@ -2015,7 +2017,7 @@ static int run_bwd(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaStrea
     else if (a.mode == kModeSwa) sel_dq_merge_kernel<64, kModeSwa><<<mblocks, 256, 0, st>>>(P);
     else sel_dq_merge_kernel<64, kModeCmp><<<mblocks, 256, 0, st>>>(P);
     CUDA_TRY(cudaGetLastError());
-    count_launches(3);   // delta, backward kernel, dQ merge
+    count_launches(2 + own_delta);   // (delta,) backward kernel, dQ merge
     return NSA_OK;
   }
   constexpr int NC = D / 64;
@@ -2024,7 +2026,7 @@ static int run_bwd(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaStrea
   CUDA_TRY(cudaFuncSetAttribute(sel_bwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   sel_bwd_kernel<D><<<num_sms() * per_sm, kRows, smem, st>>>(tmK, tmV, P);
   CUDA_TRY(cudaGetLastError());
-  count_launches(2);   // delta, backward kernel
+  count_launches(1 + own_delta);   // (delta,) backward kernel
   return NSA_OK;
 }
 
@@ -2108,7 +2110,7 @@ int sm100_sel_bwd(const nsa_sel_bwd_args& b, cudaStream_t st) {
   SelProblem x;
   if (!sel_problem(x, b.fwd)) return NSA_ERR_UNSUPPORTED;
   x.dout = b.dout; x.dq = b.dq; x.dk = b.dk; x.dv = b.dv; x.slot_grads = b.slot_grads;
-  x.index = b.index; x.index_bytes = b.index_bytes; x.dq_out = b.dq_out;
+  x.index = b.index; x.index_bytes = b.index_bytes; x.dq_out = b.dq_out; x.delta = b.delta;
   return problem_bwd(x, st);
 }
 
@@ -2153,7 +2155,7 @@ int sm100_swa_bwd(const nsa_swa_bwd_args& b, cudaStream_t st) {
   SelProblem x;
   if (!swa_problem(x, b.fwd)) return NSA_ERR_UNSUPPORTED;
   x.dout = b.dout; x.dq = b.dq; x.dk = b.dk; x.dv = b.dv; x.dq_out = b.dq_out;
-  x.index = b.index; x.index_bytes = b.index_bytes;
+  x.index = b.index; x.index_bytes = b.index_bytes; x.delta = b.delta;
   return problem_bwd(x, st);
 }
 
@@ -2190,7 +2192,7 @@ int sm100_cmp_bwd(const nsa_cmp_bwd_args& b, cudaStream_t st) {
   if (!cmp_problem(x, b.fwd)) return NSA_ERR_UNSUPPORTED;
   x.importance = nullptr;
   x.dout = b.dout; x.dq = b.dq; x.dk = b.dck; x.dv = b.dcv; x.dq_out = b.dq_out;
-  x.index = b.index; x.index_bytes = b.index_bytes;
+  x.index = b.index; x.index_bytes = b.index_bytes; x.delta = b.delta;
   return problem_bwd(x, st);
 }
 

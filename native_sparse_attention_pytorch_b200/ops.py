@@ -141,6 +141,17 @@ def _dq_buffers(lib, query, fwd, q, need_fp32=False):
     return torch.empty(q.shape, dtype=torch.float32, device=q.device), None
 
 
+def _handed_over_delta(dout, shape):
+    """The row sums sum_d out * dout that the gated combine's backward attached to the branch gradient it returned
+    (delta = gate * d gate, see GatedCombine.backward), when `dout` is that very tensor; else None and the backward
+    computes them itself."""
+    delta = getattr(dout, '_nsa_delta', None)
+    if delta is None or tuple(delta.shape) != tuple(shape) or delta.dtype != torch.float32 or not delta.is_contiguous() \
+            or delta.device != dout.device:
+        return None
+    return delta
+
+
 def _call_bwd(fn, make_args, q, stream):
     """Run a backward entry point; when the tensor-core kernels decline the tensors at run time although the direct
     dq was offered, run it again with an fp32 dq."""
@@ -178,6 +189,7 @@ def _keep_index(key, ws, nbytes):
 
 
 REUSE_INDEX = True     # the selected-block backward takes the index the forward built instead of rebuilding it
+HAND_OVER_DELTA = True # the gated combine's backward hands the row sums out * d out to the three branch backwards
 
 
 class SelectedAttention(Function):
@@ -216,6 +228,7 @@ class SelectedAttention(Function):
         block, diag, impl, scale, slot_dtype = ctx.cfg
         want_slot_grads = slot_dtype is not None
         lib = L.load()
+        delta = _handed_over_delta(dout, lse.shape)
         dout = L.rowwise(dout)
         dk = torch.empty(k.shape, dtype=torch.float32, device=q.device)
         dv = torch.empty(v.shape, dtype=torch.float32, device=q.device)
@@ -230,7 +243,8 @@ class SelectedAttention(Function):
                 return L.SelBwdArgs(fwd=fwd, dout=L.t4(dout), dq=L.ptr(dq), dk=L.ptr(dk), dv=L.ptr(dv),
                                     slot_grads=L.ptr(slot), index=L.ptr(index),
                                     index_bytes=0 if index is None else index.numel(),
-                                    dq_out=L.t4(dq_out) if dq_out is not None else L.Tensor4()), dq, dq_out
+                                    dq_out=L.t4(dq_out) if dq_out is not None else L.Tensor4(),
+                                    delta=L.ptr(delta)), dq, dq_out
             dq = _call_bwd(lib.nsa_sel_bwd, make_args, q, L.stream_of(q))
         _keep_status(ws)
         del ws
@@ -319,6 +333,7 @@ class CompressedAttention(Function):
         q, ck, cv, out, lse = ctx.saved_tensors
         num_mem, stride, causal, sel_heads, impl, scale = ctx.cfg
         lib = L.load()
+        delta = None if dout is None else _handed_over_delta(dout, lse.shape)
         dout = torch.zeros_like(out) if dout is None else L.rowwise(dout)
         dck = torch.empty(ck.shape, dtype=torch.float32, device=q.device)
         dcv = torch.empty(cv.shape, dtype=torch.float32, device=q.device)
@@ -334,7 +349,7 @@ class CompressedAttention(Function):
                 dq, dq_out = _dq_buffers(lib, 'nsa_cmp_bwd_stores_dq', fwd, q, need_fp32=with_dimp or not direct)
                 return L.CmpBwdArgs(fwd=fwd, dout=L.t4(dout), dq=L.ptr(dq), dck=L.ptr(dck), dcv=L.ptr(dcv),
                                     dq_out=L.t4(dq_out) if dq_out is not None else L.Tensor4(), index=L.ptr(index),
-                                    index_bytes=0 if index is None else index.numel()), dq, dq_out
+                                    index_bytes=0 if index is None else index.numel(), delta=L.ptr(delta)), dq, dq_out
             if with_dimp:
                 args, dq32, _ = make_args(False)
                 L.check(lib.nsa_cmp_bwd(C.byref(args), L.stream_of(q)))
@@ -486,6 +501,7 @@ class SlidingAttention(Function):
         q, k, v, out, lse = ctx.saved_tensors
         window, causal, impl, scale = ctx.cfg
         lib = L.load()
+        delta = _handed_over_delta(dout, lse.shape)
         dout = L.rowwise(dout)
         dk = torch.empty(k.shape, dtype=torch.float32, device=q.device)
         dv = torch.empty(v.shape, dtype=torch.float32, device=q.device)
@@ -499,7 +515,7 @@ class SlidingAttention(Function):
                 dq, dq_out = _dq_buffers(lib, 'nsa_swa_bwd_stores_dq', fwd, q, need_fp32=not direct)
                 return L.SwaBwdArgs(fwd=fwd, dout=L.t4(dout), dq=L.ptr(dq), dk=L.ptr(dk), dv=L.ptr(dv),
                                     dq_out=L.t4(dq_out) if dq_out is not None else L.Tensor4(), index=L.ptr(index),
-                                    index_bytes=0 if index is None else index.numel()), dq, dq_out
+                                    index_bytes=0 if index is None else index.numel(), delta=L.ptr(delta)), dq, dq_out
             dq = _call_bwd(lib.nsa_swa_bwd, make_args, q, L.stream_of(q))
             if index is None:
                 _keep_index(key, ws, int(lib.nsa_swa_index_bytes(C.byref(fwd))))
@@ -555,6 +571,13 @@ class GatedCombine(Function):
                                 d_swa=L.ptr(d_swa), d_gates=L.ptr(d_gates))
         with torch.cuda.device(dout.device):
             L.check(lib.nsa_combine_bwd(C.byref(args), L.stream_of(dout)))
+        if HAND_OVER_DELTA:
+            # Every branch backward starts from delta = sum_d out_s * d out_s of each row.  With d out_s = gate_s * dout
+            # that is gate_s * (sum_d out_s * dout) = gate_s * d gate_s, which this kernel has just formed: hand it to
+            # the branch through the gradient tensor it is about to receive, and the branch skips its own pass.
+            deltas = (d_gates * gates.float()).permute(3, 0, 1, 2).contiguous()       # [3, B, H, N] fp32
+            for s_, t_ in enumerate((d_cmp, d_sel, d_swa)):
+                t_._nsa_delta = deltas[s_]
         return d_cmp, d_sel, d_swa, d_gates.to(gates.dtype)
 
 

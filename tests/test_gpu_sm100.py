@@ -459,3 +459,36 @@ def test_launch_counter_counts_the_kernels_of_a_step():
     run_gpu(q, k, v, idx, mask, up, 'sm100')
     # forward: index pre-pass (4) + forward + merge; backward on the forward's index: delta + backward + dQ merge
     assert lib.nsa_launch_count() - before == 9
+
+
+def test_combine_backward_hands_the_row_sums_to_the_branch_backwards(monkeypatch):
+    """Every branch backward needs delta = sum_d out * d out per row; the gated combine's backward has it already as
+    gate * d gate and hands it over through the gradient tensors, so the three branches skip their own pass: three
+    launches fewer per layer step, gradients the same up to the rounding of d out (bf16) that the handed-over sums do
+    not carry."""
+    from native_sparse_attention_pytorch_b200 import SparseAttention, _lib as L
+    kw = dict(dim=256, dim_head=64, heads=8, kv_heads=2, causal=True, sliding_window_size=128, compress_block_size=32,
+              compress_block_sliding_stride=16, selection_block_size=64, num_selected_blocks=4)
+    attn = SparseAttention(**kw, use_triton_kernel=True, kernel_impl='sm100')
+    recipe.fill_weights(attn, seed=7)
+    attn = attn.to(DEV).bfloat16()
+    x = recipe.randn((2, 700, 256), 11).bfloat16().to(DEV)
+    up = recipe.randn((2, 700, 256), 13).bfloat16().to(DEV)
+    lib = L.load()
+
+    def run(hand_over):
+        monkeypatch.setattr(ops, 'HAND_OVER_DELTA', hand_over)
+        attn.zero_grad(set_to_none=True)
+        xs = x.clone().requires_grad_()
+        out = attn(xs)
+        before = lib.nsa_launch_count()
+        out.backward(up)
+        ops.check_device_status()
+        return lib.nsa_launch_count() - before, xs.grad, attn.to_qkv.weight.grad.clone()
+
+    run(False)                                              # the first backward also builds the per-shape indices
+    n_own, dx_own, dw_own = run(False)
+    n_handed, dx_handed, dw_handed = run(True)
+    assert n_own - n_handed == 3, (n_own, n_handed)
+    assert_close_bf16(dx_handed, dx_own, 'd input', roundings=2)
+    assert_close_bf16(dw_handed, dw_own, 'd to_qkv.weight', roundings=2, rel_to_max=2e-3)
