@@ -560,7 +560,7 @@ def measure_rows(dev, flush, iters=5):
     qd, ckd, cvd = (t.detach().requires_grad_() for t in (q, ck, cv))
     holder = {}
     def cmp_fwd():
-        holder['o'], holder['imp'] = nsa.compressed_attend(qd, ckd, cvd, 1, st, True)
+        holder['o'], holder['imp'] = nsa.compressed_attend(qd, ckd, cvd, 1, st, True, pool=blk // st)
     add('compressed_fwd', timed(cmp_fwd), 4 * d * pairs, 'tensor')
     add('compressed_bwd', timed(lambda: torch.autograd.grad(holder['o'], (qd, ckd, cvd), do, retain_graph=True)),
         10 * d * pairs, 'tensor')
@@ -569,7 +569,7 @@ def measure_rows(dev, flush, iters=5):
     def select():
         holder['vals'], holder['idx'] = nsa.select_blocks(imp, blk, st, nsel, dtype=torch.bfloat16)
     ms = timed(select)
-    add('select', ms, imp.numel() * 4 + b * hkv * n * nsel * 12, 'hbm')
+    add('select', ms, imp.numel() * imp.element_size() + b * hkv * n * nsel * 12, 'hbm')
     idx, mask = holder['idx'], holder['vals'] > 1e-10
     # selected-block attention at this head grouping
     keys = (mask.sum(dim=-1).cpu() * blk + (i % blk + 1).view(1, 1, n)).sum().item() * g
@@ -872,7 +872,8 @@ def run_prefill(args, w):
     with torch.no_grad():
         for a in range(h1 - h0):
             _, imp = ops.compressed_attend(t['q'][:, a * g:(a + 1) * g], t['ck'][:, a:a + 1], t['cv'][:, a:a + 1],
-                                           w['num_mem'], w['stride'], True, sel_heads=1, want_importance=True)
+                                           w['num_mem'], w['stride'], True, sel_heads=1, want_importance=True,
+                                           pool=w['block'] // w['stride'])
             vals, _ = ops.select_blocks(imp, w['block'], w['stride'], w['nsel'], dtype=torch.bfloat16)
             vis += int((vals > 1e-10).sum().item())
             del imp
@@ -941,7 +942,7 @@ def prefill_rows(w, t, flush, iters=5):
 
     def cmp():
         h['o'], h['imp'] = ops.compressed_attend(q, ck, cv, w['num_mem'], w['stride'], True, sel_heads=1,
-                                                 want_importance=True)
+                                                 want_importance=True, pool=w['block'] // w['stride'])
     rows['compressed_fwd'] = timed(cmp)
     def sel():
         h['vals'], h['idx'] = ops.select_blocks(h['imp'], w['block'], w['stride'], w['nsel'], dtype=torch.bfloat16)

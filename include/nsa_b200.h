@@ -224,9 +224,27 @@ typedef struct {
   float sentinel;        /* value an invisible logit is replaced by            */
   void* workspace;       /* nsa_cmp_workspace_bytes(args, 0) bytes, may be NULL if that is 0 */
   int64_t workspace_bytes;
+  void* pooled;          /* optional, instead of importance: see nsa_cmp_fwd_pools */
+  int32_t pool;          /* block columns per selection block (selection_block_size / stride) */
 } nsa_cmp_fwd_args;
 
 int nsa_cmp_fwd(const nsa_cmp_fwd_args* args, void* stream);
+
+/* The second step of the selection chain (NSA:672-680: the mean over the
+ * `pool` block columns of every selection block) inside the forward: with
+ * `pooled` set (and importance NULL) the call writes [B, sel_heads, N,
+ * ncb / pool] bf16 instead of the importance matrix, 1 / (2 * pool) of its
+ * bytes: entry (i, c) is the mean of the head-averaged logits of columns
+ * c*pool .. c*pool+pool-1, rounded to bf16 as upstream's bf16 tensor would be,
+ * for the selection blocks c < i / (pool * stride) that lie wholly before the
+ * query's own block.  The other entries are NOT written: under the causal
+ * mask those blocks hold a masked column or are the own block, and the
+ * selection gives them probability 0 whatever their value, which is what
+ * nsa_select assumes when it is handed this tensor (`pooled` there).
+ * Returns 1 when nsa_cmp_fwd would serve `pooled` for these arguments (tensor-
+ * core family, bf16, causal, 4 / 8 / 16 query heads per KV head, pool a power
+ * of two up to 16, num_mem <= 64), else 0: pass importance instead. */
+int nsa_cmp_fwd_pools(const nsa_cmp_fwd_args* args);
 
 /* Bytes of work buffer nsa_cmp_fwd (backward != 0: nsa_cmp_bwd) needs; 0 when
  * the SIMT family serves the problem.  The tensor-core family serves bf16,
@@ -283,6 +301,10 @@ typedef struct {
   int32_t exclude_own;
   int32_t input_is_prob;
   int32_t dtype;         /* dtype whose rounding the probabilities follow     */
+  const void* pooled;    /* optional, instead of importance: [rows, N, ncb] bf16 as written by nsa_cmp_fwd
+                            (`pooled` there; ncb here = its column count, cpf = 1): column c of query i is read
+                            only for c < i / block, every other column has probability 0                         */
+  int32_t causal_limit;  /* with importance: likewise read only the columns c < i / block of the averaged row   */
 } nsa_select_args;
 
 int nsa_select(const nsa_select_args* args, void* stream);

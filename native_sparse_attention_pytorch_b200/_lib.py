@@ -41,7 +41,8 @@ class CmpFwdArgs(C.Structure):
     _fields_ = [('q', Tensor4), ('ck', Tensor4), ('cv', Tensor4), ('out', Tensor4), ('lse', vp), ('importance', vp),
                 ('batch', i32), ('q_heads', i32), ('kv_heads', i32), ('sel_heads', i32), ('seq', i32), ('dim_head', i32),
                 ('num_mem', i32), ('ncb', i32), ('stride', i32), ('causal', i32), ('dtype', i32), ('impl', i32),
-                ('scale', f32), ('sentinel', f32), ('workspace', vp), ('workspace_bytes', i64)]
+                ('scale', f32), ('sentinel', f32), ('workspace', vp), ('workspace_bytes', i64), ('pooled', vp),
+                ('pool', i32)]
 
 
 class CmpBwdArgs(C.Structure):
@@ -51,7 +52,8 @@ class CmpBwdArgs(C.Structure):
 
 class SelectArgs(C.Structure):
     _fields_ = [('importance', vp), ('idx', vp), ('vals', vp), ('rows', i32), ('seq', i32), ('ncb', i32), ('cpf', i32),
-                ('k', i32), ('block', i32), ('exclude_own', i32), ('input_is_prob', i32), ('dtype', i32)]
+                ('k', i32), ('block', i32), ('exclude_own', i32), ('input_is_prob', i32), ('dtype', i32),
+                ('pooled', vp), ('causal_limit', i32)]
 
 
 class SwaFwdArgs(C.Structure):
@@ -122,7 +124,7 @@ _STRUCTS = [Tensor4, SelFwdArgs, SelBwdArgs, CmpFwdArgs, CmpBwdArgs, SelectArgs,
 
 ENTRY_POINTS = ['nsa_sel_fwd', 'nsa_sel_bwd', 'nsa_sel_workspace_bytes', 'nsa_sel_index_bytes', 'nsa_cmp_index_bytes', 'nsa_swa_index_bytes', 'nsa_sel_bwd_stores_dq', 'nsa_cmp_bwd_stores_dq', 'nsa_swa_bwd_stores_dq',
                 'nsa_sel_fwd_static', 'nsa_sel_static_status', 'nsa_launch_count', 'nsa_selftest_bounded_wait', 'nsa_decode_step',
-                'nsa_sel_static_scratch_bytes', 'nsa_cmp_workspace_bytes', 'nsa_swa_workspace_bytes', 'nsa_cmp_fwd', 'nsa_cmp_bwd', 'nsa_select',
+                'nsa_sel_static_scratch_bytes', 'nsa_cmp_workspace_bytes', 'nsa_swa_workspace_bytes', 'nsa_cmp_fwd', 'nsa_cmp_fwd_pools', 'nsa_cmp_bwd', 'nsa_select',
                 'nsa_swa_fwd', 'nsa_swa_bwd', 'nsa_combine_fwd', 'nsa_combine_bwd', 'nsa_combine_fwd_gather', 'nsa_rotary', 'nsa_windows_fwd', 'nsa_windows_bwd', 'nsa_rmsnorm_fwd', 'nsa_rmsnorm_bwd', 'nsa_last_error',
                 'nsa_abi_version', 'nsa_struct_size']
 

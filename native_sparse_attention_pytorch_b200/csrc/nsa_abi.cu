@@ -293,10 +293,21 @@ int64_t nsa_cmp_workspace_bytes(const nsa_cmp_fwd_args* a, int backward) {
   return need;
 }
 
+int nsa_cmp_fwd_pools(const nsa_cmp_fwd_args* a) {
+  if (a == nullptr) return 0;
+  return sm100_cmp_fwd_pools(*a) ? 1 : 0;
+}
+
 int nsa_cmp_fwd(const nsa_cmp_fwd_args* a, void* stream) {
   if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
   AttnParams P;
   NSA_TRY(fill_cmp(P, *a));
+  if (a->pooled != nullptr) {
+    if (a->importance != nullptr) return fail(NSA_ERR_SHAPE, "pass importance or pooled, not both");
+    if (reinterpret_cast<uintptr_t>(a->pooled) & 1u) return fail(NSA_ERR_ALIGN, "pooled must be 2-byte aligned");
+    if (!sm100_cmp_fwd_pools(*a))
+      return fail(NSA_ERR_UNSUPPORTED, "pooled: not served for these arguments (nsa_cmp_fwd_pools); pass importance");
+  }
   if (a->impl != NSA_IMPL_SIMT) {
     const int rc = sm100_cmp_fwd(*a, (cudaStream_t)stream);
     if (rc != NSA_ERR_UNSUPPORTED) return rc;
@@ -343,9 +354,12 @@ int nsa_select(const nsa_select_args* a, void* stream) {
   const int cols = a->ncb / a->cpf;
   if (a->k > cols) return fail(NSA_ERR_SHAPE, "k exceeds the number of block columns");
   if (a->input_is_prob && a->cpf != 1) return fail(NSA_ERR_SHAPE, "input_is_prob needs cpf == 1");
-  if (!a->importance || !a->idx || !a->vals) return fail(NSA_ERR_NULL, "importance/idx/vals: NULL pointer");
+  if ((!a->importance && !a->pooled) || !a->idx || !a->vals) return fail(NSA_ERR_NULL, "importance/idx/vals: NULL pointer");
+  if (a->pooled != nullptr && (a->importance != nullptr || a->cpf != 1 || a->input_is_prob))
+    return fail(NSA_ERR_SHAPE, "pooled excludes importance and input_is_prob and needs cpf == 1");
   SelectParams P;
   P.imp = a->importance; P.idx = a->idx; P.vals = a->vals;
+  P.pooled = a->pooled; P.causal_limit = (a->pooled != nullptr || a->causal_limit) ? 1 : 0;
   P.rows = a->rows; P.seq = a->seq; P.ncb = a->ncb; P.cpf = a->cpf; P.cols = cols; P.k = a->k;
   P.block = a->block; P.exclude_own = a->exclude_own; P.input_is_prob = a->input_is_prob;
   P.round_bf16 = a->dtype == NSA_BF16;

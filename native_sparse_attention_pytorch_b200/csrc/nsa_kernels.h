@@ -39,6 +39,8 @@ struct AttnParams {
 
 struct SelectParams {
   const float* imp;
+  const void* pooled;      // bf16 [rows, seq, cols], instead of imp
+  int causal_limit;        // columns at and past i / block are not read: probability 0
   int64_t* idx;
   float* vals;
   int rows, seq, ncb, cpf, cols, k, block, exclude_own, input_is_prob, round_bf16;
@@ -137,6 +139,7 @@ int sm100_swa_fwd(const nsa_swa_fwd_args& a, cudaStream_t stream);
 int sm100_swa_bwd(const nsa_swa_bwd_args& a, cudaStream_t stream);
 int64_t sm100_cmp_workspace_bytes(const nsa_cmp_fwd_args& a, bool backward);
 int sm100_cmp_fwd(const nsa_cmp_fwd_args& a, cudaStream_t stream);
+bool sm100_cmp_fwd_pools(const nsa_cmp_fwd_args& a);
 int sm100_cmp_bwd(const nsa_cmp_bwd_args& a, cudaStream_t stream);
 int64_t sm100_static_scratch_bytes();
 int sm100_sel_static_status(int* out, cudaStream_t stream);

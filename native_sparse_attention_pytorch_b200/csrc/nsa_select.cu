@@ -18,10 +18,16 @@ __global__ void __launch_bounds__(128) select_kernel(const SelectParams P, int w
   const int i = (int)(task % P.seq);
   float* buf = sbuf + (size_t)warp * P.cols;
   const float* src = P.imp + task * P.ncb;
+  const __nv_bfloat16* psrc = static_cast<const __nv_bfloat16*>(P.pooled) + task * P.ncb;
+  const int limit = P.causal_limit ? min(P.cols, i / P.block) : P.cols;
 
   for (int j = lane; j < P.cols; j += 32) {
     float v;
-    if (P.cpf == 1) {
+    if (j >= limit) {
+      v = P.neg_max;
+    } else if (P.pooled != nullptr) {
+      v = __bfloat162float(psrc[j]);
+    } else if (P.cpf == 1) {
       v = src[j];
     } else {
       float sum = 0.f;
@@ -98,13 +104,12 @@ __device__ __forceinline__ float from_ordered_bits(unsigned k) {
   return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
 }
 
+// `limit`: columns at and past it are not read, they hold probability 0 (causal_limit); `need`: columns that can
+// appear among the k picks (all of them, or with a limit the first limit + k: zeros are picked in column order).
 template <int CPL>
-__global__ void __launch_bounds__(128) select_reg_kernel(const SelectParams P) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t task = (int64_t)blockIdx.x * 4 + warp;
-  if (task >= (int64_t)P.rows * P.seq) return;
-  const int i = (int)(task % P.seq);
+__device__ __forceinline__ void select_row(const SelectParams& P, int64_t task, int i, int lane, int limit, int need) {
   const float* src = P.imp + task * P.ncb;
+  const __nv_bfloat16* psrc = static_cast<const __nv_bfloat16*>(P.pooled) + task * P.ncb;
   const bool vec4 = P.cpf == 4 && (P.ncb & 3) == 0 && (reinterpret_cast<uintptr_t>(P.imp) & 15u) == 0;
   float v[CPL];
   unsigned alive = 0;
@@ -112,10 +117,14 @@ __global__ void __launch_bounds__(128) select_reg_kernel(const SelectParams P) {
   for (int t = 0; t < CPL; ++t) {
     const int j = lane + 32 * t;
     v[t] = 0.f;
-    if (j < P.cols) {
+    if (j < need) {
       alive |= 1u << t;
       float x;
-      if (P.cpf == 1) {
+      if (j >= limit) {
+        x = P.neg_max;
+      } else if (P.pooled != nullptr) {
+        x = __bfloat162float(psrc[j]);
+      } else if (P.cpf == 1) {
         x = src[j];
       } else {
         float sum = 0.f;
@@ -230,6 +239,24 @@ __global__ void __launch_bounds__(128) select_reg_kernel(const SelectParams P) {
     P.idx[task * P.k + lane] = my_idx;
     P.vals[task * P.k + lane] = my_val;
   }
+}
+
+// One warp per query row; the row takes the smallest register variant that holds the columns it needs (with a causal
+// limit the early queries of a sequence need few).
+template <int CPLMAX>
+__global__ void __launch_bounds__(128) select_reg_kernel(const SelectParams P) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t task = (int64_t)blockIdx.x * 4 + warp;
+  if (task >= (int64_t)P.rows * P.seq) return;
+  const int i = (int)(task % P.seq);
+  const int limit = P.causal_limit ? min(P.cols, i / P.block) : P.cols;
+  const int need = P.causal_limit ? min(P.cols, limit + P.k) : P.cols;
+  if (CPLMAX > 1 && need <= 32) select_row<1>(P, task, i, lane, limit, need);
+  else if (CPLMAX > 2 && need <= 64) select_row<2>(P, task, i, lane, limit, need);
+  else if (CPLMAX > 4 && need <= 128) select_row<4>(P, task, i, lane, limit, need);
+  else if (CPLMAX > 8 && need <= 256) select_row<8>(P, task, i, lane, limit, need);
+  else if (CPLMAX > 16 && need <= 512) select_row<16>(P, task, i, lane, limit, need);
+  else select_row<CPLMAX>(P, task, i, lane, limit, need);
 }
 
 int launch_select(const SelectParams& P, cudaStream_t stream) {

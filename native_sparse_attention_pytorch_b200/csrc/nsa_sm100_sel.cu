@@ -117,6 +117,11 @@ struct SelParams {
   // compressed branch only: the head-averaged logits of every compressed block column, [B, Hkv, N, ncb] fp32
   float* importance;
   int ncb, round_bf16;
+  // or, instead of it, those logits averaged over runs of `cpf` columns (one value per selection block of
+  // pool_block = cpf * stride queries) and rounded to bf16: [B, Hkv, N, pool_cols], written for the blocks that lie
+  // wholly before the query's own block
+  __nv_bfloat16* pooled;
+  int cpf, pool_cols, pool_block;
 };
 
 // Number of items of the index, or 0 (and status 2) when the index was not built for these sizes: a caller-kept
@@ -663,8 +668,10 @@ __global__ void __launch_bounds__(256) sel_merge_kernel(const SelParams P) {
 //   * The accumulator is rescaled lazily: a row keeps its reference maximum until a block exceeds it by more than 2^8;
 //     only then is the O row read from tensor memory, scaled and written back (P stays below 2^8, exact in bf16's
 //     range, and the sum is fp32).
-//   * MODE compressed with IMP also writes the head-averaged logits of the visible columns (the importance).
-template <int D, int MODE, int GI>   // GI: 0 = no importance output, else the number of heads per KV head (importance written)
+//   * MODE compressed with IMP also writes the head-averaged logits of the visible columns (the importance), or with
+//     POOL their per-selection-block means: the head means of the last 128 compressed columns of every query wait in
+//     a ring in shared memory, and after every key block the threads average the selection blocks it completed.
+template <int D, int MODE, int GI, bool POOL = false>   // GI: 0 = no importance output, else the heads per KV head
 __global__ void __launch_bounds__(2 * kRows, 2)
 dense_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const SelParams P) {
   constexpr int NC = D / 64;
@@ -686,6 +693,10 @@ dense_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
   const uint32_t sStage = sQ;
   int* const row_dst = reinterpret_cast<int*>(dense_smem + kRows * kStageStride);
   float* const xchg = reinterpret_cast<float*>(dense_smem + kTileQ);   // [2 halves][kRows]
+  // POOL: the head means of the last 128 logit columns of every query of the tile, [QT][kRing] bf16 (rows padded so
+  // that neighbouring queries fall on different banks)
+  constexpr int kRing = 128 + 32;
+  __nv_bfloat16* const ring = reinterpret_cast<__nv_bfloat16*>(dense_smem + kTileQ + 1024);
   // barriers: K buffers full (2), V buffers full (2), S buffers complete (2), PV complete, drain
   const uint32_t bar0 = smem_u32(&bars[0]), bar_pv = bar0 + 48;
   auto bar_k = [&](int t) { return bar0 + (uint32_t)(t & 1) * 8; };
@@ -788,6 +799,11 @@ dense_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     if (nb > 1) issue_s(1);
   }
 
+  // POOL: selection blocks per key block, and the (batch, head) slice of the pooled output
+  const int cpf_shift = POOL ? 31 - __clz(P.cpf) : 0, kb_shift = 6 - cpf_shift;
+  const float inv_cpf = POOL ? 1.f / (float)P.cpf : 1.f;
+  __nv_bfloat16* const pooled_head = POOL ? P.pooled + ((int64_t)b * P.Hkv + h) * P.N * P.pool_cols : nullptr;
+
   float m_ref = -INFINITY, l = 0.f;   // l: this thread's half of the row sum
   for (int t = 0; t < nb; ++t) {
     const int j = jb + t, sb = t & 1;
@@ -840,10 +856,21 @@ dense_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
       float* imp_row = P.importance + (((int64_t)b * P.Hkv + h) * P.N + (valid ? i : 0)) * P.ncb;
       constexpr float inv_g = 1.f / (float)(IMP ? GI : 1);
       const int col0 = j * kBlock + half * 32 + first - P.rule.num_mem;
+      if constexpr (POOL) {
+        // this lane's `owned` neighbouring columns in one store (indexed by logit column, memory slots included)
+        uint32_t w[owned / 2];
 #pragma unroll
-      for (int x = 0; x < owned; ++x) {
-        const int col = col0 + x;
-        if (valid && first + x <= lim && col >= 0 && col < P.ncb) imp_row[col] = round_bf16(v[x] * inv_g);
+        for (int x = 0; x < owned / 2; ++x) w[x] = pack_bf16(v[2 * x] * inv_g, v[2 * x + 1] * inv_g);
+        __nv_bfloat16* dst = ring + q_local * kRing + ((j & 1) * kBlock + half * 32 + first);
+        if constexpr (owned == 2) *reinterpret_cast<uint32_t*>(dst) = w[0];
+        else if constexpr (owned == 4) *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
+        else *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+      } else {
+#pragma unroll
+        for (int x = 0; x < owned; ++x) {
+          const int col = col0 + x;
+          if (valid && first + x <= lim && col >= 0 && col < P.ncb) imp_row[col] = round_bf16(v[x] * inv_g);
+        }
       }
     }
     // most blocks are fully visible to every row of the warp: they take the loops without per-column tests
@@ -860,6 +887,25 @@ dense_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     xchg[half * kRows + row] = m;
     __syncthreads();
     m = fmaxf(m, xchg[(half ^ 1) * kRows + row]);
+    if constexpr (POOL) {
+      // the selection blocks whose last column this key block brought: mean of their cpf columns in the order and
+      // with the roundings of the selection kernel's own averaging; only blocks wholly before the query's own block
+      // are stored (all others have probability 0 in the selection, whatever their logits)
+      const int nm = P.rule.num_mem;
+      const int b_lo = t == 0 ? 0 : (j * kBlock - nm) >> cpf_shift;
+      const int b_hi = min(P.pool_cols, (j * kBlock + kBlock - nm) >> cpf_shift);
+      for (int e = tid; e < (QT << kb_shift); e += kThreads) {
+        const int pq = e >> kb_shift, bb = b_lo + (e & ((1 << kb_shift) - 1));
+        const int qi = i0 + pq;
+        if (bb < b_hi && qi < P.N && (bb + 1) * P.pool_block <= qi) {
+          const __nv_bfloat16* src = ring + pq * kRing;
+          const int c0 = (bb << cpf_shift) + nm;
+          float sum = 0.f;
+          for (int c = 0; c < (1 << cpf_shift); ++c) sum += __bfloat162float(src[(c0 + c) & 127]);
+          pooled_head[(int64_t)qi * P.pool_cols + bb] = __float2bfloat16_rn(sum * inv_cpf);   // cpf is a power of two
+        }
+      }
+    }
     const float m_blk2 = m * P.scale_log2;   // -inf when the row sees nothing of this block
     bool need = false;
     float alpha = 1.f;
@@ -1730,6 +1776,8 @@ struct SelProblem {
   float *dq, *dk, *dv, *slot_grads;
   nsa_tensor dq_out;       // backward, optional: dq in the dtype and strides the caller chose
   float* importance;
+  __nv_bfloat16* pooled;   // compressed forward, instead of importance: per-selection-block means, see SelParams
+  int cpf;
   void* workspace;
   int64_t workspace_bytes;
   const void* index;       // backward: the index part of the forward's work buffer, or NULL to rebuild it
@@ -1910,6 +1958,7 @@ static void fill_params(SelParams& P, const SelProblem& a, const SelPlan& p, uin
   P.diag = a.diag; P.scale = a.scale; P.scale_log2 = a.scale * kLog2e;
   P.rule = make_rule(a, p);
   P.importance = a.importance; P.ncb = a.ncb; P.round_bf16 = a.round_bf16;
+  P.pooled = a.pooled; P.cpf = a.cpf > 0 ? a.cpf : 1; P.pool_cols = a.ncb / P.cpf; P.pool_block = P.cpf * a.stride;
 }
 
 static int num_sms() {
@@ -1945,7 +1994,18 @@ static int run_fwd(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaStrea
                                     cudaSharedmemCarveoutMaxShared));                                                 \
       dense_fwd_kernel<D, MODE, GI><<<(unsigned)tiles, 2 * kRows, smem, st>>>(tmK, tmV, P);                               \
     } while (0)
+#define NSA_DENSE_LAUNCH_POOL(GI)                                                                                     \
+    do {                                                                                                              \
+      CUDA_TRY(cudaFuncSetAttribute(dense_fwd_kernel<D, kModeCmp, GI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
+      CUDA_TRY(cudaFuncSetAttribute(dense_fwd_kernel<D, kModeCmp, GI, true>, cudaFuncAttributePreferredSharedMemoryCarveout, \
+                                    cudaSharedmemCarveoutMaxShared));                                                 \
+      dense_fwd_kernel<D, kModeCmp, GI, true><<<(unsigned)tiles, 2 * kRows, smem, st>>>(tmK, tmV, P);                   \
+    } while (0)
     if (a.mode == kModeSwa) NSA_DENSE_LAUNCH(kModeSwa, 0);
+    else if (P.pooled != nullptr && p.G == 4) NSA_DENSE_LAUNCH_POOL(4);
+    else if (P.pooled != nullptr && p.G == 8) NSA_DENSE_LAUNCH_POOL(8);
+    else if (P.pooled != nullptr && p.G == 16) NSA_DENSE_LAUNCH_POOL(16);
+    else if (P.pooled != nullptr) return NSA_ERR_UNSUPPORTED;
     else if (P.importance == nullptr) NSA_DENSE_LAUNCH(kModeCmp, 0);
     else if (p.G == 1) NSA_DENSE_LAUNCH(kModeCmp, 1);
     else if (p.G == 2) NSA_DENSE_LAUNCH(kModeCmp, 2);
@@ -1953,6 +2013,7 @@ static int run_fwd(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaStrea
     else if (p.G == 8) NSA_DENSE_LAUNCH(kModeCmp, 8);
     else NSA_DENSE_LAUNCH(kModeCmp, 16);
 #undef NSA_DENSE_LAUNCH
+#undef NSA_DENSE_LAUNCH_POOL
     CUDA_TRY(cudaGetLastError());
     count_launches(1);
     return NSA_OK;
@@ -2062,7 +2123,20 @@ static bool cmp_problem(SelProblem& x, const nsa_cmp_fwd_args& a) {
   x.B = a.batch; x.Hq = a.q_heads; x.Hkv = a.kv_heads; x.N = a.seq; x.Nk = a.num_mem + a.ncb; x.D = a.dim_head;
   x.mode = kModeCmp; x.stride = a.stride; x.num_mem = a.num_mem; x.ncb = a.ncb; x.round_bf16 = 1;
   x.importance = a.importance; x.scale = a.scale;
+  x.pooled = static_cast<__nv_bfloat16*>(a.pooled); x.cpf = a.pool;
   return supported(x);
+}
+
+// The forward can average the importance over the selection blocks itself (`pooled`) when the ring of head means fits
+// beside the row maxima in shared memory (128 / G queries x 128 columns of bf16: G >= 4) and every key block of 64
+// columns completes a whole number of selection blocks' worth of columns (cpf a power of two).
+bool sm100_cmp_fwd_pools(const nsa_cmp_fwd_args& a) {
+  SelProblem x;
+  if (a.impl == NSA_IMPL_SIMT || !cmp_problem(x, a) || !dense_forward_serves(x)) return false;
+  const int G = x.Hq / x.Hkv;
+  if (G != 4 && G != 8 && G != 16) return false;
+  if (a.pool != 1 && a.pool != 2 && a.pool != 4 && a.pool != 8 && a.pool != 16) return false;
+  return a.num_mem <= kBlock && a.ncb / a.pool >= 1;
 }
 
 static int check_ws(const SelProblem& x, const SelPlan& p, uint8_t** ws) {
@@ -2167,6 +2241,10 @@ int64_t sm100_cmp_workspace_bytes(const nsa_cmp_fwd_args& a, bool backward) {
 int sm100_cmp_fwd(const nsa_cmp_fwd_args& a, cudaStream_t st) {
   SelProblem x;
   if (!cmp_problem(x, a) || !dense_forward_serves(x)) return NSA_ERR_UNSUPPORTED;
+  if (x.pooled != nullptr) {
+    if (!sm100_cmp_fwd_pools(a)) return NSA_ERR_UNSUPPORTED;
+    x.importance = nullptr;
+  }
   if (x.importance != nullptr) {
     // columns a query cannot see carry the head mean of the sentinel; the kernel overwrites the visible ones
     float fill = 0.f;
@@ -2191,6 +2269,7 @@ int sm100_cmp_bwd(const nsa_cmp_bwd_args& b, cudaStream_t st) {
   SelProblem x;
   if (!cmp_problem(x, b.fwd)) return NSA_ERR_UNSUPPORTED;
   x.importance = nullptr;
+  x.pooled = nullptr;
   x.dout = b.dout; x.dq = b.dq; x.dk = b.dck; x.dv = b.dcv; x.dq_out = b.dq_out;
   x.index = b.index; x.index_bytes = b.index_bytes; x.delta = b.delta;
   return problem_bwd(x, st);

@@ -224,8 +224,10 @@ class SparseAttention(Module):
         ck_full, cv_full = torch.cat((mem_k, ck), dim=-2), torch.cat((mem_v, cv), dim=-2)
         sel_heads = hkv if self.query_heads_share_selected_kv else h
         num_selected = min(self.num_selected_blocks, ncb, ncb // (sel // st))
+        # the kernel also averages the logits per selection block where it can, unless their gradient is wanted
+        pool = sel // st if self.causal and not self.use_diff_topk and sel % st == 0 else 0
         o_cmp, importance = ops.compressed_attend(q, ck_full, cv_full, num_mem, st, self.causal, sel_heads=sel_heads,
-                                                  want_importance=True, impl=impl) if num_selected > 0 else \
+                                                  want_importance=True, impl=impl, pool=pool) if num_selected > 0 else \
             (ops.compressed_attend(q, ck_full, cv_full, num_mem, st, self.causal, want_importance=False, impl=impl), None)
 
         qr, kr = self.rotary_emb.rotate_queries_with_cached_keys(q, k)

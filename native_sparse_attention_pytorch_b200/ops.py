@@ -290,9 +290,9 @@ def mask_sentinel(dtype):
     return torch.tensor(-torch.finfo(dtype).max // 10, dtype=dtype).float().item()
 
 
-def _cmp_args(q, ck, cv, out, lse, imp, sel_heads, num_mem, stride, causal, impl, scale):
+def _cmp_args(q, ck, cv, out, lse, imp, sel_heads, num_mem, stride, causal, impl, scale, pooled=None, pool=0):
     b, hq, n, d = q.shape
-    return L.CmpFwdArgs(q=L.t4(q), ck=L.t4(ck), cv=L.t4(cv), out=L.t4(out), lse=L.ptr(lse), importance=L.ptr(imp),
+    return L.CmpFwdArgs(pooled=L.ptr(pooled), pool=pool, q=L.t4(q), ck=L.t4(ck), cv=L.t4(cv), out=L.t4(out), lse=L.ptr(lse), importance=L.ptr(imp),
                         batch=b, q_heads=hq, kv_heads=ck.shape[1], sel_heads=sel_heads, seq=n, dim_head=d,
                         num_mem=num_mem, ncb=ck.shape[2] - num_mem, stride=stride, causal=int(causal),
                         dtype=L.dtype_code(q), impl=impl, scale=scale, sentinel=mask_sentinel(q.dtype), workspace=None,
@@ -300,11 +300,13 @@ def _cmp_args(q, ck, cv, out, lse, imp, sel_heads, num_mem, stride, causal, impl
 
 
 class CompressedAttention(Function):
-    """out, importance = f(q, ck, cv, num_mem, stride, causal, sel_heads, want_importance, impl);
-    ck, cv carry the memory slots in front.  importance is [B, sel_heads, N, ncb] fp32, no gradient."""
+    """out, importance = f(q, ck, cv, num_mem, stride, causal, sel_heads, want_importance, impl, pool);
+    ck, cv carry the memory slots in front.  importance is [B, sel_heads, N, ncb] fp32, no gradient; with pool > 0,
+    where the library can (nsa_cmp_fwd_pools), it is instead the bf16 tensor [B, sel_heads, N, ncb // pool] of
+    per-selection-block means that `select_blocks` recognises by its dtype."""
 
     @staticmethod
-    def forward(ctx, q, ck, cv, num_mem, stride, causal, sel_heads, want_importance, impl):
+    def forward(ctx, q, ck, cv, num_mem, stride, causal, sel_heads, want_importance, impl, pool=0):
         L.require_cuda(q, ck, cv)
         lib = L.load()
         q, ck, cv = L.rowwise(q), L.rowwise(ck), L.rowwise(cv)
@@ -312,10 +314,18 @@ class CompressedAttention(Function):
         ncb = ck.shape[2] - num_mem
         out = _empty_like_rows(q)
         lse = torch.empty(b, hq, n, dtype=torch.float32, device=q.device)
-        imp = torch.empty(b, sel_heads, n, ncb, dtype=torch.float32, device=q.device) if want_importance else None
         scale = d ** -0.5
+        pooled = None
+        if want_importance and pool > 0:
+            probe = _cmp_args(q, ck, cv, out, lse, None, sel_heads, num_mem, stride, causal, impl, scale, None, pool)
+            if lib.nsa_cmp_fwd_pools(C.byref(probe)):
+                # entries at and past a query's own block are never written nor read
+                pooled = torch.empty(b, sel_heads, n, ncb // pool, dtype=torch.bfloat16, device=q.device)
+        imp = torch.empty(b, sel_heads, n, ncb, dtype=torch.float32, device=q.device) \
+            if want_importance and pooled is None else None
         with torch.cuda.device(q.device):
-            args = _cmp_args(q, ck, cv, out, lse, imp, sel_heads, num_mem, stride, causal, impl, scale)
+            args = _cmp_args(q, ck, cv, out, lse, imp, sel_heads, num_mem, stride, causal, impl, scale, pooled,
+                             pool if pooled is not None else 0)
             ws = _with_workspace(args, False, q.device, 'nsa_cmp_workspace_bytes')
             L.check(lib.nsa_cmp_fwd(C.byref(args), L.stream_of(q)))
             _keep_status(ws)
@@ -323,7 +333,10 @@ class CompressedAttention(Function):
         ctx.save_for_backward(q, ck, cv, out, lse)
         ctx.cfg = (num_mem, stride, causal, sel_heads, impl, scale)
         ctx.set_materialize_grads(False)   # no gradient through the importance unless the top-k is differentiable
-        if imp is None:
+        if pooled is not None:
+            imp = pooled
+            ctx.mark_non_differentiable(imp)
+        elif imp is None:
             imp = torch.empty(0, device=q.device)
             ctx.mark_non_differentiable(imp)
         return out, imp
@@ -361,7 +374,7 @@ class CompressedAttention(Function):
                 _keep_index(key, ws, int(lib.nsa_cmp_index_bytes(C.byref(fwd))))
             _keep_status(ws)
             del ws
-        return dq, dck.to(ck.dtype), dcv.to(cv.dtype), None, None, None, None, None, None
+        return dq, dck.to(ck.dtype), dcv.to(cv.dtype), None, None, None, None, None, None, None
 
 
 def _importance_backward(dimp, q, ck, dq, dck, num_mem, stride, causal, sel_heads, scale):
@@ -387,10 +400,15 @@ def _importance_backward(dimp, q, ck, dq, dck, num_mem, stride, causal, sel_head
     dck[:, :, num_mem:] += dck_part.view(b, hkv, per_kv, ncb, d).sum(dim=2)
 
 
-def compressed_attend(q, ck, cv, num_mem, stride, causal, sel_heads=None, want_importance=True, impl='auto'):
+def compressed_attend(q, ck, cv, num_mem, stride, causal, sel_heads=None, want_importance=True, impl='auto', pool=0):
+    """Compressed attention and, with `want_importance`, the head-averaged logits [B, sel_heads, N, ncb] in fp32.
+    `pool` = block columns per selection block (selection_block_size // stride) lets the kernel do the per-block mean
+    of the selection chain as well, where it can: the second result is then a bf16 tensor [B, sel_heads, N,
+    ncb // pool] (defined before each query's own block only, no gradient) for `select_blocks`; callers that need the
+    full matrix or its gradient leave pool at 0."""
     sel_heads = ck.shape[1] if sel_heads is None else sel_heads
     out, imp = CompressedAttention.apply(q, ck, cv, num_mem, stride, causal, sel_heads, want_importance,
-                                         L.IMPL_BY_NAME[impl])
+                                         L.IMPL_BY_NAME[impl], pool)
     return (out, imp) if want_importance else out
 
 
@@ -435,7 +453,8 @@ class _SelectValuesGrad(Function):
 
 
 def select_blocks(importance, block, stride, nsel, dtype=torch.float32, input_is_prob=False):
-    """As `_select_blocks`; when `importance` requires grad, the returned values carry it (differentiable top-k)."""
+    """As `_select_blocks`; when `importance` requires grad, the returned values carry it (differentiable top-k).
+    A bf16 `importance` is the pooled tensor of `compressed_attend(..., pool=block // stride)`."""
     vals, idx = _select_blocks(importance.detach(), block, stride, nsel, dtype, input_is_prob)
     if torch.is_grad_enabled() and importance.requires_grad and not input_is_prob and vals.numel() > 0:
         vals = _SelectValuesGrad.apply(importance, vals, idx, block, stride)
@@ -448,18 +467,21 @@ def _select_blocks(importance, block, stride, nsel, dtype=torch.float32, input_i
     k = min(nsel, ncb // (block // stride)).  See nsa_select in include/nsa_b200.h."""
     L.require_cuda(importance)
     lib = L.load()
-    importance = importance.contiguous().float()
+    pooled = importance.dtype == torch.bfloat16 and not input_is_prob
+    importance = importance.contiguous() if pooled else importance.contiguous().float()
     b, hs, n, ncb = importance.shape
-    cpf = 1 if input_is_prob else block // stride
+    cpf = 1 if input_is_prob or pooled else block // stride
     cols = ncb // cpf
     k = min(nsel, cols)
     idx = torch.empty(b, hs, n, k, dtype=torch.int64, device=importance.device)
     vals = torch.empty(b, hs, n, k, dtype=torch.float32, device=importance.device)
     if k > 0 and idx.numel() > 0:
         code = L.NSA_BF16 if dtype == torch.bfloat16 else L.NSA_F32
-        args = L.SelectArgs(importance=L.ptr(importance), idx=L.ptr(idx), vals=L.ptr(vals), rows=b * hs, seq=n,
-                            ncb=ncb, cpf=cpf, k=k, block=block, exclude_own=int(block != stride and not input_is_prob),
-                            input_is_prob=int(input_is_prob), dtype=code)
+        args = L.SelectArgs(importance=None if pooled else L.ptr(importance), idx=L.ptr(idx), vals=L.ptr(vals),
+                            rows=b * hs, seq=n, ncb=ncb, cpf=cpf, k=k, block=block,
+                            exclude_own=int(block != stride and not input_is_prob),
+                            input_is_prob=int(input_is_prob), dtype=code,
+                            pooled=L.ptr(importance) if pooled else None, causal_limit=int(pooled))
         with torch.cuda.device(importance.device):
             L.check(lib.nsa_select(C.byref(args), L.stream_of(importance)))
     return vals.to(dtype), idx

@@ -88,11 +88,12 @@ def attend_core(q, qr, kr, v, ck, cv, gates, *, num_mem, stride, block, num_sele
                           selected=ops.native_sparse_attend, sliding=ops.sliding_window_attend,
                           combine=ops.gated_combine)
         kw = dict(impl=impl)
+        ckw = dict(impl=impl, pool=block // stride if causal and block % stride == 0 else 0)
     else:
-        kw = {}
+        kw = ckw = {}
     hkv = v.shape[1]
     o_cmp, importance = attend_fns['compressed'](q, ck, cv, num_mem, stride, causal, sel_heads=hkv,
-                                                 want_importance=True, **kw)
+                                                 want_importance=True, **ckw)
     vals, idx = attend_fns['select'](importance, block, stride, num_selected, dtype=q.dtype)
     fmask = vals > 1e-10
     o_sel = attend_fns['selected'](qr, kr, v, block, idx, fmask, include_block_causal=causal, **kw)

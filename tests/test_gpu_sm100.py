@@ -216,6 +216,61 @@ def test_sm100_compressed_matches_oracle(case):
     check_importance(imp_simt, q, ck, cv, mem, st, m, 'importance of the generic kernels')
 
 
+POOL_CASES = [
+    # b, hq, hkv, n, d, stride, num_mem, cpf, nsel
+    (2, 8, 2, 1000, 64, 4, 1, 4, 6),       # selection block 16
+    (1, 8, 1, 2077, 128, 16, 1, 4, 16),    # the long-context grouping: 8 heads per KV head, dim_head 128, block 64
+    (1, 16, 4, 1500, 64, 16, 1, 4, 16),    # four heads per KV head (32 queries per tile)
+    (1, 16, 1, 700, 64, 8, 2, 2, 5),       # sixteen; two memory slots; two columns per block
+    (1, 8, 2, 900, 64, 16, 1, 1, 8),       # selection block = stride: no averaging, no own-block exclusion
+    (1, 4, 1, 1300, 64, 4, 3, 8, 4),       # three memory slots, eight columns per block
+]
+
+
+@pytest.mark.parametrize('case', POOL_CASES)
+def test_compressed_forward_pools_the_importance_per_selection_block(case):
+    """With `pool` the compressed forward also does the per-block mean of the selection chain and hands a bf16 tensor
+    of one value per selection block to the selection, instead of the fp32 matrix of every block column.  Wherever it
+    is defined (the blocks before a query's own) it must hold, bit for bit, the mean the selection kernel would have
+    formed from the full matrix, and the selection from it must be the same in every slot, masked ones included."""
+    b, hq, hkv, n, d, st, m, cpf, nsel = case
+    block = st * cpf
+    ncb = (n - 2 * st) // st + 1
+    q = recipe.randn((b, hq, n, d), 1).bfloat16().to(DEV)
+    ck = recipe.randn((b, hkv, m + ncb, d), 2).bfloat16().to(DEV)
+    cv = recipe.randn((b, hkv, m + ncb, d), 3).bfloat16().to(DEV)
+    out0, imp = nsa.compressed_attend(q, ck, cv, m, st, True, impl='sm100')
+    out1, pooled = nsa.compressed_attend(q, ck, cv, m, st, True, impl='sm100', pool=cpf)
+    ops.check_device_status()
+    assert imp.dtype == torch.float32 and pooled.dtype == torch.bfloat16
+    cols = ncb // cpf
+    assert pooled.shape == (b, hkv, n, cols)
+    assert torch.equal(out0, out1)
+    # the selection kernel's own averaging: the columns of a block added one after the other in fp32, divided, rounded
+    x = imp[..., : cols * cpf].reshape(b, hkv, n, cols, cpf)
+    acc = torch.zeros_like(x[..., 0])
+    for c in range(cpf):
+        acc = acc + x[..., c]
+    want = (acc / float(cpf)).bfloat16() if cpf > 1 else x[..., 0].bfloat16()
+    defined = torch.arange(cols, device=DEV)[None, :] < (torch.arange(n, device=DEV) // block)[:, None]
+    assert defined.any()
+    assert torch.equal(pooled[..., defined], want[..., defined])
+    k = min(nsel, cols)
+    vals0, idx0 = nsa.select_blocks(imp, block, st, k, dtype=torch.bfloat16)
+    vals1, idx1 = nsa.select_blocks(pooled, block, st, k, dtype=torch.bfloat16)
+    assert torch.equal(idx0, idx1) and torch.equal(vals0, vals1)
+    assert (vals1 > 1e-10).any()
+    observe(f'pooled selection {case}', identical_rows=float(torch.equal(idx0, idx1)),
+            selected_share=(vals1 > 1e-10).float().mean().item())
+
+
+def test_pooled_importance_is_refused_where_it_is_not_served():
+    q = recipe.randn((1, 2, 200, 64), 1).bfloat16().to(DEV)         # two heads per KV head: the ring does not fit
+    ck = recipe.randn((1, 1, 51, 64), 2).bfloat16().to(DEV)
+    out, imp = nsa.compressed_attend(q, ck, ck, 1, 4, True, pool=4)
+    assert imp.dtype == torch.float32                                # the operator falls back to the full matrix
+
+
 @pytest.mark.parametrize('d', [64, 128])
 def test_dense_forward_rescales_when_later_keys_dominate(d):
     # Keys grow with their position, so the running maximum of a row jumps by far more than 2^8 from one key block to
