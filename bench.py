@@ -81,7 +81,11 @@ PREFILL_WORKLOADS = {
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, from single-launch ncu captures of this command
 # (`ncu --set full -k regex:<kernel> -c 1 python bench.py --steps 2 --warmup 3 --no-cpu-baseline`) at this build.
 NCU_DRAM_BYTES = {
-    'sel_fwd_kernel': 899.0e6 + 2427.3e6,
+    'sel_bwd_ws_kernel': 701.6e6 + 2195.7e6,
+    'sel_fwd_kernel': 902.5e6 + 2425.9e6,
+    'sel_merge_kernel': 2417.0e6,      # dram__bytes.sum.per_second x gpu__time_duration of a sections-only capture
+    'sel_dq_merge_kernel': 2312.0e6,
+    'sel_delta_kernel': 276.0e6,
 }
 # the other workloads whose numbers ride on the default line: (name, timed steps)
 EXTRA_WORKLOADS = (('layer_fwd_bwd_b2_n16384_dim1024_h16kv4_d64', 5), ('prefill_b1_n65536_h64kv8_d128', 3))

@@ -371,6 +371,8 @@ typedef struct {
   void* d_sel;
   void* d_swa;
   float* d_gates;                 /* [B, q_heads, N, 3] contiguous fp32       */
+  float* delta;                   /* optional, [3, B, q_heads, N] fp32: gates_s * d_gates_s, which is the row sum
+                                     sum_c o_s * d_o_s every branch backward starts from (`delta` there)        */
 } nsa_combine_bwd_args;
 
 int nsa_combine_bwd(const nsa_combine_bwd_args* args, void* stream);

@@ -74,7 +74,8 @@ class CombineFwdArgs(C.Structure):
 
 
 class CombineBwdArgs(C.Structure):
-    _fields_ = [('fwd', CombineFwdArgs), ('dout', vp), ('d_cmp', vp), ('d_sel', vp), ('d_swa', vp), ('d_gates', vp)]
+    _fields_ = [('fwd', CombineFwdArgs), ('dout', vp), ('d_cmp', vp), ('d_sel', vp), ('d_swa', vp), ('d_gates', vp),
+                ('delta', vp)]
 
 
 MAX_GATHER = 8

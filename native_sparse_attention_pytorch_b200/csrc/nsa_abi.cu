@@ -517,6 +517,7 @@ int nsa_combine_bwd(const nsa_combine_bwd_args* a, void* stream) {
   P.dout = a->dout;
   P.d_o[0] = a->d_cmp; P.d_o[1] = a->d_sel; P.d_o[2] = a->d_swa;
   P.d_gates = a->d_gates;
+  P.delta = a->delta;
   return launch_combine(P, a->fwd.dtype, true, (cudaStream_t)stream);
 }
 

@@ -123,7 +123,10 @@ __global__ void __launch_bounds__(128) combine_bwd_kernel(const CombineParams P)
 #pragma unroll
   for (int s = 0; s < 3; ++s) {
     const float t = warp_sum(dg[s]);
-    if (lane == 0) P.d_gates[task * 3 + s] = t;
+    if (lane == 0) {
+      P.d_gates[task * 3 + s] = t;
+      if (P.delta != nullptr) P.delta[s * ((int64_t)P.batch * P.q_heads * P.seq) + task] = gs[s] * t;
+    }
   }
 }
 
@@ -135,7 +138,7 @@ __global__ void __launch_bounds__(256) combine_bwd_vec_kernel(const CombineParam
   const int64_t task = ((int64_t)blockIdx.x * 256 + threadIdx.x) / TPR;
   const int part = threadIdx.x % TPR;
   const bool live = task < tasks;
-  float dg[3] = {0.f, 0.f, 0.f};
+  float dg[3] = {0.f, 0.f, 0.f}, gate[3] = {0.f, 0.f, 0.f};
   if (live) {
     const Coord4 at = split4(task, P.seq, P.q_heads, 1);
     const int n = at.i0, h = at.i1, b = at.i3;
@@ -146,6 +149,7 @@ __global__ void __launch_bounds__(256) combine_bwd_vec_kernel(const CombineParam
 #pragma unroll
     for (int s = 0; s < 3; ++s) {
       const float gs = Elem<T>::to_float(g[s]);
+      gate[s] = gs;
       const uint4 oraw = *reinterpret_cast<const uint4*>((const T*)P.o[s] + b * P.o_sb[s] + h * P.o_sh[s] +
                                                         (int64_t)n * P.o_sn[s] + c);
       const T* ov = reinterpret_cast<const T*>(&oraw);
@@ -164,7 +168,10 @@ __global__ void __launch_bounds__(256) combine_bwd_vec_kernel(const CombineParam
   for (int s = 0; s < 3; ++s) {
 #pragma unroll
     for (int o = TPR / 2; o > 0; o >>= 1) dg[s] += __shfl_xor_sync(kFullMask, dg[s], o);
-    if (live && part == 0) P.d_gates[task * 3 + s] = dg[s];
+    if (live && part == 0) {
+      P.d_gates[task * 3 + s] = dg[s];
+      if (P.delta != nullptr) P.delta[s * tasks + task] = gate[s] * dg[s];
+    }
   }
 }
 

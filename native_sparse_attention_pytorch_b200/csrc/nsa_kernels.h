@@ -54,6 +54,7 @@ struct CombineParams {
   void* out;
   void* d_o[3];
   float* d_gates;
+  float* delta;            // backward, optional: [3][batch * q_heads * seq] gate x d gate
   int batch, q_heads, seq, d;
 };
 

@@ -587,17 +587,17 @@ class GatedCombine(Function):
         b, h, n, d = o_cmp.shape
         d_cmp, d_sel, d_swa = (torch.empty(b, h, n, d, dtype=o_cmp.dtype, device=o_cmp.device) for _ in range(3))
         d_gates = torch.empty(b, h, n, 3, dtype=torch.float32, device=o_cmp.device)
+        # Every branch backward starts from delta = sum_d out_s * d out_s of each row.  With d out_s = gate_s * dout
+        # that is gate_s * (sum_d out_s * dout) = gate_s * d gate_s, which this kernel forms anyway: it writes it out,
+        # the branch receives it through the gradient tensor it is about to get, and skips its own pass.
+        deltas = torch.empty(3, b, h, n, dtype=torch.float32, device=o_cmp.device) if HAND_OVER_DELTA else None
         fwd = L.CombineFwdArgs(o_cmp=L.t4(o_cmp), o_sel=L.t4(o_sel), o_swa=L.t4(o_swa), gates=L.t4(gates),
                                out=None, batch=b, q_heads=h, seq=n, dim_head=d, dtype=L.dtype_code(o_cmp))
         args = L.CombineBwdArgs(fwd=fwd, dout=L.ptr(dout), d_cmp=L.ptr(d_cmp), d_sel=L.ptr(d_sel),
-                                d_swa=L.ptr(d_swa), d_gates=L.ptr(d_gates))
+                                d_swa=L.ptr(d_swa), d_gates=L.ptr(d_gates), delta=L.ptr(deltas))
         with torch.cuda.device(dout.device):
             L.check(lib.nsa_combine_bwd(C.byref(args), L.stream_of(dout)))
-        if HAND_OVER_DELTA:
-            # Every branch backward starts from delta = sum_d out_s * d out_s of each row.  With d out_s = gate_s * dout
-            # that is gate_s * (sum_d out_s * dout) = gate_s * d gate_s, which this kernel has just formed: hand it to
-            # the branch through the gradient tensor it is about to receive, and the branch skips its own pass.
-            deltas = (d_gates * gates.float()).permute(3, 0, 1, 2).contiguous()       # [3, B, H, N] fp32
+        if deltas is not None:
             for s_, t_ in enumerate((d_cmp, d_sel, d_swa)):
                 t_._nsa_delta = deltas[s_]
         return d_cmp, d_sel, d_swa, d_gates.to(gates.dtype)
