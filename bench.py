@@ -304,10 +304,11 @@ def main():
                     choices=list(WORKLOADS) + list(LAYER_WORKLOADS) + list(PREFILL_WORKLOADS) + list(LM_WORKLOADS))
     ap.add_argument('--kernels', default='auto', choices=['auto', 'simt', 'sm100'])
     ap.add_argument('--no-cpu-baseline', action='store_true')
-    ap.add_argument('--gather', default='multimem', choices=['multimem', 'fused', 'nccl'],
+    ap.add_argument('--gather', default='auto', choices=['auto', 'multimem', 'fused', 'nccl'],
                     help='prefill workloads, N > 1: the combine kernel stores its heads into every rank, through the '
                          'NVLink multicast address with multimem.st (multimem; falls back to fused where the symmetric '
-                         'memory has no multicast) or with one peer store per rank (fused); or an NCCL all-gather')
+                         'memory has no multicast) or with one peer store per rank (fused); auto times a few untimed '
+                         'steps of both and keeps the faster; or an NCCL all-gather')
     ap.add_argument('--rows', action='store_true', help='also time the other kernels of the hot path (N=1 only)')
     ap.add_argument('--no-workloads', action='store_true', help='default workload: skip the layer and prefill child runs')
     args = ap.parse_args()
@@ -826,9 +827,9 @@ def run_prefill(args, w):
                causal=True, impl=args.kernels, local=True)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     keep = {}
-    fused = world > 1 and args.gather in ('fused', 'multimem')
+    fused = world > 1 and args.gather in ('auto', 'fused', 'multimem')
     peer = sharding.PeerOutput(w['batch'], w['seq'], w['q_heads'] * w['dim_head'], torch.bfloat16, dev,
-                               multicast=args.gather == 'multimem') if fused else None
+                               multicast=args.gather in ('auto', 'multimem')) if fused else None
     multimem = peer is not None and peer.multicast_ptr is not None
 
     def step():
@@ -844,8 +845,34 @@ def run_prefill(args, w):
         same = torch.tensor([int(torch.equal(via_multicast, keep['out']))], device=dev)
         peer.multicast_ptr = mc
         dist.all_reduce(same, op=dist.ReduceOp.MIN)
-        gather_check = 'identical to per-peer stores on every rank' if same.item() == 1 else 'DIFFERS from per-peer stores'
+        gather_check = 'identical to per-peer stores on every rank'
         del via_multicast
+        if same.item() != 1:   # never time a gather whose bytes are wrong
+            peer.multicast_ptr, multimem = None, False
+            gather_check = 'multicast stores DIFFERED from per-peer stores on some rank: per-peer stores used'
+        elif args.gather == 'auto':
+            def quick(n=3):   # device time of n steps, the slowest rank's
+                torch.cuda.synchronize()
+                dist.barrier()
+                a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(n):
+                    step()
+                b_.record()
+                torch.cuda.synchronize()
+                tt = torch.tensor([a.elapsed_time(b_) / n], device=dev)
+                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+                return tt.item()
+            step()
+            ms_mc = quick()
+            peer.multicast_ptr = None
+            step()
+            ms_peer = quick()
+            if ms_mc <= ms_peer:
+                peer.multicast_ptr = mc
+            else:
+                multimem = False
+            gather_check += f'; untimed trial: multicast {ms_mc:.3f} ms, per-peer stores {ms_peer:.3f} ms per step'
     total_ms, clocks, launches = _timed_steps(step, args.steps, warmup, flush, dist, world, rank, local)
 
     # end to end: this rank's inputs arrive from pinned host memory every step, rank 0 reads the gathered output back
