@@ -88,7 +88,8 @@ NCU_DRAM_BYTES = {
     'sel_delta_kernel': 276.0e6,
 }
 # the other workloads whose numbers ride on the default line: (name, timed steps)
-EXTRA_WORKLOADS = (('layer_fwd_bwd_b2_n16384_dim1024_h16kv4_d64', 5), ('prefill_b1_n65536_h64kv8_d128', 3))
+EXTRA_WORKLOADS = (('layer_fwd_bwd_b2_n16384_dim1024_h16kv4_d64', 5), ('prefill_b1_n65536_h64kv8_d128', 3),
+                   ('lm_step_b8_n8192_dim512_depth8', 3))
 CHILD_TIMEOUT_S = 240
 
 
