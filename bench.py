@@ -310,6 +310,9 @@ def main():
                          'NVLink multicast address with multimem.st (multimem; falls back to fused where the symmetric '
                          'memory has no multicast) or with one peer store per rank (fused); auto times a few untimed '
                          'steps of both and keeps the faster; or an NCCL all-gather')
+    ap.add_argument('--overlap', action='store_true', help='prefill, fused gather: stores on a side stream')
+    ap.add_argument('--head-splits', type=int, default=1,
+                    help='prefill, fused gather: query heads of a KV head in this many runs, each stored when complete')
     ap.add_argument('--rows', action='store_true', help='also time the other kernels of the hot path (N=1 only)')
     ap.add_argument('--no-workloads', action='store_true', help='default workload: skip the layer and prefill child runs')
     args = ap.parse_args()
@@ -833,47 +836,71 @@ def run_prefill(args, w):
                                multicast=args.gather in ('auto', 'multimem')) if fused else None
     multimem = peer is not None and peer.multicast_ptr is not None
 
+    # how the fused gather runs: through the multicast address or with per-peer stores; on a side stream or not; the
+    # query heads of a KV head in one piece or several (sharding.sharded_attend_core)
+    mode = {'multicast': multimem, 'overlap': bool(args.overlap), 'splits': args.head_splits}
+    mc_ptr = peer.multicast_ptr if peer is not None else None
+
     def step():
+        if peer is not None:
+            peer.multicast_ptr = mc_ptr if mode['multicast'] else None
         keep['out'] = sharding.sharded_attend_core(t['q'], t['qr'], t['kr'], t['v'], t['ck'], t['cv'], t['gates'],
-                                                   peer_output=peer, **cfg)
+                                                   peer_output=peer, overlap=mode['overlap'] and fused,
+                                                   head_splits=mode['splits'] if fused else 1, **cfg)
+
+    def quick(n=3):   # device time of n steps, the slowest rank's
+        torch.cuda.synchronize()
+        dist.barrier()
+        a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            step()
+        b_.record()
+        torch.cuda.synchronize()
+        tt = torch.tensor([a.elapsed_time(b_) / n], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return tt.item()
 
     gather_check = None
-    if multimem:   # once, untimed: the multicast stores give every rank the bytes the per-peer stores give
+    if fused:
+        # Untimed: the plain form (per-peer stores, one piece, same stream) gives the bytes every other form must
+        # reproduce on every rank; a form that differs is never timed.  With --gather auto the forms are then tried
+        # for three steps each and the fastest is kept.
+        g = w['q_heads'] // w['kv_heads']
+        forms = [dict(multicast=False, overlap=False, splits=1)]
+        if args.gather == 'auto':
+            for mcast in ((False, True) if multimem else (False,)):
+                for ov, sp in ((False, 1), (True, 1), (True, 2), (True, 4)):
+                    f = dict(multicast=mcast, overlap=ov, splits=sp)
+                    if g % sp == 0 and g // sp >= 1 and f not in forms:
+                        forms.append(f)
+        elif mode != forms[0]:
+            forms.append(dict(mode))
+        mode.update(forms[0])
         step()
-        via_multicast = keep['out'].clone()
-        mc, peer.multicast_ptr = peer.multicast_ptr, None
-        step()
-        same = torch.tensor([int(torch.equal(via_multicast, keep['out']))], device=dev)
-        peer.multicast_ptr = mc
-        dist.all_reduce(same, op=dist.ReduceOp.MIN)
-        gather_check = 'identical to per-peer stores on every rank'
-        del via_multicast
-        if same.item() != 1:   # never time a gather whose bytes are wrong
-            peer.multicast_ptr, multimem = None, False
-            gather_check = 'multicast stores DIFFERED from per-peer stores on some rank: per-peer stores used'
-        elif args.gather == 'auto':
-            def quick(n=3):   # device time of n steps, the slowest rank's
-                torch.cuda.synchronize()
-                dist.barrier()
-                a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record()
-                for _ in range(n):
-                    step()
-                b_.record()
-                torch.cuda.synchronize()
-                tt = torch.tensor([a.elapsed_time(b_) / n], device=dev)
-                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-                return tt.item()
+        plain = keep['out'].clone()
+        notes, best = [], (None, None)
+        for f in forms:
+            mode.update(f)
             step()
-            ms_mc = quick()
-            peer.multicast_ptr = None
-            step()
-            ms_peer = quick()
-            if ms_mc <= ms_peer:
-                peer.multicast_ptr = mc
+            same = torch.tensor([int(torch.equal(plain, keep['out']))], device=dev)
+            dist.all_reduce(same, op=dist.ReduceOp.MIN)
+            name = ('multicast' if f['multicast'] else 'per-peer') + (', side stream' if f['overlap'] else '') + \
+                   (f', {f["splits"]} head runs' if f['splits'] > 1 else '')
+            if same.item() != 1:
+                notes.append(f'{name}: DIFFERS from the plain form, not used')
+                continue
+            ms_f = quick() if len(forms) > 1 else 0.0
+            notes.append(f'{name}: {ms_f:.3f} ms' if len(forms) > 1 else f'{name}: identical on every rank')
+            if args.gather == 'auto':
+                if best[0] is None or ms_f < best[0]:
+                    best = (ms_f, dict(f))
             else:
-                multimem = False
-            gather_check += f'; untimed trial: multicast {ms_mc:.3f} ms, per-peer stores {ms_peer:.3f} ms per step'
+                best = (ms_f, dict(f))      # the requested form, if it is correct; else the plain one stays
+        mode.update(best[1] if best[1] is not None else forms[0])
+        multimem = mode['multicast']
+        gather_check = 'every form identical to the plain one unless noted; untimed trial per step: ' + '; '.join(notes)
+        del plain
     total_ms, clocks, launches = _timed_steps(step, args.steps, warmup, flush, dist, world, rank, local)
 
     # end to end: this rank's inputs arrive from pinned host memory every step, rank 0 reads the gathered output back
@@ -931,7 +958,9 @@ def run_prefill(args, w):
                    'sharding': f'{w["kv_heads"] // world} KV-head group(s) per rank, output gathered by '
                                + ('the combine kernel storing once through the NVLink multicast address (multimem.st)'
                                   if multimem else 'the combine kernel storing into every rank' if fused
-                                  else 'NCCL all-gather'),
+                                  else 'NCCL all-gather')
+                               + ((', on a side stream' if mode['overlap'] else '') +
+                                  (f', query heads in {mode["splits"]} runs' if mode['splits'] > 1 else '') if fused else ''),
                    'gather_check': gather_check},
         'roofline': {'bound': 'tensor', 'kernel': 'whole forward step of all branches (per GPU)',
                      'achieved': f_step / world / (ms / 1e3) / 1e12, 'peak': burst, 'unit': 'TFLOP/s',

@@ -101,6 +101,32 @@ def attend_core(q, qr, kr, v, ck, cv, gates, *, num_mem, stride, block, num_sele
     return (combine or attend_fns['combine'])(o_cmp, o_sel, o_swa, gates)
 
 
+def _split_pass(q, qr, kr, v, ck, cv, gates, peer_output, offset, splits, overlap, *, num_mem, stride, block,
+                num_selected, window, causal=True, impl='auto'):
+    """One pass of `sharded_attend_core` over the given KV heads with the query heads of every KV head cut into
+    `splits` runs: compressed attention and selection for all heads, then selected + sliding + combine-and-store per
+    run.  The features of run r of KV head h sit where the unsplit pass puts them."""
+    from . import ops
+    hkv, g, d = v.shape[1], q.shape[1] // v.shape[1], q.shape[-1]
+    if g % splits:
+        raise ValueError(f'{g} query heads per KV head do not split into {splits} runs')
+    per = g // splits
+    pool = block // stride if causal and block % stride == 0 else 0
+    o_cmp, importance = ops.compressed_attend(q, ck, cv, num_mem, stride, causal, sel_heads=hkv, want_importance=True,
+                                              impl=impl, pool=pool)
+    vals, idx = ops.select_blocks(importance, block, stride, num_selected, dtype=q.dtype)
+    fmask = vals > 1e-10
+    del importance
+    for r in range(splits):
+        for h in range(hkv) if hkv > 1 else (0,):
+            heads = slice(h * g + r * per, h * g + (r + 1) * per)
+            kh = slice(h, h + 1)
+            o_sel = ops.native_sparse_attend(qr[:, heads], kr[:, kh], v[:, kh], block, idx[:, kh], fmask[:, kh],
+                                             include_block_causal=causal, impl=impl)
+            o_swa = ops.sliding_window_attend(qr[:, heads], kr[:, kh], v[:, kh], window, causal, impl=impl)
+            peer_output.store(o_cmp[:, heads], o_sel, o_swa, gates[:, heads], offset + heads.start * d, overlap)
+
+
 def kv_head_range(kv_heads, world, rank):
     """KV heads owned by `rank` when the heads of one batch element are dealt out over `world` ranks."""
     if kv_heads % world != 0:
@@ -143,19 +169,48 @@ class PeerOutput:
         mc = int(getattr(self.handle, 'multicast_ptr', 0) or 0) if multicast else 0
         self.multicast_ptr = mc + inside if mc != 0 else None
 
+        self.side = torch.cuda.Stream(device=device)    # the stores of one pass travel while the next pass computes
+        self._alive = []
+
     def begin(self):
         self.handle.barrier(channel=0)
 
+    def store(self, o_cmp, o_sel, o_swa, gates, offset, overlap):
+        """Combine the three branch outputs of some heads and store them at feature `offset` of every rank's buffer.
+        With `overlap` the kernel runs on the side stream, behind everything the current stream has queued so far, so
+        that the NVLink traffic of this piece overlaps whatever the caller launches next."""
+        from . import ops
+        main = torch.cuda.current_stream(self.buffer.device)
+        if overlap:
+            self.side.wait_stream(main)
+            self._alive.append((o_cmp, o_sel, o_swa, gates))     # until end(): the side stream still reads them
+        with torch.cuda.stream(self.side if overlap else main):
+            if self.multicast_ptr is not None:
+                ops.gated_combine_gather(o_cmp, o_sel, o_swa, gates, [self.multicast_ptr], self.features, offset,
+                                         multicast=True)
+            else:
+                ops.gated_combine_gather(o_cmp, o_sel, o_swa, gates, self.ptrs, self.features, offset)
+
     def end(self):
+        torch.cuda.current_stream(self.buffer.device).wait_stream(self.side)
         self.handle.barrier(channel=1)
+        self._alive.clear()     # the barrier is queued behind the stores; the caching allocator frees in stream order
         return self.buffer
 
 
-def sharded_attend_core(q, qr, kr, v, ck, cv, gates, *, group=None, heads_per_pass=1, peer_output=None, **cfg):
+def sharded_attend_core(q, qr, kr, v, ck, cv, gates, *, group=None, heads_per_pass=1, peer_output=None,
+                        overlap=False, head_splits=1, **cfg):
     """`attend_core` with the KV-head groups split over the ranks of `group` (long-context prefill: batch 1, one or a
     few KV heads per GPU).  Every rank passes tensors that hold (at least) its own heads -- either the full tensors or
     already the local slices (`local=True` in cfg) -- and receives the full merged output [B, N, Hq * d].  The local
-    heads are processed `heads_per_pass` KV heads at a time to bound the work buffers."""
+    heads are processed `heads_per_pass` KV heads at a time to bound the work buffers.
+
+    With a `peer_output`, `overlap` sends each pass's combine + stores to a side stream, so they travel while the next
+    pass computes, and `head_splits` > 1 cuts a pass once more: compressed attention and the selection run for all
+    query heads of the KV head (the selection is shared by them), the selected and the sliding branch then run for
+    1 / head_splits of the query heads at a time, each piece stored as soon as it is complete.  Every rank must
+    receive the whole output over NVLink whatever the form of the gather (7/8 of it on eight GPUs); only what
+    follows the last piece is not hidden behind compute."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     rank = dist.get_rank(group) if dist.is_initialized() else 0
     local = cfg.pop('local', False)
@@ -171,13 +226,14 @@ def sharded_attend_core(q, qr, kr, v, ck, cv, gates, *, group=None, heads_per_pa
             z = min(a + heads_per_pass, h1)
             hs, qs = slice(a, z), slice(a * g, z * g)
 
-            def combine_into_peers(o_cmp, o_sel, o_swa, gts, offset=first + (a - h0) * g * d):
-                from . import ops
-                if peer_output.multicast_ptr is not None:
-                    ops.gated_combine_gather(o_cmp, o_sel, o_swa, gts, [peer_output.multicast_ptr], peer_output.features,
-                                             offset, multicast=True)
-                else:
-                    ops.gated_combine_gather(o_cmp, o_sel, o_swa, gts, peer_output.ptrs, peer_output.features, offset)
+            offset = first + (a - h0) * g * d
+            if head_splits > 1:
+                _split_pass(q[:, qs], qr[:, qs], kr[:, hs], v[:, hs], ck[:, hs], cv[:, hs], gates[:, qs], peer_output,
+                            offset, head_splits, overlap, **cfg)
+                continue
+
+            def combine_into_peers(o_cmp, o_sel, o_swa, gts, offset=offset):
+                peer_output.store(o_cmp, o_sel, o_swa, gts, offset, overlap)
 
             attend_core(q[:, qs], qr[:, qs], kr[:, hs], v[:, hs], ck[:, hs], cv[:, hs], gates[:, qs],
                         combine=combine_into_peers, **cfg)

@@ -32,10 +32,14 @@ def _worker(rank, world, port, ret):
         via_nccl = sharding.sharded_attend_core(q, qr, kr, v, ck, cv, gates, **cfg)
         peer = sharding.PeerOutput(b, n, hkv * g * d, torch.bfloat16, dev)
         fused = sharding.sharded_attend_core(q, qr, kr, v, ck, cv, gates, peer_output=peer, **cfg).clone()
-        fused2 = sharding.sharded_attend_core(q, qr, kr, v, ck, cv, gates, peer_output=peer, **cfg)   # buffer reuse
+        fused2 = sharding.sharded_attend_core(q, qr, kr, v, ck, cv, gates, peer_output=peer, **cfg).clone()  # buffer reuse
+        # the stores on a side stream, and the query heads of every KV head in two and four runs
+        over = [sharding.sharded_attend_core(q, qr, kr, v, ck, cv, gates, peer_output=peer, overlap=True,
+                                             head_splits=sp, **cfg).clone() for sp in (1, 2, 4)]
         ops.check_device_status()
         torch.cuda.synchronize()
-        ret[rank] = (bool(torch.equal(via_nccl, full)), bool(torch.equal(fused, full)), bool(torch.equal(fused2, full)))
+        ret[rank] = (bool(torch.equal(via_nccl, full)), bool(torch.equal(fused, full)), bool(torch.equal(fused2, full)),
+                     all(bool(torch.equal(o, full)) for o in over))
     finally:
         dist.destroy_process_group()
 
@@ -47,4 +51,4 @@ def test_fused_gather_equals_nccl_gather_on_two_gpus():
     port = 33500 + os.getpid() % 2000
     ret = mp.Manager().dict()
     mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
-    assert dict(ret) == {0: (True, True, True), 1: (True, True, True)}, dict(ret)
+    assert dict(ret) == {0: (True, True, True, True), 1: (True, True, True, True)}, dict(ret)
