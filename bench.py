@@ -289,7 +289,7 @@ def child_workload(name, steps, world, index):
     full = json.loads(lines[-1])
     keep = ('metric', 'value', 'unit', 'n_gpus', 'steps', 'ms_per_step', 'scaling', 'gpu_launches')
     short = {k: full.get(k) for k in keep}
-    short['config'] = {k: v for k, v in full.get('config', {}).items() if k in ('workload', 'sharding', 'parallelism', 'per_rank', 'gather_check')}
+    short['config'] = {k: v for k, v in full.get('config', {}).items() if k in ('workload', 'sharding', 'parallelism', 'per_rank', 'gather_check', 'step')}
     short['roofline'] = {k: v for k, v in full.get('roofline', {}).items() if k in ('achieved', 'peak', 'unit', 'frac', 'kernel')}
     short['e2e'] = full.get('e2e')
     return short
@@ -313,6 +313,7 @@ def main():
     ap.add_argument('--overlap', action='store_true', help='prefill, fused gather: stores on a side stream')
     ap.add_argument('--head-splits', type=int, default=1,
                     help='prefill, fused gather: query heads of a KV head in this many runs, each stored when complete')
+    ap.add_argument('--no-graph', action='store_true', help='language-model step: issue the kernels one by one')
     ap.add_argument('--rows', action='store_true', help='also time the other kernels of the hot path (N=1 only)')
     ap.add_argument('--no-workloads', action='store_true', help='default workload: skip the layer and prefill child runs')
     args = ap.parse_args()
@@ -1137,33 +1138,79 @@ def run_lm(args, w):
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     keep = {}
 
-    def step():
+    reducer = None
+    if world > 1:
+        # data-parallel gradient sum, one bucket per block in the order the backward reaches them: a block's
+        # all-reduce travels while the blocks below it are still in their backward
+        from native_sparse_attention_pytorch_b200.sharding import BucketedGradientSum
+        in_blocks = {id(p) for blk in model.layers for p in blk.parameters()}
+        rest = [p for p in params if id(p) not in in_blocks]
+        reducer = BucketedGradientSum([rest] + [list(blk.parameters()) for blk in reversed(model.layers)])
+
+    def eager_step():
         model.zero_grad(set_to_none=True)
+        if reducer is not None:
+            reducer.start()
         loss = model(ids)
         loss.backward()
-        if world > 1:   # data-parallel gradient sum: one flat bucket, one all-reduce
+        if reducer is not None:
+            reducer.finish()
+        keep['loss'] = loss
+
+    # Forward + backward of the step as one CUDA graph: with the batch split over the ranks the kernels get short
+    # (774 launches in 36 ms at four sequences per rank, of which the host needs 31 ms to issue them), so the step
+    # is replayed instead of issued; the gradient sum then follows the replay as one flat all-reduce.  Everything
+    # runs on a stream of its own: a graph cannot be recorded around a model whose gradients were first accumulated
+    # on the default stream.
+    stream = torch.cuda.Stream(device=dev)
+    graphed = {'graph': None, 'loss': None, 'launches': 0, 'how': 'issued kernel by kernel'}
+
+    def step():
+        if graphed['graph'] is None:
+            return eager_step()
+        graphed['graph'].replay()
+        if world > 1:
             grads = [p.grad for p in params if p.grad is not None]
             flat = torch._utils._flatten_dense_tensors(grads)
             dist.all_reduce(flat)
-            for g, f in zip(grads, torch._utils._unflatten_dense_tensors(flat, grads)):
-                g.copy_(f)
-        keep['loss'] = loss
+            for g_, f in zip(grads, torch._utils._unflatten_dense_tensors(flat, grads)):
+                g_.copy_(f)
+        keep['loss'] = graphed['loss']
 
-    total_ms, clocks, launches = _timed_steps(step, args.steps, warmup, flush, dist, world, rank, local)
-    h_loss = torch.empty(1, dtype=torch.float32).pin_memory()
-    def e2e_step():
-        ids.copy_(ids_host, non_blocking=True)
-        step()
-        h_loss.copy_(keep['loss'].detach().float().view(1), non_blocking=True)
-    e2e_step()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2e_steps = max(3, min(args.steps, 10))
-    e0.record()
-    for _ in range(e2e_steps):
+    with torch.cuda.stream(stream):
+        for _ in range(2):
+            eager_step()          # builds the per-shape indices and fills the allocator's pools
+        torch.cuda.synchronize()
+        if not args.no_graph:
+            try:
+                graph = torch.cuda.CUDAGraph()
+                before = launch_count()
+                with torch.cuda.graph(graph, stream=stream):
+                    model.zero_grad(set_to_none=True)
+                    g_loss = model(ids)
+                    g_loss.backward()
+                graphed.update(graph=graph, loss=g_loss, launches=launch_count() - before,
+                               how='replayed as one CUDA graph (forward + backward); gradient sum after the replay')
+            except Exception as exc:   # the step still runs, kernel by kernel
+                graphed['how'] = f'issued kernel by kernel (graph capture failed: {type(exc).__name__})'
+                torch.cuda.synchronize()
+        total_ms, clocks, launches = _timed_steps(step, args.steps, warmup, flush, dist, world, rank, local)
+        if graphed['graph'] is not None:
+            launches = graphed['launches'] * args.steps     # a replay launches what the capture recorded
+        h_loss = torch.empty(1, dtype=torch.float32).pin_memory()
+        def e2e_step():
+            ids.copy_(ids_host, non_blocking=True)
+            step()
+            h_loss.copy_(keep['loss'].detach().float().view(1), non_blocking=True)
         e2e_step()
-    e1.record()
-    torch.cuda.synchronize()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e2e_steps = max(3, min(args.steps, 10))
+        e0.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        e1.record()
+        torch.cuda.synchronize()
     t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -1187,8 +1234,12 @@ def run_lm(args, w):
         'steps': args.steps, 'warmup': warmup, 'ms_per_step': ms, 'higher_is_better': True, 'scaling': 'strong',
         'vs_baseline': None, 'dtype': 'bf16', 'data': 'synthetic',
         'config': {'workload': args.workload, **w, 'l2': 'flushed between timed steps', 'parameters': n_params,
-                   'parallelism': f'data parallel, {per_rank} sequences per rank, one NCCL all-reduce of '
-                                  f'{n_params * 2 / 1e6:.0f} MB of bf16 gradients per step'},
+                   'parallelism': f'data parallel, {per_rank} sequences per rank, {n_params * 2 / 1e6:.0f} MB of bf16 '
+                                  + ('gradients summed by one NCCL all-reduce after the replay'
+                                     if graphed['graph'] is not None else
+                                     'gradients summed by one NCCL all-reduce per block, launched as the backward '
+                                     'leaves the block'),
+                   'step': graphed['how']},
         'roofline': {'bound': 'tensor', 'kernel': 'whole training step; FLOPs of the three attention branches only',
                      'achieved': f_step / world / (ms / 1e3) / 1e12, 'peak': burst, 'unit': 'TFLOP/s',
                      'frac': f_step / world / (ms / 1e3) / 1e12 / burst, 'peak_source': src,
@@ -1196,7 +1247,7 @@ def run_lm(args, w):
         'e2e': {'value': tokens / (t.item() / e2e_steps / 1e3), 'unit': 'tokens/s',
                 'h2d_bytes_per_step': ids_host.numel() * 8 * world, 'd2h_bytes_per_step': 4, 'steps': e2e_steps},
         'gpu_launches': launches, 'clocks': clocks,
-        'loss': float(keep['loss']),
+        'loss': float(keep['loss'].detach()),
     }
     if not args.no_cpu_baseline and world == 1:
         base = layer_cpu_sample(kw)

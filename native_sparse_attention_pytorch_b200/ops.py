@@ -90,6 +90,8 @@ def poll_device_status(device):
     """The same check without a synchronisation, one call late: looks at the status copy the previous poll started
     (if it has landed) and starts the next one.  `SparseAttention.forward` calls this, so a training loop learns of
     an invalid step at its next forward without any host wait on the hot path."""
+    if torch.cuda.is_current_stream_capturing():
+        return                          # a CUDA graph is being recorded: nothing here may touch the host
     key = torch.device(device).index
     if key is None:
         key = torch.cuda.current_device()

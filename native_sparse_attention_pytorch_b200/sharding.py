@@ -245,3 +245,59 @@ def sharded_attend_core(q, qr, kr, v, ck, cv, gates, *, group=None, heads_per_pa
         part = attend_core(q[:, qs], qr[:, qs], kr[:, hs], v[:, hs], ck[:, hs], cv[:, hs], gates[:, qs], **cfg)
         merged[..., (a - h0) * g * d:(z - h0) * g * d] = part
     return gather_heads(merged, group)
+
+
+class BucketedGradientSum:
+    """Data-parallel gradient sum that overlaps the backward: the parameters are grouped into buckets (one per layer, in
+    the order the backward reaches them) and a bucket's all-reduce is launched, asynchronously, as soon as the last of
+    its gradients has been accumulated; `finish()` waits for all of them and copies the sums back.  The result equals
+    one flat all-reduce after the backward (the same element-wise sums over the ranks).  The only collective of the
+    training step (NCCL over NVLink on GPUs; the CPU tests run it over gloo)."""
+
+    def __init__(self, buckets, group=None):
+        self.group = group
+        self.buckets = [[p for p in b if p.requires_grad] for b in buckets]
+        self.buckets = [b for b in self.buckets if b]
+        self._left = [0] * len(self.buckets)
+        self._works = []
+        self._fired = [False] * len(self.buckets)
+        for bi, bucket in enumerate(self.buckets):
+            for p in bucket:
+                p.register_post_accumulate_grad_hook(self._make_hook(bi))
+        self.start()
+
+    def start(self):
+        """Call before every backward."""
+        self._left = [len(b) for b in self.buckets]
+        self._fired = [False] * len(self.buckets)
+        self._works = []
+
+    def _make_hook(self, bi):
+        def hook(_param):
+            if torch.cuda.is_available() and torch.cuda.is_current_stream_capturing():
+                return      # a CUDA graph of the step is being recorded: its owner sums the gradients after replay
+            self._left[bi] -= 1
+            if self._left[bi] == 0 and not self._fired[bi]:
+                self._launch(bi)
+        return hook
+
+    def _launch(self, bi):
+        self._fired[bi] = True
+        grads = [p.grad for p in self.buckets[bi] if p.grad is not None]
+        if not grads:
+            return
+        flat = torch._utils._flatten_dense_tensors(grads)
+        work = dist.all_reduce(flat, group=self.group, async_op=True)
+        self._works.append((work, flat, grads))
+
+    def finish(self):
+        """Call after the backward: buckets whose parameters did not all receive a gradient are summed now, then every
+        sum is awaited (on a GPU: the current stream waits, the host does not) and written back to the gradients."""
+        for bi in range(len(self.buckets)):
+            if not self._fired[bi]:
+                self._launch(bi)
+        for work, flat, grads in self._works:
+            work.wait()
+            for g, f in zip(grads, torch._utils._unflatten_dense_tensors(flat, grads)):
+                g.copy_(f)
+        self._works = []

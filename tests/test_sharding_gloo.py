@@ -131,3 +131,47 @@ def test_kv_head_range():
     assert [sharding.kv_head_range(8, 4, r) for r in range(4)] == [(0, 2), (2, 4), (4, 6), (6, 8)]
     with pytest.raises(ValueError):
         sharding.kv_head_range(8, 3, 0)
+
+
+def grad_worker(rank, world, port, ret):
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    try:
+        torch.manual_seed(3)
+        layers = torch.nn.ModuleList([torch.nn.Linear(6, 6) for _ in range(3)])
+        unused = torch.nn.Linear(6, 6)                    # never reached by the backward: summed by finish()
+        x = recipe.randn((4, 6), 10 + rank)
+
+        def backward():
+            for p in list(layers.parameters()) + list(unused.parameters()):
+                p.grad = None
+            h = x
+            for layer in layers:
+                h = torch.tanh(layer(h))
+            h.square().sum().backward()
+
+        backward()
+        want = []
+        for p in layers.parameters():                     # the flat form: one all-reduce per gradient after the backward
+            g = p.grad.clone()
+            dist.all_reduce(g)
+            want.append(g)
+        reducer = sharding.BucketedGradientSum([list(layer.parameters()) for layer in reversed(layers)] +
+                                               [list(unused.parameters())])
+        for _ in range(2):                                # twice: the counters are reset by start()
+            reducer.start()
+            backward()
+            reducer.finish()
+            got = [p.grad for p in layers.parameters()]
+            ok = all(torch.equal(a, b) for a, b in zip(got, want))
+        ret[rank] = ok and all(p.grad is None for p in unused.parameters())
+    finally:
+        dist.destroy_process_group()
+
+
+def test_bucketed_gradient_sum_equals_the_flat_all_reduce():
+    port = 31500 + (os.getpid() % 2000)
+    ret = mp.Manager().dict()
+    mp.spawn(grad_worker, args=(2, port, ret), nprocs=2, join=True)
+    assert dict(ret) == {0: True, 1: True}
