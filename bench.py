@@ -313,7 +313,7 @@ def main():
     ap.add_argument('--overlap', action='store_true', help='prefill, fused gather: stores on a side stream')
     ap.add_argument('--head-splits', type=int, default=1,
                     help='prefill, fused gather: query heads of a KV head in this many runs, each stored when complete')
-    ap.add_argument('--no-graph', action='store_true', help='language-model step: issue the kernels one by one')
+    ap.add_argument('--no-graph', action='store_true', help='layer and language-model step: issue the kernels one by one instead of replaying a CUDA graph')
     ap.add_argument('--rows', action='store_true', help='also time the other kernels of the hot path (N=1 only)')
     ap.add_argument('--no-workloads', action='store_true', help='default workload: skip the layer and prefill child runs')
     args = ap.parse_args()
@@ -682,39 +682,67 @@ def run_layer(args, w):
     x, up = x_host.to(dev).requires_grad_(), g_host.to(dev)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
-    def step():
+    def eager_step():
         layer.zero_grad(set_to_none=True)
         x.grad = None
         out = layer(x)
         out.backward(up)
         return out
 
-    with torch.no_grad():
-        _, mid = layer(x, return_intermediates=True)
-    n, d, hkv = w['seq'], w['dim_head'], w['kv_heads']
-    st = w['compress_block_sliding_stride']
-    flops = hot_path_flops(n, d, w['heads'] // hkv, w['batch'] * hkv, st, n // st, 1, w['selection_block_size'],
-                           w['sliding_window_size'], mid['fmask'].sum().item())
-    del mid
-    total_ms, clocks, launches = _timed_steps(step, args.steps, warmup, flush, dist, world, rank, local)
+    # The step is recorded once as a CUDA graph and replayed (--no-graph: issued kernel by kernel); all of it on a
+    # stream of its own, since a graph cannot be recorded around gradients first accumulated on the default stream.
+    stream = torch.cuda.Stream(device=dev)
+    graphed = {'graph': None, 'out': None, 'launches': 0, 'how': 'issued kernel by kernel'}
 
-    # end to end: the input arrives from pinned host memory, the output and the input gradient go back
-    h_out, h_dx = torch.empty_like(x_host).pin_memory(), torch.empty_like(x_host).pin_memory()
-    def e2e_step():
-        x.data.copy_(x_host, non_blocking=True)
-        up.copy_(g_host, non_blocking=True)
-        out = step()
-        h_out.copy_(out.detach(), non_blocking=True)
-        h_dx.copy_(x.grad, non_blocking=True)
-    e2e_step()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2e_steps = max(3, min(args.steps, 10))
-    e0.record()
-    for _ in range(e2e_steps):
+    def step():
+        if graphed['graph'] is None:
+            return eager_step()
+        graphed['graph'].replay()
+        return graphed['out']
+
+    with torch.cuda.stream(stream):
+        with torch.no_grad():
+            _, mid = layer(x, return_intermediates=True)
+        n, d, hkv = w['seq'], w['dim_head'], w['kv_heads']
+        st = w['compress_block_sliding_stride']
+        flops = hot_path_flops(n, d, w['heads'] // hkv, w['batch'] * hkv, st, n // st, 1, w['selection_block_size'],
+                               w['sliding_window_size'], mid['fmask'].sum().item())
+        del mid
+        for _ in range(2):
+            eager_step()
+        torch.cuda.synchronize()
+        if not args.no_graph:
+            try:
+                graph = torch.cuda.CUDAGraph()
+                before = launch_count()
+                with torch.cuda.graph(graph, stream=stream):
+                    g_out = eager_step()
+                graphed.update(graph=graph, out=g_out, launches=launch_count() - before,
+                               how='replayed as one CUDA graph (forward + backward)')
+            except Exception as exc:
+                graphed['how'] = f'issued kernel by kernel (graph capture failed: {type(exc).__name__})'
+                torch.cuda.synchronize()
+        total_ms, clocks, launches = _timed_steps(step, args.steps, warmup, flush, dist, world, rank, local)
+        if graphed['graph'] is not None:
+            launches = graphed['launches'] * args.steps     # a replay launches what the capture recorded
+
+        # end to end: the input arrives from pinned host memory, the output and the input gradient go back
+        h_out, h_dx = torch.empty_like(x_host).pin_memory(), torch.empty_like(x_host).pin_memory()
+        def e2e_step():
+            x.data.copy_(x_host, non_blocking=True)
+            up.copy_(g_host, non_blocking=True)
+            out = step()
+            h_out.copy_(out.detach(), non_blocking=True)
+            h_dx.copy_(x.grad, non_blocking=True)
         e2e_step()
-    e1.record()
-    torch.cuda.synchronize()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e2e_steps = max(3, min(args.steps, 10))
+        e0.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        e1.record()
+        torch.cuda.synchronize()
     t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -729,7 +757,7 @@ def run_layer(args, w):
         'steps': args.steps, 'warmup': warmup, 'ms_per_step': ms, 'higher_is_better': True, 'scaling': 'weak',
         'vs_baseline': None, 'dtype': 'bf16', 'data': 'synthetic',
         'config': {'workload': args.workload, **w, 'l2': 'flushed between timed steps',
-                   'per_rank': 'each rank runs the layer on its own seeded batch'},
+                   'per_rank': 'each rank runs the layer on its own seeded batch', 'step': graphed['how']},
         'roofline': {'bound': 'tensor', 'kernel': 'whole layer step; FLOPs of the three attention branches only',
                      'achieved': f_step / (ms / 1e3) / 1e12, 'peak': burst, 'unit': 'TFLOP/s',
                      'frac': f_step / (ms / 1e3) / 1e12 / burst, 'peak_source': src, 'peak_sustained': sustained,
