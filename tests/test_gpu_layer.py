@@ -211,3 +211,52 @@ def test_decode_step_kernel_matches_the_restated_step(case):
     gt = f(gates).view(b, hkv, g, 3)
     ref = (gt[..., 0:1] * o_cmp + gt[..., 1:2] * o_sel + gt[..., 2:3] * o_swa).reshape(b, hq * d)
     (assert_close_f32 if dtype == torch.float32 else assert_close_bf16)(got, ref, 'merged row')
+
+
+@pytest.mark.gpu
+def test_layer_step_can_be_recorded_as_a_cuda_graph():
+    """Forward + backward of the module recorded once as a CUDA graph and replayed on new inputs gives what issuing the
+    kernels one by one gives: nothing on the path synchronises with the host or allocates outside PyTorch's allocator,
+    and the module's status poll leaves a capture alone.  (Everything runs on a side stream: a graph cannot be
+    recorded around gradients that were first accumulated on the default stream.)"""
+    from native_sparse_attention_pytorch_b200 import ops
+    kw = dict(dim=256, dim_head=64, heads=8, kv_heads=2, causal=True, sliding_window_size=128, compress_block_size=32,
+              compress_block_sliding_stride=16, selection_block_size=64, num_selected_blocks=4)
+    attn = SparseAttention(**kw, use_triton_kernel=True, kernel_impl='sm100')
+    recipe.fill_weights(attn, seed=7)
+    attn = attn.to(DEV).bfloat16()
+    x = recipe.randn((1, 700, 256), 11).bfloat16().to(DEV).requires_grad_()
+    up = recipe.randn((1, 700, 256), 13).bfloat16().to(DEV)
+    x2, up2 = recipe.randn((1, 700, 256), 17).bfloat16().to(DEV), recipe.randn((1, 700, 256), 19).bfloat16().to(DEV)
+
+    def step():
+        attn.zero_grad(set_to_none=True)
+        x.grad = None
+        out = attn(x)
+        out.backward(up)
+        return out
+
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        for _ in range(2):
+            step()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            g_out = step()
+        with torch.no_grad():
+            x.copy_(x2)
+            up.copy_(up2)
+        graph.replay()
+        torch.cuda.synchronize()
+        got = (g_out.clone(), x.grad.clone(), attn.to_qkv.weight.grad.clone())
+        want_out = step()                       # the same inputs, issued kernel by kernel
+        torch.cuda.synchronize()
+        ops.check_device_status()
+        assert torch.equal(got[0], want_out)
+        # dk / dv are sums of atomics (their order is not fixed), everything downstream of them may differ in the last bits
+        assert_close_bf16(got[1], x.grad.float().cpu(), 'd input of the replay', roundings=2)
+        assert_close_bf16(got[2], attn.to_qkv.weight.grad.float().cpu(), 'd to_qkv.weight of the replay', roundings=2,
+                          rel_to_max=2e-3)
+    torch.cuda.current_stream().wait_stream(stream)
