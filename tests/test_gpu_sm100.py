@@ -547,3 +547,24 @@ def test_combine_backward_hands_the_row_sums_to_the_branch_backwards(monkeypatch
     assert n_own - n_handed == 3, (n_own, n_handed)
     assert_close_bf16(dx_handed, dx_own, 'd input', roundings=2)
     assert_close_bf16(dw_handed, dw_own, 'd to_qkv.weight', roundings=2, rel_to_max=2e-3)
+
+
+@pytest.mark.parametrize('cols,k', [(1100, 16), (300, 40), (200, 7)])
+def test_selection_from_pooled_input_in_every_kernel_variant(cols, k):
+    """The pooled bf16 input through the selection kernels the forward's shapes do not reach: rows of more than 1024
+    block columns and more than 32 picks use the shared-memory variant, which must honour `pooled` and the causal limit
+    as the register variant does.  Reference: the same values as an fp32 matrix with the columns at and past the own
+    block set to the masked value by hand."""
+    block = 4
+    n = cols * block
+    pooled = (recipe.randn((1, 2, n, cols), 3) * 3).bfloat16().to(DEV)
+    full = pooled.float().clone()
+    own = (torch.arange(n, device=DEV) // block)[:, None] <= torch.arange(cols, device=DEV)[None, :]
+    full[..., own] = ops.mask_sentinel(torch.bfloat16)
+    vals0, idx0 = nsa.select_blocks(full, block, block, k, dtype=torch.bfloat16)
+    vals1, idx1 = nsa.select_blocks(pooled, block, block, k, dtype=torch.bfloat16)
+    assert torch.equal(vals0, vals1)
+    live = vals1 > 1e-10
+    assert live.any() and torch.equal(idx0[live], idx1[live])
+    # slots without a visible block: probability 0 in both; their column is the lowest zero column in both
+    assert torch.equal(idx0, idx1)
