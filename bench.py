@@ -898,10 +898,14 @@ def run_prefill(args, w):
         g = w['q_heads'] // w['kv_heads']
         forms = [dict(multicast=False, overlap=False, splits=1)]
         if args.gather == 'auto':
+            # runs of query heads per KV head: one; two halves; a half and two quarters; ... (the last run's transfer
+            # is the one that no compute hides, so the runs get shorter towards the end)
+            run_sets = [1] + [r for r in ((g // 2, g // 2), (g // 2, g // 4, g // 4), (g // 2, g // 4, g // 8, g // 8))
+                              if min(r) >= 1 and sum(r) == g]
             for mcast in ((False, True) if multimem else (False,)):
-                for ov, sp in ((False, 1), (True, 1), (True, 2), (True, 4)):
+                for ov, sp in [(False, 1)] + [(True, r) for r in run_sets]:
                     f = dict(multicast=mcast, overlap=ov, splits=sp)
-                    if g % sp == 0 and g // sp >= 1 and f not in forms:
+                    if f not in forms and not (mcast and sp != 1):
                         forms.append(f)
         elif mode != forms[0]:
             forms.append(dict(mode))
@@ -915,7 +919,7 @@ def run_prefill(args, w):
             same = torch.tensor([int(torch.equal(plain, keep['out']))], device=dev)
             dist.all_reduce(same, op=dist.ReduceOp.MIN)
             name = ('multicast' if f['multicast'] else 'per-peer') + (', side stream' if f['overlap'] else '') + \
-                   (f', {f["splits"]} head runs' if f['splits'] > 1 else '')
+                   (f', head runs {f["splits"]}' if f['splits'] != 1 else '')
             if same.item() != 1:
                 notes.append(f'{name}: DIFFERS from the plain form, not used')
                 continue
@@ -989,7 +993,7 @@ def run_prefill(args, w):
                                   if multimem else 'the combine kernel storing into every rank' if fused
                                   else 'NCCL all-gather')
                                + ((', on a side stream' if mode['overlap'] else '') +
-                                  (f', query heads in {mode["splits"]} runs' if mode['splits'] > 1 else '') if fused else ''),
+                                  (f', query heads in runs {mode["splits"]}' if mode['splits'] != 1 else '') if fused else ''),
                    'gather_check': gather_check},
         'roofline': {'bound': 'tensor', 'kernel': 'whole forward step of all branches (per GPU)',
                      'achieved': f_step / world / (ms / 1e3) / 1e12, 'peak': burst, 'unit': 'TFLOP/s',

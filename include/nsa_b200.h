@@ -98,6 +98,12 @@ typedef struct {
   float scale;           /* logit scale, upstream uses dim_head^-0.5          */
   void* workspace;       /* nsa_sel_workspace_bytes(args, 0) bytes, may be NULL if that is 0 */
   int64_t workspace_bytes;
+  const void* index;     /* optional, forward only: the first nsa_sel_index_bytes(args) bytes of the work buffer of
+                            an earlier nsa_sel_fwd call with the same idx, mask and sizes (q_heads / kv_heads
+                            included); the call then skips its index pre-pass.  16-byte aligned.  A copy that does
+                            not fit the sizes is detected on the device (status 2, nothing computed).  Ignored
+                            inside nsa_sel_bwd_args, which has an index field of its own                          */
+  int64_t index_bytes;
 } nsa_sel_fwd_args;
 
 int nsa_sel_fwd(const nsa_sel_fwd_args* args, void* stream);

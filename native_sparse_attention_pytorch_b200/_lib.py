@@ -29,7 +29,7 @@ class SelFwdArgs(C.Structure):
                 ('idx', vp), ('mask', vp), ('lse', vp),
                 ('batch', i32), ('q_heads', i32), ('kv_heads', i32), ('sel_heads', i32), ('seq', i32), ('dim_head', i32),
                 ('block', i32), ('nsel', i32), ('diag', i32), ('dtype', i32), ('impl', i32), ('scale', f32),
-                ('workspace', vp), ('workspace_bytes', i64)]
+                ('workspace', vp), ('workspace_bytes', i64), ('index', vp), ('index_bytes', i64)]
 
 
 class SelBwdArgs(C.Structure):

@@ -178,6 +178,8 @@ int nsa_sel_fwd(const nsa_sel_fwd_args* a, void* stream) {
   if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
   AttnParams P;
   NSA_TRY(fill_sel(P, *a));
+  if (a->index != nullptr && (reinterpret_cast<uintptr_t>(a->index) & 15u))
+    return fail(NSA_ERR_ALIGN, "index must be 16-byte aligned");
   cudaStream_t st = (cudaStream_t)stream;
   if (a->impl != NSA_IMPL_SIMT) {
     const int rc = sm100_sel_fwd(*a, st);

@@ -2018,10 +2018,17 @@ static int run_fwd(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaStrea
     count_launches(1);
     return NSA_OK;
   }
-  rc = build_index(a, p, ws, st);
-  if (rc != NSA_OK) return rc;
+  const uint8_t* ix = nullptr;
+  if (a.index != nullptr) {   // the caller kept the index of an earlier forward over the same selection
+    if (a.index_bytes != p.index_bytes) return fail(NSA_ERR_WORKSPACE, "index: not the size nsa_sel_index_bytes reports");
+    ix = static_cast<const uint8_t*>(a.index);
+    CUDA_TRY(cudaMemsetAsync(ws + p.off_status, 0, 256, st));
+  } else {
+    rc = build_index(a, p, ws, st);
+    if (rc != NSA_OK) return rc;
+  }
   SelParams P;
-  fill_params(P, a, p, ws);
+  fill_params(P, a, p, ws, ix);
   P.partial = reinterpret_cast<__nv_bfloat16*>(ws + p.off_partial);
   P.stats = reinterpret_cast<float2*>(ws + p.off_stats);
   // a slot that no list holds keeps (0, 0): the merge reads the statistics of every slot and skips those
@@ -2178,6 +2185,7 @@ int64_t sm100_sel_index_bytes(const nsa_sel_fwd_args& a) {
 int sm100_sel_fwd(const nsa_sel_fwd_args& a, cudaStream_t st) {
   SelProblem x;
   if (!sel_problem(x, a)) return NSA_ERR_UNSUPPORTED;
+  x.index = a.index; x.index_bytes = a.index_bytes;
   return problem_fwd(x, st);
 }
 int sm100_sel_bwd(const nsa_sel_bwd_args& b, cudaStream_t st) {

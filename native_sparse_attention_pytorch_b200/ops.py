@@ -195,10 +195,10 @@ HAND_OVER_DELTA = True # the gated combine's backward hands the row sums out * d
 
 
 class SelectedAttention(Function):
-    """out, lse = f(q, k, v, idx, mask, slot_scale, block, diag, impl)."""
+    """out, lse = f(q, k, v, idx, mask, slot_scale, block, diag, impl, index_cache)."""
 
     @staticmethod
-    def forward(ctx, q, k, v, idx, mask, slot_scale, block, diag, impl):
+    def forward(ctx, q, k, v, idx, mask, slot_scale, block, diag, impl, index_cache=None):
         L.require_cuda(q, k, v, idx, mask)
         lib = L.load()
         q, k, v = L.rowwise(q), L.rowwise(k), L.rowwise(v)
@@ -212,11 +212,20 @@ class SelectedAttention(Function):
         with torch.cuda.device(q.device):
             args = _sel_args(q, k, v, out, idx, mask, lse, block, diag, impl, scale)
             ws = _with_workspace(args, False, q.device)
+            # `index_cache`: a dict the caller owns while it calls several times with the SAME idx and mask (runs of
+            # query heads of one KV head); the first call of a shape leaves its index there, the later ones take it
+            cache_key = (tuple(q.shape), tuple(k.shape), None if idx is None else tuple(idx.shape), block, diag, impl)
+            shared = index_cache.get(cache_key) if index_cache is not None else None
+            if shared is not None:
+                args.index, args.index_bytes = shared.data_ptr(), shared.numel()
             L.check(lib.nsa_sel_fwd(C.byref(args), L.stream_of(q)))
             # the index of which queries attend which key block: a few MB the backward need not rebuild
-            keep = REUSE_INDEX and ws is not None and any(ctx.needs_input_grad[:3])
+            keep = ws is not None and ((REUSE_INDEX and any(ctx.needs_input_grad[:3])) or
+                                       (index_cache is not None and shared is None))
             index_bytes = int(lib.nsa_sel_index_bytes(C.byref(args))) if keep else 0
-        ctx.index = ws[:index_bytes].clone() if index_bytes > 0 else None
+        ctx.index = shared if shared is not None else (ws[:index_bytes].clone() if index_bytes > 0 else None)
+        if index_cache is not None and shared is None and ctx.index is not None:
+            index_cache[cache_key] = ctx.index
         _keep_status(ws)
         del ws
         ctx.save_for_backward(q, k, v, idx, mask, out, lse)
@@ -251,12 +260,12 @@ class SelectedAttention(Function):
         _keep_status(ws)
         del ws
         return (dq, dk.to(k.dtype), dv.to(v.dtype), None, None,
-                None if slot is None else slot.to(slot_dtype), None, None, None)
+                None if slot is None else slot.to(slot_dtype), None, None, None, None)
 
 
 def native_sparse_attend(fq, fk, fv, block_size, selected_block_indices, fmask, sel_scale=None,
                          include_block_causal=True, return_lse=False, block_dk_dv_use_dot=False,
-                         return_sliding_window_out=False, impl='auto'):
+                         return_sliding_window_out=False, impl='auto', index_cache=None):
     """Drop-in for upstream's ``native_sparse_attend`` (TRI:1938-1987): selected-
     block attention with GQA head grouping.  fq [b,qh,n,d]; fk, fv [b,kh,n,d];
     indices / mask / sel_scale [b,kh,n,sel] or [b,qh,n,sel].  ``sel_scale`` must
@@ -264,7 +273,10 @@ def native_sparse_attend(fq, fk, fv, block_size, selected_block_indices, fmask, 
     ``block_dk_dv_use_dot`` is accepted and ignored (a Triton tuning switch).
     The fused second sliding-window output of upstream's kernel is not offered;
     use ``sliding_window_attend``.  Unlike upstream there is no block_size >= 16
-    or fp16 restriction, and float32 inputs are computed in float32."""
+    or fp16 restriction, and float32 inputs are computed in float32.  ``index_cache``:
+    a dict a caller passes to several calls that share ``selected_block_indices`` and
+    ``fmask`` (and the shapes); the first call leaves its index of which queries attend
+    which key block there and the later ones skip building it."""
     if return_sliding_window_out:
         raise NotImplementedError('return_sliding_window_out: use sliding_window_attend for the sliding branch')
     q_heads, kv_heads, sel_heads = fq.shape[1], fk.shape[1], selected_block_indices.shape[1]
@@ -272,7 +284,7 @@ def native_sparse_attend(fq, fk, fv, block_size, selected_block_indices, fmask, 
     assert sel_heads in (q_heads, kv_heads)
     diag = L.DIAG_CAUSAL if include_block_causal else L.DIAG_NONE
     out, lse = SelectedAttention.apply(fq, fk, fv, selected_block_indices, fmask, sel_scale, block_size, diag,
-                                       L.IMPL_BY_NAME[impl])
+                                       L.IMPL_BY_NAME[impl], index_cache)
     return (out, lse) if return_lse else out
 
 

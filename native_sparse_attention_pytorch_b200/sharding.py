@@ -108,23 +108,26 @@ def _split_pass(q, qr, kr, v, ck, cv, gates, peer_output, offset, splits, overla
     run.  The features of run r of KV head h sit where the unsplit pass puts them."""
     from . import ops
     hkv, g, d = v.shape[1], q.shape[1] // v.shape[1], q.shape[-1]
-    if g % splits:
-        raise ValueError(f'{g} query heads per KV head do not split into {splits} runs')
-    per = g // splits
+    runs = tuple(splits) if isinstance(splits, (tuple, list)) else (g // splits,) * splits
+    if sum(runs) != g or any(r < 1 or r & (r - 1) for r in runs):
+        raise ValueError(f'{g} query heads per KV head do not split into runs of {runs} (powers of two that add up)')
     pool = block // stride if causal and block % stride == 0 else 0
     o_cmp, importance = ops.compressed_attend(q, ck, cv, num_mem, stride, causal, sel_heads=hkv, want_importance=True,
                                               impl=impl, pool=pool)
     vals, idx = ops.select_blocks(importance, block, stride, num_selected, dtype=q.dtype)
     fmask = vals > 1e-10
     del importance
-    for r in range(splits):
-        for h in range(hkv) if hkv > 1 else (0,):
-            heads = slice(h * g + r * per, h * g + (r + 1) * per)
+    shared = [{} for _ in range(hkv)]      # per KV head: runs of equal size share the index of their selection
+    first = 0
+    for per in runs:
+        for h in range(hkv):
+            heads = slice(h * g + first, h * g + first + per)
             kh = slice(h, h + 1)
             o_sel = ops.native_sparse_attend(qr[:, heads], kr[:, kh], v[:, kh], block, idx[:, kh], fmask[:, kh],
-                                             include_block_causal=causal, impl=impl)
+                                             include_block_causal=causal, impl=impl, index_cache=shared[h])
             o_swa = ops.sliding_window_attend(qr[:, heads], kr[:, kh], v[:, kh], window, causal, impl=impl)
             peer_output.store(o_cmp[:, heads], o_sel, o_swa, gates[:, heads], offset + heads.start * d, overlap)
+        first += per
 
 
 def kv_head_range(kv_heads, world, rank):
@@ -206,9 +209,10 @@ def sharded_attend_core(q, qr, kr, v, ck, cv, gates, *, group=None, heads_per_pa
     heads are processed `heads_per_pass` KV heads at a time to bound the work buffers.
 
     With a `peer_output`, `overlap` sends each pass's combine + stores to a side stream, so they travel while the next
-    pass computes, and `head_splits` > 1 cuts a pass once more: compressed attention and the selection run for all
-    query heads of the KV head (the selection is shared by them), the selected and the sliding branch then run for
-    1 / head_splits of the query heads at a time, each piece stored as soon as it is complete.  Every rank must
+    pass computes, and `head_splits` (a number of equal runs, or a tuple of run sizes such as (4, 2, 2)) cuts a pass
+    once more: compressed attention and the selection run for all query heads of the KV head (the selection is shared
+    by them), the selected and the sliding branch then run for one run of query heads at a time, each run stored as
+    soon as it is complete; runs of equal size share the index of the selection.  Every rank must
     receive the whole output over NVLink whatever the form of the gather (7/8 of it on eight GPUs); only what
     follows the last piece is not hidden behind compute."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -227,7 +231,7 @@ def sharded_attend_core(q, qr, kr, v, ck, cv, gates, *, group=None, heads_per_pa
             hs, qs = slice(a, z), slice(a * g, z * g)
 
             offset = first + (a - h0) * g * d
-            if head_splits > 1:
+            if head_splits != 1:
                 _split_pass(q[:, qs], qr[:, qs], kr[:, hs], v[:, hs], ck[:, hs], cv[:, hs], gates[:, qs], peer_output,
                             offset, head_splits, overlap, **cfg)
                 continue

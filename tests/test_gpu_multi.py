@@ -33,9 +33,9 @@ def _worker(rank, world, port, ret):
         peer = sharding.PeerOutput(b, n, hkv * g * d, torch.bfloat16, dev)
         fused = sharding.sharded_attend_core(q, qr, kr, v, ck, cv, gates, peer_output=peer, **cfg).clone()
         fused2 = sharding.sharded_attend_core(q, qr, kr, v, ck, cv, gates, peer_output=peer, **cfg).clone()  # buffer reuse
-        # the stores on a side stream, and the query heads of every KV head in two and four runs
+        # the stores on a side stream, and the query heads of every KV head in two, four and uneven runs
         over = [sharding.sharded_attend_core(q, qr, kr, v, ck, cv, gates, peer_output=peer, overlap=True,
-                                             head_splits=sp, **cfg).clone() for sp in (1, 2, 4)]
+                                             head_splits=sp, **cfg).clone() for sp in (1, 2, 4, (2, 1, 1))]
         ops.check_device_status()
         torch.cuda.synchronize()
         ret[rank] = (bool(torch.equal(via_nccl, full)), bool(torch.equal(fused, full)), bool(torch.equal(fused2, full)),

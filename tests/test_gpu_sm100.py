@@ -516,6 +516,35 @@ def test_launch_counter_counts_the_kernels_of_a_step():
     assert lib.nsa_launch_count() - before == 9
 
 
+def test_forward_index_is_shared_between_calls_over_the_same_selection():
+    """Runs of query heads of one KV head attend the same selected blocks: with an `index_cache` the second call takes
+    the first call's index instead of building its own (four launches fewer) and computes the same."""
+    from native_sparse_attention_pytorch_b200 import _lib as L
+    lib = L.load()
+    q, k, v, idx, mask, up = make_case(1, 8, 1, 700, 64, 4, seed=5)
+    qa, qb = q[:, :4].to(DEV), q[:, 4:].to(DEV)
+    kd, vd, idxd, maskd = k.to(DEV), v.to(DEV), idx.to(DEV), mask.to(DEV)
+    alone = nsa.native_sparse_attend(qb, kd, vd, 64, idxd, maskd, impl='sm100')
+    cache = {}
+    n0 = lib.nsa_launch_count()
+    nsa.native_sparse_attend(qa, kd, vd, 64, idxd, maskd, impl='sm100', index_cache=cache)
+    n1 = lib.nsa_launch_count()
+    shared = nsa.native_sparse_attend(qb, kd, vd, 64, idxd, maskd, impl='sm100', index_cache=cache)
+    n2 = lib.nsa_launch_count()
+    ops.check_device_status()
+    assert len(cache) == 1 and (n1 - n0) - (n2 - n1) == 4
+    assert torch.equal(shared, alone)
+    # an index of another grouping is refused, not followed (its size differs: caught on the host; an index of the
+    # right size built for other sizes fails the tag check on the device)
+    q2 = q[:, :2].to(DEV)
+    key = next(iter(cache))
+    wrong = {(tuple(q2.shape),) + key[1:]: cache[key]}
+    with pytest.raises(RuntimeError):
+        nsa.native_sparse_attend(q2, kd, vd, 64, idxd, maskd, impl='sm100', index_cache=wrong)
+        ops.check_device_status()
+    ops.check_device_status()
+
+
 def test_combine_backward_hands_the_row_sums_to_the_branch_backwards(monkeypatch):
     """Every branch backward needs delta = sum_d out * d out per row; the gated combine's backward has it already as
     gate * d gate and hands it over through the gradient tensors, so the three branches skip their own pass: three
