@@ -271,20 +271,26 @@ def native_sparse_attend(fq, fk, fv, block_size, selected_block_indices, fmask, 
     indices / mask / sel_scale [b,kh,n,sel] or [b,qh,n,sel].  ``sel_scale`` must
     be all ones (TRI:1860-1861) and only adds a gradient output for it.
     ``block_dk_dv_use_dot`` is accepted and ignored (a Triton tuning switch).
-    The fused second sliding-window output of upstream's kernel is not offered;
-    use ``sliding_window_attend``.  Unlike upstream there is no block_size >= 16
+    ``return_sliding_window_out`` adds upstream's second output (TRI:199-201, 273-277,
+    1975-1987): causal attention over the last ``block_size`` keys and the query's own
+    position, here one more call of the sliding-window kernels; out and lse then
+    are pairs, as upstream's.  Unlike upstream there is no block_size >= 16
     or fp16 restriction, and float32 inputs are computed in float32.  ``index_cache``:
     a dict a caller passes to several calls that share ``selected_block_indices`` and
     ``fmask`` (and the shapes); the first call leaves its index of which queries attend
     which key block there and the later ones skip building it."""
-    if return_sliding_window_out:
-        raise NotImplementedError('return_sliding_window_out: use sliding_window_attend for the sliding branch')
+    if return_sliding_window_out and not include_block_causal:
+        raise ValueError('return_sliding_window_out needs include_block_causal: upstream computes the sliding output '
+                         'in the pass over the causal own block')
     q_heads, kv_heads, sel_heads = fq.shape[1], fk.shape[1], selected_block_indices.shape[1]
     assert q_heads % kv_heads == 0
     assert sel_heads in (q_heads, kv_heads)
     diag = L.DIAG_CAUSAL if include_block_causal else L.DIAG_NONE
     out, lse = SelectedAttention.apply(fq, fk, fv, selected_block_indices, fmask, sel_scale, block_size, diag,
                                        L.IMPL_BY_NAME[impl], index_cache)
+    if return_sliding_window_out:
+        sliding_out, sliding_lse = SlidingAttention.apply(fq, fk, fv, block_size, True, L.IMPL_BY_NAME[impl])
+        out, lse = (out, sliding_out), (lse, sliding_lse)
     return (out, lse) if return_lse else out
 
 
@@ -530,10 +536,11 @@ class SlidingAttention(Function):
             del ws
         ctx.save_for_backward(q, k, v, out, lse)
         ctx.cfg = (window, causal, impl, scale)
-        return out
+        ctx.mark_non_differentiable(lse)
+        return out, lse
 
     @staticmethod
-    def backward(ctx, dout):
+    def backward(ctx, dout, _dlse):
         q, k, v, out, lse = ctx.saved_tensors
         window, causal, impl, scale = ctx.cfg
         lib = L.load()
@@ -560,9 +567,10 @@ class SlidingAttention(Function):
         return dq, dk.to(k.dtype), dv.to(v.dtype), None, None, None
 
 
-def sliding_window_attend(q, k, v, window, causal, impl='auto'):
+def sliding_window_attend(q, k, v, window, causal, impl='auto', return_lse=False):
     """q [b,qh,n,d]; k, v [b,kh,n,d] (not repeated over the query-head groups)."""
-    return SlidingAttention.apply(q, k, v, window, causal, L.IMPL_BY_NAME[impl])
+    out, lse = SlidingAttention.apply(q, k, v, window, causal, L.IMPL_BY_NAME[impl])
+    return (out, lse) if return_lse else out
 
 
 # --------------------------------------------------------------------------

@@ -251,6 +251,46 @@ def test_sliding_matches_oracle(case, dtype):
         close(g, r, w)
 
 
+@pytest.mark.parametrize('dtype,block,n', [(torch.float32, 16, 100), (torch.bfloat16, 64, 300)])
+def test_selected_attend_returns_upstreams_sliding_output_too(dtype, block, n):
+    """`return_sliding_window_out` (TRI:1949, 1975-1987): a second output, causal attention over the query's own
+    position and the `block_size` keys before it, with its own log-sum-exp; gradients flow through both."""
+    b, hq, hkv, d, nsel = 1, 8, 2, 64, 3
+    q = recipe.randn((b, hq, n, d), 1).to(dtype)
+    k = recipe.randn((b, hkv, n, d), 2).to(dtype)
+    v = recipe.randn((b, hkv, n, d), 3).to(dtype)
+    up = recipe.randn((b, hq, n, d), 4).to(dtype)
+    idx = recipe.randint(0, -(-n // block), (b, hkv, n, nsel), 5)
+    mask = idx < (torch.arange(n) // block)[None, None, :, None]
+    qo, ko, vo = (t.float().requires_grad_() for t in (q, k, v))
+    ref_sel = O.selected_attend(qo, ko, vo, block, idx, mask, True)
+    ref_swa = O.sliding_attend(qo, ko, vo, block, True)
+    rd = grads_of(ref_sel + ref_swa, up.float(), (qo, ko, vo))
+    # the sliding branch's log-sum-exp, restated: scaled logits of the visible keys
+    g = hq // hkv
+    logits = torch.einsum('bhid,bhjd->bhij', qo.detach(), ko.detach().repeat_interleave(g, dim=1)) * d ** -0.5
+    i, j = torch.arange(n)[:, None], torch.arange(n)[None, :]
+    logits = logits.masked_fill(~((j <= i) & (i - j <= block)), float('-inf'))
+    ref_lse = logits.logsumexp(dim=-1)
+    qg, kg, vg = (t.to(DEV).requires_grad_() for t in (q, k, v))
+    (out, swa), (lse, swa_lse) = nsa.native_sparse_attend(qg, kg, vg, block, idx.to(DEV), mask.to(DEV),
+                                                            return_lse=True, return_sliding_window_out=True)
+    gd = grads_of(out + swa, up.to(DEV), (qg, kg, vg))
+    close = closeness(dtype)
+    close(out, ref_sel, 'out')
+    close(swa, ref_swa, 'sliding out')
+    assert torch.allclose(swa_lse.cpu(), ref_lse, atol=1e-4 if dtype == torch.float32 else 2e-2)
+    assert lse.shape == swa_lse.shape == (b, hq, n)
+    for got, want, w in zip(gd, rd, ('dq', 'dk', 'dv')):
+        if dtype == torch.bfloat16 and w != 'dq':     # sums over every later query of four heads, two branches
+            assert_close_bf16(got, want, w, rel_to_max=2e-3)
+        else:
+            close(got, want, w)
+    with pytest.raises(ValueError):
+        nsa.native_sparse_attend(qg, kg, vg, block, idx.to(DEV), mask.to(DEV), include_block_causal=False,
+                                 return_sliding_window_out=True)
+
+
 # ----------------------------------------------------------------- combine ---
 
 @pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16])
