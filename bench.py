@@ -311,6 +311,8 @@ def main():
                          'memory has no multicast) or with one peer store per rank (fused); auto times a few untimed '
                          'steps of both and keeps the faster; or an NCCL all-gather')
     ap.add_argument('--overlap', action='store_true', help='prefill, fused gather: stores on a side stream')
+    ap.add_argument('--fuse-merge', action='store_true',
+                    help="prefill, fused gather: the selected branch's last kernel combines and stores")
     ap.add_argument('--head-splits', type=int, default=1,
                     help='prefill, fused gather: query heads of a KV head in this many runs, each stored when complete')
     ap.add_argument('--no-graph', action='store_true', help='layer and language-model step: issue the kernels one by one instead of replaying a CUDA graph')
@@ -867,7 +869,8 @@ def run_prefill(args, w):
 
     # how the fused gather runs: through the multicast address or with per-peer stores; on a side stream or not; the
     # query heads of a KV head in one piece or several (sharding.sharded_attend_core)
-    mode = {'multicast': multimem, 'overlap': bool(args.overlap), 'splits': args.head_splits}
+    mode = {'multicast': multimem, 'overlap': bool(args.overlap), 'splits': args.head_splits,
+            'fuse': bool(args.fuse_merge)}
     mc_ptr = peer.multicast_ptr if peer is not None else None
 
     def step():
@@ -875,7 +878,8 @@ def run_prefill(args, w):
             peer.multicast_ptr = mc_ptr if mode['multicast'] else None
         keep['out'] = sharding.sharded_attend_core(t['q'], t['qr'], t['kr'], t['v'], t['ck'], t['cv'], t['gates'],
                                                    peer_output=peer, overlap=mode['overlap'] and fused,
-                                                   head_splits=mode['splits'] if fused else 1, **cfg)
+                                                   head_splits=mode['splits'] if fused else 1,
+                                                   fuse_merge=mode['fuse'] and fused, **cfg)
 
     def quick(n=3):   # device time of n steps, the slowest rank's
         torch.cuda.synchronize()
@@ -896,15 +900,15 @@ def run_prefill(args, w):
         # reproduce on every rank; a form that differs is never timed.  With --gather auto the forms are then tried
         # for three steps each and the fastest is kept.
         g = w['q_heads'] // w['kv_heads']
-        forms = [dict(multicast=False, overlap=False, splits=1)]
+        forms = [dict(multicast=False, overlap=False, splits=1, fuse=False)]
         if args.gather == 'auto':
             # runs of query heads per KV head: one; two halves; a half and two quarters; ... (the last run's transfer
             # is the one that no compute hides, so the runs get shorter towards the end)
             run_sets = [1] + [r for r in ((g // 2, g // 2), (g // 2, g // 4, g // 4), (g // 2, g // 4, g // 8, g // 8))
                               if min(r) >= 1 and sum(r) == g]
             for mcast in ((False, True) if multimem else (False,)):
-                for ov, sp in [(False, 1)] + [(True, r) for r in run_sets]:
-                    f = dict(multicast=mcast, overlap=ov, splits=sp)
+                for ov, sp, fu in [(False, 1, False)] + [(True, r, False) for r in run_sets] + [(False, 1, True)]:
+                    f = dict(multicast=mcast, overlap=ov, splits=sp, fuse=fu)
                     if f not in forms and not (mcast and sp != 1):
                         forms.append(f)
         elif mode != forms[0]:
@@ -919,6 +923,7 @@ def run_prefill(args, w):
             same = torch.tensor([int(torch.equal(plain, keep['out']))], device=dev)
             dist.all_reduce(same, op=dist.ReduceOp.MIN)
             name = ('multicast' if f['multicast'] else 'per-peer') + (', side stream' if f['overlap'] else '') + \
+                   (", stored by the selected branch's merge" if f['fuse'] else '') + \
                    (f', head runs {f["splits"]}' if f['splits'] != 1 else '')
             if same.item() != 1:
                 notes.append(f'{name}: DIFFERS from the plain form, not used')
@@ -993,6 +998,7 @@ def run_prefill(args, w):
                                   if multimem else 'the combine kernel storing into every rank' if fused
                                   else 'NCCL all-gather')
                                + ((', on a side stream' if mode['overlap'] else '') +
+                                  (", from the selected branch's merge kernel" if mode['fuse'] else '') +
                                   (f', query heads in runs {mode["splits"]}' if mode['splits'] != 1 else '') if fused else ''),
                    'gather_check': gather_check},
         'roofline': {'bound': 'tensor', 'kernel': 'whole forward step of all branches (per GPU)',

@@ -406,6 +406,16 @@ typedef struct {
 
 int nsa_combine_fwd_gather(const nsa_combine_gather_args* args, void* stream);
 
+/* The selected-block forward (nsa_sel_fwd, NSA:723-730) with the gated combine, the head merge and the gather
+ * (NSA:854-860) in its last kernel: the kernel that merges the partial results of a query's selected blocks also
+ * reads the compressed and the sliding row and the gates, and stores the combined row into every destination.  For
+ * the branch that runs last this saves the selected output's round trip through memory and the combine's own
+ * launch, and the peer stores leave from a kernel that is already streaming.  `sel`: as for nsa_sel_fwd (out may be
+ * NULL, it is not written; lse is); `combine`: as for nsa_combine_fwd_gather, fwd.o_sel ignored.  Same bytes as the
+ * two calls one after the other.  Tensor-core family only (bf16, block 64, ...): NSA_ERR_UNSUPPORTED otherwise, and
+ * the caller makes the two calls.  (No counterpart in upstream, which combines in PyTorch.) */
+int nsa_sel_fwd_combine_gather(const nsa_sel_fwd_args* sel, const nsa_combine_gather_args* combine, void* stream);
+
 /* Rotary position embedding of the queries / keys that feed the selected and the sliding branch: replaces the calls
  * into the third-party rotary_embedding_torch package at NSA:643 (rotate_queries_with_cached_keys) and NSA:384-385
  * (rotate_queries_or_keys).  out[b,h,n,2m]   = x[2m] cos[n,m] - x[2m+1] sin[n,m],

@@ -126,7 +126,7 @@ _STRUCTS = [Tensor4, SelFwdArgs, SelBwdArgs, CmpFwdArgs, CmpBwdArgs, SelectArgs,
 ENTRY_POINTS = ['nsa_sel_fwd', 'nsa_sel_bwd', 'nsa_sel_workspace_bytes', 'nsa_sel_index_bytes', 'nsa_cmp_index_bytes', 'nsa_swa_index_bytes', 'nsa_sel_bwd_stores_dq', 'nsa_cmp_bwd_stores_dq', 'nsa_swa_bwd_stores_dq',
                 'nsa_sel_fwd_static', 'nsa_sel_static_status', 'nsa_launch_count', 'nsa_selftest_bounded_wait', 'nsa_decode_step',
                 'nsa_sel_static_scratch_bytes', 'nsa_cmp_workspace_bytes', 'nsa_swa_workspace_bytes', 'nsa_cmp_fwd', 'nsa_cmp_fwd_pools', 'nsa_cmp_bwd', 'nsa_select',
-                'nsa_swa_fwd', 'nsa_swa_bwd', 'nsa_combine_fwd', 'nsa_combine_bwd', 'nsa_combine_fwd_gather', 'nsa_rotary', 'nsa_windows_fwd', 'nsa_windows_bwd', 'nsa_rmsnorm_fwd', 'nsa_rmsnorm_bwd', 'nsa_last_error',
+                'nsa_swa_fwd', 'nsa_swa_bwd', 'nsa_combine_fwd', 'nsa_combine_bwd', 'nsa_combine_fwd_gather', 'nsa_sel_fwd_combine_gather', 'nsa_rotary', 'nsa_windows_fwd', 'nsa_windows_bwd', 'nsa_rmsnorm_fwd', 'nsa_rmsnorm_bwd', 'nsa_last_error',
                 'nsa_abi_version', 'nsa_struct_size']
 
 _lib = None

@@ -480,34 +480,64 @@ int nsa_combine_fwd(const nsa_combine_fwd_args* a, void* stream) {
   return launch_combine(P, a->dtype, false, (cudaStream_t)stream);
 }
 
-int nsa_combine_fwd_gather(const nsa_combine_gather_args* a, void* stream) {
-  if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
-  CombineParams P;
-  NSA_TRY(fill_combine(P, a->fwd));
-  const nsa_combine_fwd_args& f = a->fwd;
+// checks of a gather call shared by nsa_combine_fwd_gather and nsa_sel_fwd_combine_gather (`skip`: a branch whose
+// tensor the caller does not pass because the call computes it)
+static int fill_gather(CombineParams& P, GatherTargets& Gt, const nsa_combine_gather_args& a, int skip) {
+  nsa_combine_fwd_args f = a.fwd;
+  nsa_tensor* o[3] = {&f.o_cmp, &f.o_sel, &f.o_swa};
+  if (skip >= 0) *o[skip] = *o[(skip + 1) % 3];      // stands in for the checks only
+  NSA_TRY(fill_combine(P, f));
   const int V = f.dtype == NSA_F32 ? 4 : 8;
-  if (a->num_outs < 1 || a->num_outs > NSA_MAX_GATHER) return fail(NSA_ERR_SHAPE, "num_outs must be 1..NSA_MAX_GATHER");
+  if (a.num_outs < 1 || a.num_outs > NSA_MAX_GATHER) return fail(NSA_ERR_SHAPE, "num_outs must be 1..NSA_MAX_GATHER");
   if (f.dim_head % V) return fail(NSA_ERR_ALIGN, "dim_head must be a multiple of 16 bytes");
-  if (a->feature_offset < 0 || a->feature_offset % V || a->total_features % V ||
-      a->feature_offset + (int64_t)f.q_heads * f.dim_head > a->total_features)
+  if (a.feature_offset < 0 || a.feature_offset % V || a.total_features % V ||
+      a.feature_offset + (int64_t)f.q_heads * f.dim_head > a.total_features)
     return fail(NSA_ERR_SHAPE, "feature_offset / total_features do not hold these heads in 16-byte pieces");
-  const nsa_tensor* o[3] = {&f.o_cmp, &f.o_sel, &f.o_swa};
   for (int s = 0; s < 3; ++s)
     if ((reinterpret_cast<uintptr_t>(o[s]->ptr) & 15u) || o[s]->stride_b % V || o[s]->stride_h % V || o[s]->stride_n % V)
       return fail(NSA_ERR_ALIGN, "branch outputs must keep 16-byte pieces aligned");
-  GatherTargets Gt;
   memset(&Gt, 0, sizeof(Gt));
-  for (int r = 0; r < a->num_outs; ++r) {
-    if (a->outs[r] == nullptr) return fail(NSA_ERR_NULL, "outs: NULL pointer");
-    if (reinterpret_cast<uintptr_t>(a->outs[r]) & 15u) return fail(NSA_ERR_ALIGN, "outs must be 16-byte aligned");
-    Gt.outs[r] = a->outs[r];
+  for (int r = 0; r < a.num_outs; ++r) {
+    if (a.outs[r] == nullptr) return fail(NSA_ERR_NULL, "outs: NULL pointer");
+    if (reinterpret_cast<uintptr_t>(a.outs[r]) & 15u) return fail(NSA_ERR_ALIGN, "outs must be 16-byte aligned");
+    Gt.outs[r] = a.outs[r];
   }
-  if (a->multicast != 0 && a->num_outs != 1)
+  if (a.multicast != 0 && a.num_outs != 1)
     return fail(NSA_ERR_SHAPE, "a multicast destination is the only destination (num_outs == 1)");
-  Gt.num_outs = a->num_outs;
-  Gt.multicast = a->multicast != 0;
-  Gt.total_features = a->total_features;
-  Gt.feature_offset = a->feature_offset;
+  Gt.num_outs = a.num_outs;
+  Gt.multicast = a.multicast != 0;
+  Gt.total_features = a.total_features;
+  Gt.feature_offset = a.feature_offset;
+  return NSA_OK;
+}
+
+int nsa_sel_fwd_combine_gather(const nsa_sel_fwd_args* s, const nsa_combine_gather_args* c, void* stream) {
+  if (s == nullptr || c == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
+  if (s->impl == NSA_IMPL_SIMT) return fail(NSA_ERR_UNSUPPORTED, "the fused merge is part of the tensor-core family");
+  nsa_sel_fwd_args sel = *s;
+  if (sel.out.ptr == nullptr) sel.out = sel.q;       // never written by this call: any tensor of the shape passes the checks
+  AttnParams A;
+  NSA_TRY(fill_sel(A, sel));
+  if (sel.index != nullptr && (reinterpret_cast<uintptr_t>(sel.index) & 15u))
+    return fail(NSA_ERR_ALIGN, "index must be 16-byte aligned");
+  if (c->fwd.dtype != NSA_BF16 || s->dtype != NSA_BF16) return fail(NSA_ERR_UNSUPPORTED, "the fused merge serves bf16");
+  if (c->fwd.batch != s->batch || c->fwd.q_heads != s->q_heads || c->fwd.seq != s->seq || c->fwd.dim_head != s->dim_head)
+    return fail(NSA_ERR_SHAPE, "the combine's sizes must be those of the selected-block call");
+  CombineParams P;
+  GatherTargets Gt;
+  NSA_TRY(fill_gather(P, Gt, *c, 1));
+  P.o[1] = nullptr;
+  const int rc = sm100_sel_fwd_combine(sel, P, Gt, (cudaStream_t)stream);
+  if (rc == NSA_ERR_UNSUPPORTED) return fail(NSA_ERR_UNSUPPORTED, "selected branch: shape outside the tensor-core family");
+  return rc;
+}
+
+int nsa_combine_fwd_gather(const nsa_combine_gather_args* a, void* stream) {
+  if (a == nullptr) return fail(NSA_ERR_NULL, "args: NULL pointer");
+  CombineParams P;
+  GatherTargets Gt;
+  NSA_TRY(fill_gather(P, Gt, *a, -1));
+  const nsa_combine_fwd_args& f = a->fwd;
   return launch_combine_gather(P, Gt, f.dtype, (cudaStream_t)stream);
 }
 

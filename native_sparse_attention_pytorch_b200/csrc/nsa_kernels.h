@@ -141,6 +141,7 @@ int sm100_swa_bwd(const nsa_swa_bwd_args& a, cudaStream_t stream);
 int64_t sm100_cmp_workspace_bytes(const nsa_cmp_fwd_args& a, bool backward);
 int sm100_cmp_fwd(const nsa_cmp_fwd_args& a, cudaStream_t stream);
 bool sm100_cmp_fwd_pools(const nsa_cmp_fwd_args& a);
+int sm100_sel_fwd_combine(const nsa_sel_fwd_args& a, const CombineParams& c, const GatherTargets& t, cudaStream_t stream);
 int sm100_cmp_bwd(const nsa_cmp_bwd_args& a, cudaStream_t stream);
 int64_t sm100_static_scratch_bytes();
 int sm100_sel_static_status(int* out, cudaStream_t stream);

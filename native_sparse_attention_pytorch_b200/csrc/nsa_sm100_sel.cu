@@ -653,6 +653,97 @@ __global__ void __launch_bounds__(256) sel_merge_kernel(const SelParams P) {
   if (part == 0) P.lse[row] = L > 0.f ? (M + log2f(L)) * kLn2 : -INFINITY;
 }
 
+// The merge of the selected branch that also does the gated combine and the head merge (and, with several
+// destinations, the all-gather of the head-sharded layout): the merged selected row is rounded to bf16 as the tensor
+// between the two kernels would be, combined with the compressed and the sliding row exactly as combine_gather_kernel
+// does (the same three fused multiply-adds in the same order), and stored into every destination.  The selected
+// branch's own output tensor is not written.  Thread groups walk the rows position-major (b, i, head), so that the
+// heads of one position land next to each other in the destinations' [B, N, features] rows.
+template <int D, bool MC>
+__global__ void __launch_bounds__(256) sel_merge_combine_kernel(const SelParams P, const CombineParams Cp, const GatherTargets Gt) {
+  constexpr int TPR = D / 8;
+  const int64_t t = ((int64_t)blockIdx.x * 256 + threadIdx.x) / TPR;
+  const int part = threadIdx.x % TPR;
+  const int64_t nrows = (int64_t)P.B * P.Hq * P.N;
+  if (t < nrows) {
+    const int hq = (int)(t % P.Hq);
+    const int i = (int)((t / P.Hq) % P.N);
+    const int b = (int)(t / ((int64_t)P.N * P.Hq));
+    const int64_t row = ((int64_t)b * P.Hq + hq) * P.N + i;
+    const int ns = P.ns;
+    const float2* st = P.stats + row * ns;
+    const __nv_bfloat16* prow = P.partial + row * ns * D + part * 8;
+    float M = -INFINITY;
+#pragma unroll 4
+    for (int s = 0; s < ns; ++s) {
+      const float2 ml = st[s];
+      if (ml.y > 0.f) M = fmaxf(M, ml.x);
+    }
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    float Lsum = 0.f;
+    for (int s0 = 0; s0 < ns; s0 += 8) {
+      float w[8];
+      uint4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const bool in = s0 + u < ns;
+        const float2 ml = in ? st[s0 + u] : make_float2(0.f, 0.f);
+        const bool ok = ml.y > 0.f;
+        w[u] = ok ? ex2(ml.x - M) : 0.f;
+        Lsum = fmaf(w[u], ml.y, Lsum);
+        v[u] = ok ? *reinterpret_cast<const uint4*>(prow + (int64_t)(s0 + u) * D) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const uint32_t q[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          acc[2 * x] = fmaf(w[u], __uint_as_float(q[x] << 16), acc[2 * x]);
+          acc[2 * x + 1] = fmaf(w[u], __uint_as_float(q[x] & 0xffff0000u), acc[2 * x + 1]);
+        }
+      }
+    }
+    const float inv = Lsum > 0.f ? 1.f / Lsum : 0.f;
+    if (part == 0 && P.lse != nullptr) P.lse[row] = Lsum > 0.f ? (M + log2f(Lsum)) * kLn2 : -INFINITY;
+    // combine: gates in the order compressed, selected, sliding
+    const __nv_bfloat16* g = (const __nv_bfloat16*)Cp.gates + b * Cp.g_sb + hq * Cp.g_sh + (int64_t)i * Cp.g_sn;
+    const float g0 = __bfloat162float(g[0]), g1 = __bfloat162float(g[1]), g2 = __bfloat162float(g[2]);
+    const uint4 rc = *reinterpret_cast<const uint4*>((const __nv_bfloat16*)Cp.o[0] + b * Cp.o_sb[0] + hq * Cp.o_sh[0] +
+                                                     (int64_t)i * Cp.o_sn[0] + part * 8);
+    const uint4 rw = *reinterpret_cast<const uint4*>((const __nv_bfloat16*)Cp.o[2] + b * Cp.o_sb[2] + hq * Cp.o_sh[2] +
+                                                     (int64_t)i * Cp.o_sn[2] + part * 8);
+    const uint32_t qc[4] = {rc.x, rc.y, rc.z, rc.w}, qw[4] = {rw.x, rw.y, rw.z, rw.w};
+    uint32_t packed[4];
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      // the selected row as its bf16 tensor would hold it
+      const uint32_t os = pack_bf16(acc[2 * x] * inv, acc[2 * x + 1] * inv);
+      float lo = fmaf(g0, __uint_as_float(qc[x] << 16), 0.f);
+      float hi = fmaf(g0, __uint_as_float(qc[x] & 0xffff0000u), 0.f);
+      lo = fmaf(g1, __uint_as_float(os << 16), lo);
+      hi = fmaf(g1, __uint_as_float(os & 0xffff0000u), hi);
+      lo = fmaf(g2, __uint_as_float(qw[x] << 16), lo);
+      hi = fmaf(g2, __uint_as_float(qw[x] & 0xffff0000u), hi);
+      packed[x] = pack_bf16(lo, hi);
+    }
+    const int64_t at = ((int64_t)b * P.N + i) * Gt.total_features + Gt.feature_offset + (int64_t)hq * D + part * 8;
+    if (MC) {
+      asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"((__nv_bfloat16*)Gt.outs[0] + at),
+                   "f"(__uint_as_float(packed[0])), "f"(__uint_as_float(packed[1])), "f"(__uint_as_float(packed[2])),
+                   "f"(__uint_as_float(packed[3]))
+                   : "memory");
+    } else {
+      const int rot = (int)(blockIdx.x % (unsigned)Gt.num_outs);
+      for (int r = 0; r < Gt.num_outs; ++r) {
+        int k = r + rot;
+        if (k >= Gt.num_outs) k -= Gt.num_outs;
+        *reinterpret_cast<uint4*>((__nv_bfloat16*)Gt.outs[k] + at) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      }
+    }
+  }
+  if (MC) __threadfence_system();
+}
+
 // ---- forward of the dense causal branches, query-tile stationary ---------------------------------------------
 //
 // The compressed and the sliding-window branch attend a contiguous range of key blocks per query, the same range for
@@ -1780,6 +1871,8 @@ struct SelProblem {
   int cpf;
   void* workspace;
   int64_t workspace_bytes;
+  const CombineParams* fuse_combine;   // selected forward, optional: the merge also combines and stores (see
+  const GatherTargets* fuse_targets;   // sel_merge_combine_kernel); `out` is then not written
   const void* index;       // backward: the index part of the forward's work buffer, or NULL to rebuild it
   int64_t index_bytes;
   const float* delta;      // backward, optional: sum_d out * dout per row from the caller
@@ -2040,7 +2133,12 @@ static int run_fwd(const SelProblem& a, const SelPlan& p, uint8_t* ws, cudaStrea
   sel_fwd_kernel<D><<<num_sms() * per_sm, 2 * kRows, smem, st>>>(tmK, tmV, P);
   const int64_t threads = (int64_t)a.B * a.Hq * a.N * (D / 8);
   const unsigned mblocks = (unsigned)((threads + 255) / 256);
-  sel_merge_kernel<D><<<mblocks, 256, 0, st>>>(P);
+  if (a.fuse_combine != nullptr) {
+    if (a.fuse_targets->multicast) sel_merge_combine_kernel<D, true><<<mblocks, 256, 0, st>>>(P, *a.fuse_combine, *a.fuse_targets);
+    else sel_merge_combine_kernel<D, false><<<mblocks, 256, 0, st>>>(P, *a.fuse_combine, *a.fuse_targets);
+  } else {
+    sel_merge_kernel<D><<<mblocks, 256, 0, st>>>(P);
+  }
   CUDA_TRY(cudaGetLastError());
   count_launches(2);   // forward kernel, merge
   return NSA_OK;
@@ -2186,6 +2284,14 @@ int sm100_sel_fwd(const nsa_sel_fwd_args& a, cudaStream_t st) {
   SelProblem x;
   if (!sel_problem(x, a)) return NSA_ERR_UNSUPPORTED;
   x.index = a.index; x.index_bytes = a.index_bytes;
+  return problem_fwd(x, st);
+}
+int sm100_sel_fwd_combine(const nsa_sel_fwd_args& a, const CombineParams& c, const GatherTargets& t, cudaStream_t st) {
+  SelProblem x;
+  if (!sel_problem(x, a)) return NSA_ERR_UNSUPPORTED;
+  if (c.batch != x.B || c.q_heads != x.Hq || c.seq != x.N || c.d != x.D) return NSA_ERR_UNSUPPORTED;
+  x.index = a.index; x.index_bytes = a.index_bytes;
+  x.fuse_combine = &c; x.fuse_targets = &t;
   return problem_fwd(x, st);
 }
 int sm100_sel_bwd(const nsa_sel_bwd_args& b, cudaStream_t st) {

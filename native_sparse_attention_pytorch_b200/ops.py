@@ -507,6 +507,55 @@ def _select_blocks(importance, block, stride, nsel, dtype=torch.float32, input_i
     return vals.to(dtype), idx
 
 
+@torch.no_grad()
+def selected_attend_combine_gather(fq, fk, fv, block_size, idx, fmask, o_cmp, o_swa, gates, out_ptrs, total_features,
+                                   feature_offset, include_block_causal=True, multicast=False, impl='auto',
+                                   index_cache=None):
+    """Forward only: the selected branch for `fq`'s heads with the gated combine, the head merge and the stores into
+    every [B, N, total_features] buffer of `out_ptrs` done by its last kernel (nsa_sel_fwd_combine_gather) -- what
+    `native_sparse_attend` followed by `gated_combine_gather` gives, byte for byte, without the selected output's
+    round trip.  Returns False, having done nothing, where the tensor-core family does not serve the shapes: the
+    caller then makes the two calls."""
+    L.require_cuda(fq, fk, fv, idx, fmask, o_cmp, o_swa, gates)
+    lib = L.load()
+    if fq.dtype != torch.bfloat16 or impl == 'simt' or idx.shape[1] != fk.shape[1]:
+        return False
+    q, k, v = L.rowwise(fq), L.rowwise(fk), L.rowwise(fv)
+    idx = idx.to(torch.int64).contiguous()
+    mask = fmask.to(torch.bool).contiguous().view(torch.uint8)
+    o_cmp, o_swa = (t if _vec_ok(t) else t.contiguous() for t in (o_cmp, o_swa))
+    if gates.stride(-1) != 1:
+        gates = gates.contiguous()
+    b, hq, n, d = q.shape
+    lse = torch.empty(b, hq, n, dtype=torch.float32, device=q.device)
+    diag = L.DIAG_CAUSAL if include_block_causal else L.DIAG_NONE
+    with torch.cuda.device(q.device):
+        args = _sel_args(q, k, v, q, idx, mask, lse, block_size, diag, L.IMPL_BY_NAME[impl], d ** -0.5)
+        args.out = L.Tensor4()
+        need = lib.nsa_sel_workspace_bytes(C.byref(args), 0)
+        if need <= 0:
+            return False
+        ws = torch.empty(need, dtype=torch.uint8, device=q.device)
+        args.workspace, args.workspace_bytes = ws.data_ptr(), need
+        cache_key = (tuple(q.shape), tuple(k.shape), tuple(idx.shape), block_size, diag, L.IMPL_BY_NAME[impl])
+        shared = index_cache.get(cache_key) if index_cache is not None else None
+        if shared is not None:
+            args.index, args.index_bytes = shared.data_ptr(), shared.numel()
+        fwd = L.CombineFwdArgs(o_cmp=L.t4(o_cmp), o_sel=L.Tensor4(), o_swa=L.t4(o_swa), gates=L.t4(gates), out=None,
+                               batch=b, q_heads=hq, seq=n, dim_head=d, dtype=L.dtype_code(q))
+        outs = (C.c_void_p * L.MAX_GATHER)(*[int(p) for p in out_ptrs])
+        cargs = L.CombineGatherArgs(fwd=fwd, outs=outs, num_outs=len(out_ptrs), multicast=int(bool(multicast)),
+                                    total_features=total_features, feature_offset=feature_offset)
+        rc = lib.nsa_sel_fwd_combine_gather(C.byref(args), C.byref(cargs), L.stream_of(q))
+        if rc == L.NSA_ERR_UNSUPPORTED:
+            return False
+        L.check(rc)
+        if index_cache is not None and shared is None:
+            index_cache[cache_key] = ws[:int(lib.nsa_sel_index_bytes(C.byref(args)))].clone()
+        _keep_status(ws)
+    return True
+
+
 # --------------------------------------------------------------------------
 # sliding window (replaces the LocalAttention call NSA:841-850)
 # --------------------------------------------------------------------------

@@ -102,10 +102,12 @@ def attend_core(q, qr, kr, v, ck, cv, gates, *, num_mem, stride, block, num_sele
 
 
 def _split_pass(q, qr, kr, v, ck, cv, gates, peer_output, offset, splits, overlap, *, num_mem, stride, block,
-                num_selected, window, causal=True, impl='auto'):
+                num_selected, window, causal=True, impl='auto', fuse_merge=False):
     """One pass of `sharded_attend_core` over the given KV heads with the query heads of every KV head cut into
     `splits` runs: compressed attention and selection for all heads, then selected + sliding + combine-and-store per
-    run.  The features of run r of KV head h sit where the unsplit pass puts them."""
+    run.  The features of run r of KV head h sit where the unsplit pass puts them.  With `fuse_merge` the sliding
+    branch of a run goes first and the selected branch's last kernel does the combine and the stores
+    (`ops.selected_attend_combine_gather`), where the library serves that."""
     from . import ops
     hkv, g, d = v.shape[1], q.shape[1] // v.shape[1], q.shape[-1]
     runs = tuple(splits) if isinstance(splits, (tuple, list)) else (g // splits,) * splits
@@ -123,10 +125,22 @@ def _split_pass(q, qr, kr, v, ck, cv, gates, peer_output, offset, splits, overla
         for h in range(hkv):
             heads = slice(h * g + first, h * g + first + per)
             kh = slice(h, h + 1)
+            at = offset + heads.start * d
+            if fuse_merge:
+                o_swa = ops.sliding_window_attend(qr[:, heads], kr[:, kh], v[:, kh], window, causal, impl=impl)
+                mc = peer_output.multicast_ptr
+                if ops.selected_attend_combine_gather(
+                        qr[:, heads], kr[:, kh], v[:, kh], block, idx[:, kh], fmask[:, kh], o_cmp[:, heads], o_swa,
+                        gates[:, heads], [mc] if mc is not None else peer_output.ptrs, peer_output.features, at,
+                        include_block_causal=causal, multicast=mc is not None, impl=impl, index_cache=shared[h]):
+                    continue
+            else:
+                o_swa = None
             o_sel = ops.native_sparse_attend(qr[:, heads], kr[:, kh], v[:, kh], block, idx[:, kh], fmask[:, kh],
                                              include_block_causal=causal, impl=impl, index_cache=shared[h])
-            o_swa = ops.sliding_window_attend(qr[:, heads], kr[:, kh], v[:, kh], window, causal, impl=impl)
-            peer_output.store(o_cmp[:, heads], o_sel, o_swa, gates[:, heads], offset + heads.start * d, overlap)
+            if o_swa is None:
+                o_swa = ops.sliding_window_attend(qr[:, heads], kr[:, kh], v[:, kh], window, causal, impl=impl)
+            peer_output.store(o_cmp[:, heads], o_sel, o_swa, gates[:, heads], at, overlap)
         first += per
 
 
@@ -202,7 +216,7 @@ class PeerOutput:
 
 
 def sharded_attend_core(q, qr, kr, v, ck, cv, gates, *, group=None, heads_per_pass=1, peer_output=None,
-                        overlap=False, head_splits=1, **cfg):
+                        overlap=False, head_splits=1, fuse_merge=False, **cfg):
     """`attend_core` with the KV-head groups split over the ranks of `group` (long-context prefill: batch 1, one or a
     few KV heads per GPU).  Every rank passes tensors that hold (at least) its own heads -- either the full tensors or
     already the local slices (`local=True` in cfg) -- and receives the full merged output [B, N, Hq * d].  The local
@@ -212,7 +226,9 @@ def sharded_attend_core(q, qr, kr, v, ck, cv, gates, *, group=None, heads_per_pa
     pass computes, and `head_splits` (a number of equal runs, or a tuple of run sizes such as (4, 2, 2)) cuts a pass
     once more: compressed attention and the selection run for all query heads of the KV head (the selection is shared
     by them), the selected and the sliding branch then run for one run of query heads at a time, each run stored as
-    soon as it is complete; runs of equal size share the index of the selection.  Every rank must
+    soon as it is complete; runs of equal size share the index of the selection.  `fuse_merge` lets the selected
+    branch's last kernel do the combine and the stores (the sliding branch then runs before it): no separate store
+    kernel, and the stores leave from a kernel that is streaming anyway.  Every rank must
     receive the whole output over NVLink whatever the form of the gather (7/8 of it on eight GPUs); only what
     follows the last piece is not hidden behind compute."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -231,9 +247,9 @@ def sharded_attend_core(q, qr, kr, v, ck, cv, gates, *, group=None, heads_per_pa
             hs, qs = slice(a, z), slice(a * g, z * g)
 
             offset = first + (a - h0) * g * d
-            if head_splits != 1:
+            if head_splits != 1 or fuse_merge:
                 _split_pass(q[:, qs], qr[:, qs], kr[:, hs], v[:, hs], ck[:, hs], cv[:, hs], gates[:, qs], peer_output,
-                            offset, head_splits, overlap, **cfg)
+                            offset, head_splits, overlap, fuse_merge=fuse_merge, **cfg)
                 continue
 
             def combine_into_peers(o_cmp, o_sel, o_swa, gts, offset=offset):

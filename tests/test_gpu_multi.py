@@ -36,6 +36,9 @@ def _worker(rank, world, port, ret):
         # the stores on a side stream, and the query heads of every KV head in two, four and uneven runs
         over = [sharding.sharded_attend_core(q, qr, kr, v, ck, cv, gates, peer_output=peer, overlap=True,
                                              head_splits=sp, **cfg).clone() for sp in (1, 2, 4, (2, 1, 1))]
+        # the combine and the stores done by the selected branch's last kernel
+        over += [sharding.sharded_attend_core(q, qr, kr, v, ck, cv, gates, peer_output=peer, fuse_merge=True,
+                                              head_splits=sp, **cfg).clone() for sp in (1, 2)]
         ops.check_device_status()
         torch.cuda.synchronize()
         ret[rank] = (bool(torch.equal(via_nccl, full)), bool(torch.equal(fused, full)), bool(torch.equal(fused2, full)),

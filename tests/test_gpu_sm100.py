@@ -545,6 +545,32 @@ def test_forward_index_is_shared_between_calls_over_the_same_selection():
     ops.check_device_status()
 
 
+@pytest.mark.parametrize('case', [(1, 8, 2, 700, 64, 4), (1, 8, 1, 600, 128, 3), (2, 4, 1, 333, 64, 2)])
+def test_selected_forward_that_combines_and_stores_in_its_merge(case):
+    """nsa_sel_fwd_combine_gather: the selected branch whose last kernel also does the gated combine, the head merge
+    and the stores must write, byte for byte, what the selected operator followed by the combine writes -- here into
+    two local buffers standing in for two ranks, at a feature offset."""
+    b, hq, hkv, n, d, nsel = case
+    q, k, v, idx, mask, _ = make_case(b, hq, hkv, n, d, nsel, seed=9)
+    qd, kd, vd, idxd, maskd = (t.to(DEV) for t in (q, k, v, idx, mask))
+    o_cmp = recipe.randn((b, hq, n, d), 31).bfloat16().to(DEV)
+    o_swa = recipe.randn((b, hq, n, d), 32).bfloat16().to(DEV)
+    gates = torch.sigmoid(recipe.randn((b, hq, n, 3), 33)).bfloat16().to(DEV)
+    feats, off = hq * d + 2 * d, d
+    want = [torch.zeros(b, n, feats, dtype=torch.bfloat16, device=DEV) for _ in range(2)]
+    o_sel = nsa.native_sparse_attend(qd, kd, vd, 64, idxd, maskd, impl='sm100')
+    ops.gated_combine_gather(o_cmp, o_sel, o_swa, gates, [w.data_ptr() for w in want], feats, off)
+    got = [torch.zeros(b, n, feats, dtype=torch.bfloat16, device=DEV) for _ in range(2)]
+    assert ops.selected_attend_combine_gather(qd, kd, vd, 64, idxd, maskd, o_cmp, o_swa, gates,
+                                              [g.data_ptr() for g in got], feats, off, impl='sm100')
+    ops.check_device_status()
+    assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1])
+    assert got[0][..., :off].abs().max() == 0 and got[0][..., off + hq * d:].abs().max() == 0
+    # shapes the tensor-core family does not serve are declined, nothing is written
+    assert not ops.selected_attend_combine_gather(qd.float(), kd.float(), vd.float(), 64, idxd, maskd, o_cmp, o_swa, gates,
+                                                  [got[0].data_ptr()], feats, off)
+
+
 def test_combine_backward_hands_the_row_sums_to_the_branch_backwards(monkeypatch):
     """Every branch backward needs delta = sum_d out * d out per row; the gated combine's backward has it already as
     gate * d gate and hands it over through the gradient tensors, so the three branches skip their own pass: three
