@@ -862,9 +862,14 @@ def run_prefill(args, w):
                causal=True, impl=args.kernels, local=True)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     keep = {}
-    fused = world > 1 and args.gather in ('auto', 'fused', 'multimem')
-    peer = sharding.PeerOutput(w['batch'], w['seq'], w['q_heads'] * w['dim_head'], torch.bfloat16, dev,
-                               multicast=args.gather in ('auto', 'multimem')) if fused else None
+    # one GPU: the same code path with this GPU's output tensor as the only destination (no collective, no peers)
+    fused = args.gather in ('auto', 'fused', 'multimem')
+    peer = None
+    if fused and world > 1:
+        peer = sharding.PeerOutput(w['batch'], w['seq'], w['q_heads'] * w['dim_head'], torch.bfloat16, dev,
+                                   multicast=args.gather in ('auto', 'multimem'))
+    elif fused:
+        peer = sharding.LocalOutput(w['batch'], w['seq'], w['q_heads'] * w['dim_head'], torch.bfloat16, dev)
     multimem = peer is not None and peer.multicast_ptr is not None
 
     # how the fused gather runs: through the multicast address or with per-peer stores; on a side stream or not; the
@@ -883,7 +888,8 @@ def run_prefill(args, w):
 
     def quick(n=3):   # device time of n steps, the slowest rank's
         torch.cuda.synchronize()
-        dist.barrier()
+        if world > 1:
+            dist.barrier()
         a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         for _ in range(n):
@@ -891,7 +897,8 @@ def run_prefill(args, w):
         b_.record()
         torch.cuda.synchronize()
         tt = torch.tensor([a.elapsed_time(b_) / n], device=dev)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         return tt.item()
 
     gather_check = None
@@ -907,7 +914,8 @@ def run_prefill(args, w):
             run_sets = [1] + [r for r in ((g // 2, g // 2), (g // 2, g // 4, g // 4), (g // 2, g // 4, g // 8, g // 8))
                               if min(r) >= 1 and sum(r) == g]
             for mcast in ((False, True) if multimem else (False,)):
-                for ov, sp, fu in [(False, 1, False)] + [(True, r, False) for r in run_sets] + [(False, 1, True)]:
+                for ov, sp, fu in [(False, 1, False)] + [(True, r, False) for r in (run_sets if world > 1 else [1])] + \
+                                  [(False, 1, True)]:
                     f = dict(multicast=mcast, overlap=ov, splits=sp, fuse=fu)
                     if f not in forms and not (mcast and sp != 1):
                         forms.append(f)
@@ -921,7 +929,8 @@ def run_prefill(args, w):
             mode.update(f)
             step()
             same = torch.tensor([int(torch.equal(plain, keep['out']))], device=dev)
-            dist.all_reduce(same, op=dist.ReduceOp.MIN)
+            if world > 1:
+                dist.all_reduce(same, op=dist.ReduceOp.MIN)
             name = ('multicast' if f['multicast'] else 'per-peer') + (', side stream' if f['overlap'] else '') + \
                    (", stored by the selected branch's merge" if f['fuse'] else '') + \
                    (f', head runs {f["splits"]}' if f['splits'] != 1 else '')
@@ -993,10 +1002,12 @@ def run_prefill(args, w):
         'steps': args.steps, 'warmup': warmup, 'ms_per_step': ms, 'higher_is_better': True, 'scaling': 'strong',
         'vs_baseline': None, 'dtype': 'bf16', 'data': 'synthetic',
         'config': {'workload': args.workload, **w, 'kernels': args.kernels, 'l2': 'flushed between timed steps',
-                   'sharding': f'{w["kv_heads"] // world} KV-head group(s) per rank, output gathered by '
-                               + ('the combine kernel storing once through the NVLink multicast address (multimem.st)'
-                                  if multimem else 'the combine kernel storing into every rank' if fused
-                                  else 'NCCL all-gather')
+                   'sharding': f'{w["kv_heads"] // world} KV-head group(s) per rank, output '
+                               + ('gathered by the combine kernel storing once through the NVLink multicast address '
+                                  '(multimem.st)' if multimem else
+                                  'gathered by the combine kernel storing into every rank' if fused and world > 1
+                                  else 'written by the combine kernel of each pass (one GPU holds all heads)'
+                                  if world == 1 else 'gathered by an NCCL all-gather')
                                + ((', on a side stream' if mode['overlap'] else '') +
                                   (", from the selected branch's merge kernel" if mode['fuse'] else '') +
                                   (f', query heads in runs {mode["splits"]}' if mode['splits'] != 1 else '') if fused else ''),

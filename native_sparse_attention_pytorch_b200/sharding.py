@@ -215,6 +215,30 @@ class PeerOutput:
         return self.buffer
 
 
+class LocalOutput:
+    """The interface of `PeerOutput` for one GPU that holds all heads: the merged output [B, N, features] is a plain
+    tensor and the only destination, so the forms of `sharded_attend_core` that store per pass (side stream, runs of
+    query heads, the selected branch's merge doing the combine) can be used, and measured, without other ranks."""
+
+    def __init__(self, batch, seq, features, dtype, device):
+        self.buffer = torch.empty(batch, seq, features, dtype=dtype, device=device)
+        self.ptrs = [self.buffer.data_ptr()]
+        self.features = features
+        self.multicast_ptr = None
+        self.side = torch.cuda.Stream(device=device)
+        self._alive = []
+
+    def begin(self):
+        pass
+
+    store = PeerOutput.store
+
+    def end(self):
+        torch.cuda.current_stream(self.buffer.device).wait_stream(self.side)
+        self._alive.clear()
+        return self.buffer
+
+
 def sharded_attend_core(q, qr, kr, v, ck, cv, gates, *, group=None, heads_per_pass=1, peer_output=None,
                         overlap=False, head_splits=1, fuse_merge=False, **cfg):
     """`attend_core` with the KV-head groups split over the ranks of `group` (long-context prefill: batch 1, one or a
