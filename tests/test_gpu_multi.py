@@ -9,6 +9,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 import recipe
+from util import free_port
 
 
 def _worker(rank, world, port, ret):
@@ -51,7 +52,7 @@ def _worker(rank, world, port, ret):
 def test_fused_gather_equals_nccl_gather_on_two_gpus():
     if torch.cuda.device_count() < 2:
         pytest.skip('needs two GPUs')
-    port = 33500 + os.getpid() % 2000
+    port = free_port()
     ret = mp.Manager().dict()
     mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
     assert dict(ret) == {0: (True, True, True, True), 1: (True, True, True, True)}, dict(ret)

@@ -8,6 +8,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 import recipe
+from util import free_port
 from oracle import nsa_oracle as O
 from native_sparse_attention_pytorch_b200 import sharding
 
@@ -55,7 +56,7 @@ def worker(rank, world, port, batch, hkv, ret):
 
 @pytest.mark.parametrize('world,batch,hkv', [(2, 2, 2), (2, 1, 4), (4, 2, 2)])
 def test_sharded_attend_equals_unsharded(world, batch, hkv):
-    port = 29500 + (os.getpid() % 2000) + world * 7 + batch
+    port = free_port()
     ret = mp.Manager().dict()
     mp.spawn(worker, args=(world, port, batch, hkv, ret), nprocs=world, join=True)
     assert len(ret) == world and all(e < 1e-6 for e in ret.values()), dict(ret)
@@ -119,7 +120,7 @@ def core_worker(rank, world, port, ret):
 
 @pytest.mark.parametrize('world', [2, 4])
 def test_head_sharded_hot_path_equals_unsharded(world):
-    port = 31500 + (os.getpid() % 2000) + world * 11
+    port = free_port()
     ret = mp.Manager().dict()
     mp.spawn(core_worker, args=(world, port, ret), nprocs=world, join=True)
     assert len(ret) == world
@@ -171,7 +172,7 @@ def grad_worker(rank, world, port, ret):
 
 
 def test_bucketed_gradient_sum_equals_the_flat_all_reduce():
-    port = 31500 + (os.getpid() % 2000)
+    port = free_port()
     ret = mp.Manager().dict()
     mp.spawn(grad_worker, args=(2, port, ret), nprocs=2, join=True)
     assert dict(ret) == {0: True, 1: True}

@@ -127,3 +127,12 @@ class Checks:
 
     def done(self):
         assert not self.failures, '; '.join(self.failures)
+
+
+def free_port():
+    """A TCP port nobody listens on right now, for the rendezvous of a test's child processes (a port derived from the
+    process id can collide with a socket an earlier run left in TIME_WAIT)."""
+    import socket
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+        s.bind(('127.0.0.1', 0))
+        return s.getsockname()[1]
