@@ -75,6 +75,9 @@ PREFILL_WORKLOADS = {
                                           compress_block_size=32, stride=16, block=64, nsel=16, window=512, num_mem=1),
     'prefill_small': dict(batch=1, seq=4096, q_heads=16, kv_heads=2, dim_head=128, compress_block_size=32, stride=16,
                           block=64, nsel=16, window=512, num_mem=1),
+    # the same grouping at a length whose work buffers exceed the L2 but stay under 2 GB: the size for profiler captures
+    'prefill_mid': dict(batch=1, seq=16384, q_heads=16, kv_heads=2, dim_head=128, compress_block_size=32, stride=16,
+                        block=64, nsel=16, window=512, num_mem=1),
 }
 
 
